@@ -1,0 +1,96 @@
+/* ojb200 — C ABI of the B200-native prefix-tree scoring forward.
+ *
+ * Every entry point takes plain device (or, where stated, host) pointers and sizes, launches on the given CUDA
+ * stream (a cudaStream_t passed as void*), never synchronises, never allocates and never reads results back, so each
+ * call can be captured into a CUDA graph. Return value: OJB_OK or a negative OJB_ERR_* code. Kernels with device-side
+ * waits additionally take `status`, a device int32 that stays 0 unless a bounded wait ran out.
+ *
+ * Each declaration names the interface of lyuyiqi/open-jev-fast that it stands in for (path inside that project).
+ * Tensors are row-major and contiguous; "bf16" is __nv_bfloat16; shapes are written [rows, cols].
+ */
+#ifndef OJB200_H_
+#define OJB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OJB_OK 0
+#define OJB_ERR_ARG (-1)      /* shape / alignment / null-pointer precondition violated */
+#define OJB_ERR_LAUNCH (-2)   /* CUDA reported a launch or API failure */
+#define OJB_ERR_DRIVER (-3)   /* the tensor-map encoder of the CUDA driver could not be obtained */
+#define OJB_ERR_LIMIT (-4)    /* size beyond a documented maximum */
+
+/* device-side status codes written into `status` */
+#define OJB_DEV_WAIT_TIMEOUT 1
+
+typedef void* ojb_stream_t;
+
+/* Library/ABI version (checked by the Python shim). */
+int ojb_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * GEMM — replaces src/lt.cpp:43 lt_matmul / src/fastmodel.py:168 _mm (cuBLASLt) and src/fastmodel.py:158 _skmm
+ * (torch.bmm split-K partials). out[M,N] = x[M,K] · w[N,K]^T, bf16 operands, fp32 accumulation in tensor memory.
+ * Requirements: K % 8 == 0, x / w / out 16-byte aligned. variant: 0 = 128x256 tile, 1 = 128x128 tile.
+ * ------------------------------------------------------------------------------------------------------------------ */
+int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int variant,
+                  int32_t* status, ojb_stream_t stream);
+
+/* Same GEMM with the SwiGLU of src/kernels.cu:1304 silu_mul_lut fused into the epilogue. `w_blk` is the gate/up weight
+ * re-laid in blocks of 256 rows: rows [256b, 256b+128) = gate rows [128b, 128b+128), rows [256b+128, 256b+256) = the
+ * matching up rows. N = 2*I must be a multiple of 256. out[M, I] = bf16(bf16(silu(bf16(g))) * bf16(u)). */
+int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
+                         int32_t* status, ojb_stream_t stream);
+
+/* Split-K partial products, fp32: parts[s, M, N] = x[:, s*K/S:(s+1)*K/S] · w[:, same]^T, S = splits in [1, 8].
+ * K must be a multiple of 64*S. Replaces src/fastmodel.py:158-166 (_skmm) — note that `w` stays [N, K] (K-major); the
+ * pre-split [S, K/S, N] copy of src/fastmodel.py:186 (_split) is not needed. */
+int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, int64_t N, int64_t K, int splits,
+                         int variant, int32_t* status, ojb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Row-wise and element-wise kernels.
+ * ------------------------------------------------------------------------------------------------------------------ */
+
+/* src/kernels.cu:41,755 add_rmsnorm. h = bf16(x + delta) (delta may be null: then h_out is not written and h == x);
+ * hn = bf16(h * rsqrt(mean(h^2) + eps) * w1) with w1 = 1 + weight in fp32; rows with rowmask[n] == 0 give hn = 0
+ * (rowmask may be null). H % 8 == 0. */
+int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
+                    void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream);
+
+/* src/kernels.cu:1444,1488 add_rmsnorm_sk2. delta = bf16(sum_s parts[s]) with parts fp32 [S, rows, H], S in [1, 8];
+ * otherwise as ojb_add_rmsnorm (h_out always written). */
+int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits, const float* w1, const int32_t* rowmask,
+                       void* h_out, void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream);
+
+/* src/kernels.cu:1288,1296 act_tables. silu_tab[65536] bf16 and sig_tab[65536] fp32, indexed by the bf16 bit pattern:
+ * silu_tab[b] = bf16(x / (1 + expf(-x))), sig_tab[b] = 1 / (1 + expf(-x)). */
+int ojb_act_tables(void* silu_tab, float* sig_tab, ojb_stream_t stream);
+
+/* src/kernels.cu:76,769 silu_mul and :1304,1322 silu_mul_lut. gu = [gate | up] of width 2*I per row;
+ * out[rows, I] = bf16(bf16(silu(gate)) * up). silu_tab may be null (computed) or the table above (identical bits). */
+int ojb_silu_mul(const void* gu, const void* silu_tab, void* out, int64_t rows, int64_t I, ojb_stream_t stream);
+
+/* src/kernels.cu:1416 gate_mul3 (and gate_mul / gate_mul2 through the strides). att element (t, h, d) is read at
+ * att[h*att_stride_h + t*att_stride_t + d]; gate is [T, HQ*D]; y[T, HQ*D] = bf16(att * bf16(sigmoid(gate))). */
+int ojb_gate_mul(const void* att, int64_t att_stride_t, int64_t att_stride_h, const void* gate, void* y, int64_t T,
+                 int64_t HQ, int64_t D, ojb_stream_t stream);
+
+/* src/kernels.cu:4759,4767 pack_bits. vis uint8/bool [N, N] -> bits int32 [N, N/32], bit b of word w = key 32w+b. */
+int ojb_pack_bits(const uint8_t* vis, int32_t* bits, int64_t N, ojb_stream_t stream);
+
+/* src/kernels.cu:302,843 fullattn_prep2. proj [N, HQ*2D + 2*HKV*D] = per q head [q(D) | gate(D)], then k heads, then
+ * v heads. Writes qt [HQ, N, D], kt / vt [HKV, N, D] (head-major), gate [N, HQ*D]. q, k: RMSNorm over D with (1+w)
+ * weights qw1 / kw1 (fp32) rounded to bf16, then rotary on the first RD dims (cos / sin bf16 [N, RD], rotate-half
+ * pairing d <-> d + RD/2) with a bf16 rounding after each product and the sum. D % 64 == 0, D <= 256. */
+int ojb_fullattn_prep(const void* proj, const float* qw1, const float* kw1, const void* cosb, const void* sinb,
+                      void* qt, void* kt, void* vt, void* gate, int64_t N, int64_t HQ, int64_t HKV, int64_t D,
+                      int64_t RD, float eps, ojb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OJB200_H_ */

@@ -1,0 +1,492 @@
+// bf16 GEMM for the projection / MLP shapes of the scoring forward, written for sm_100a:
+//   out[M,N] = x[M,K] · w[N,K]^T, both operands K-major, fp32 accumulation in tensor memory (TMEM).
+//
+// One persistent CTA per SM, 192 threads, three roles:
+//   warp 0      TMA producer  — cp.async.bulk.tensor (plain, non-multicast) of a 128xBK x-tile and a BNxBK w-tile per stage,
+//                               128-byte swizzle, completion on an mbarrier
+//   warp 1      MMA issuer    — one lane issues tcgen05.mma (M=128, N=BN, K=16) x4 per stage into one of two TMEM
+//                               accumulators; tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2..5  epilogue      — tcgen05.ld of their 32-lane quarter, conversion and global stores, while the MMA warp is
+//                               already filling the other accumulator
+// Work units are (m-block, k-split, n-block) with the m-block varying fastest, so that the CTAs running at the same time
+// share one w-tile column (read once from HBM, then from L2) while x (a few MB) stays L2-resident.
+//
+// Every wait on an mbarrier is bounded: after kWaitLimitNs the kernel raises the CTA's abort flag, records
+// OJB_DEV_WAIT_TIMEOUT in the status word, lets copies in flight land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace ojb {
+namespace {
+
+constexpr int kBM = 128;           // rows of x per tile (UMMA M)
+constexpr int kBK = 64;            // bf16 elements per stage along K = one 128-byte swizzle row
+constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
+constexpr int kGemmThreads = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+enum Epilogue { kEpiBf16 = 0, kEpiSwiglu = 1, kEpiPartialF32 = 2 };
+
+struct GemmArgs {
+  int M, N, K;
+  int num_m, num_n, splits, kb_per_split, kb_total;
+  void* out;
+  int64_t ldo;          // leading dimension of out in elements
+  int64_t split_stride; // elements between consecutive split planes (fp32 partials)
+  int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the limit ran out or another role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes (64 elements) and which TMA wrote with
+// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset); the leading byte offset is not used by
+// swizzled K-major layouts; bits 46-47 carry the descriptor version of this architecture; bits 61-63 the swizzle mode.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+         (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+template <int BN, int STAGES>
+struct SmemPlan {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = BN * kBK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kTileBytes = STAGES * kStageBytes;
+  static constexpr uint32_t kBarBytes = (2 * STAGES + 4) * 8 + 16;
+  static constexpr uint32_t kTotal = kTileBytes + kBarBytes + 1024;  // + slack for the 1024-byte alignment
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmArgs g) {
+  using Plan = SmemPlan<BN, STAGES>;
+  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns (256 or 512: both powers of two)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Plan::kTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const uint32_t tiles0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * STAGES;
+  const uint32_t accfull0 = empty0 + 8 * STAGES;
+  const uint32_t accempty0 = accfull0 + 16;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(accfull0 + 8 * a, 1);
+      mbar_init(accempty0 + 8 * a, 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_units = g.num_m * g.num_n * g.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int m_blk = unit % g.num_m;
+        const int rest = unit / g.num_m;
+        const int split = rest % g.splits, n_blk = rest / g.splits;
+        const int kb0 = split * g.kb_per_split;
+        const int kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t a_dst = tiles0 + stage * Plan::kStageBytes;
+          const uint32_t fb = full0 + 8 * stage;
+          mbar_expect_tx(fb, Plan::kStageBytes);
+          tma_load_2d(a_dst, &map_x, fb, kb * kBK, m_blk * kBM);
+          tma_load_2d(a_dst + Plan::kABytes, &map_w, fb, kb * kBK, n_blk * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int rest = unit / g.num_m;
+        const int split = rest % g.splits;
+        const int kb0 = split * g.kb_per_split;
+        const int kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        if (!mbar_wait(accempty0 + 8 * acc, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = tiles0 + stage * Plan::kStageBytes;
+          const uint64_t adesc = smem_desc_sw128(a_addr);
+          const uint64_t bdesc = smem_desc_sw128(a_addr + Plan::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
+            umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(accfull0 + 8 * acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const int m_blk = unit % g.num_m;
+      const int rest = unit / g.num_m;
+      const int split = rest % g.splits, n_blk = rest / g.splits;
+      if (!mbar_wait(accfull0 + 8 * acc, acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m_blk * kBM + quarter * 32 + lane;
+      const bool row_ok = row < g.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      if constexpr (EPI == kEpiSwiglu) {
+        // columns [0,128) of the tile are gate_j, columns [128,256) the matching up_j
+        static_assert(EPI != kEpiSwiglu || BN == 256, "SwiGLU epilogue needs the 256-wide tile");
+        bf16_t* orow = reinterpret_cast<bf16_t*>(g.out) + static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(n_blk) * 128;
+        const int ncols = g.N / 2 - n_blk * 128;  // valid output columns of this tile
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t gr[32], ur[32];
+          tmem_ld32(taddr + c * 32, gr);
+          tmem_ld32(taddr + 128 + c * 32, ur);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (c * 32 + j < ncols) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float gv = round_bf(__uint_as_float(gr[j + e]));
+                  const float uv = round_bf(__uint_as_float(ur[j + e]));
+                  o[e] = round_bf(silu_f(gv)) * uv;
+                }
+                *reinterpret_cast<uint4*>(orow + c * 32 + j) = pack8(o);
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == kEpiBf16) {
+        bf16_t* orow = reinterpret_cast<bf16_t*>(g.out) + static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(n_blk) * BN;
+        const int ncols = g.N - n_blk * BN;
+        const bool vec_ok = (g.ldo % 8) == 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int col = c * 32 + j;
+              if (col + 8 <= ncols && vec_ok) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
+                *reinterpret_cast<uint4*>(orow + col) = pack8(o);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (col + e < ncols) orow[col + e] = f2bf(__uint_as_float(r[j + e]));
+              }
+            }
+          }
+        }
+      } else {
+        float* orow = reinterpret_cast<float*>(g.out) + static_cast<int64_t>(split) * g.split_stride +
+                      static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(n_blk) * BN;
+        const int ncols = g.N - n_blk * BN;
+        const bool vec_ok = (g.ldo % 4) == 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const int col = c * 32 + j;
+              if (col + 4 <= ncols && vec_ok) {
+                *reinterpret_cast<uint4*>(orow + col) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (col + e < ncols) orow[col + e] = __uint_as_float(r[j + e]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accempty0 + 8 * acc);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) report_status(g.status, OJB_DEV_WAIT_TIMEOUT);
+    // copies that were already issued must land before the shared memory of this CTA is handed on
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return OJB_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+  }
+  return n;
+}
+
+template <int BN, int STAGES, int EPI>
+int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int64_t ldo,
+                int32_t* status, cudaStream_t stream) {
+  using Plan = SmemPlan<BN, STAGES>;
+  static bool attr_set = false;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, EPI>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal) != cudaSuccess)
+      return OJB_ERR_LAUNCH;
+    attr_set = true;
+  }
+  CUtensorMap map_x, map_w;
+  int rc = make_map(&map_x, x, M, K, kBM);
+  if (rc != OJB_OK) return rc;
+  rc = make_map(&map_w, w, N, K, BN);
+  if (rc != OJB_OK) return rc;
+  GemmArgs g;
+  g.M = static_cast<int>(M);
+  g.N = static_cast<int>(N);
+  g.K = static_cast<int>(K);
+  g.num_m = static_cast<int>(ceil_div(M, kBM));
+  g.num_n = static_cast<int>(ceil_div(N, BN));
+  g.splits = splits;
+  g.kb_total = static_cast<int>(ceil_div(K, kBK));
+  g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
+  g.out = out;
+  g.ldo = ldo;
+  g.split_stride = M * N;
+  g.status = status;
+  const int sms = sm_count();
+  if (sms <= 0) return OJB_ERR_LAUNCH;
+  const int64_t units = static_cast<int64_t>(g.num_m) * g.num_n * splits;
+  const int grid = static_cast<int>(units < sms ? units : sms);
+  kern<<<grid, kGemmThreads, Plan::kTotal, stream>>>(map_x, map_w, g);
+  return launch_status(cudaGetLastError());
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace ojb
+
+using namespace ojb;
+
+extern "C" int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int variant,
+                             int32_t* status, ojb_stream_t stream) {
+  OJB_REQUIRE(x && w && out && M > 0 && N > 0 && K > 0 && K % 8 == 0);
+  OJB_REQUIRE(aligned16(x) && aligned16(w) && aligned16(out));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (variant == 1) return launch_gemm<128, 6, kEpiBf16>(x, w, out, M, N, K, 1, N, status, st);
+  OJB_REQUIRE(variant == 0);
+  return launch_gemm<256, 4, kEpiBf16>(x, w, out, M, N, K, 1, N, status, st);
+}
+
+extern "C" int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
+                                    int32_t* status, ojb_stream_t stream) {
+  OJB_REQUIRE(x && w_blk && out && M > 0 && N > 0 && K > 0 && K % 8 == 0 && N % 256 == 0);
+  OJB_REQUIRE(aligned16(x) && aligned16(w_blk) && aligned16(out));
+  return launch_gemm<256, 4, kEpiSwiglu>(x, w_blk, out, M, N, K, 1, N / 2, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, int64_t N, int64_t K,
+                                    int splits, int variant, int32_t* status, ojb_stream_t stream) {
+  OJB_REQUIRE(x && w && parts && M > 0 && N > 0 && K > 0 && splits >= 1 && splits <= 8);
+  OJB_REQUIRE(K % (64 * splits) == 0);
+  OJB_REQUIRE(aligned16(x) && aligned16(w) && aligned16(parts));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (variant == 1) return launch_gemm<128, 6, kEpiPartialF32>(x, w, parts, M, N, K, splits, N, status, st);
+  OJB_REQUIRE(variant == 0);
+  return launch_gemm<256, 4, kEpiPartialF32>(x, w, parts, M, N, K, splits, N, status, st);
+}

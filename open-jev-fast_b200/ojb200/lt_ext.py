@@ -1,0 +1,122 @@
+"""GEMM surface of open-jev-fast's src/lt_ext.py / src/lt.cpp, backed by the tcgen05 GEMM of libojb200.so.
+
+The reference enumerates cuBLASLt algorithms per shape (lt_setup) and runs one by index (lt_matmul); split-K plans go
+through lt2_*. Here an "algorithm" is a tile variant of the hand-written kernel: 0 = 128x256 tile, 1 = 128x128 tile.
+Two entry points have no counterpart in the reference: gemm_swiglu (SwiGLU fused into the epilogue) and gemm_splitk
+(fp32 partial sums from the un-split [N, K] weight).
+"""
+import sys
+
+import torch
+
+from . import _lib
+from ._lib import call, i32, i64, ptr, stream_ptr
+
+bf16 = torch.bfloat16
+N_VARIANTS = 2
+_plans = []          # lt2 plans: dicts
+_wl1_cache = {}      # data_ptr of a [S, K/S, N] weight -> its [N, K] re-layout
+
+
+def load():
+    """Counterpart of src/lt_ext.py:5 load()."""
+    _lib.lib()
+    return sys.modules[__name__]
+
+
+def _check(x, w):
+    if not (x.is_cuda and w.is_cuda and x.is_contiguous() and w.is_contiguous() and x.dtype == bf16 and w.dtype == bf16):
+        raise RuntimeError("lt_matmul: x and w must be contiguous CUDA bf16 tensors")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise RuntimeError("lt_matmul: x [M, K] and w [N, K] expected")
+
+
+def lt_setup(M, N, K, max_algos):
+    """src/lt.cpp:15 — number of candidate algorithms for (M, N, K)."""
+    return min(int(max_algos), N_VARIANTS)
+
+
+def lt_matmul(x, w, idx):
+    """src/lt.cpp:43 — out[M, N] = x[M, K] @ w[N, K]^T (bf16, fp32 accumulate)."""
+    _check(x, w)
+    if not 0 <= idx < N_VARIANTS:
+        raise RuntimeError("lt_matmul: algorithm index out of range")
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N, dtype=bf16, device=x.device)
+    call("ojb_gemm_bf16", ptr(x), ptr(w), ptr(out), i64(M), i64(N), i64(K), i32(idx), ptr(_lib.status_word(x.device)),
+         stream_ptr())
+    return out
+
+
+def gemm_swiglu(x, w_blk):
+    """out[M, I] = silu(x @ gate^T) * (x @ up^T) with w_blk = block-interleaved [2I, K] weight (see interleave_gate_up)."""
+    _check(x, w_blk)
+    M, K = x.shape
+    N = w_blk.shape[0]
+    out = torch.empty(M, N // 2, dtype=bf16, device=x.device)
+    call("ojb_gemm_bf16_swiglu", ptr(x), ptr(w_blk), ptr(out), i64(M), i64(N), i64(K), ptr(_lib.status_word(x.device)),
+         stream_ptr())
+    return out
+
+
+def interleave_gate_up(w_gate, w_up):
+    """[I, K] gate and up weights -> [2I, K] in blocks of 128 gate rows followed by their 128 up rows (I % 128 == 0)."""
+    I, K = w_gate.shape
+    if I % 128:
+        raise RuntimeError("interleave_gate_up: I must be a multiple of 128")
+    return torch.stack([w_gate.view(I // 128, 128, K), w_up.view(I // 128, 128, K)], 1).reshape(2 * I, K).contiguous()
+
+
+def gemm_splitk(x, w, S, idx=1):
+    """fp32 partials [S, M, N] of x @ w^T over S equal K ranges; w stays [N, K]."""
+    _check(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    parts = torch.empty(S, M, N, dtype=torch.float32, device=x.device)
+    call("ojb_gemm_bf16_splitk", ptr(x), ptr(w), ptr(parts), i64(M), i64(N), i64(K), i32(S), i32(idx),
+         ptr(_lib.status_word(x.device)), stream_ptr())
+    return parts
+
+
+# ---------------------------------------------------------------------------------------------- lt2_* (src/lt.cpp:64-190)
+def lt2_plan(M, N, K, S, f32, wl):
+    """src/lt.cpp:64 — plan handle. wl = 0: w [N, K]; wl = 1: w [S, K/S, N] (the reference's pre-split layout)."""
+    if wl not in (0, 1) or (wl == 0 and S != 1 and False):
+        raise RuntimeError("lt2_plan: wl must be 0 or 1")
+    _plans.append(dict(M=M, N=N, K=K, S=S, f32=bool(f32), wl=wl))
+    return len(_plans) - 1
+
+
+def lt2_search(h, max_cands, min_waves):
+    """src/lt.cpp:93 — number of candidates of plan h."""
+    return N_VARIANTS
+
+
+def lt2_info(h, i):
+    """src/lt.cpp:170 — description of candidate i."""
+    return f"tcgen05 tile 128x{256 if i == 0 else 128}, plan {_plans[h]}"
+
+
+def lt2_run(h, x, w, i):
+    """src/lt.cpp:160 — [S, M, N] partial products (fp32 if the plan says so, else bf16)."""
+    p = _plans[h]
+    if p["wl"] == 1:
+        key = (w.data_ptr(), tuple(w.shape))
+        w2 = _wl1_cache.get(key)
+        if w2 is None:
+            S, Ks, N = w.shape
+            w2 = _wl1_cache[key] = w.permute(2, 0, 1).reshape(N, S * Ks).contiguous()
+        w = w2
+    parts = gemm_splitk(x, w, p["S"], i)
+    return parts if p["f32"] else parts.to(bf16)
+
+
+def lt2_raw(h, i):
+    """src/lt.cpp:179 — opaque algorithm bytes; here the variant index."""
+    return [int(i)]
+
+
+def lt2_add_raw(h, raw):
+    """src/lt.cpp:183 — register an algorithm from lt2_raw; returns its index."""
+    return int(raw[0])

@@ -1,0 +1,71 @@
+"""tcgen05 GEMM against torch.matmul on fp32-upcast operands (the check BASELINE's GEMM sweep names)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+bf16 = torch.bfloat16
+
+
+def _mk(M, N, K, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(M, K, generator=g, device="cuda", dtype=torch.float32).to(bf16)
+    w = (torch.randn(N, K, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(bf16)
+    return x, w
+
+
+def _ref(x, w):
+    return x.float() @ w.float().t()
+
+
+# tolerance: bf16 output rounding (2^-9 relative) + fp32 accumulation-order noise
+def _close(out, ref):
+    err = (out.float() - ref).abs().max().item()
+    tol = ref.abs().max().item() * 2 ** -8 + 1e-3
+    assert err <= tol, (err, tol)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(64, 512, 256), (128, 256, 64), (288, 1280, 5120), (539, 12352, 5120), (100, 200, 72),
+                                   (1024, 5120, 6144), (544, 5120, 4096)])
+def test_gemm_plain(M, N, K, variant):
+    from ojb200 import lt_ext, _lib
+    x, w = _mk(M, N, K, 1)
+    out = lt_ext.lt_matmul(x, w, variant)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _close(out, _ref(x, w))
+
+
+@pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120)])
+def test_gemm_swiglu(M, I, K):
+    from ojb200 import lt_ext, _lib
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(M, K, generator=g, device="cuda").to(bf16)
+    wg = (torch.randn(I, K, generator=g, device="cuda") * 0.02).to(bf16)
+    wu = (torch.randn(I, K, generator=g, device="cuda") * 0.02).to(bf16)
+    out = lt_ext.gemm_swiglu(x, lt_ext.interleave_gate_up(wg, wu))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    gg = _ref(x, wg).to(bf16).float()
+    uu = _ref(x, wu).to(bf16).float()
+    ref = torch.nn.functional.silu(gg).to(bf16).float() * uu
+    err = (out.float() - ref).abs().max().item()
+    # one bf16 ulp of gate or up can flip through the product: 2^-7 relative on the largest value
+    tol = ref.abs().max().item() * 2 ** -6 + 1e-3
+    assert err <= tol, (err, tol)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("M,N,K,S", [(64, 256, 256, 2), (288, 5120, 6144, 2), (544, 5120, 17408, 4), (539, 5120, 4096, 2)])
+def test_gemm_splitk(M, N, K, S, variant):
+    from ojb200 import lt_ext, _lib
+    x, w = _mk(M, N, K, 3)
+    parts = lt_ext.gemm_splitk(x, w, S, variant)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert parts.shape == (S, M, N)
+    ks = K // S
+    for s in range(S):
+        ref = x[:, s * ks:(s + 1) * ks].float() @ w[:, s * ks:(s + 1) * ks].float().t()
+        err = (parts[s] - ref).abs().max().item()
+        assert err <= ref.abs().max().item() * 1e-4 + 1e-4, (s, err)
