@@ -90,6 +90,24 @@ int ojb_fullattn_prep(const void* proj, const float* qw1, const float* kw1, cons
                       void* qt, void* kt, void* vt, void* gate, int64_t N, int64_t HQ, int64_t HKV, int64_t D,
                       int64_t RD, float eps, ojb_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Prefix-tree layout (HOST functions, no CUDA) — replaces src/fastmodel.py:321-398 FastQwen35.gtree_build.
+ * Input: S candidate token lists concatenated in `tokens`, candidate c = tokens[seq_off[c] .. seq_off[c+1]); groups[c] =
+ * question index of candidate c (every index in 0..max must occur). NB / PB = row / path-length buckets (NB % 32 == 0).
+ * ojb_gtree_dims fills dims[10] = {N, S, R, L2, Lr, Nreal, int64 elements of buf64, int32 elements of buf32, int32
+ * elements of ext32, chunk-table capacity}. ojb_gtree_fill writes
+ *   buf64 = ids[N] | pos[N] | lastidx[S]              (ids / pos padded to a multiple of 4 elements)
+ *   buf32 = src[S,L2] | inv[N] | rep_ptr[N+2] | rep_pos[S*L2] | hist[N+1,4] | canon[S*L2] | rowmask[N] | vbits[N,N/32]
+ *           (every field padded to a multiple of 8 elements), bit-identical to the reference's tensors, and, if ext32 is
+ *   not null, ext32 = krange[N,8] | nodes[1+2S,4] | chunks[cap,4] | steps[cap,4] | meta[8] (tables of this
+ *   implementation only: key ranges for the attention kernel, node / chunk / walk tables for the tree-native
+ *   Gated DeltaNet pass).
+ * ------------------------------------------------------------------------------------------------------------------ */
+int ojb_gtree_dims(const int64_t* tokens, const int64_t* seq_off, const int32_t* groups, int64_t S, int64_t NB,
+                   int64_t PB, int64_t* dims);
+int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, const int32_t* groups, int64_t S, int64_t pad_id,
+                   int64_t NB, int64_t PB, int64_t* buf64, int32_t* buf32, int32_t* ext32);
+
 #ifdef __cplusplus
 }
 #endif

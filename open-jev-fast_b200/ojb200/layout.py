@@ -1,0 +1,94 @@
+"""Prefix-tree layout: host builder (C++ in libojb200.so) + upload. Mirrors FastQwen35.gtree_build of open-jev-fast
+(src/fastmodel.py:321-398): same arguments, same returned (ids, lay) with the same field names, shapes and dtypes."""
+import ctypes
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_I64P = ctypes.POINTER(ctypes.c_int64)
+_I32P = ctypes.POINTER(ctypes.c_int32)
+
+
+def _pad8(n):
+    return n + (-n) % 8
+
+
+def _flatten(seqs, groups):
+    S = len(seqs)
+    off = np.zeros(S + 1, np.int64)
+    np.cumsum([len(s) for s in seqs], out=off[1:])
+    tok = np.fromiter((t for s in seqs for t in s), np.int64, count=int(off[-1]))
+    return tok, off, np.asarray(groups, np.int32)
+
+
+def gtree_host(seqs, groups, pad_id, NB=32, PB=16, pin=False):
+    """Runs the host builder. Returns (dims dict, buf64, buf32, ext32) as CPU torch tensors (pinned if asked)."""
+    if len(seqs) == 0 or len(groups) != len(seqs):
+        raise RuntimeError("gtree_build: need one group index per candidate and at least one candidate")
+    tok, off, grp = _flatten(seqs, groups)
+    dims = np.zeros(10, np.int64)
+    L = _lib.lib()
+    args = (tok.ctypes.data_as(_I64P), off.ctypes.data_as(_I64P), grp.ctypes.data_as(_I32P), ctypes.c_int64(len(seqs)))
+    rc = L.ojb_gtree_dims(*args, ctypes.c_int64(NB), ctypes.c_int64(PB), dims.ctypes.data_as(_I64P))
+    if rc != 0:
+        raise RuntimeError("gtree_build: invalid request (empty candidate, unused question index, or row bucket not a "
+                           "multiple of 32)")
+    N, S, R, L2, Lr, Nreal, n64, n32, next_, cap = (int(v) for v in dims)
+    buf64 = torch.empty(n64, dtype=torch.int64, pin_memory=pin)
+    buf32 = torch.empty(n32, dtype=torch.int32, pin_memory=pin)
+    ext32 = torch.empty(next_, dtype=torch.int32, pin_memory=pin)
+    rc = L.ojb_gtree_fill(*args, ctypes.c_int64(pad_id), ctypes.c_int64(NB), ctypes.c_int64(PB),
+                          ctypes.cast(buf64.data_ptr(), _I64P), ctypes.cast(buf32.data_ptr(), _I32P),
+                          ctypes.cast(ext32.data_ptr(), _I32P))
+    if rc != 0:
+        raise RuntimeError("gtree_build: layout fill failed")
+    d = dict(N=N, S=S, R=R, L2=L2, Lr=Lr, Nreal=Nreal, cap=cap)
+    return d, buf64, buf32, ext32
+
+
+def field_views(d, g64, g32, e32):
+    """Named views into the three packed buffers (host or device)."""
+    N, S, L2, cap = d["N"], d["S"], d["L2"], d["cap"]
+    n64 = N + (-N) % 4
+    sizes = [S * L2, N, N + 2, S * L2, (N + 1) * 4, S * L2, N, N * (N // 32)]
+    o = np.cumsum([0] + [_pad8(x) for x in sizes])
+    v = lambda k: g32[o[k]:o[k] + sizes[k]]
+    eo = np.cumsum([0, N * 8, (1 + 2 * S) * 4, cap * 4, cap * 4, 8])
+    e = lambda k: e32[eo[k]:eo[k + 1]]
+    return dict(ids=g64[:N], pos=g64[n64:n64 + N], lastidx=g64[2 * n64:2 * n64 + S],
+                src=v(0).view(S, L2), inv=v(1), rep_ptr=v(2), rep_pos=v(3), hist=v(4).view(N + 1, 4), canon=v(5),
+                rowmask=v(6), vbits=v(7).view(N, N // 32),
+                krange=e(0).view(N, 8), nodes=e(1).view(1 + 2 * S, 4), chunks=e(2).view(cap, 4), steps=e(3).view(cap, 4),
+                meta=e(4))
+
+
+def dense_masks(vbits):
+    """amask bool [1,1,N,N] and amask_add bf16 (0 / -inf) from the packed visibility words (device-side torch ops)."""
+    N = vbits.shape[0]
+    sh = torch.arange(32, device=vbits.device, dtype=torch.int32)
+    vis = ((vbits.unsqueeze(-1) >> sh) & 1).bool().view(N, N)
+    add = torch.zeros((N, N), dtype=torch.bfloat16, device=vbits.device).masked_fill_(~vis, float("-inf"))
+    return vis[None, None], add[None, None]
+
+
+def gtree_build(seqs, groups, pad_id, NB=32, PB=16, dev="cuda", dense=True):
+    """Drop-in for FastQwen35.gtree_build: returns (ids, lay). Three host-to-device copies (int64 fields, int32 fields,
+    extension tables); the dense masks, which only the SDPA-style paths of the reference read, are expanded on the device
+    from the packed bits instead of being copied (skip them with dense=False)."""
+    on_gpu = torch.device(dev).type == "cuda"
+    d, b64, b32, e32 = gtree_host(seqs, groups, pad_id, NB, PB, pin=on_gpu)
+    g64 = b64.to(dev, non_blocking=True)
+    g32 = b32.to(dev, non_blocking=True)
+    ge = e32.to(dev, non_blocking=True)
+    f = field_views(d, g64, g32, ge)
+    lay = SimpleNamespace(N=d["N"], S=d["S"], R=d["R"], L2=d["L2"], Lr=d["Lr"], Nreal=d["Nreal"], key=(d["N"], d["S"], d["L2"]),
+                          cap=d["cap"], _host=(b64, b32, e32), _dev=(g64, g32, ge))
+    ids = f.pop("ids")
+    for k, v in f.items():
+        setattr(lay, k, v)
+    if dense:
+        lay.amask, lay.amask_add = dense_masks(lay.vbits)
+    return ids, lay

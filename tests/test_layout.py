@@ -1,0 +1,106 @@
+"""Prefix-tree layout: oracle restatement and the C++ host builder against the reference's own outputs (golden file),
+bit-exact. Runs without a GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import trees
+from oracle import layout as OL
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "layout_golden.npz"))
+FIELDS = ("pos", "rowmask", "vbits", "src", "inv", "lastidx", "rep_ptr", "rep_pos", "hist", "canon")
+CASES = trees.layout_cases()
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_oracle_matches_reference_golden(name):
+    seqs, groups, pad_id, NB, PB = CASES[name]
+    lay = OL.gtree_layout(seqs, groups, pad_id, NB, PB)
+    N, S, R, L2, Lr, Nreal = GOLD[f"{name}/meta"]
+    assert (lay["N"], lay["S"], lay["R"], lay["L2"], lay["Lr"], lay["Nreal"]) == (N, S, R, L2, Lr, Nreal)
+    assert np.array_equal(lay["ids"], GOLD[f"{name}/ids"])
+    for f in FIELDS:
+        a, b = lay[f], GOLD[f"{name}/{f}"]
+        assert a.dtype == b.dtype and a.shape == b.shape and np.array_equal(a, b), f
+    assert np.array_equal(np.packbits(lay["vis"], axis=1, bitorder="little"), GOLD[f"{name}/amask"])
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_host_builder_matches_reference_golden(name):
+    from ojb200 import layout as PL
+    seqs, groups, pad_id, NB, PB = CASES[name]
+    d, b64, b32, e32 = PL.gtree_host(seqs, groups, pad_id, NB, PB)
+    N, S, R, L2, Lr, Nreal = GOLD[f"{name}/meta"]
+    assert (d["N"], d["S"], d["R"], d["L2"], d["Lr"], d["Nreal"]) == (N, S, R, L2, Lr, Nreal)
+    f = PL.field_views(d, b64, b32, e32)
+    assert np.array_equal(f["ids"].numpy(), GOLD[f"{name}/ids"])
+    for k in FIELDS:
+        a, b = f[k].numpy(), GOLD[f"{name}/{k}"]
+        assert a.dtype == b.dtype and a.shape == b.shape and np.array_equal(a, b), k
+    # the packed buffers themselves are laid out as the reference's (32-byte aligned fields, zero padding)
+    ref = OL.gtree_layout(seqs, groups, pad_id, NB, PB)
+    parts = [ref[k].reshape(-1) for k in ("src", "inv", "rep_ptr", "rep_pos", "hist", "canon", "rowmask", "vbits")]
+    want = np.concatenate([np.concatenate([p.astype(np.int32), np.zeros((-len(p)) % 8, np.int32)]) for p in parts])
+    assert np.array_equal(b32.numpy(), want)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_extension_tables(name):
+    """krange reproduces the visibility bits; chunks tile every node; the walk visits each chunk once, parents first."""
+    from ojb200 import layout as PL
+    seqs, groups, pad_id, NB, PB = CASES[name]
+    d, b64, b32, e32 = PL.gtree_host(seqs, groups, pad_id, NB, PB)
+    f = {k: v.numpy() for k, v in PL.field_views(d, b64, b32, e32).items()}
+    ref = OL.gtree_layout(seqs, groups, pad_id, NB, PB)
+    N = d["N"]
+    vis = np.zeros((N, N), bool)
+    for n in range(N):
+        k = f["krange"][n]
+        vis[n, 0:k[0]] = True
+        vis[n, k[1]:k[2]] = True
+        vis[n, k[3]:k[4]] = True
+    assert np.array_equal(vis, ref["vis"])
+    nc, ns = f["meta"][0], f["meta"][1]
+    assert nc <= d["cap"] and ns == nc
+    covered = np.zeros(N, int)
+    for row0, rows, node, _ in f["chunks"][:nc]:
+        assert 0 < rows <= 64
+        n0, nl = f["nodes"][node][:2]
+        assert n0 <= row0 and row0 + rows <= n0 + nl
+        covered[row0:row0 + rows] += 1
+    assert np.array_equal(covered, ref["rowmask"])
+    seen, done_nodes = set(), set()
+    for chunk, load, save, _ in f["steps"][:ns]:
+        assert chunk not in seen
+        seen.add(chunk)
+        node = f["chunks"][chunk][2]
+        parent = f["nodes"][node][2]
+        if load in (2, 3):
+            assert parent >= 0
+        done_nodes.add(node)
+    assert len(seen) == nc
+
+
+def test_rejects_bad_requests():
+    from ojb200 import layout as PL
+    with pytest.raises(RuntimeError):
+        PL.gtree_host([[1, 2], []], [0, 0], 0)          # empty candidate
+    with pytest.raises(RuntimeError):
+        PL.gtree_host([[1, 2], [1, 3]], [0, 2], 0)      # question 1 has no candidate
+    with pytest.raises(RuntimeError):
+        PL.gtree_host([[1, 2]], [0], 0, NB=8)           # 8 rows: not a whole 32-key word
+    with pytest.raises(RuntimeError):
+        PL.gtree_host([], [], 0)
+
+
+@pytest.mark.parametrize("name", list(trees.state_cases()))
+def test_state_layout_oracle_matches_reference_golden(name):
+    pre, suf, msk, pad = trees.state_cases()[name]
+    lay = OL.state_layout(len(pre), msk, pad)
+    Lp, S, Ls, N = GOLD[f"{name}/meta"]
+    assert (lay["Lp"], lay["S"], lay["Ls"], lay["N"]) == (Lp, S, Ls, N)
+    for f in ("pos", "rowmask", "lastidx", "repidx"):
+        assert np.array_equal(lay[f], GOLD[f"{name}/{f}"]), f
+    assert np.array_equal(np.packbits(lay["vis"], axis=1, bitorder="little"), GOLD[f"{name}/amask"])
