@@ -108,6 +108,44 @@ int ojb_gtree_dims(const int64_t* tokens, const int64_t* seq_off, const int32_t*
 int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, const int32_t* groups, int64_t S, int64_t pad_id,
                    int64_t NB, int64_t PB, int64_t* buf64, int32_t* buf32, int32_t* ext32);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Gated DeltaNet (linear attention).
+ * ------------------------------------------------------------------------------------------------------------------ */
+
+/* src/kernels.cu:1173-1283 linattn_prep_dedup2 (rep_ptr != null: results scattered to the replicated slots
+ * rep_pos[rep_ptr[n] .. rep_ptr[n+1]) of every packed row n, pad slots zeroed; q, k, v, g, beta have n_slots rows) and its
+ * unreplicated form (rep_ptr == null: one output row per packed row). proj bf16 [N, 2KD+2VD+2HV] = [q|k|v|z|b|a];
+ * hist int32 [N+1, 4] = rows t-3..t on the row's own path (-1 = none); convw bf16 [2KD+VD, 4]; A_log, dt_bias bf16 [HV].
+ * Head dim is 128: KD = 128*HK, VD = 128*HV. q, k bf16 [*, KD]; v bf16 [*, VD]; g fp32 [*, HV]; beta bf16 [*, HV]. */
+int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t* rep_ptr, const int32_t* rep_pos, int64_t n_slots,
+                 const void* convw, const void* A_log, const void* dt_bias, void* q, void* k, void* v, float* g,
+                 void* beta, int64_t N, int64_t KD, int64_t VD, int64_t HV, int64_t HK, ojb_stream_t stream);
+
+/* Bytes of scratch that ojb_gdn_chunked needs for n_chunks chunk-table entries and HV value heads. */
+int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV);
+
+/* src/kernels.cu:4225 gdn_fused6 (and gdn_fused .. gdn_fused9) — chunked gated delta rule, two launches (state-independent
+ * pass over all chunks, then the state pass). Rows are addressed through tables so that the same code serves the
+ * reference's replicated [B, T] layout and the packed prefix tree:
+ *   chunks int32 [n_chunks, 4] = (first row, rows <= 64 (0 = unused entry), -, -)
+ *   steps  int32 [*, 4]        = (chunk, load, save, aux) in execution order; load: 0 carry on, 1 zero state, 2 / 3 restore
+ *                                parked slot A / B, 4 initial state number (aux >> 16) - 1; save: bit 0 park in slot A,
+ *                                bit 1 in slot B; (aux & 0xffff) - 1 = index in final_state written after the step
+ *   walk_ptr int32 [n_walks+1] = step ranges that are independent of each other (one CTA column each)
+ * q, k bf16 [rows, HK, 128]; v bf16 [rows, HV, 128]; g fp32 (natural-log decay) and beta bf16 [rows, HV];
+ * init_state / final_state fp32 [*, HV, 128(dk), 128(dv)] or null; out bf16 [rows, HV, 128], rows not covered by a chunk
+ * are left untouched. o = scale * (...). scratch: ojb_gdn_scratch_bytes(n_chunks, HV) bytes, 16-byte aligned. */
+int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const void* beta, const int32_t* chunks,
+                    int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr, int64_t n_walks,
+                    const float* init_state, float* final_state, void* scratch, void* out, int64_t HK, int64_t HV,
+                    float scale, ojb_stream_t stream);
+
+/* src/kernels.cu:1333-1374 gated_rmsnorm_inv2 (inv != null) and :143 gated_rmsnorm (inv == null).
+ * out[n, h, :] = bf16(((x[r, h, :] * rstd) * w) * z * sigmoid(z)), r = inv[n] or n, z = proj[n, zoff + h*128 ...],
+ * rstd = 1/sqrt(mean(x^2) + eps) over the 128 dims. x bf16 [*, HV, 128]; proj bf16 [N, P]; w bf16 [128]. */
+int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* proj, const void* w, void* out, int64_t N,
+                      int64_t HV, int64_t HD, int64_t zoff, int64_t P, float eps, ojb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

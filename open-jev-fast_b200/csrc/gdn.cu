@@ -1,0 +1,649 @@
+// Chunked Gated DeltaNet (linear attention) for the scoring forward, tree-native.
+//
+//   gdn_prep   per packed row: causal depthwise conv (width 4, history taken along the row's own tree path) + SiLU, L2 norm
+//              of q and k per head, beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias). Optionally scattered to the
+//              replicated per-candidate slots of the reference layout.
+//   gdn_intra  per (chunk of <= 64 rows, value head), all chunks in parallel — everything that does not depend on the
+//              recurrent state: G = cumsum(g); A = strict_lower((k beta) k^T * exp(G_i - G_j)); u = (I+A)^-1 (v beta),
+//              w = (I+A)^-1 (k beta e^G) by fp32 forward substitution; Aqk = tril(q k^T * exp(G_i - G_j)) * scale;
+//              qg = q e^G scale; kg = k e^(G_L - G). KK^T and QK^T run on the tensor cores (mma.sync bf16, fp32 accumulate).
+//              Results go to a scratch item of 36 872 bf16 per (chunk, head).
+//   gdn_state  per (value head, 32-column slice of the state, walk): walks the chunks of the tree depth first with the
+//              fp32 state slice [128 x 32] in registers; per chunk v' = u - w S, o = qg S + Aqk v', S = S e^(G_L) + kg^T v'
+//              (mma.sync). The state at the end of the root and of a question stem is parked in shared memory and restored
+//              for every child, so shared prefixes are computed once. The next chunk's operands are prefetched with
+//              cp.async while the current one is computed.
+//   gated_rmsnorm  per (row, head): RMSNorm over 128 dims times weight times z * sigmoid(z), optional row gather.
+#include "common.cuh"
+
+namespace ojb {
+namespace {
+
+constexpr int kHD = 128;          // head dim of q, k and v
+constexpr int kChunk = 64;
+constexpr int kItemElems = 4 * kChunk * kHD + kChunk * kChunk + 8;  // w | u | qg | kg | Aqk | (float e^{G_L}, pad)
+constexpr int kOffW = 0, kOffU = kChunk * kHD, kOffQg = 2 * kChunk * kHD, kOffKg = 3 * kChunk * kHD,
+              kOffA = 4 * kChunk * kHD, kOffGl = 4 * kChunk * kHD + kChunk * kChunk;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ------------------------------------------------------------------------------------------------------------ gdn_prep
+// grid (ceil(C/8/256), rows [+ pad-slot groups when scattering]); one thread = 8 consecutive channels of one packed row.
+// proj [N, P] = [q(KD) | k(KD) | v(VD) | z(VD) | b(HV) | a(HV)].
+template <bool SCATTER>
+__global__ void __launch_bounds__(256)
+gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, const int32_t* __restrict__ rep_ptr,
+                const int32_t* __restrict__ rep_pos, const bf16_t* __restrict__ convw, const bf16_t* __restrict__ A_log,
+                const bf16_t* __restrict__ dt_bias, bf16_t* __restrict__ q, bf16_t* __restrict__ k, bf16_t* __restrict__ v,
+                float* __restrict__ g, bf16_t* __restrict__ beta, int N, int KD, int VD, int HV) {
+  const int C = 2 * KD + VD, P = C + VD + 2 * HV;
+  const int n = blockIdx.y;
+  const bool pad = n >= N;  // only when scattering: groups of 16 pad slots
+  int p0 = 0, p1 = 1;
+  if constexpr (SCATTER) {
+    if (!pad) { p0 = rep_ptr[n]; p1 = rep_ptr[n + 1]; }
+    else { p0 = rep_ptr[N] + (n - N) * 16; p1 = min(rep_ptr[N + 1], p0 + 16); }
+    if (p0 >= p1) return;
+  }
+  int4 hr = make_int4(-1, -1, -1, -1);
+  if (!pad) hr = hist[n];
+  if (blockIdx.x == 0 && threadIdx.x < HV) {
+    const int h = threadIdx.x;
+    float bv = 0.f, gv = 0.f;
+    if (!pad) {
+      const bf16_t* pr = proj + static_cast<int64_t>(hr.w) * P + C + VD;
+      bv = sigmoid_f(bf2f(pr[h]));
+      const float xs = bf2f(pr[HV + h]) + bf2f(dt_bias[h]);
+      gv = -expf(bf2f(A_log[h])) * (xs > 20.f ? xs : log1pf(expf(xs)));
+    }
+    if constexpr (SCATTER) {
+      for (int p = p0; p < p1; ++p) {
+        const int64_t slot = rep_pos[p];
+        beta[slot * HV + h] = f2bf(bv);
+        g[slot * HV + h] = gv;
+      }
+    } else {
+      beta[static_cast<int64_t>(n) * HV + h] = f2bf(bv);
+      g[static_cast<int64_t>(n) * HV + h] = gv;
+    }
+  }
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const bool isqk = c0 < 2 * KD;
+  uint4 ov = make_uint4(0u, 0u, 0u, 0u);
+  if (!pad) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    // taps in the order of the reference: oldest row first, weight column i multiplies history row i
+    uint4 wv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) wv[u] = __ldg(reinterpret_cast<const uint4*>(convw + static_cast<int64_t>(c0) * 4 + u * 8));
+    const bf16_t* wb = reinterpret_cast<const bf16_t*>(wv);  // wb[e*4 + tap]
+    const int rows[4] = {hr.x, hr.y, hr.z, hr.w};
+#pragma unroll
+    for (int tap = 0; tap < 4; ++tap) {
+      if (rows[tap] >= 0) {
+        float xv[8];
+        unpack8(*reinterpret_cast<const uint4*>(proj + static_cast<int64_t>(rows[tap]) * P + c0), xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += bf2f(wb[e * 4 + tap]) * xv[e];
+      }
+    }
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = round_bf(silu_f(acc[e]));
+    if (isqk) {  // 16 consecutive threads cover one 128-wide head
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += o[e] * o[e];
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      const float rn = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] *= rn;
+    }
+    ov = pack8(o);
+  }
+  bf16_t* dst;
+  int64_t width;
+  int col;
+  if (c0 < KD) { dst = q; width = KD; col = c0; }
+  else if (c0 < 2 * KD) { dst = k; width = KD; col = c0 - KD; }
+  else { dst = v; width = VD; col = c0 - 2 * KD; }
+  if constexpr (SCATTER) {
+    for (int p = p0; p < p1; ++p) *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(rep_pos[p]) * width + col) = ov;
+  } else {
+    *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(n) * width + col) = ov;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------- gdn_intra
+constexpr int kLd = kHD + 8;      // padded row length (bf16) of a [64 x 128] tile in shared memory: 272 bytes
+constexpr int kIntraThreads = 256;
+constexpr int kIntraSmem = 4 * kChunk * kLd * 2 + kChunk * kChunk * 4 + 4 * kChunk * 4;
+
+__global__ void __launch_bounds__(kIntraThreads)
+gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, const bf16_t* __restrict__ v,
+                 const float* __restrict__ g, const bf16_t* __restrict__ beta, const int32_t* __restrict__ chunks,
+                 bf16_t* __restrict__ scratch, int HK, int HV, float scale) {
+  const int4 ch = reinterpret_cast<const int4*>(chunks)[blockIdx.x];
+  const int row0 = ch.x, nrows = ch.y;
+  if (nrows <= 0) return;
+  const int h = blockIdx.y, hk = h / (HV / HK);
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16_t* Ks = reinterpret_cast<bf16_t*>(smem_raw);
+  bf16_t* Qs = Ks + kChunk * kLd;
+  bf16_t* Vs = Qs + kChunk * kLd;
+  bf16_t* KGs = Vs + kChunk * kLd;
+  float* As = reinterpret_cast<float*>(KGs + kChunk * kLd);   // [64][64]
+  float* Gs = As + kChunk * kChunk;                            // G * log2e (inclusive cumsum)
+  float* Bs = Gs + kChunk;                                     // beta
+  float* EGs = Bs + kChunk;                                    // exp(G)
+  float* EKs = EGs + kChunk;                                   // exp(G_L - G)
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int KD = HK * kHD, VD = HV * kHD;
+
+  // ---- load K, Q, V rows (zero rows past the end of the chunk)
+  for (int i = tid; i < 3 * kChunk * (kHD / 8); i += kIntraThreads) {
+    const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
+    const int r = rem >> 4, cv = (rem & 15) * 8;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (r < nrows) {
+      const int64_t row = row0 + r;
+      const bf16_t* src = which == 0 ? k + row * KD + hk * kHD : which == 1 ? q + row * KD + hk * kHD : v + row * VD + h * kHD;
+      val = *reinterpret_cast<const uint4*>(src + cv);
+    }
+    bf16_t* dst = which == 0 ? Ks : which == 1 ? Qs : Vs;
+    *reinterpret_cast<uint4*>(dst + r * kLd + cv) = val;
+  }
+  // ---- cumulative log-decay (warp 0): two elements per lane
+  if (warp == 0) {
+    const int r0 = lane * 2, r1 = r0 + 1;
+    float g0 = r0 < nrows ? g[static_cast<int64_t>(row0 + r0) * HV + h] : 0.f;
+    float g1 = r1 < nrows ? g[static_cast<int64_t>(row0 + r1) * HV + h] : 0.f;
+    Bs[r0] = r0 < nrows ? bf2f(beta[static_cast<int64_t>(row0 + r0) * HV + h]) : 0.f;
+    Bs[r1] = r1 < nrows ? bf2f(beta[static_cast<int64_t>(row0 + r1) * HV + h]) : 0.f;
+    float s = g0 + g1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
+    }
+    const float c1 = s, c0 = s - g1;      // inclusive sums at r1 and r0
+    const float total = __shfl_sync(0xffffffffu, s, 31);
+    Gs[r0] = c0 * kLog2e; Gs[r1] = c1 * kLog2e;
+    EGs[r0] = exp2f(c0 * kLog2e); EGs[r1] = exp2f(c1 * kLog2e);
+    EKs[r0] = exp2f((total - c0) * kLog2e); EKs[r1] = exp2f((total - c1) * kLog2e);
+    if (lane == 0) {
+      float* gl = reinterpret_cast<float*>(scratch + (static_cast<int64_t>(blockIdx.x) * HV + h) * kItemElems + kOffGl);
+      gl[0] = exp2f(total * kLog2e);
+    }
+  }
+  __syncthreads();
+
+  bf16_t* item = scratch + (static_cast<int64_t>(blockIdx.x) * HV + h) * kItemElems;
+  // ---- K K^T (warps 0-3) and Q K^T (warps 4-7): 16 rows x 64 columns per warp
+  {
+    const bool is_qk = warp >= 4;
+    const int m0 = (warp & 3) * 16;
+    const bf16_t* Am = is_qk ? Qs : Ks;
+    float acc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+    const int a_row = m0 + (lane & 15), a_col = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + ((lane >> 4) << 3), b_col = ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int ks = 0; ks < kHD / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(smem_u32(Am + a_row * kLd + ks * 16 + a_col), a0, a1, a2, a3);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {  // two 8-column tiles per ldmatrix.x4
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(smem_u32(Ks + (np * 16 + b_row) * kLd + ks * 16 + b_col), b0, b1, b2, b3);
+        mma_bf16(acc[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    const int gr = lane >> 2, tc = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int i = m0 + gr + half * 8;
+        const float gi = Gs[i];
+        float o2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = nt * 8 + tc + e;
+          const float a = acc[nt][half * 2 + e];
+          if (is_qk) o2[e] = j <= i ? a * exp2f(gi - Gs[j]) * scale : 0.f;
+          else o2[e] = j < i ? a * Bs[i] * exp2f(gi - Gs[j]) : 0.f;
+        }
+        if (is_qk) {
+          *reinterpret_cast<uint32_t*>(item + kOffA + i * kChunk + nt * 8 + tc) = pack2(o2[0], o2[1]);
+        } else {
+          As[i * kChunk + nt * 8 + tc] = o2[0];
+          As[i * kChunk + nt * 8 + tc + 1] = o2[1];
+        }
+      }
+    }
+  }
+  // ---- qg = q e^G scale (in place), kg = k e^(G_L - G)
+  for (int i = tid; i < kChunk * (kHD / 8); i += kIntraThreads) {
+    const int r = i >> 4, cv = (i & 15) * 8;
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(Qs + r * kLd + cv), f);
+    const float sq = EGs[r] * scale;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] *= sq;
+    *reinterpret_cast<uint4*>(Qs + r * kLd + cv) = pack8(f);
+    unpack8(*reinterpret_cast<const uint4*>(Ks + r * kLd + cv), f);
+    const float sk = EKs[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] *= sk;
+    *reinterpret_cast<uint4*>(KGs + r * kLd + cv) = pack8(f);
+  }
+  __syncthreads();
+
+  // ---- forward substitution, one right-hand-side column per thread: x_i = b_i - sum_{j<i} A[i][j] x_j
+  {
+    const bool is_w = tid >= kHD;
+    const int c = is_w ? tid - kHD : tid;
+    bf16_t* col = (is_w ? Ks : Vs) + c;
+    float x[kChunk];
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      float b = bf2f(col[i * kLd]) * Bs[i];
+      if (is_w) b *= EGs[i];
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      const float4* arow = reinterpret_cast<const float4*>(As + i * kChunk);
+#pragma unroll
+      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+        const float4 a = arow[j4];   // entries at or right of the diagonal are zero
+        s0 += a.x * x[4 * j4];
+        if (4 * j4 + 1 < i) s1 += a.y * x[4 * j4 + 1];
+        if (4 * j4 + 2 < i) s2 += a.z * x[4 * j4 + 2];
+        if (4 * j4 + 3 < i) s3 += a.w * x[4 * j4 + 3];
+      }
+      x[i] = b - ((s0 + s1) + (s2 + s3));
+    }
+    // each thread owns its column: results replace the inputs in place
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) col[i * kLd] = f2bf(x[i]);
+  }
+  __syncthreads();
+  // ---- copy w (Ks), u (Vs), qg (Qs), kg (KGs) to the scratch item, 16 bytes per thread
+  for (int i = tid; i < 4 * kChunk * (kHD / 8); i += kIntraThreads) {
+    const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
+    const int r = rem >> 4, cv = (rem & 15) * 8;
+    const bf16_t* srcb = which == 0 ? Ks : which == 1 ? Vs : which == 2 ? Qs : KGs;
+    *reinterpret_cast<uint4*>(item + which * (kChunk * kHD) + r * kHD + cv) = *reinterpret_cast<const uint4*>(srcb + r * kLd + cv);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------- gdn_state
+constexpr int kDv = 32;                 // state columns per CTA
+constexpr int kLdS = kDv + 8;           // padded row (bf16) of [* x 32] tiles: 80 bytes
+constexpr int kLdA = kChunk + 8;        // padded row (bf16) of the [64 x 64] tile: 144 bytes
+constexpr int kStateThreads = 128;
+constexpr int kBufElems = 3 * kChunk * kLd + kChunk * kLdS + kChunk * kLdA;  // w | qg | kg | u-slice | Aqk
+constexpr int kStateSmem = 2 * kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 2 * kStateThreads * 32 * 4 + 16;
+
+__device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, int dv0, int tid) {
+  // w, qg, kg: [64][128] each
+  for (int i = tid; i < 3 * kChunk * 16; i += kStateThreads) {
+    const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
+    const int r = rem >> 4, cv = (rem & 15) * 8;
+    const int src_off = (which == 0 ? kOffW : which == 1 ? kOffQg : kOffKg) + r * kHD + cv;
+    cp_async16(smem_u32(buf + which * (kChunk * kLd) + r * kLd + cv), item + src_off);
+  }
+  bf16_t* us = buf + 3 * kChunk * kLd;
+  for (int i = tid; i < kChunk * (kDv / 8); i += kStateThreads) {
+    const int r = i >> 2, cv = (i & 3) * 8;
+    cp_async16(smem_u32(us + r * kLdS + cv), item + kOffU + r * kHD + dv0 + cv);
+  }
+  bf16_t* as = us + kChunk * kLdS;
+  for (int i = tid; i < kChunk * (kChunk / 8); i += kStateThreads) {
+    const int r = i >> 3, cv = (i & 7) * 8;
+    cp_async16(smem_u32(as + r * kLdA + cv), item + kOffA + r * kChunk + cv);
+  }
+}
+
+// steps[s] = (chunk, load, save, aux): load 0 carry on / 1 zero / 2 slot A / 3 slot B / 4 initial state aux>>16 - 1;
+// save bit 0 slot A, bit 1 slot B; (aux & 0xffff) - 1 = index of a final-state output written after the step.
+__global__ void __launch_bounds__(kStateThreads)
+gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__ chunks, const int32_t* __restrict__ steps,
+                 const int32_t* __restrict__ walk_ptr, const float* __restrict__ init_state, float* __restrict__ final_state,
+                 bf16_t* __restrict__ out, int HV) {
+  const int h = blockIdx.x, dv0 = blockIdx.y * kDv;
+  const int s_begin = walk_ptr[blockIdx.z], s_end = walk_ptr[blockIdx.z + 1];
+  if (s_begin >= s_end) return;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16_t* bufs = reinterpret_cast<bf16_t*>(smem_raw);
+  bf16_t* Sb = bufs + 2 * kBufElems;              // bf16 copy of the state slice [128 dk][32 dv]
+  bf16_t* Vn = Sb + kHD * kLdS;                   // v' [64][32]
+  float* slots = reinterpret_cast<float*>(Vn + kChunk * kLdS);   // [2][32 regs][128 threads]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gr = lane >> 2, tc = (lane & 3) * 2;
+  const int64_t VD = static_cast<int64_t>(HV) * kHD;
+
+  // state slice in mma accumulator layout: warp owns dk rows [32*warp, 32*warp+32): 2 m-tiles x 4 n-tiles x 4
+  float S[2][4][4];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) S[a][b][e] = 0.f;
+
+  auto item_of = [&](int s) {
+    const int c = steps[s * 4];
+    return scratch + (static_cast<int64_t>(c) * HV + h) * kItemElems;
+  };
+  state_prefetch(bufs, item_of(s_begin), dv0, tid);
+  cp_async_commit();
+
+  for (int s = s_begin; s < s_end; ++s) {
+    const int4 st = reinterpret_cast<const int4*>(steps)[s];
+    const int4 ch = reinterpret_cast<const int4*>(chunks)[st.x];
+    bf16_t* buf = bufs + ((s - s_begin) & 1) * kBufElems;
+    const bf16_t* item = item_of(s);
+    if (s + 1 < s_end) state_prefetch(bufs + ((s + 1 - s_begin) & 1) * kBufElems, item_of(s + 1), dv0, tid);
+    cp_async_commit();
+
+    // ---- choose the incoming state
+    if (st.y == 1) {
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) S[a][b][e] = 0.f;
+    } else if (st.y == 2 || st.y == 3) {
+      const float* sl = slots + (st.y - 2) * (32 * kStateThreads);
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) S[a][b][e] = sl[((a * 4 + b) * 4 + e) * kStateThreads + tid];
+    } else if (st.y == 4) {
+      const float* is = init_state + (static_cast<int64_t>((st.w >> 16) - 1) * HV + h) * (kHD * kHD);
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int dk = warp * 32 + a * 16 + gr + (e >> 1) * 8, dv = dv0 + b * 8 + tc + (e & 1);
+            S[a][b][e] = is[dk * kHD + dv];
+          }
+    }
+    // ---- bf16 copy of the state for the tensor-core operands
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int dk = warp * 32 + a * 16 + gr + half * 8;
+          *reinterpret_cast<uint32_t*>(Sb + dk * kLdS + b * 8 + tc) = pack2(S[a][b][half * 2], S[a][b][half * 2 + 1]);
+        }
+    cp_async_wait<1>();   // this step's operands have landed (the prefetch of the next step may still be in flight)
+    __syncthreads();
+
+    const bf16_t* Ws = buf;
+    const bf16_t* Qg = buf + kChunk * kLd;
+    const bf16_t* Kg = buf + 2 * kChunk * kLd;
+    const bf16_t* Us = buf + 3 * kChunk * kLd;
+    const bf16_t* Aq = Us + kChunk * kLdS;
+    const int m0 = warp * 16;
+    const int a_row = m0 + (lane & 15), a_col = (lane >> 4) * 8;
+    // B operand from [k][n] storage through ldmatrix.trans: lanes 0-15 rows k0..k0+15 at column n0, lanes 16-31 at n0+8
+    const int bt_row = lane & 15, bt_col = (lane >> 4) * 8;
+
+    // ---- (1) acc_w = w S ; acc_o = qg S   (16 rows x 32 columns per warp, K = 128)
+    float accw[4][4], acco[4][4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { accw[b][e] = 0.f; acco[b][e] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < kHD / 16; ++ks) {
+      uint32_t w0, w1, w2, w3, q0, q1, q2, q3;
+      ldsm_x4(smem_u32(Ws + a_row * kLd + ks * 16 + a_col), w0, w1, w2, w3);
+      ldsm_x4(smem_u32(Qg + a_row * kLd + ks * 16 + a_col), q0, q1, q2, q3);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(Sb + (ks * 16 + bt_row) * kLdS + np * 16 + bt_col), b0, b1, b2, b3);
+        mma_bf16(accw[2 * np], w0, w1, w2, w3, b0, b1);
+        mma_bf16(accw[2 * np + 1], w0, w1, w2, w3, b2, b3);
+        mma_bf16(acco[2 * np], q0, q1, q2, q3, b0, b1);
+        mma_bf16(acco[2 * np + 1], q0, q1, q2, q3, b2, b3);
+      }
+    }
+    // v' = u - w S  -> shared memory (bf16) for the two products that follow
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = m0 + gr + half * 8;
+        const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(Us + r * kLdS + b * 8 + tc);
+        const float2 uf = __bfloat1622float2(u2);
+        *reinterpret_cast<uint32_t*>(Vn + r * kLdS + b * 8 + tc) = pack2(uf.x - accw[b][half * 2], uf.y - accw[b][half * 2 + 1]);
+      }
+    __syncthreads();
+
+    // ---- (2) o = qg S + Aqk v'   (K = 64)
+#pragma unroll
+    for (int ks = 0; ks < kChunk / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(smem_u32(Aq + a_row * kLdA + ks * 16 + a_col), a0, a1, a2, a3);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(Vn + (ks * 16 + bt_row) * kLdS + np * 16 + bt_col), b0, b1, b2, b3);
+        mma_bf16(acco[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acco[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = m0 + gr + half * 8;
+      if (r < ch.y) {
+        bf16_t* orow = out + static_cast<int64_t>(ch.x + r) * VD + h * kHD + dv0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          *reinterpret_cast<uint32_t*>(orow + b * 8 + tc) = pack2(acco[b][half * 2], acco[b][half * 2 + 1]);
+      }
+    }
+    // ---- (3) S = S e^(G_L) + kg^T v'   (warp owns dk rows 32*warp.., K = 64 chunk rows)
+    {
+      const float gl = *reinterpret_cast<const float*>(item + kOffGl);
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) S[a][b][e] *= gl;
+      // A operand = kg^T: A[m = dk][k = row] = kg[row][dk]; ldmatrix.trans over rows of kg
+      const int at_row = (lane & 7) + ((lane >> 4) << 3);   // chunk row (k) inside the 16-row step
+      const int at_col = ((lane >> 3) & 1) * 8;             // dk offset (m) inside the 16-row tile
+#pragma unroll
+      for (int ks = 0; ks < kChunk / 16; ++ks) {
+        uint32_t b0[2], b1[2], b2[2], b3[2];
+#pragma unroll
+        for (int np = 0; np < 2; ++np)
+          ldsm_x4_t(smem_u32(Vn + (ks * 16 + bt_row) * kLdS + np * 16 + bt_col), b0[np], b1[np], b2[np], b3[np]);
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+          uint32_t a0, a1, a2, a3;
+          ldsm_x4_t(smem_u32(Kg + (ks * 16 + at_row) * kLd + warp * 32 + a * 16 + at_col), a0, a1, a2, a3);
+#pragma unroll
+          for (int np = 0; np < 2; ++np) {
+            mma_bf16(S[a][2 * np], a0, a1, a2, a3, b0[np], b1[np]);
+            mma_bf16(S[a][2 * np + 1], a0, a1, a2, a3, b2[np], b3[np]);
+          }
+        }
+      }
+    }
+    // ---- park / export the state
+    if (st.z & 3) {
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl)
+        if (st.z & (1 << sl)) {
+          float* dst = slots + sl * (32 * kStateThreads);
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) dst[((a * 4 + b) * 4 + e) * kStateThreads + tid] = S[a][b][e];
+        }
+    }
+    if ((st.w & 0xffff) != 0 && final_state != nullptr) {
+      float* fs = final_state + (static_cast<int64_t>((st.w & 0xffff) - 1) * HV + h) * (kHD * kHD);
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int dk = warp * 32 + a * 16 + gr + (e >> 1) * 8, dv = dv0 + b * 8 + tc + (e & 1);
+            fs[dk * kHD + dv] = S[a][b][e];
+          }
+    }
+    __syncthreads();   // everyone is done with Sb, Vn and this buffer before they are overwritten
+  }
+  cp_async_wait<0>();
+}
+
+// ------------------------------------------------------------------------------------------------------ gated RMSNorm
+// one warp per (row, head); 4 dims per lane. x row of packed row n is x[inv[n]] (inv may be null: identity).
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_kernel(const bf16_t* __restrict__ x, const int32_t* __restrict__ inv, const bf16_t* __restrict__ proj,
+                     const bf16_t* __restrict__ w, bf16_t* __restrict__ out, int64_t items, int HV, int zoff, int P, float eps) {
+  const int64_t it = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (it >= items) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t n = it / HV;
+  const int h = static_cast<int>(it - n * HV);
+  const int64_t srow = inv ? inv[n] : n;
+  const int d0 = lane * 4;
+  const uint2 xa = *reinterpret_cast<const uint2*>(x + (srow * HV + h) * kHD + d0);
+  const uint2 za = *reinterpret_cast<const uint2*>(proj + n * P + zoff + h * kHD + d0);
+  const uint2 wa = __ldg(reinterpret_cast<const uint2*>(w + d0));
+  const bf16_t* xb = reinterpret_cast<const bf16_t*>(&xa);
+  const bf16_t* zb = reinterpret_cast<const bf16_t*>(&za);
+  const bf16_t* wb = reinterpret_cast<const bf16_t*>(&wa);
+  float xv[4], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { xv[e] = bf2f(xb[e]); ss += xv[e] * xv[e]; }
+  ss = warp_sum(ss);
+  const float rstd = 1.0f / sqrtf(ss / static_cast<float>(kHD) + eps);
+  uint2 oa;
+  bf16_t* ob = reinterpret_cast<bf16_t*>(&oa);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float z = bf2f(zb[e]);
+    ob[e] = f2bf(((xv[e] * rstd) * bf2f(wb[e])) * z * sigmoid_f(z));
+  }
+  *reinterpret_cast<uint2*>(out + n * (static_cast<int64_t>(HV) * kHD) + h * kHD + d0) = oa;
+}
+
+}  // namespace
+}  // namespace ojb
+
+using namespace ojb;
+
+extern "C" int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t* rep_ptr, const int32_t* rep_pos,
+                            int64_t n_slots, const void* convw, const void* A_log, const void* dt_bias, void* q, void* k,
+                            void* v, float* g, void* beta, int64_t N, int64_t KD, int64_t VD, int64_t HV, int64_t HK,
+                            ojb_stream_t stream) {
+  if (N == 0) return OJB_OK;
+  OJB_REQUIRE(proj && hist && convw && A_log && dt_bias && q && k && v && g && beta && N > 0);
+  OJB_REQUIRE(HK > 0 && HV > 0 && KD == HK * kHD && VD == HV * kHD && HV <= 256);
+  const int C = static_cast<int>(2 * KD + VD);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned gx = static_cast<unsigned>(ceil_div(C / 8, 256));
+  if (rep_ptr != nullptr) {
+    OJB_REQUIRE(rep_pos != nullptr && n_slots > 0);
+    dim3 grid(gx, static_cast<unsigned>(N + ceil_div(n_slots, 16)));
+    gdn_prep_kernel<true><<<grid, 256, 0, st>>>(static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), rep_ptr, rep_pos,
+                                                static_cast<const bf16_t*>(convw), static_cast<const bf16_t*>(A_log),
+                                                static_cast<const bf16_t*>(dt_bias), static_cast<bf16_t*>(q), static_cast<bf16_t*>(k),
+                                                static_cast<bf16_t*>(v), g, static_cast<bf16_t*>(beta), static_cast<int>(N),
+                                                static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV));
+  } else {
+    dim3 grid(gx, static_cast<unsigned>(N));
+    gdn_prep_kernel<false><<<grid, 256, 0, st>>>(static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), nullptr, nullptr,
+                                                 static_cast<const bf16_t*>(convw), static_cast<const bf16_t*>(A_log),
+                                                 static_cast<const bf16_t*>(dt_bias), static_cast<bf16_t*>(q), static_cast<bf16_t*>(k),
+                                                 static_cast<bf16_t*>(v), g, static_cast<bf16_t*>(beta), static_cast<int>(N),
+                                                 static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV));
+  }
+  return launch_status(cudaGetLastError());
+}
+
+extern "C" int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV) { return n_chunks * HV * kItemElems * 2; }
+
+extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                               const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                               int64_t n_walks, const float* init_state, float* final_state, void* scratch, void* out,
+                               int64_t HK, int64_t HV, float scale, ojb_stream_t stream) {
+  if (n_chunks == 0 || n_walks == 0) return OJB_OK;
+  OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && scratch && out);
+  OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_walks > 0 && n_walks <= 65535 && HV <= 65535);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
+      return OJB_ERR_LAUNCH;
+    attr = true;
+  }
+  gdn_intra_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), kIntraThreads, kIntraSmem, st>>>(
+      static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
+      static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
+  if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
+  gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
+      static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out),
+      static_cast<int>(HV));
+  return launch_status(cudaGetLastError());
+}
+
+extern "C" int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* proj, const void* w, void* out, int64_t N,
+                                 int64_t HV, int64_t HD, int64_t zoff, int64_t P, float eps, ojb_stream_t stream) {
+  if (N == 0) return OJB_OK;
+  OJB_REQUIRE(x && proj && w && out && N > 0 && HV > 0 && HD == kHD && zoff >= 0 && zoff + HV * HD <= P && zoff % 4 == 0 && P % 4 == 0);
+  const int64_t items = N * HV;
+  gated_rmsnorm_kernel<<<static_cast<unsigned>(ceil_div(items, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf16_t*>(x), inv, static_cast<const bf16_t*>(proj), static_cast<const bf16_t*>(w), static_cast<bf16_t*>(out),
+      items, static_cast<int>(HV), static_cast<int>(zoff), static_cast<int>(P), eps);
+  return launch_status(cudaGetLastError());
+}

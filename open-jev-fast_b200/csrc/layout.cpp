@@ -9,7 +9,7 @@
 //   steps  [NC_max, 4] depth-first walk over the chunks for the state pass: (chunk, load, save, 0) where load is
 //                      0 = carry on, 1 = start from zero, 2 = restore slot A (root end), 3 = restore slot B (question
 //                      end); save is 0 = none, 1 = store slot A, 2 = store slot B
-//   meta   [8]         (number of chunks, number of steps, Lr, R, S, 0, 0, 0)
+//   meta   [8]         (number of chunks, number of steps, Lr, R, S, 0, walk begin = 0, walk end = number of steps)
 // The tree is: root = longest common prefix of all candidates (capped so that every candidate keeps one row), one node
 // per question = common prefix of its candidates beyond the root (same cap), one leaf per candidate.
 #include <stdint.h>
@@ -279,5 +279,6 @@ extern "C" int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, con
   }
   meta[0] = static_cast<int32_t>(nc); meta[1] = static_cast<int32_t>(ns); meta[2] = static_cast<int32_t>(Lr);
   meta[3] = static_cast<int32_t>(R); meta[4] = static_cast<int32_t>(S);
+  meta[6] = 0; meta[7] = static_cast<int32_t>(ns);  // walk_ptr of the single depth-first walk
   return OJB_OK;
 }

@@ -148,3 +148,137 @@ def fullattn_prep2(proj, qw1, kw1, cosb, sinb, B, T, HQ, HKV, D, eps):
 
 
 fullattn_prep = fullattn_prep2   # src/ext.py:10 — same contract
+
+
+# ------------------------------------------------------------------------------------------------ Gated DeltaNet
+def _prep(proj, hist, rep_ptr, rep_pos, n_out, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+    _chk(proj, hist, rep_ptr, rep_pos, convw, A_log, dt_bias)
+    if HD != 128 or HK * HD != KD or HV * HD != VD or convw.shape[1] != 4:
+        raise RuntimeError("linattn_prep: head dim must be 128 and the conv width 4")
+    N = proj.shape[0]
+    if proj.shape[1] != 2 * KD + 2 * VD + 2 * HV or hist.shape != (N + 1, 4) or hist.dtype != torch.int32:
+        raise RuntimeError("linattn_prep: proj must be [N, 2KD+2VD+2HV] and hist int32 [N+1, 4]")
+    dev = proj.device
+    q = torch.empty(n_out, KD, dtype=bf16, device=dev)
+    k = torch.empty(n_out, KD, dtype=bf16, device=dev)
+    v = torch.empty(n_out, VD, dtype=bf16, device=dev)
+    g = torch.empty(n_out, HV, dtype=torch.float32, device=dev)
+    beta = torch.empty(n_out, HV, dtype=bf16, device=dev)
+    call("ojb_gdn_prep", ptr(proj), ptr(hist), ptr(rep_ptr), ptr(rep_pos), i64(0 if rep_pos is None else rep_pos.numel()),
+         ptr(convw), ptr(A_log), ptr(dt_bias), ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), i64(N), i64(KD), i64(VD),
+         i64(HV), i64(HK), stream_ptr())
+    return q, k, v, g, beta
+
+
+def _expand(x, HK, HV, HD):
+    return x.view(-1, HK, 1, HD).expand(-1, HK, HV // HK, HD).reshape(-1, HV * HD).contiguous()
+
+
+def linattn_prep_rows(proj, hist, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+    """One output row per packed row (no replication): [q [N,KD], k [N,KD], v [N,VD], g f32 [N,HV], beta [N,HV]].
+    Not in the reference; the tree-native Gated DeltaNet pass consumes this layout."""
+    return list(_prep(proj, hist, None, None, proj.shape[0], convw, A_log, dt_bias, KD, VD, HV, HK, HD))
+
+
+def linattn_prep_dedup2(proj, hist, rep_ptr, rep_pos, L2, convw, A_log, dt_bias, KD, VD, HV, HK, HD, rep_qk):
+    """src/ext.py:22 — replicated slots [S*L2, ...]; rep_qk expands q / k to the value heads."""
+    R = rep_pos.numel()
+    if rep_ptr.numel() != proj.shape[0] + 2 or R % L2:
+        raise RuntimeError("linattn_prep_dedup2: rep_ptr must have N+2 entries and rep_pos a multiple of L2")
+    q, k, v, g, beta = _prep(proj, hist, rep_ptr, rep_pos, R, convw, A_log, dt_bias, KD, VD, HV, HK, HD)
+    if rep_qk:
+        q, k = _expand(q, HK, HV, HD), _expand(k, HK, HV, HD)
+    return [q, k, v, g, beta]
+
+
+def linattn_prep_dedup3(proj, hist, rep_ptr, rep_pos, L2, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+    """src/ext.py:27 — as dedup2 plus a copy of k expanded to the value heads: [q, k, krep, v, g, beta]."""
+    q, k, v, g, beta = linattn_prep_dedup2(proj, hist, rep_ptr, rep_pos, L2, convw, A_log, dt_bias, KD, VD, HV, HK, HD, False)
+    return [q, k, _expand(k, HK, HV, HD), v, g, beta]
+
+
+_table_cache = {}
+
+
+def _seq_tables(B, T, device):
+    """chunk / step / walk tables for B independent sequences of T rows laid out back to back."""
+    key = (B, T, str(device))
+    t = _table_cache.get(key)
+    if t is None:
+        nc = (T + 63) // 64
+        chunks = torch.zeros(B * nc, 4, dtype=torch.int32)
+        steps = torch.zeros(B * nc, 4, dtype=torch.int32)
+        for b in range(B):
+            for j in range(nc):
+                i = b * nc + j
+                chunks[i, 0], chunks[i, 1] = b * T + j * 64, min(64, T - j * 64)
+                steps[i, 0], steps[i, 1] = i, 1 if j == 0 else 0
+        walks = torch.arange(0, (B + 1) * nc, nc, dtype=torch.int32)
+        t = _table_cache[key] = tuple(x.to(device) for x in (chunks, steps, walks))
+    return t
+
+
+def gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walk_ptr, n_walks, init_state=None, final_state=None, out=None):
+    """Table-driven chunked gated delta rule (see include/ojb200.h ojb_gdn_chunked). q, k [rows, HK, 128],
+    v [rows, HV, 128], g f32 / beta bf16 [rows, HV]. Returns out bf16 [rows, HV, 128]."""
+    _chk(q, k, v, g, beta, chunks, steps, walk_ptr, init_state, final_state)
+    rows, HV, HD = v.shape[-3], v.shape[-2], v.shape[-1]
+    HK = k.shape[-2]
+    if HD != 128 or k.shape[-1] != 128 or g.dtype != torch.float32 or beta.dtype != bf16:
+        raise RuntimeError("gdn: head dim must be 128, g fp32 and beta bf16")
+    nch = chunks.shape[0]
+    nbytes = _lib.lib().ojb_gdn_scratch_bytes
+    nbytes.restype = _lib.ctypes.c_int64
+    scratch = torch.empty(nbytes(i64(nch), i64(HV)), dtype=torch.uint8, device=v.device)
+    if out is None:
+        out = torch.empty(v.shape, dtype=bf16, device=v.device)
+    call("ojb_gdn_chunked", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(chunks), i64(nch), ptr(steps), ptr(walk_ptr),
+         i64(n_walks), ptr(init_state), ptr(final_state), ptr(scratch), ptr(out), i64(HK), i64(HV), f32(scale), stream_ptr())
+    return out
+
+
+def gdn_fused6(q, k, v, g, beta, scale):
+    """src/ext.py:34 — q, k [B,T,HK,128], v [B,T,HV,128], g f32 / beta [B,T,HV] -> o [B,T,HV,128]; zero initial state,
+    rows of the last partial chunk beyond T do not exist, pad slots inside T produce zeros only if their inputs are."""
+    B, T = v.shape[0], v.shape[1]
+    chunks, steps, walks = _seq_tables(B, T, v.device)
+    return gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walks, B)
+
+
+gdn_fused = gdn_fused2 = gdn_fused3 = gdn_fused4 = gdn_fused8 = gdn_fused9 = gdn_fused6   # src/ext.py:30-33,41-42
+
+
+def gdn_tree(q, k, v, g, beta, scale, lay, final_state=None):
+    """Tree-native pass over packed rows: q, k [N, HK*128], v [N, HV*128] from linattn_prep_rows; the chunk / walk tables
+    come from the layout (lay.chunks, lay.steps, lay.meta). Shared nodes are computed once. Returns o [N, HV, 128]; rows
+    that belong to no node (end padding) are zero."""
+    N = v.shape[0]
+    HV = g.shape[1]
+    HK = q.shape[1] // 128
+    out = torch.zeros(N, HV, 128, dtype=bf16, device=v.device)
+    return gdn_chunked(q.view(N, HK, 128), k.view(N, HK, 128), v.view(N, HV, 128), g, beta, scale, lay.chunks, lay.steps,
+                       lay.meta[6:8], 1, None, final_state, out)
+
+
+def _gated_norm(x, inv, proj, w, HV, HD, zoff, eps):
+    _chk(x, inv, proj, w)
+    N, P = proj.shape
+    out = torch.empty(N, HV * HD, dtype=bf16, device=proj.device)
+    call("ojb_gated_rmsnorm", ptr(x), ptr(inv), ptr(proj), ptr(w), ptr(out), i64(N), i64(HV), i64(HD), i64(zoff), i64(P),
+         f32(eps), stream_ptr())
+    return out
+
+
+def gated_rmsnorm(x, proj, w, HV, HD, zoff, eps):
+    """src/ext.py:9 — x [N, HV, HD] in packed-row order."""
+    return _gated_norm(x, None, proj, w, HV, HD, zoff, eps)
+
+
+def gated_rmsnorm_inv(x, inv, proj, w, HV, HD, zoff, eps):
+    """src/ext.py:19 — x read at slot inv[n]."""
+    return _gated_norm(x, inv, proj, w, HV, HD, zoff, eps)
+
+
+def gated_rmsnorm_inv2(x, inv, proj, w, sig, HV, HD, zoff, eps):
+    """src/ext.py:25 — as gated_rmsnorm_inv; the sigmoid is computed (same bits as the table)."""
+    return _gated_norm(x, inv, proj, w, HV, HD, zoff, eps)

@@ -17,6 +17,8 @@ def _same(a, b, frac=0.995, atol_ulps=2):
     """bf16 outputs: at least `frac` bit-identical, the rest within a couple of bf16 ulps (reduction-order noise)."""
     a, b = a.float().cpu(), b.float().cpu()
     assert a.shape == b.shape
+    if a.numel() == 0:
+        return
     eq = (a == b).float().mean().item()
     err = (a - b).abs()
     tol = b.abs() * 2 ** -8 * atol_ulps + 1e-6
