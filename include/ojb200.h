@@ -146,6 +146,25 @@ int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g,
 int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* proj, const void* w, void* out, int64_t N,
                       int64_t HV, int64_t HD, int64_t zoff, int64_t P, float eps, ojb_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Tree attention — replaces src/kernels.cu:4287-4458 fattn_tree (and, above 384 rows, the reference's
+ * F.scaled_dot_product_attention + gate_mul3 of src/fastmodel.py:470-473).
+ * qt bf16 [HQ, N, D], kt / vt bf16 [HKV, N, D] (head-major, from ojb_fullattn_prep), gate bf16 [N, HQ*D].
+ * Mask: vbits int32 [N, N/32] (bit b of word w of row n = key 32w+b visible), or, when vbits is null,
+ * krange int32 [N, 8] = (e0, a1, e1, a2, e2, -, -, -): row n sees keys [0,e0) + [a1,e1) + [a2,e2).
+ * y[N, HQ*D] = bf16(bf16(softmax(scale * q k^T + mask) v) * bf16(sigmoid(gate))). N % 32 == 0; D in {64, 128, 256};
+ * gq = query heads per CTA, a divisor of HQ/HKV, at most 6. Every row must see at least one key.
+ * ------------------------------------------------------------------------------------------------------------------ */
+int ojb_tree_attn(const void* qt, const void* kt, const void* vt, const void* gate, const int32_t* vbits,
+                  const int32_t* krange, void* y, int64_t N, int64_t HQ, int64_t HKV, int64_t D, int64_t gq, float scale,
+                  ojb_stream_t stream);
+
+/* Scoring head — replaces src/server.py:37 `mdl.head(forward_gtree(...).float())` together with the gather
+ * src/fastmodel.py:482 `hn[lay.lastidx]`: out[s, a] = bias[a] + sum_h float(hn[rows[s], h]) * W[a, h], all fp32.
+ * hn bf16 [N, H] (final-norm output), rows int64 [S] (last row of each candidate), W fp32 [A, H], bias fp32 [A] or null. */
+int ojb_score_head(const void* hn, const int64_t* rows, const float* W, const float* bias, float* out, int64_t S, int64_t A,
+                   int64_t H, ojb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -331,3 +331,39 @@ extern "C" int ojb_fullattn_prep(const void* proj, const float* qw1, const float
 #undef OJB_PREP
   return launch_status(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------------------------- scoring head
+namespace ojb {
+namespace {
+// one warp per (candidate, output): out[s, a] = bias[a] + sum_h float(hn[rows[s], h]) * W[a, h]
+__global__ void __launch_bounds__(256)
+score_head_kernel(const bf16_t* __restrict__ hn, const int64_t* __restrict__ rows, const float* __restrict__ W,
+                  const float* __restrict__ bias, float* __restrict__ out, int S, int A, int H) {
+  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= S * A) return;
+  const int lane = threadIdx.x & 31;
+  const int s = wid / A, a = wid - s * A;
+  const bf16_t* x = hn + rows[s] * static_cast<int64_t>(H);
+  const float* w = W + static_cast<int64_t>(a) * H;
+  float acc = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + c), f);
+    const float4 w0 = *reinterpret_cast<const float4*>(w + c), w1 = *reinterpret_cast<const float4*>(w + c + 4);
+    acc += f[0] * w0.x + f[1] * w0.y + f[2] * w0.z + f[3] * w0.w + f[4] * w1.x + f[5] * w1.y + f[6] * w1.z + f[7] * w1.w;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) out[wid] = acc + (bias ? bias[a] : 0.f);
+}
+}  // namespace
+}  // namespace ojb
+
+extern "C" int ojb_score_head(const void* hn, const int64_t* rows, const float* W, const float* bias, float* out, int64_t S,
+                              int64_t A, int64_t H, ojb_stream_t stream) {
+  if (S == 0 || A == 0) return OJB_OK;
+  OJB_REQUIRE(hn && rows && W && out && S > 0 && A > 0 && H > 0 && H % 8 == 0);
+  const int64_t warps = S * A;
+  ojb::score_head_kernel<<<static_cast<unsigned>(ojb::ceil_div(warps, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const ojb::bf16_t*>(hn), rows, W, bias, out, static_cast<int>(S), static_cast<int>(A), static_cast<int>(H));
+  return ojb::launch_status(cudaGetLastError());
+}

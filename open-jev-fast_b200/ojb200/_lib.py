@@ -75,12 +75,23 @@ def check_status(device=None):
             raise RuntimeError(f"ojb200: device-side wait ran out (status {v}); results of the last calls are invalid")
 
 
+_KERNELS_PER_CALL = {"ojb_gdn_chunked": 2}
+_launches = 0
+
+
+def launch_count():
+    """Number of kernels this process has launched through the C ABI so far."""
+    return _launches
+
+
 def call(name, *args):
+    global _launches
     fn = getattr(lib(), name)
     fn.restype = ctypes.c_int
     rc = fn(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed: {_ERR.get(rc, rc)}")
+    _launches += _KERNELS_PER_CALL.get(name, 1)
 
 
 def need_cuda_bf16(*tensors):

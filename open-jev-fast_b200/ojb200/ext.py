@@ -282,3 +282,54 @@ def gated_rmsnorm_inv(x, inv, proj, w, HV, HD, zoff, eps):
 def gated_rmsnorm_inv2(x, inv, proj, w, sig, HV, HD, zoff, eps):
     """src/ext.py:25 — as gated_rmsnorm_inv; the sigmoid is computed (same bits as the table)."""
     return _gated_norm(x, inv, proj, w, HV, HD, zoff, eps)
+
+
+# ------------------------------------------------------------------------------------------------ tree attention
+def _tree_attn(qt, kt, vt, gate, vbits, krange, scale, gq):
+    _chk(qt, kt, vt, gate, vbits, krange)
+    if qt.dim() != 4 or qt.shape[0] != 1:
+        raise RuntimeError("fattn_tree: qt must be [1, HQ, N, D]")
+    _, HQ, N, D = qt.shape
+    HKV = kt.shape[1]
+    if N % 32 or (HQ // HKV) % gq or D not in (64, 128, 256):
+        raise RuntimeError("fattn_tree: N % 32 == 0, gq | HQ/HKV and D in {64,128,256} required")
+    y = torch.empty(N, HQ * D, dtype=bf16, device=qt.device)
+    call("ojb_tree_attn", ptr(qt), ptr(kt), ptr(vt), ptr(gate), ptr(vbits), ptr(krange), ptr(y), i64(N), i64(HQ), i64(HKV),
+         i64(D), i64(gq), f32(scale), stream_ptr())
+    return y
+
+
+def fattn_tree(qt, kt, vt, gate, sig, vbits, scale, gq):
+    """src/ext.py:37 — ancestor-masked attention + gate from the packed visibility words; gq in {3, 6} heads per CTA."""
+    return _tree_attn(qt, kt, vt, gate, vbits, None, scale, gq)
+
+
+def fattn_tree3(qt, kt, vt, gate, sig, vbits, scale):
+    """src/ext.py:39 — the reference's two-warps-per-head schedule; same result, served by the 3-heads-per-CTA launch."""
+    G = qt.shape[1] // kt.shape[1]
+    return _tree_attn(qt, kt, vt, gate, vbits, None, scale, 3 if G % 3 == 0 else 1)
+
+
+def fattn_tree_ranges(qt, kt, vt, gate, krange, scale, gq):
+    """Same attention with the mask given as three key ranges per row (lay.krange): no N x N structure anywhere."""
+    return _tree_attn(qt, kt, vt, gate, None, krange, scale, gq)
+
+
+def fattn_tree2(proj, qw1, kw1, cosb, sinb, sig, vbits, HQ, HKV, scale, eps):
+    """src/ext.py:38 — q/k preparation + attention + gate from the in-projection output (two launches here)."""
+    N = proj.shape[0]
+    D = qw1.shape[0]
+    qt, kt, vt, gate = fullattn_prep2(proj, qw1, kw1, cosb, sinb, 1, N, HQ, HKV, D, eps)
+    G = HQ // HKV
+    return _tree_attn(qt, kt, vt, gate, vbits, None, scale, 3 if G % 3 == 0 else 1)
+
+
+# ------------------------------------------------------------------------------------------------ scoring head
+def score_head(hn, rows, W, bias):
+    """hn bf16 [N, H], rows int64 [S], W f32 [A, H], bias f32 [A] or None -> f32 [S, A] (gather + fp32 linear in one
+    launch; the reference does `head(hn[lastidx].float())` with torch, src/server.py:37)."""
+    _chk(hn, rows, W, bias)
+    S, (A, H) = rows.numel(), W.shape
+    out = torch.empty(S, A, dtype=torch.float32, device=hn.device)
+    call("ojb_score_head", ptr(hn), ptr(rows), ptr(W), ptr(bias), ptr(out), i64(S), i64(A), i64(H), stream_ptr())
+    return out

@@ -89,6 +89,45 @@ def gtree_build(seqs, groups, pad_id, NB=32, PB=16, dev="cuda", dense=True):
     ids = f.pop("ids")
     for k, v in f.items():
         setattr(lay, k, v)
+    lay.walk_ptr, lay.n_walks = lay.meta[6:8], 1
     if dense:
         lay.amask, lay.amask_add = dense_masks(lay.vbits)
     return ids, lay
+
+
+def batch_layout(attention_mask, dev):
+    """Layout of a right-padded batch [B, T] of independent sequences (the non-tree forward of src/fastmodel.py:205-241)
+    in the vocabulary of the tree kernels: every sequence is its own path, rows are b*T + t, padded up to a multiple of 32
+    rows. Returns a namespace with pos, rowmask, hist, krange, chunks, steps, walk_ptr, n_walks, lastidx, N."""
+    m = attention_mask.detach().cpu().numpy().astype(bool)
+    B, T = m.shape
+    N = -(-(B * T) // 32) * 32
+    lens = m.sum(1)
+    pos = np.zeros(N, np.int64)
+    rowmask = np.zeros(N, np.int32)
+    hist = np.full((N + 1, 4), -1, np.int32)
+    krange = np.zeros((N, 8), np.int32)
+    chunks, steps, walks = [], [], [0]
+    for b in range(B):
+        L = int(lens[b])
+        for t in range(T):
+            n = b * T + t
+            krange[n, 3], krange[n, 4] = (b * T, n + 1) if t < L else (n, n + 1)
+            if t < L:
+                pos[n], rowmask[n] = t, 1
+                for i in range(4):
+                    if t - 3 + i >= 0:
+                        hist[n, i] = n - 3 + i
+        for j in range(0, L, 64):
+            steps.append([len(chunks), 1 if j == 0 else 0, 0, 0])
+            chunks.append([b * T + j, min(64, L - j), 0, 0])
+        walks.append(len(steps))
+    for n in range(B * T, N):
+        krange[n, 3], krange[n, 4] = n, n + 1
+    if not chunks:
+        chunks, steps = [[0, 0, 0, 0]], [[0, 1, 0, 0]]
+    t32 = lambda a: torch.as_tensor(np.asarray(a, np.int32)).to(dev)
+    last = np.array([b * T + max(int(lens[b]) - 1, 0) for b in range(B)], np.int64)
+    return SimpleNamespace(N=N, S=B, L2=T, pos=torch.as_tensor(pos).to(dev), rowmask=t32(rowmask), hist=t32(hist),
+                           krange=t32(krange), chunks=t32(chunks), steps=t32(steps), walk_ptr=t32(walks), n_walks=B,
+                           lastidx=torch.as_tensor(last).to(dev))

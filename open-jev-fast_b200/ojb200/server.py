@@ -1,0 +1,145 @@
+"""Serving shim of the scoring forward: per-shape CUDA graphs, request -> scores, data-parallel sharding of requests.
+
+Follows open-jev-fast's src/server.py: `Entry` (src/server.py:32-49) owns static input buffers and one CUDA graph per
+key (N, S, L2); `Scorer.forward(records)` keeps the contract of `_forward(records)` (src/server.py:86-142): one score per
+candidate, `noul` questions answered as [0, score], an LRU of at most MAX_GRAPHS graphs, one access-log record per request.
+What is outside this repository's scope (HTTP, tokenizer, chat template: the un-vendored `jev` package) is replaced by
+token-id lists: a record is {"kind": "noul" | "choice" | "score", "candidates": [[token ids], ...]}.
+"""
+import collections
+import json
+import os
+import threading
+import time
+
+import torch
+
+from . import _lib
+from . import layout as _layout
+
+NB, PB = int(os.environ.get("ROW_BUCKET", "32")), int(os.environ.get("PATH_BUCKET", "16"))
+MAX_GRAPHS = int(os.environ.get("MAX_GRAPHS", "512"))
+USE_GRAPH = os.environ.get("USE_GRAPH", "1") == "1"
+
+
+class Entry:
+    """Static buffers + CUDA graph of `score_gtree` for one key (N, S, L2). The tree structure lives in the index tables,
+    so every request with the same key replays the same graph after three host-to-device copies."""
+
+    def __init__(self, scorer, dims, host_bufs):
+        fast = scorer.fast
+        dev = scorer.device
+        self.dims = dict(dims)
+        self.g64, self.g32, self.ge = (b.to(dev) for b in host_bufs)
+        f = _layout.field_views(dims, self.g64, self.g32, self.ge)
+        self.ids = f.pop("ids")
+        self.lay = _layout.SimpleNamespace(N=dims["N"], S=dims["S"], L2=dims["L2"], key=(dims["N"], dims["S"], dims["L2"]), **f)
+        self.lay.walk_ptr, self.lay.n_walks = self.lay.meta[6:8], 1
+        body = lambda: fast.score_gtree(self.ids, self.lay, scorer.head_w, scorer.head_b)
+        st = torch.cuda.Stream(device=dev)
+        st.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(st):
+            for _ in range(2):          # warm-up: also lets the GEMM dispatcher time its candidates for these shapes
+                body()
+        torch.cuda.current_stream(dev).wait_stream(st)
+        torch.cuda.synchronize(dev)
+        self.g = None
+        if scorer.use_graph:
+            self.g = torch.cuda.CUDAGraph()
+            n0 = _lib.launch_count()
+            with torch.cuda.graph(self.g, pool=scorer.pool):
+                self.out = body()
+            self.launches = _lib.launch_count() - n0
+            torch.cuda.synchronize(dev)
+        else:
+            n0 = _lib.launch_count()
+            self.out = body()
+            self.launches = _lib.launch_count() - n0
+        self._body = body
+
+    def run(self, host_bufs):
+        """Upload one request's tables (pinned host buffers) and replay. Returns the static fp32 [S, A] output."""
+        self.g64.copy_(host_bufs[0], non_blocking=True)
+        self.g32.copy_(host_bufs[1], non_blocking=True)
+        self.ge.copy_(host_bufs[2], non_blocking=True)
+        return self.replay()
+
+    def replay(self):
+        if self.g is not None:
+            self.g.replay()
+        else:
+            self.out = self._body()
+        return self.out
+
+
+class Scorer:
+    """One GPU's worth of the service: model + head + graph cache + lock (one request at a time per GPU, src/server.py:97)."""
+
+    def __init__(self, fast, head_w, head_b=None, pad_id=0, device=None, use_graph=USE_GRAPH, max_graphs=MAX_GRAPHS,
+                 access_log=None):
+        self.fast, self.head_w, self.head_b, self.pad_id = fast, head_w, head_b, pad_id
+        self.device = torch.device(device if device is not None else head_w.device)
+        self.use_graph, self.max_graphs = use_graph, max_graphs
+        self.graphs = collections.OrderedDict()
+        self.pool = torch.cuda.graph_pool_handle() if use_graph else None
+        self.lock = threading.Lock()
+        self.nreq = 0
+        self.log = open(access_log, "a", buffering=1 << 16) if access_log else None
+        self.last = {}
+
+    def entry_for(self, dims, host_bufs):
+        key = (dims["N"], dims["S"], dims["L2"])
+        ent = self.graphs.get(key)
+        captured = ent is None
+        if captured:
+            ent = self.graphs[key] = Entry(self, dims, host_bufs)
+            while len(self.graphs) > self.max_graphs:
+                self.graphs.popitem(last=False)
+        else:
+            self.graphs.move_to_end(key)
+        return ent, captured
+
+    def score_tokens(self, seqs, groups):
+        """Candidate token lists + question index per candidate -> fp32 [S, A] scores on the GPU (not synchronised)."""
+        t0 = time.perf_counter()
+        dims, b64, b32, e32 = _layout.gtree_host(seqs, groups, self.pad_id, NB, PB, pin=True)
+        t1 = time.perf_counter()
+        with self.lock, torch.cuda.device(self.device):
+            ent, captured = self.entry_for(dims, (b64, b32, e32))
+            out = ent.run((b64, b32, e32))
+        self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=ent.lay.key, rows=dims["Nreal"],
+                         h2d_bytes=b64.numel() * 8 + b32.numel() * 4 + e32.numel() * 4, launches=ent.launches)
+        return out
+
+    def forward(self, records):
+        """src/server.py:86-142 on token ids: list of per-record score tensors (CPU, fp32)."""
+        t0 = time.perf_counter()
+        seqs, groups, counts = [], [], []
+        for ri, r in enumerate(records):
+            c = r["candidates"]
+            counts.append(len(c))
+            seqs += c
+            groups += [ri] * len(c)
+        scores = self.score_tokens(seqs, groups).cpu()      # device-to-host read = the synchronisation point
+        _lib.check_status(self.device)
+        t1 = time.perf_counter()
+        self.nreq += 1
+        if self.log:
+            rec = dict(ts=time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), req=self.nreq, path="tree2", gpu=self.device.index,
+                       questions=len(records), candidates=len(seqs), tokens=sum(map(len, seqs)), rows=self.last["rows"],
+                       key=self.last["key"], captured=int(self.last["captured"]), build_ms=round(self.last["build_ms"], 3),
+                       ms=round((t1 - t0) * 1e3, 3))
+            self.log.write(json.dumps(rec) + "\n")
+        out, off = [], 0
+        for r, c in zip(records, counts):
+            v = scores[off:off + c]
+            if r.get("kind") == "noul":
+                v = torch.stack([torch.zeros_like(v[0]), v[0]])
+            out.append(v)
+            off += c
+        return out
+
+
+def shard_requests(n_requests, rank, world):
+    """Data-parallel split: request i goes to rank i % world (requests are independent; no collective on this path)."""
+    return list(range(rank, n_requests, world))

@@ -1,0 +1,104 @@
+"""Whole forward + scoring head on a small hybrid model against the reference's PyTorch path (Hugging Face modules, fp32
+on CPU, one full sequence per candidate), and tree attention (BASELINE config 3 shape) against the masked-softmax oracle."""
+import pytest
+import torch
+
+import trees
+from oracle import hf_path as OH
+from oracle import layout as OL
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+bf16 = torch.bfloat16
+
+
+@pytest.mark.parametrize("N_case,HQ,HKV,D,gq", [("baseline", 24, 4, 256, 3), ("baseline", 24, 4, 256, 6), ("example", 6, 2, 128, 3),
+                                                ("doc", 2, 1, 64, 1), ("ragged", 4, 2, 256, 2)])
+@pytest.mark.parametrize("mask_form", ["bits", "ranges"])
+def test_tree_attention(N_case, HQ, HKV, D, gq, mask_form):
+    from ojb200 import ext as K
+    from ojb200 import layout as PL
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()[N_case]
+    ids, lay = PL.gtree_build(seqs, groups, pad_id, NB, PB, dev="cuda", dense=False)
+    N, RD = lay.N, D // 4
+    g = torch.Generator().manual_seed(21)
+    proj = torch.randn(N, 2 * HQ * D + 2 * HKV * D, generator=g).to(bf16)          # BASELINE config 3: N(0, 1)
+    qw1 = 1.0 + torch.randn(D, generator=g) * 0.02
+    kw1 = 1.0 + torch.randn(D, generator=g) * 0.02
+    inv_freq = 1.0 / (10000 ** (torch.arange(0, RD, 2).float() / RD))
+    ang = lay.pos.cpu().float()[:, None] * inv_freq[None]
+    cosb, sinb = torch.cat([ang.cos()] * 2, -1).to(bf16), torch.cat([ang.sin()] * 2, -1).to(bf16)
+    scale = D ** -0.5
+    qt, kt, vt, gate = K.fullattn_prep2(proj.cuda(), qw1.cuda(), kw1.cuda(), cosb.cuda(), sinb.cuda(), 1, N, HQ, HKV, D, 1e-6)
+    if mask_form == "bits":
+        y = K.fattn_tree(qt, kt, vt, gate, None, lay.vbits, scale, gq)
+    else:
+        y = K.fattn_tree_ranges(qt, kt, vt, gate, lay.krange, scale, gq)
+    torch.cuda.synchronize()
+    vis = torch.as_tensor(OL.gtree_layout(seqs, groups, pad_id, NB, PB)["vis"])
+    ref = O.tree_attention(qt[0].cpu(), kt[0].cpu(), vt[0].cpu(), gate.cpu(), vis, scale).float()
+    got = y.float().cpu()
+    rel = ((got - ref).norm() / ref.norm()).item()
+    # bf16 P and exp2 in the kernel: the reference reports rel-L2 1.2e-3 for its own kernel against cuDNN
+    assert rel < 4e-3, rel
+    assert (got - ref).abs().max().item() < 3e-2
+
+
+def _small_model(seed=0):
+    from ojb200 import modelgen as MG
+    cfg = MG.make_config(**MG.SMALL)
+    core = MG.build_core(cfg, device="cpu", seed=seed, std=0.05, draw_on="cpu")
+    return cfg, core
+
+
+@pytest.mark.parametrize("case", ["doc", "example", "nostem", "ragged"])
+@pytest.mark.parametrize("tree_native", [True, False])
+def test_forward_gtree_matches_reference_path(case, tree_native):
+    from ojb200 import fastmodel as FM
+    from ojb200 import modelgen as MG
+    cfg, core = _small_model()
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()[case]
+    seqs = [[t % cfg.vocab_size for t in s] for s in seqs]
+    oracle = OH.prepare(core, upcast=True)
+    ref_h = OH.candidate_hidden(oracle, seqs)
+    # yardstick: what the reference's PyTorch path itself loses when it runs in bf16 (the way the reference runs it)
+    ref16 = OH.candidate_hidden(OH.prepare(core, upcast=False), seqs)
+    noise = ((ref16 - ref_h).norm() / ref_h.norm()).item()
+    W, b = MG.make_head(cfg.hidden_size, A=3, seed=1, device="cuda")
+    ref_s = OH.scores(ref_h, W, b)
+    fast = FM.FastQwen35(core.to("cuda"))
+    FM.TREE_NATIVE = tree_native
+    try:
+        ids, lay = fast.gtree_build(seqs, groups, pad_id % cfg.vocab_size, NB, PB)
+        hid = fast.forward_gtree(ids, lay).float().cpu()
+        sc = fast.score_gtree(ids, lay, W, b).cpu()
+    finally:
+        FM.TREE_NATIVE = True
+    from ojb200 import _lib
+    _lib.check_status()
+    rel = ((hid - ref_h).norm() / ref_h.norm()).item()
+    assert rel < max(1e-2, 1.25 * noise), (rel, noise)
+    err = (sc - ref_s).abs().max().item()
+    assert err <= 3e-2, err                                 # BASELINE: max abs logit error 3e-2 ...
+    top2 = ref_s.topk(min(2, ref_s.shape[0]), 0).values
+    clear = (top2[0] - top2[-1]) > 2 * err if ref_s.shape[0] > 1 else torch.ones(ref_s.shape[1], dtype=torch.bool)
+    assert torch.equal(sc.argmax(0)[clear], ref_s.argmax(0)[clear])   # ... with identical argmax over the candidates
+
+
+def test_batch_forward_matches_reference_path():
+    from ojb200 import fastmodel as FM
+    cfg, core = _small_model(seed=2)
+    g = torch.Generator().manual_seed(5)
+    B, T = 3, 50
+    ids = torch.randint(0, cfg.vocab_size, (B, T), generator=g)
+    lens = [50, 17, 33]
+    mask = torch.zeros(B, T, dtype=torch.long)
+    for i, l in enumerate(lens):
+        mask[i, :l] = 1
+    oracle = OH.prepare(core, upcast=True)
+    fast = FM.FastQwen35(core.to("cuda"))
+    out = fast.forward(ids.cuda(), mask.cuda()).last_hidden_state.float().cpu()
+    for i, l in enumerate(lens):
+        ref = OH.all_hidden(oracle, ids[i, :l].tolist())
+        rel = ((out[i, :l] - ref).norm() / ref.norm()).item()
+        assert rel < 4e-2, (i, rel)      # bf16 run of a narrow 8-layer model against fp32 (its own bf16 run loses ~3e-2)
