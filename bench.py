@@ -88,40 +88,43 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
 
 
-def cpu_reference_sample(cfg_kwargs, seqs, threads):
+_CPU_CORE = {}
+
+
+def cpu_reference_sample(cfg_kwargs, seqs, threads, reps=0):
     """The reference's PyTorch path on the host: one linear-attention decoder layer and one full-attention decoder layer
     (each with its MLP) at full width, bf16 weights, over every candidate path; a forward costs n_lin * t_lin + n_full *
-    t_full (the 64 layers of one type do identical work). Returns (seconds per request, description)."""
+    t_full (the layers of one type do identical work). Returns (t_lin, t_full) in seconds."""
     from ojb200 import modelgen as MG
     from oracle import hf_path as OH
     torch.set_num_threads(threads)
-    types = ["linear_attention", "full_attention"]
-    kw = dict(cfg_kwargs)
-    kw.update(num_hidden_layers=2, layer_types=types)
-    cfg = MG.make_config(**kw)
-    core = MG.build_core(cfg, device="cpu", seed=0, draw_on="cpu")
-    t_lin, t_full = OH.time_layers(core, seqs, reps=1)
-    return t_lin, t_full
+    if "core" not in _CPU_CORE:
+        kw = dict(cfg_kwargs)
+        kw.update(num_hidden_layers=2, layer_types=["linear_attention", "full_attention"])
+        _CPU_CORE["core"] = MG.build_core(MG.make_config(**kw), device="cpu", seed=0, draw_on="cpu")
+    return OH.time_layers(_CPU_CORE["core"], seqs, reps=reps)
 
 
 def run_reference(args, cfg_kwargs, seqs, n_lin, n_full):
+    """`--impl reference`: K timed samples (after W untimed ones) of the reference's PyTorch path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     times = []
-    for _ in range(max(1, args.warmup > 0) + args.steps):
+    for i in range(args.warmup + args.steps):
         t_lin, t_full = cpu_reference_sample(cfg_kwargs, seqs, threads)
-        times.append(n_lin * t_lin + n_full * t_full)
-    times = sorted(times[1:] if len(times) > 1 else times)
-    sec = times[len(times) // 2]
+        if i >= args.warmup:
+            times.append(n_lin * t_lin + n_full * t_full)
+    sec = sum(times) / len(times)
     v = 1.0 / sec
-    sample = (f"Hugging Face qwen3_5 torch path, bf16 weights, {threads} threads: 1 linear-attention + 1 full-attention decoder "
-              f"layer (with MLP) at full width over the {len(seqs)} candidate paths ({sum(map(len, seqs))} tokens), "
-              f"x({n_lin},{n_full}) layers")
+    sample = (f"Hugging Face qwen3_5 torch path, bf16 weights, {threads} threads: per step 1 linear-attention + 1 full-attention "
+              f"decoder layer (with MLP) at full width over the {len(seqs)} candidate paths ({sum(map(len, seqs))} tokens), "
+              f"scaled by ({n_lin},{n_full}) layers")
     line = {"metric": METRIC, "value": v, "unit": "requests/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "impl": "reference", "config": {"workload": args.workload, "timed": "host cores, extrapolated from 2 layers"},
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": args.workload, "timed": "host cores; one layer of each type timed, scaled to 64 layers"},
             "cpu_baseline": {"value": v, "unit": "requests/s", "cores": threads, "kind": "reference", "sample": sample},
             "e2e": {"value": v, "unit": "requests/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -163,6 +166,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="baseline", choices=["baseline", "example"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", type=int, default=0, help="run this many eager (graph-free) forwards between "
+                    "cudaProfilerStart/Stop and exit: for `ncu --profile-from-start off`")
     ap.add_argument("--layers", type=int, default=64, help="debugging only: a run with fewer than 64 layers is not a result")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -201,6 +206,16 @@ def main():
     assert bool(torch.isfinite(out).all()), "non-finite scores"
     key = scorer.last["key"]
     ent = scorer.graphs[key]
+
+    if args.profile > 0:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for _ in range(args.profile):
+            fast.score_gtree(ent.ids, ent.lay, W, b)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled_forwards": args.profile, "key": key}), flush=True)
+        return
 
     def barrier():
         torch.cuda.synchronize()
@@ -261,7 +276,7 @@ def main():
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            t_lin, t_full = cpu_reference_sample(cfg_kwargs, reqs[0][0], threads)
+            t_lin, t_full = cpu_reference_sample(cfg_kwargs, reqs[0][0], threads, reps=1)
             sec = n_lin * t_lin + n_full * t_full
             line["cpu_baseline"] = {"value": 1.0 / sec, "unit": "requests/s", "cores": threads, "kind": "reference",
                                     "sample": f"Hugging Face qwen3_5 torch path (bf16, {threads} threads): 1 linear-attention + 1 "

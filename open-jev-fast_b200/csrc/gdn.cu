@@ -59,15 +59,17 @@ gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, 
                 float* __restrict__ g, bf16_t* __restrict__ beta, int N, int KD, int VD, int HV) {
   const int C = 2 * KD + VD, P = C + VD + 2 * HV;
   const int n = blockIdx.y;
-  const bool pad = n >= N;  // only when scattering: groups of 16 pad slots
+  int4 hr = make_int4(-1, -1, -1, -1);
+  if (n < N) hr = hist[n];
+  // padding: blocks past N stand for groups of 16 pad slots (scatter form); packed rows that lie on no path (end padding
+  // of the row bucket) have no history entry, not even themselves, and produce zeros
+  const bool pad = n >= N || hr.w < 0;
   int p0 = 0, p1 = 1;
   if constexpr (SCATTER) {
-    if (!pad) { p0 = rep_ptr[n]; p1 = rep_ptr[n + 1]; }
+    if (n < N) { p0 = rep_ptr[n]; p1 = rep_ptr[n + 1]; }
     else { p0 = rep_ptr[N] + (n - N) * 16; p1 = min(rep_ptr[N + 1], p0 + 16); }
     if (p0 >= p1) return;
   }
-  int4 hr = make_int4(-1, -1, -1, -1);
-  if (!pad) hr = hist[n];
   if (blockIdx.x == 0 && threadIdx.x < HV) {
     const int h = threadIdx.x;
     float bv = 0.f, gv = 0.f;
