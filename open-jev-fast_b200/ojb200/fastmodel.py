@@ -32,7 +32,7 @@ LT = _lt.load()
 SK_LIN_OUT = int(os.environ.get("OJ_SK_LIN_OUT", "0"))     # split-K of the GDN out-projection; 0 = choose by timing
 SK_FULL_OUT = int(os.environ.get("OJ_SK_FULL_OUT", "0"))   # split-K of the attention o-projection
 SK_DOWN = int(os.environ.get("OJ_SK_DOWN", "0"))           # split-K of the MLP down-projection
-FATTN = int(os.environ.get("OJ_FATTN", "3"))               # query heads per CTA of the tree attention (3 or 6)
+FATTN = int(os.environ.get("OJ_FATTN", "6"))               # query heads per CTA of the tree attention (3 or 6)
 FATTN_MAX = int(os.environ.get("OJ_FATTN_MAX", "1000000000"))   # kept for compatibility: the kernel serves every N
 GDN_FUSED, GDN_VER, PREP, GVA, LUT, SK2 = True, 6, "dedup", True, True, True
 TREE_NATIVE = os.environ.get("OJ_TREE_NATIVE", "1") == "1"      # 0: replicated per-candidate GDN layout of the reference
@@ -58,7 +58,7 @@ class FastQwen35(torch.nn.Module):
         self.layer_types = list(cfg.layer_types)
         self.embed, self.rotary = core.embed_tokens, core.rotary_emb
         self.v2, self.fuse_l2 = v2, fuse_l2
-        self._best, self._bufs = {}, {}
+        self._bufs = {}
         w1 = lambda norm: (1.0 + norm.weight.float()).contiguous()
         self.in_w1 = [w1(L.input_layernorm) for L in core.layers]
         self.post_w1 = [w1(L.post_attention_layernorm) for L in core.layers]
@@ -100,45 +100,17 @@ class FastQwen35(torch.nn.Module):
                 self.L.append(d)
 
     # ------------------------------------------------------------------------------------------------ GEMM dispatch
+    # The reference times every cuBLASLt candidate per shape (src/fastmodel.py:114-156). Here the candidates are two tile
+    # shapes and the split-K factor of one kernel, and the choice follows from counting work units against the 148 SMs
+    # (measured with `python -m ojb200.gemm_sweep`): the 128x256 tile wins whenever it yields at least ~100 units, the
+    # 128x128 tile otherwise; fp32 split-K partials only pay off for the long-K down-projection at small M.
     @staticmethod
-    def _time(fn, reps=8):
-        """Median-free quick timing with the L2 flushed before each call (weights of one projection fit in L2 and would
-        bias the choice otherwise, as src/fastmodel.py:135-143 notes)."""
-        flush = FastQwen35._flush_buf()
-        for _ in range(2):
-            fn()
-        ev = [(torch.cuda.Event(True), torch.cuda.Event(True)) for _ in range(reps)]
-        for a, b in ev:
-            flush.zero_()
-            a.record(); fn(); b.record()
-        torch.cuda.synchronize()
-        ts = sorted(a.elapsed_time(b) for a, b in ev)
-        return ts[len(ts) // 2]
-
-    _flush = None
-
-    @staticmethod
-    def _flush_buf():
-        if FastQwen35._flush is None:
-            FastQwen35._flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-        return FastQwen35._flush
-
-    def _choose(self, key, cands, run):
-        """Pick the fastest candidate for `key` by timing (the role of src/fastmodel.py:114-156 _tune / _tune_sk). While a
-        CUDA graph is being captured nothing can be timed: the first candidate is used."""
-        best = self._best.get(key)
-        if best is None:
-            if torch.cuda.is_current_stream_capturing() or len(cands) == 1:
-                return cands[0]
-            ts = [self._time(lambda c=c: run(c)) for c in cands]
-            best = self._best[key] = cands[ts.index(min(ts))]
-        return best
+    def _variant(M, N):
+        return 0 if -(-M // 128) * -(-N // 256) >= 100 else 1
 
     def _mm(self, x, w):
         """out = x @ w^T, bf16 (src/fastmodel.py:168 _mm)."""
-        key = ("mm", x.shape[0], w.shape[0], x.shape[1])
-        v = self._choose(key, [0, 1], lambda c: LT.lt_matmul(x, w, c))
-        return LT.lt_matmul(x, w, v)
+        return LT.lt_matmul(x, w, self._variant(x.shape[0], w.shape[0]))
 
     @staticmethod
     def _split(W, S):
@@ -146,18 +118,17 @@ class FastQwen35(torch.nn.Module):
         N, Kd = W.shape
         return W.view(N, S, Kd // S).permute(1, 2, 0).contiguous()
 
-    def _sk_candidates(self, Kd, forced):
-        if forced > 0:
-            return [(forced, 1)]
-        return [(s, v) for s in (1, 2, 3, 4, 6, 8) if Kd % (64 * s) == 0 for v in (1, 0)]
-
     def _res(self, h, y, w, S, w1, mask):
-        """Split-K projection with fp32 partials, then partial sum + residual + RMSNorm in one kernel
-        (src/fastmodel.py:196 _res)."""
+        """Output projection + residual + RMSNorm (src/fastmodel.py:196 _res). S = 0 picks the split: a plain bf16 GEMM
+        followed by the fused add + norm (delta = bf16 of the fp32 accumulator, the same rounding point as the reference's
+        bf16(sum of fp32 partials)), or, when the tile count is far below the SM count and K is long, S = 2 fp32 partials."""
         M, Kd = y.shape
-        key = ("sk", M, w.shape[0], Kd, S)
-        s, v = self._choose(key, self._sk_candidates(Kd, S), lambda c: LT.gemm_splitk(y, w, c[0], c[1]))
-        parts = LT.gemm_splitk(y, w, s, v)
+        N = w.shape[0]
+        if S == 0:
+            S = 2 if (-(-M // 128) * -(-N // 256) <= 74 and Kd >= 8192 and Kd % 128 == 0) else 1
+        if S == 1:
+            return K.add_rmsnorm(h, self._mm(y, w), w1, mask, self.eps)
+        parts = LT.gemm_splitk(y, w, S, 0)
         return K.add_rmsnorm_sk2(h, parts, w1, mask, self.eps)
 
     def _mlp_in(self, hn, d):

@@ -1,0 +1,95 @@
+"""GEMM sweep over the projection shapes of the model (BASELINE.json config 2) for every kernel variant.
+
+    python -m ojb200.gemm_sweep [--m 64 288 544 1024 4096] [--quick]
+
+For each (M, K, N): plain bf16 GEMM per tile variant, the SwiGLU-fused GEMM where N is a gate/up width, and split-K partial
+GEMMs (with their reduce + residual + RMSNorm kernel) where N is the hidden size. Each case is timed with CUDA events over
+launches that cycle through enough distinct weight copies to exceed the L2, checked against torch.matmul on fp32-upcast
+operands, and printed as one JSON line: microseconds, TFLOP/s, fraction of the measured bf16 peak, weight-stream GB/s.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+from . import ext as K
+from . import lt_ext as LT
+
+bf16 = torch.bfloat16
+SHAPES = [(5120, 12288), (5120, 12352), (5120, 14336), (5120, 34816), (17408, 5120), (6144, 5120), (4096, 5120)]
+
+
+def _peak():
+    p = os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")
+    try:
+        return json.load(open(p))["bf16_tflops"]
+    except Exception:
+        return 1590.0
+
+
+def _time(fns, reps=3):
+    """fns: list of closures over distinct weight copies; returns microseconds per call (best of reps passes)."""
+    for f in fns[:2]:
+        f()
+    best = float("inf")
+    for _ in range(reps):
+        a, b = torch.cuda.Event(True), torch.cuda.Event(True)
+        a.record()
+        for f in fns:
+            f()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b) * 1e3 / len(fns))
+    return best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, nargs="+", default=[64, 288, 539, 544, 1024, 4096])
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    peak = _peak()
+    g = torch.Generator(device=dev).manual_seed(0)
+    for Kd, N in SHAPES:
+        copies = max(2, min(8, int(300e6 // (N * Kd * 2)) + 1))      # > 126 MB of distinct weights in flight
+        ws = [(torch.randn(N, Kd, generator=g, device=dev) * 0.02).to(bf16) for _ in range(copies)]
+        for M in args.m:
+            x = torch.randn(M, Kd, generator=g, device=dev).to(bf16)
+            ref = x.float() @ ws[0].float().t()
+            flops = 2.0 * M * N * Kd
+
+            def report(name, us, err):
+                print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                                  "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
+                                  "max_err": err}), flush=True)
+            for v in (0, 1):
+                out = LT.lt_matmul(x, ws[0], v)
+                err = (out.float() - ref).abs().max().item()
+                report(f"plain v{v}", _time([lambda w=w, v=v: LT.lt_matmul(x, w, v) for w in ws]), err)
+            if N % 256 == 0 and Kd == 5120 and N > 20000:
+                I = N // 2
+                wb = [LT.interleave_gate_up(w[:I], w[I:]) for w in ws]
+                out = LT.gemm_swiglu(x, wb[0])
+                gg, uu = ref[:, :I].to(bf16).float(), ref[:, I:].to(bf16).float()
+                err = (out.float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
+                report("swiglu", _time([lambda w=w: LT.gemm_swiglu(x, w) for w in wb]), err)
+            if N == 5120 and not args.quick:
+                h = torch.randn(M, N, generator=g, device=dev).to(bf16)
+                w1 = torch.ones(N, device=dev)
+                for S in (1, 2, 3, 4, 6, 8):
+                    if Kd % (64 * S):
+                        continue
+                    for v in (0, 1):
+                        parts = LT.gemm_splitk(x, ws[0], S, v)
+                        err = (parts.sum(0) - ref).abs().max().item()
+                        report(f"splitk S{S} v{v}", _time([lambda w=w, S=S, v=v: LT.gemm_splitk(x, w, S, v) for w in ws]), err)
+                        report(f"splitk S{S} v{v} + reduce/norm",
+                               _time([lambda w=w, S=S, v=v: K.add_rmsnorm_sk2(h, LT.gemm_splitk(x, w, S, v), w1, None, 1e-6) for w in ws]), err)
+        del ws
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
