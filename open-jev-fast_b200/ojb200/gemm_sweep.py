@@ -48,12 +48,16 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, nargs="+", default=[64, 288, 539, 544, 1024, 4096])
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--shape", type=int, nargs=2, default=None, metavar=("K", "N"), help="only this weight shape")
+    ap.add_argument("--only", default=None, help="only kernels whose name starts with this (plain, swiglu, splitk)")
+    ap.add_argument("--copies", type=int, default=0, help="distinct weight copies to cycle through (default: enough to exceed L2)")
     args = ap.parse_args()
     dev = torch.device("cuda")
     peak = _peak()
     g = torch.Generator(device=dev).manual_seed(0)
-    for Kd, N in SHAPES:
-        copies = max(2, min(8, int(300e6 // (N * Kd * 2)) + 1))      # > 126 MB of distinct weights in flight
+    want = lambda name: args.only is None or name.startswith(args.only)
+    for Kd, N in ([tuple(args.shape)] if args.shape else SHAPES):
+        copies = args.copies or max(2, min(8, int(300e6 // (N * Kd * 2)) + 1))      # > 126 MB of distinct weights in flight
         ws = [(torch.randn(N, Kd, generator=g, device=dev) * 0.02).to(bf16) for _ in range(copies)]
         for M in args.m:
             x = torch.randn(M, Kd, generator=g, device=dev).to(bf16)
@@ -64,18 +68,18 @@ def main():
                 print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
                                   "max_err": err}), flush=True)
-            for v in (0, 1):
+            for v in ((0, 1) if want("plain") else ()):
                 out = LT.lt_matmul(x, ws[0], v)
                 err = (out.float() - ref).abs().max().item()
                 report(f"plain v{v}", _time([lambda w=w, v=v: LT.lt_matmul(x, w, v) for w in ws]), err)
-            if N % 256 == 0 and Kd == 5120 and N > 20000:
+            if N % 256 == 0 and Kd == 5120 and N > 20000 and want("swiglu"):
                 I = N // 2
                 wb = [LT.interleave_gate_up(w[:I], w[I:]) for w in ws]
                 out = LT.gemm_swiglu(x, wb[0])
                 gg, uu = ref[:, :I].to(bf16).float(), ref[:, I:].to(bf16).float()
                 err = (out.float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
                 report("swiglu", _time([lambda w=w: LT.gemm_swiglu(x, w) for w in wb]), err)
-            if N == 5120 and not args.quick:
+            if N == 5120 and not args.quick and want("splitk"):
                 h = torch.randn(M, N, generator=g, device=dev).to(bf16)
                 w1 = torch.ones(N, device=dev)
                 for S in (1, 2, 3, 4, 6, 8):

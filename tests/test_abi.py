@@ -1,0 +1,44 @@
+"""The C-ABI library loads without a GPU and exports every entry point that include/ojb200.h declares; host-only entry
+points (layout builder) are exercised in test_layout.py. No compute call is made here."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    src = open(os.path.join(ROOT, "include", "ojb200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(ojb_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_declares_the_hot_path():
+    names = _declared()
+    for must in ("ojb_gemm_bf16", "ojb_gemm_bf16_swiglu", "ojb_gemm_bf16_splitk", "ojb_add_rmsnorm", "ojb_add_rmsnorm_sk",
+                 "ojb_gdn_prep", "ojb_gdn_chunked", "ojb_gated_rmsnorm", "ojb_fullattn_prep", "ojb_tree_attn", "ojb_score_head",
+                 "ojb_gtree_dims", "ojb_gtree_fill"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from ojb200 import _lib
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    missing = [n for n in _declared() if not hasattr(lib, n)]
+    assert not missing, missing
+    lib.ojb_abi_version.restype = ctypes.c_int
+    assert lib.ojb_abi_version() == _lib.ABI_VERSION
+
+
+def test_argument_checks_need_no_gpu():
+    """Precondition failures are reported before anything touches CUDA."""
+    from ojb200 import _lib
+    lib = _lib.lib()
+    lib.ojb_gemm_bf16.restype = ctypes.c_int
+    rc = lib.ojb_gemm_bf16(None, None, None, ctypes.c_int64(1), ctypes.c_int64(1), ctypes.c_int64(8), 0, None, None)
+    assert rc == -1
+    lib.ojb_tree_attn.restype = ctypes.c_int
+    one = ctypes.c_void_p(16)
+    rc = lib.ojb_tree_attn(one, one, one, one, one, None, one, ctypes.c_int64(33), ctypes.c_int64(4), ctypes.c_int64(2),
+                           ctypes.c_int64(256), ctypes.c_int64(2), ctypes.c_float(1.0), None)
+    assert rc == -1      # N must be a multiple of 32

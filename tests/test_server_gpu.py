@@ -1,0 +1,62 @@
+"""Graph-per-shape serving shim: replay equals the eager forward, trees of the same key share one graph, the `noul`
+convention, LRU eviction, and the scoring head against the oracle."""
+import pytest
+import torch
+
+import trees
+from oracle import hf_path as OH
+
+pytestmark = pytest.mark.gpu
+
+
+def _scorer(use_graph=True, max_graphs=4, A=2):
+    from ojb200 import fastmodel as FM, modelgen as MG, server as SV
+    cfg = MG.make_config(**MG.SMALL)
+    core = MG.build_core(cfg, device="cpu", seed=3, std=0.05, draw_on="cpu")
+    fast = FM.FastQwen35(core.to("cuda"))
+    W, b = MG.make_head(cfg.hidden_size, A=A, seed=2, device="cuda")
+    return cfg, fast, SV.Scorer(fast, W, b, pad_id=0, use_graph=use_graph, max_graphs=max_graphs), W, b
+
+
+def _tree(seed, vocab):
+    s, g = trees.make_tree(seed, 40, [5, 9], [3, 6, 2, 8], [0, 0, 1, 1], vocab)
+    return s, g
+
+
+def test_graph_replay_equals_eager_and_is_shared_by_key():
+    cfg, fast, sc, W, b = _scorer()
+    outs = []
+    for seed in (1, 2, 3):
+        seqs, groups = _tree(seed, cfg.vocab_size)
+        got = sc.score_tokens(seqs, groups).clone()
+        ids, lay = fast.gtree_build(seqs, groups, 0)
+        want = fast.score_gtree(ids, lay, W, b)
+        assert torch.equal(got, want)                       # same kernels, same inputs: bit-identical
+        outs.append(got)
+    assert len(sc.graphs) == 1                              # three different trees, one key, one graph
+    assert not torch.equal(outs[0], outs[1])
+    assert sc.last["launches"] > 0
+
+
+def test_forward_records_noul_and_lru():
+    cfg, fast, sc, W, b = _scorer(max_graphs=2, A=1)
+    s1, g1 = _tree(5, cfg.vocab_size)
+    recs = [{"kind": "choice", "candidates": s1[:2]}, {"kind": "noul", "candidates": s1[2:3]}]
+    out = sc.forward(recs)
+    assert out[0].shape == (2, 1) and out[1].shape == (2, 1)
+    assert float(out[1][0]) == 0.0                          # noul -> [0, score]
+    for n_root in (70, 110, 150):                           # three more keys -> the oldest graphs are evicted
+        s, g = trees.make_tree(9, n_root, [4], [3, 5], [0, 0], cfg.vocab_size)
+        sc.forward([{"kind": "choice", "candidates": s}])
+    assert len(sc.graphs) == 2
+
+
+def test_score_head_matches_oracle():
+    from ojb200 import ext as K
+    g = torch.Generator().manual_seed(0)
+    hn = torch.randn(64, 256, generator=g).to(torch.bfloat16)
+    rows = torch.tensor([3, 17, 63])
+    W, b = torch.randn(5, 256, generator=g), torch.randn(5, generator=g)
+    got = K.score_head(hn.cuda(), rows.cuda(), W.cuda(), b.cuda()).cpu()
+    want = OH.scores(hn[rows].float(), W, b)
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-4)
