@@ -140,6 +140,22 @@ int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g,
                     const float* init_state, float* final_state, void* scratch, void* out, int64_t HK, int64_t HV,
                     float scale, ojb_stream_t stream);
 
+/* Scratch-free form of ojb_gdn_chunked. It has no counterpart in open-jev-fast. Same arguments without `scratch`: the
+ * per-(chunk, head) work items live in a fixed 72 MiB array inside the library's device image (every GPU that loads the
+ * library holds it until the process exits), so the call needs no device allocation at all. It is meant for callers that
+ * cannot allocate around the call — an inference process whose memory plan is frozen after start-up, or host code that has
+ * no allocator for device memory. Limits and rules:
+ *   - n_chunks * HV <= ojb_gdn_static_max_items() (1024), else OJB_ERR_LIMIT and nothing is launched;
+ *   - the first call on each device looks up the array's device address and raises two kernel attributes; make that first
+ *     call with the device current and before any stream capture starts;
+ *   - all calls on one GPU share the array: calls that may overlap on the GPU (different streams, no ordering) race;
+ *     the array keeps the previous call's contents, and nothing in it needs clearing between calls. */
+int64_t ojb_gdn_static_max_items(void);
+int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                           const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                           int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK, int64_t HV,
+                           float scale, ojb_stream_t stream);
+
 /* src/kernels.cu:1333-1374 gated_rmsnorm_inv2 (inv != null) and :143 gated_rmsnorm (inv == null).
  * out[n, h, :] = bf16(((x[r, h, :] * rstd) * w) * z * sigmoid(z)), r = inv[n] or n, z = proj[n, zoff + h*128 ...],
  * rstd = 1/sqrt(mean(x^2) + eps) over the 128 dims. x bf16 [*, HV, 128]; proj bf16 [N, P]; w bf16 [128]. */

@@ -649,3 +649,52 @@ extern "C" int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* 
       items, static_cast<int>(HV), static_cast<int>(zoff), static_cast<int>(P), eps);
   return launch_status(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------------------------- scratch-free entry point
+// Same two kernels as ojb_gdn_chunked, but the (chunk, head) scratch items live in a fixed array inside this library's
+// device image instead of a buffer the caller has to allocate. It exists for callers that must not allocate device
+// memory around the call: code running under a frozen memory plan (a CUDA-graph memory pool that is already sized, an
+// inference server whose allocator is locked after start-up) or host code without access to an allocator at all.
+namespace ojb {
+namespace {
+constexpr int64_t kStaticItems = 1024;   // (chunk-table entries) x (value heads) that fit: 1024 x 73 744 B = 72 MiB per GPU
+static __device__ __align__(256) unsigned char g_gdn_static_scratch[kStaticItems * kItemElems * 2];
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace
+}  // namespace ojb
+
+extern "C" int64_t ojb_gdn_static_max_items(void) { return ojb::kStaticItems; }
+
+extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                                      const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                                      int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK,
+                                      int64_t HV, float scale, ojb_stream_t stream) {
+  if (n_chunks == 0 || n_walks == 0) return OJB_OK;
+  OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && out);
+  OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_walks > 0 && n_walks <= 65535 && HV <= 65535);
+  if (n_chunks * HV > kStaticItems) return OJB_ERR_LIMIT;   // the fixed array holds at most kStaticItems items
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return OJB_ERR_LAUNCH;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // Once per device, with that device current: the array's name is only a host-side handle, the kernels need the
+    // device address. Also raises the shared-memory limits of the two kernels for this device.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_gdn_static_scratch) != cudaSuccess || p == nullptr) return OJB_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
+      return OJB_ERR_LAUNCH;
+    g_static_scratch_addr[dev] = p;
+  }
+  bf16_t* scratch = static_cast<bf16_t*>(g_static_scratch_addr[dev]);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Nothing in the array has to start at zero: the first kernel overwrites every byte of every item that the second one
+  // reads (items of unused chunk-table entries are neither written nor read).
+  gdn_intra_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), kIntraThreads, kIntraSmem, st>>>(
+      static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
+      static_cast<const bf16_t*>(beta), chunks, scratch, static_cast<int>(HK), static_cast<int>(HV), scale);
+  if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
+  gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
+      scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
+  return launch_status(cudaGetLastError());
+}
