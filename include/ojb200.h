@@ -34,7 +34,9 @@ int ojb_abi_version(void);
 /* ------------------------------------------------------------------------------------------------------------------
  * GEMM — replaces src/lt.cpp:43 lt_matmul / src/fastmodel.py:168 _mm (cuBLASLt) and src/fastmodel.py:158 _skmm
  * (torch.bmm split-K partials). out[M,N] = x[M,K] · w[N,K]^T, bf16 operands, fp32 accumulation in tensor memory.
- * Requirements: K % 8 == 0, x / w / out 16-byte aligned. variant: 0 = 128x256 tile, 1 = 128x128 tile.
+ * Requirements: K % 8 == 0, x / w / out 16-byte aligned. variant: 0 = the library chooses; 1 / 2 = 128-row tile kernel with
+ * 128x256 / 128x128 tiles; 3 = 256-row block kernel, automatic w-tile width; a multiple of 16 in [16, 256] = that kernel
+ * with this w-tile width.
  * ------------------------------------------------------------------------------------------------------------------ */
 int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int variant,
                   int32_t* status, ojb_stream_t stream);
@@ -45,8 +47,8 @@ int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N,
 int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
                          int32_t* status, ojb_stream_t stream);
 
-/* Split-K partial products, fp32: parts[s, M, N] = x[:, s*K/S:(s+1)*K/S] · w[:, same]^T, S = splits in [1, 8].
- * K must be a multiple of 64*S. Replaces src/fastmodel.py:158-166 (_skmm) — note that `w` stays [N, K] (K-major); the
+/* Split-K partial products, fp32: parts[s, M, N] = x[:, range s] · w[:, range s]^T, S = splits in [1, 16]; range s covers
+ * k-blocks (64 columns) [s*c, min((s+1)*c, ceil(K/64))) with c = ceil(ceil(K/64)/S); no range may be empty. Replaces src/fastmodel.py:158-166 (_skmm) — note that `w` stays [N, K] (K-major); the
  * pre-split [S, K/S, N] copy of src/fastmodel.py:186 (_split) is not needed. */
 int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, int64_t N, int64_t K, int splits,
                          int variant, int32_t* status, ojb_stream_t stream);
@@ -61,7 +63,7 @@ int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, 
 int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
                     void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream);
 
-/* src/kernels.cu:1444,1488 add_rmsnorm_sk2. delta = bf16(sum_s parts[s]) with parts fp32 [S, rows, H], S in [1, 8];
+/* src/kernels.cu:1444,1488 add_rmsnorm_sk2. delta = bf16(sum_s parts[s]) with parts fp32 [S, rows, H], S in [1, 16];
  * otherwise as ojb_add_rmsnorm (h_out always written). */
 int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits, const float* w1, const int32_t* rowmask,
                        void* h_out, void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream);

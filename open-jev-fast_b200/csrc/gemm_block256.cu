@@ -1,0 +1,437 @@
+// bf16 GEMM, 256-row block kernel (one of two kernels behind ojb_gemm_bf16*; the other is gemm_tile128.cu), sm_100a:
+//   out[M,N] = x[M,K] · w[N,K]^T, both operands K-major, fp32 accumulation in tensor memory (TMEM).
+//
+// One persistent CTA per SM, 320 threads:
+//   warp 0      TMA producer  — cp.async.bulk.tensor (plain, non-multicast), 128-byte swizzle, mbarrier completion
+//   warp 1      MMA issuer    — one lane issues tcgen05.mma.cta_group::1.kind::f16; tcgen05.commit releases shared-memory
+//                               stages and publishes the accumulators
+//   warps 2..9  epilogue      — tcgen05.ld of their 32-lane quarter of one of the two accumulators, conversion, stores
+// Two kinds of work unit:
+//   block unit  256 rows of x (two 128-row sub-tiles) times BN rows of w. Per 64-wide k-block the two MMAs (M = 128, N = BN)
+//               share the w tile, so a CTA pulls (256 + BN) rows from L2 for 256 x BN outputs — one third less than a
+//               128 x 256 tile. BN is chosen per shape (multiple of 16, <= 256) so that the units fill the SMs.
+//   tail unit   the last M mod 256 (<= 128) rows of x with the operands swapped: 256 rows of w are the M side (two MMAs
+//               with M = 128), the x tail is the N side (N = rows rounded up to 16). The tail costs what it is worth
+//               instead of a whole 128-row tile of zero padding; the epilogue writes the transposed accumulator.
+// Units run x-block fastest, then k-split, then w tile, so that CTAs running at the same time share w tiles in L2.
+//
+// Every wait on an mbarrier is bounded: after kWaitLimitNs the kernel raises the CTA's abort flag, records
+// OJB_DEV_WAIT_TIMEOUT in the status word, lets copies in flight land, frees its TMEM and returns.
+#include "gemm_common.cuh"
+
+namespace ojb {
+namespace {
+
+constexpr int kBlockM = 256;       // rows of x per block unit (two UMMA M sub-tiles)
+constexpr int kGemmThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kABytes = kBlockM * kBK * 2;   // 32 KB: 256 rows of x (block unit) or 256 rows of w (tail unit)
+constexpr uint32_t kSubBytes = kBM * kBK * 2;     // 16 KB: one 128-row sub-tile
+constexpr uint32_t kAcc1Col = 256;                // TMEM column of the second accumulator
+
+struct GemmArgs {
+  int M, N, K;
+  int BN;          // rows of w per block unit: multiple of 16, <= 256
+  int n_xblk;      // 256-row blocks of x served by block units
+  int tail_rows;   // rows of x served by tail units (<= 128), starting at row n_xblk * 256
+  int tail_box;    // tail_rows rounded up to a multiple of 16 = UMMA N of the tail units
+  int n_wtile;     // ceil(N / BN)
+  int n_wtile256;  // ceil(N / 256)
+  int splits, kb_per_split, kb_total;
+  int stages;
+  uint32_t stage_bytes;
+  void* out;
+  int64_t ldo;           // leading dimension of out in elements
+  int64_t split_stride;  // elements between split planes (fp32 partials)
+  int32_t* status;
+};
+
+struct Unit {
+  bool tail;
+  int xb, split, wt, kb0, kb1;
+};
+
+// Units are ordered by the w rows they read: w tile j contributes its block units (x-block fastest, then k-split) followed
+// by the tail units that start inside it, so a tail unit finds its w rows in L2 instead of streaming them from HBM again.
+// group_begin(j) = position of the first unit of tile j; tails_before(j) = tail tiles (256 w rows each) that start before
+// row j * BN.
+__device__ __forceinline__ int tails_before(const GemmArgs& g, int j) {
+  if (g.tail_rows == 0) return 0;
+  const int t = (j * g.BN + 255) / 256;
+  return t < g.n_wtile256 ? t : g.n_wtile256;
+}
+__device__ __forceinline__ int group_begin(const GemmArgs& g, int j) {
+  return (j * g.n_xblk + tails_before(g, j)) * g.splits;
+}
+
+__device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int total_block) {
+  (void)total_block;
+  Unit u;
+  const int nb = g.n_xblk * g.splits;
+  int j = static_cast<int>(unit / (nb + g.splits * (g.tail_rows > 0 ? g.BN / 256.0f : 0.0f) + 1e-6f));
+  if (j > g.n_wtile - 1) j = g.n_wtile - 1;
+  while (j > 0 && group_begin(g, j) > unit) --j;
+  while (j + 1 < g.n_wtile && group_begin(g, j + 1) <= unit) ++j;
+  const int off = unit - group_begin(g, j);
+  u.tail = off >= nb;
+  if (!u.tail) {
+    u.xb = off % g.n_xblk;
+    u.split = off / g.n_xblk;
+    u.wt = j;
+  } else {
+    const int o2 = off - nb;
+    u.xb = g.n_xblk;
+    u.split = o2 % g.splits;
+    u.wt = tails_before(g, j) + o2 / g.splits;
+  }
+  u.kb0 = u.split * g.kb_per_split;
+  u.kb1 = min(u.kb0 + g.kb_per_split, g.kb_total);
+  return u;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt, GemmArgs g) {
+  constexpr uint32_t kTmemCols = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(g.stages) * g.stage_bytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const uint32_t tiles0 = smem_u32(smem);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * kMaxStages;
+  const uint32_t accfull = empty0 + 8 * kMaxStages;
+  const uint32_t accempty = accfull + 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int STAGES = g.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(accfull, 1);
+    mbar_init(accempty, kEpiWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w256) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xt) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_block = g.n_xblk * g.n_wtile * g.splits;
+  const int total_units = total_block + (g.tail_rows > 0 ? g.n_wtile256 * g.splits : 0);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const Unit u = decode_unit(g, unit, total_block);
+        const uint32_t tx = kABytes + static_cast<uint32_t>(u.tail ? g.tail_box : g.BN) * (kBK * 2);
+        for (int kb = u.kb0; kb < u.kb1; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t a_dst = tiles0 + stage * g.stage_bytes;
+          const uint32_t fb = full0 + 8 * stage;
+          mbar_expect_tx(fb, tx);
+          if (!u.tail) {
+            tma_load_2d(a_dst, &map_x, fb, kb * kBK, u.xb * kBlockM);
+            tma_load_2d(a_dst + kABytes, &map_w, fb, kb * kBK, u.wt * g.BN);
+          } else {
+            tma_load_2d(a_dst, &map_w256, fb, kb * kBK, u.wt * 256);
+            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const Unit u = decode_unit(g, unit, total_block);
+        const uint32_t idesc = umma_idesc(u.tail ? g.tail_box : g.BN);
+        if (!mbar_wait(accempty, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = u.kb0; kb < u.kb1; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = tiles0 + stage * g.stage_bytes;
+          const uint64_t adesc0 = smem_desc_sw128(a_addr);
+          const uint64_t adesc1 = smem_desc_sw128(a_addr + kSubBytes);
+          const uint64_t bdesc = smem_desc_sw128(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
+            const uint32_t accum = (kb > u.kb0 || k > 0) ? 1u : 0u;
+            umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
+            umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
+          }
+          umma_commit(empty0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(accfull);
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
+    const int acc_id = (warp - 2) >> 2;     // warps 2-5 read accumulator 0, warps 6-9 accumulator 1
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const Unit u = decode_unit(g, unit, total_block);
+      if (!mbar_wait(accfull, acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t taddr = tlane + static_cast<uint32_t>(acc_id) * kAcc1Col;
+      if (!u.tail) {
+        // ---- block unit: this thread owns one row of x, the accumulator columns are output columns
+        const int row = u.xb * kBlockM + acc_id * kBM + quarter * 32 + lane;
+        const bool row_ok = row < g.M;
+        if constexpr (EPI == kEpiSwiglu) {
+          // BN = 256: columns [0,128) of the tile are gate_j, columns [128,256) the matching up_j
+          bf16_t* orow = reinterpret_cast<bf16_t*>(g.out) + static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * 128;
+          const int ncols = g.N / 2 - u.wt * 128;
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t gr[16], ur[16];
+            tmem_ld16(taddr + c * 16, gr);
+            tmem_ld16(taddr + 128 + c * 16, ur);
+            tmem_ld_wait();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                if (c * 16 + j < ncols) {
+                  float o[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const float gv = round_bf(__uint_as_float(gr[j + e]));
+                    const float uv = round_bf(__uint_as_float(ur[j + e]));
+                    o[e] = round_bf(silu_f(gv)) * uv;
+                  }
+                  *reinterpret_cast<uint4*>(orow + c * 16 + j) = pack8(o);
+                }
+              }
+            }
+          }
+        } else if constexpr (EPI == kEpiBf16) {
+          bf16_t* orow = reinterpret_cast<bf16_t*>(g.out) + static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * g.BN;
+          const int ncols = g.N - u.wt * g.BN;
+          const bool vec_ok = (g.ldo % 8) == 0 && (g.BN % 8) == 0;
+#pragma unroll 1
+          for (int c = 0; c < g.BN / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c * 16, r);
+            tmem_ld_wait();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                const int col = c * 16 + j;
+                if (col + 8 <= ncols && vec_ok) {
+                  float o[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
+                  *reinterpret_cast<uint4*>(orow + col) = pack8(o);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e)
+                    if (col + e < ncols) orow[col + e] = f2bf(__uint_as_float(r[j + e]));
+                }
+              }
+            }
+          }
+        } else {
+          float* orow = reinterpret_cast<float*>(g.out) + static_cast<int64_t>(u.split) * g.split_stride +
+                        static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * g.BN;
+          const int ncols = g.N - u.wt * g.BN;
+          const bool vec_ok = (g.ldo % 4) == 0 && (g.BN % 4) == 0;
+#pragma unroll 1
+          for (int c = 0; c < g.BN / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c * 16, r);
+            tmem_ld_wait();
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                const int col = c * 16 + j;
+                if (col + 4 <= ncols && vec_ok) {
+                  *reinterpret_cast<uint4*>(orow + col) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    if (col + e < ncols) orow[col + e] = __uint_as_float(r[j + e]);
+                }
+              }
+            }
+          }
+        }
+      } else {
+        // ---- tail unit (operands swapped): this thread owns one row of w = one output column, the accumulator columns
+        //      are the tail rows of x. A warp writes 32 neighbouring output columns of one row per store.
+        const int m0 = g.n_xblk * kBlockM;
+        if constexpr (EPI == kEpiSwiglu) {
+          // accumulator 0 holds gate rows, accumulator 1 the matching up rows of the same lanes
+          if (acc_id == 0) {
+            const int j = u.wt * 128 + quarter * 32 + lane;       // output column
+            const bool col_ok = j < g.N / 2;
+            bf16_t* ocol = reinterpret_cast<bf16_t*>(g.out) + j;
+#pragma unroll 1
+            for (int c = 0; c < g.tail_box / 16; ++c) {
+              uint32_t gr[16], ur[16];
+              tmem_ld16(tlane + c * 16, gr);
+              tmem_ld16(tlane + kAcc1Col + c * 16, ur);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const int m = m0 + c * 16 + e;
+                if (col_ok && m < g.M) {
+                  const float gv = round_bf(__uint_as_float(gr[e])), uv = round_bf(__uint_as_float(ur[e]));
+                  ocol[static_cast<int64_t>(m) * g.ldo] = f2bf(round_bf(silu_f(gv)) * uv);
+                }
+              }
+            }
+          }
+        } else {
+          const int col = u.wt * 256 + acc_id * kBM + quarter * 32 + lane;
+          const bool col_ok = col < g.N;
+#pragma unroll 1
+          for (int c = 0; c < g.tail_box / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(taddr + c * 16, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int m = m0 + c * 16 + e;
+              if (col_ok && m < g.M) {
+                if constexpr (EPI == kEpiBf16) {
+                  reinterpret_cast<bf16_t*>(g.out)[static_cast<int64_t>(m) * g.ldo + col] = f2bf(__uint_as_float(r[e]));
+                } else {
+                  reinterpret_cast<float*>(g.out)[static_cast<int64_t>(u.split) * g.split_stride + static_cast<int64_t>(m) * g.ldo + col] =
+                      __uint_as_float(r[e]);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accempty);
+      acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) report_status(g.status, OJB_DEV_WAIT_TIMEOUT);
+    // copies that were already issued must land before the shared memory of this CTA is handed on
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Width of the w tile of the block units: the multiple of 16 that needs the fewest waves of CTAs, wider tiles preferred
+// (they pull less from L2 per flop); tail units are short and fill the gaps.
+int choose_bn(int64_t N, int n_xblk, int splits, int sms) {
+  if (n_xblk == 0) return 256;
+  int best = 256;
+  double best_cost = 1e30;
+  for (int bn = 256; bn >= 64; bn -= 16) {
+    const int64_t units = ceil_div(N, bn) * n_xblk * splits;
+    const int64_t waves = ceil_div(units, sms);
+    const double cost = static_cast<double>(waves) * bn * (1.0 + 0.15 * (256 - bn) / 256.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+constexpr size_t kSmemBudget = 227 * 1024;
+
+template <int EPI>
+int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
+                int32_t* status, cudaStream_t stream) {
+  static bool attr_set = false;
+  auto kern = gemm_tcgen05_kernel<EPI>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)) != cudaSuccess)
+      return OJB_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) return OJB_ERR_LAUNCH;
+  GemmArgs g;
+  g.M = static_cast<int>(M);
+  g.N = static_cast<int>(N);
+  g.K = static_cast<int>(K);
+  g.n_xblk = static_cast<int>(M / kBlockM);
+  int r = static_cast<int>(M % kBlockM);
+  if (r > kBM) { g.n_xblk += 1; r = 0; }   // a long remainder is cheaper as one more (zero-padded) block
+  g.tail_rows = r;
+  g.tail_box = (r + 15) / 16 * 16;
+  g.splits = splits;
+  g.kb_total = static_cast<int>(ceil_div(K, kBK));
+  g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
+  if (static_cast<int64_t>(splits - 1) * g.kb_per_split >= g.kb_total) return OJB_ERR_ARG;   // an empty split
+  g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, splits, sms));
+  g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
+  g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
+  const int b_rows = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) : g.tail_box;
+  g.stage_bytes = kABytes + static_cast<uint32_t>(b_rows) * (kBK * 2);
+  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16;
+  g.stages = static_cast<int>((kSmemBudget - fixed) / g.stage_bytes);
+  if (g.stages > kMaxStages) g.stages = kMaxStages;
+  if (g.stages < 2) return OJB_ERR_LIMIT;
+  g.out = out;
+  g.ldo = ldo;
+  g.split_stride = M * N;
+  g.status = status;
+  CUtensorMap map_x, map_w, map_w256, map_xt;
+  int rc = make_map(&map_x, x, M, K, kBlockM);
+  if (rc == OJB_OK) rc = make_map(&map_w, w, N, K, g.BN);
+  if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256);
+  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
+  if (rc != OJB_OK) return rc;
+  const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits + (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits : 0);
+  const int grid = static_cast<int>(units < sms ? units : sms);
+  const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
+  kern<<<grid, kGemmThreads, smem, stream>>>(map_x, map_w, map_w256, map_xt, g);
+  return launch_status(cudaGetLastError());
+}
+
+}  // namespace
+
+int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
+                         int splits, int64_t ldo, int32_t* status, cudaStream_t stream) {
+  if (epi == kEpiBf16) return launch_gemm<kEpiBf16>(x, w, out, M, N, K, splits, bn_req, ldo, status, stream);
+  if (epi == kEpiSwiglu) return launch_gemm<kEpiSwiglu>(x, w, out, M, N, K, splits, bn_req, ldo, status, stream);
+  return launch_gemm<kEpiPartialF32>(x, w, out, M, N, K, splits, bn_req, ldo, status, stream);
+}
+
+}  // namespace ojb

@@ -258,7 +258,7 @@ extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1
 extern "C" int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits, const float* w1, const int32_t* rowmask,
                                   void* h_out, void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream) {
   if (rows == 0) return OJB_OK;
-  OJB_REQUIRE(x && parts && w1 && h_out && hn_out && rows > 0 && H > 0 && H % 8 == 0 && splits >= 1 && splits <= 8);
+  OJB_REQUIRE(x && parts && w1 && h_out && hn_out && rows > 0 && H > 0 && H % 8 == 0 && splits >= 1 && splits <= 16);
   if (H > kRowThreads * kRowVecs * 8) return OJB_ERR_LIMIT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t ps = rows * H;
@@ -270,6 +270,7 @@ extern "C" int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits,
     break;
   switch (splits) {
     OJB_SK(1) OJB_SK(2) OJB_SK(3) OJB_SK(4) OJB_SK(5) OJB_SK(6) OJB_SK(7) OJB_SK(8)
+    OJB_SK(9) OJB_SK(10) OJB_SK(11) OJB_SK(12) OJB_SK(13) OJB_SK(14) OJB_SK(15) OJB_SK(16)
   }
 #undef OJB_SK
   return launch_status(cudaGetLastError());

@@ -100,17 +100,12 @@ class FastQwen35(torch.nn.Module):
                 self.L.append(d)
 
     # ------------------------------------------------------------------------------------------------ GEMM dispatch
-    # The reference times every cuBLASLt candidate per shape (src/fastmodel.py:114-156). Here the candidates are two tile
-    # shapes and the split-K factor of one kernel, and the choice follows from counting work units against the 148 SMs
-    # (measured with `python -m ojb200.gemm_sweep`): the 128x256 tile wins whenever it yields at least ~100 units, the
-    # 128x128 tile otherwise; fp32 split-K partials only pay off for the long-K down-projection at small M.
-    @staticmethod
-    def _variant(M, N):
-        return 0 if -(-M // 128) * -(-N // 256) >= 100 else 1
-
+    # The reference times every cuBLASLt candidate per shape (src/fastmodel.py:114-156). Here one kernel serves all shapes;
+    # its tile width is chosen inside the library from the work-unit count, and the K split of the two projections onto the
+    # hidden size (too few tiles for 148 SMs) by lt_ext.plan_splitk.
     def _mm(self, x, w):
         """out = x @ w^T, bf16 (src/fastmodel.py:168 _mm)."""
-        return LT.lt_matmul(x, w, self._variant(x.shape[0], w.shape[0]))
+        return LT.lt_matmul(x, w, 0)
 
     @staticmethod
     def _split(W, S):
@@ -119,13 +114,12 @@ class FastQwen35(torch.nn.Module):
         return W.view(N, S, Kd // S).permute(1, 2, 0).contiguous()
 
     def _res(self, h, y, w, S, w1, mask):
-        """Output projection + residual + RMSNorm (src/fastmodel.py:196 _res). S = 0 picks the split: a plain bf16 GEMM
-        followed by the fused add + norm (delta = bf16 of the fp32 accumulator, the same rounding point as the reference's
-        bf16(sum of fp32 partials)), or, when the tile count is far below the SM count and K is long, S = 2 fp32 partials."""
+        """Output projection + residual + RMSNorm (src/fastmodel.py:196 _res): fp32 partial products over S ranges of K, then
+        one kernel for partial sum + residual + norm. S = 0 lets plan_splitk choose; S = 1 is a plain bf16 GEMM followed by
+        the fused add + norm (delta = bf16 of the fp32 accumulator, the rounding point of the reference's bf16(sum))."""
         M, Kd = y.shape
-        N = w.shape[0]
         if S == 0:
-            S = 2 if (-(-M // 128) * -(-N // 256) <= 74 and Kd >= 8192 and Kd % 128 == 0) else 1
+            S = LT.plan_splitk(M, w.shape[0], Kd)
         if S == 1:
             return K.add_rmsnorm(h, self._mm(y, w), w1, mask, self.eps)
         parts = LT.gemm_splitk(y, w, S, 0)

@@ -68,7 +68,7 @@ def main():
                 print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
                                   "max_err": err}), flush=True)
-            for v in ((0, 1) if want("plain") else ()):
+            for v in ((0, 1, 3) if want("plain") else ()):
                 out = LT.lt_matmul(x, ws[0], v)
                 err = (out.float() - ref).abs().max().item()
                 report(f"plain v{v}", _time([lambda w=w, v=v: LT.lt_matmul(x, w, v) for w in ws]), err)
@@ -82,14 +82,13 @@ def main():
             if N == 5120 and not args.quick and want("splitk"):
                 h = torch.randn(M, N, generator=g, device=dev).to(bf16)
                 w1 = torch.ones(N, device=dev)
-                for S in (1, 2, 3, 4, 6, 8):
-                    if Kd % (64 * S):
-                        continue
-                    for v in (0, 1):
+                plan = LT.plan_splitk(M, N, Kd)
+                for S in sorted({1, 2, 3, 4, 7, 11, plan}):
+                    for v in (0,):
                         parts = LT.gemm_splitk(x, ws[0], S, v)
                         err = (parts.sum(0) - ref).abs().max().item()
-                        report(f"splitk S{S} v{v}", _time([lambda w=w, S=S, v=v: LT.gemm_splitk(x, w, S, v) for w in ws]), err)
-                        report(f"splitk S{S} v{v} + reduce/norm",
+                        report(f"splitk S{S}{'*' if S == plan else ''} v{v}", _time([lambda w=w, S=S, v=v: LT.gemm_splitk(x, w, S, v) for w in ws]), err)
+                        report(f"splitk S{S}{'*' if S == plan else ''} v{v} + reduce/norm",
                                _time([lambda w=w, S=S, v=v: K.add_rmsnorm_sk2(h, LT.gemm_splitk(x, w, S, v), w1, None, 1e-6) for w in ws]), err)
         del ws
         torch.cuda.empty_cache()

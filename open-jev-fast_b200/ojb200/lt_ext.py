@@ -1,7 +1,9 @@
 """GEMM surface of open-jev-fast's src/lt_ext.py / src/lt.cpp, backed by the tcgen05 GEMM of libojb200.so.
 
 The reference enumerates cuBLASLt algorithms per shape (lt_setup) and runs one by index (lt_matmul); split-K plans go
-through lt2_*. Here an "algorithm" is a tile variant of the hand-written kernel: 0 = 128x256 tile, 1 = 128x128 tile.
+through lt2_*. Here an "algorithm" is one of the library's GEMM variants: index 0 lets the library choose, 1 / 2 force the
+128-row tile kernel with 256 / 128-wide tiles, 3 the 256-row block kernel with automatic w-tile width, 4.. that kernel
+with w-tile width 256, 192, 128.
 Two entry points have no counterpart in the reference: gemm_swiglu (SwiGLU fused into the epilogue) and gemm_splitk
 (fp32 partial sums from the un-split [N, K] weight).
 """
@@ -13,7 +15,9 @@ from . import _lib
 from ._lib import call, i32, i64, ptr, stream_ptr
 
 bf16 = torch.bfloat16
-N_VARIANTS = 2
+VARIANT_BN = [0, 1, 2, 3, 256, 192, 128]
+N_VARIANTS = len(VARIANT_BN)
+SM_COUNT = 148
 _plans = []          # lt2 plans: dicts
 _wl1_cache = {}      # data_ptr of a [S, K/S, N] weight -> its [N, K] re-layout
 
@@ -44,7 +48,7 @@ def lt_matmul(x, w, idx):
     M, K = x.shape
     N = w.shape[0]
     out = torch.empty(M, N, dtype=bf16, device=x.device)
-    call("ojb_gemm_bf16", ptr(x), ptr(w), ptr(out), i64(M), i64(N), i64(K), i32(idx), ptr(_lib.status_word(x.device)),
+    call("ojb_gemm_bf16", ptr(x), ptr(w), ptr(out), i64(M), i64(N), i64(K), i32(VARIANT_BN[idx]), ptr(_lib.status_word(x.device)),
          stream_ptr())
     return out
 
@@ -68,13 +72,35 @@ def interleave_gate_up(w_gate, w_up):
     return torch.stack([w_gate.view(I // 128, 128, K), w_up.view(I // 128, 128, K)], 1).reshape(2 * I, K).contiguous()
 
 
-def gemm_splitk(x, w, S, idx=1):
-    """fp32 partials [S, M, N] of x @ w^T over S equal K ranges; w stays [N, K]."""
+def plan_splitk(M, N, K, sms=SM_COUNT):
+    """Number of K ranges for a projection whose tile count alone cannot fill the SMs: minimises (waves of CTAs) x (k-blocks
+    per range), with a small charge per range for the fp32 partials that the reduce kernel has to read."""
+    if M > 256 and 0 < M % 256 <= 128:      # served by the 128-row tile kernel: bf16 output unless the tiles are very few
+        tiles = -(-M // 128) * -(-N // 256)
+        return 2 if (tiles <= 74 and K >= 8192 and K % 128 == 0) else 1
+    xblk = M // 256 + (1 if M % 256 > 128 else 0)
+    tail = 1 if 0 < M % 256 <= 128 else 0
+    kb = -(-K // 64)
+    best, best_cost = 1, float("inf")
+    for S in range(1, 17):
+        per = -(-kb // S)
+        if (S - 1) * per >= kb or per < 4:
+            continue
+        tiles = -(-N // 256)
+        units = xblk * tiles * S + tail * tiles * S * (M % 256) / 512.0
+        cost = -(-int(units + 0.999) // sms) * per * (1.0 + 0.03 * S)
+        if cost < best_cost:
+            best, best_cost = S, cost
+    return best
+
+
+def gemm_splitk(x, w, S, idx=0):
+    """fp32 partials [S, M, N] of x @ w^T over S K ranges of ceil(K/64/S) k-blocks; w stays [N, K]."""
     _check(x, w)
     M, K = x.shape
     N = w.shape[0]
     parts = torch.empty(S, M, N, dtype=torch.float32, device=x.device)
-    call("ojb_gemm_bf16_splitk", ptr(x), ptr(w), ptr(parts), i64(M), i64(N), i64(K), i32(S), i32(idx),
+    call("ojb_gemm_bf16_splitk", ptr(x), ptr(w), ptr(parts), i64(M), i64(N), i64(K), i32(S), i32(VARIANT_BN[idx]),
          ptr(_lib.status_word(x.device)), stream_ptr())
     return parts
 
@@ -95,7 +121,7 @@ def lt2_search(h, max_cands, min_waves):
 
 def lt2_info(h, i):
     """src/lt.cpp:170 — description of candidate i."""
-    return f"tcgen05 tile 128x{256 if i == 0 else 128}, plan {_plans[h]}"
+    return f"tcgen05 GEMM variant code {VARIANT_BN[i]}, plan {_plans[h]}"
 
 
 def lt2_run(h, x, w, i):

@@ -24,8 +24,8 @@ def _close(out, ref):
     assert err <= tol, (err, tol)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
-@pytest.mark.parametrize("M,N,K", [(64, 512, 256), (128, 256, 64), (288, 1280, 5120), (539, 12352, 5120), (100, 200, 72),
+@pytest.mark.parametrize("variant", [0, 1, 3, 5])
+@pytest.mark.parametrize("M,N,K", [(64, 512, 256), (16, 48, 64), (257, 300, 136), (400, 1000, 512), (1000, 520, 192), (128, 256, 64), (288, 1280, 5120), (539, 12352, 5120), (100, 200, 72),
                                    (1024, 5120, 6144), (544, 5120, 4096)])
 def test_gemm_plain(M, N, K, variant):
     from ojb200 import lt_ext, _lib
@@ -36,7 +36,7 @@ def test_gemm_plain(M, N, K, variant):
     _close(out, _ref(x, w))
 
 
-@pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120)])
+@pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120), (256, 256, 320), (700, 384, 512)])
 def test_gemm_swiglu(M, I, K):
     from ojb200 import lt_ext, _lib
     g = torch.Generator(device="cuda").manual_seed(2)
@@ -56,7 +56,8 @@ def test_gemm_swiglu(M, I, K):
 
 
 @pytest.mark.parametrize("variant", [0, 1])
-@pytest.mark.parametrize("M,N,K,S", [(64, 256, 256, 2), (288, 5120, 6144, 2), (544, 5120, 17408, 4), (539, 5120, 4096, 2)])
+@pytest.mark.parametrize("M,N,K,S", [(64, 256, 256, 2), (288, 5120, 6144, 2), (544, 5120, 17408, 4), (539, 5120, 4096, 2),
+                                     (544, 5120, 17408, 7), (64, 5120, 4096, 16), (300, 520, 1000, 3)])
 def test_gemm_splitk(M, N, K, S, variant):
     from ojb200 import lt_ext, _lib
     x, w = _mk(M, N, K, 3)
@@ -64,7 +65,8 @@ def test_gemm_splitk(M, N, K, S, variant):
     torch.cuda.synchronize()
     _lib.check_status()
     assert parts.shape == (S, M, N)
-    ks = K // S
+    kb = -(-K // 64)
+    ks = -(-kb // S) * 64                  # ranges are whole 64-column k-blocks, the last one may be shorter
     for s in range(S):
         ref = x[:, s * ks:(s + 1) * ks].float() @ w[:, s * ks:(s + 1) * ks].float().t()
         err = (parts[s] - ref).abs().max().item()
