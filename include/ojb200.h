@@ -101,7 +101,8 @@ int ojb_fullattn_prep(const void* proj, const float* qw1, const float* kw1, cons
  *   buf64 = ids[N] | pos[N] | lastidx[S]              (ids / pos padded to a multiple of 4 elements)
  *   buf32 = src[S,L2] | inv[N] | rep_ptr[N+2] | rep_pos[S*L2] | hist[N+1,4] | canon[S*L2] | rowmask[N] | vbits[N,N/32]
  *           (every field padded to a multiple of 8 elements), bit-identical to the reference's tensors, and, if ext32 is
- *   not null, ext32 = krange[N,8] | nodes[1+2S,4] | chunks[cap,4] | steps[cap,4] | meta[8] (tables of this
+ *   not null, ext32 = krange[N,8] | nodes[1+2S,4] | chunks[cap,4] | steps[cap,4] | meta[8] | lsteps[cap,4] |
+ *   lwalks[2+2S, padded to a multiple of 8] (tables of this
  *   implementation only: key ranges for the attention kernel, node / chunk / walk tables for the tree-native
  *   Gated DeltaNet pass).
  * ------------------------------------------------------------------------------------------------------------------ */
@@ -141,6 +142,16 @@ int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g,
                     int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr, int64_t n_walks,
                     const float* init_state, float* final_state, void* scratch, void* out, int64_t HK, int64_t HV,
                     float scale, ojb_stream_t stream);
+
+/* ojb_gdn_chunked with the state pass run level by level (1 + n_levels launches): `levels` is a HOST array of n_levels + 1
+ * walk indices; the walks [levels[l], levels[l+1]) of level l run side by side and start from the end states that walks of
+ * earlier levels exported to `states` (fp32 [slots, HV, 128, 128]; steps use load = 4 with slot (aux >> 16) - 1 and export
+ * to slot (aux & 0xffff) - 1). For a prefix tree: root | question stems | leaves (lsteps / lwalks of ojb_gtree_fill). No
+ * counterpart in the reference, whose kernel recomputes the shared nodes once per candidate (src/kernels.cu:4225). */
+int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                           const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                           const int32_t* levels, int64_t n_levels, float* states, void* scratch, void* out, int64_t HK,
+                           int64_t HV, float scale, ojb_stream_t stream);
 
 /* Scratch-free form of ojb_gdn_chunked. It has no counterpart in open-jev-fast. Same arguments without `scratch`: the
  * per-(chunk, head) work items live in a fixed 72 MiB array inside the library's device image (every GPU that loads the

@@ -4,9 +4,10 @@
 //              of q and k per head, beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias). Optionally scattered to the
 //              replicated per-candidate slots of the reference layout.
 //   gdn_intra  per (chunk of <= 64 rows, value head), all chunks in parallel — everything that does not depend on the
-//              recurrent state: G = cumsum(g); A = strict_lower((k beta) k^T * exp(G_i - G_j)); u = (I+A)^-1 (v beta),
-//              w = (I+A)^-1 (k beta e^G) by fp32 forward substitution; Aqk = tril(q k^T * exp(G_i - G_j)) * scale;
-//              qg = q e^G scale; kg = k e^(G_L - G). KK^T and QK^T run on the tensor cores (mma.sync bf16, fp32 accumulate).
+//              recurrent state: G = cumsum(g); A = strict_lower((k beta) k^T * exp(G_i - G_j)); T = (I+A)^-1 in fp32 by
+//              16 x 16 blocks; u = T (v beta), w = T (k beta e^G) with T as a bf16 value + remainder pair;
+//              Aqk = tril(q k^T * exp(G_i - G_j)) * scale; qg = q e^G scale; kg = k e^(G_L - G). K K^T, Q K^T and the two
+//              products with T run on the tensor cores (mma.sync bf16, fp32 accumulate).
 //              Results go to a scratch item of 36 872 bf16 per (chunk, head).
 //   gdn_state  per (value head, 32-column slice of the state, walk): walks the chunks of the tree depth first with the
 //              fp32 state slice [128 x 32] in registers; per chunk v' = u - w S, o = qg S + Aqk v', S = S e^(G_L) + kg^T v'
@@ -144,7 +145,10 @@ gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, 
 // ----------------------------------------------------------------------------------------------------------- gdn_intra
 constexpr int kLd = kHD + 8;      // padded row length (bf16) of a [64 x 128] tile in shared memory: 272 bytes
 constexpr int kIntraThreads = 256;
-constexpr int kIntraSmem = 4 * kChunk * kLd * 2 + kChunk * kChunk * 4 + 4 * kChunk * 4;
+constexpr int kLdT = kChunk + 8;  // padded row (bf16) of the [64 x 64] inverse
+// K | Q | V | KG tiles, A (fp32; later the bf16 pair of T) with the block scratch P behind it, four vectors, T (fp32)
+constexpr int kIntraSmem = 4 * kChunk * kLd * 2 + kChunk * kChunk * 4 + 3 * 256 * 4 + 4 * kChunk * 4 + kChunk * kChunk * 4;
+static_assert(2 * kChunk * kLdT * 2 <= kChunk * kChunk * 4 + 3 * 256 * 4, "the bf16 pair of T must fit over A and P");
 
 __global__ void __launch_bounds__(kIntraThreads)
 gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, const bf16_t* __restrict__ v,
@@ -160,10 +164,12 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
   bf16_t* Vs = Qs + kChunk * kLd;
   bf16_t* KGs = Vs + kChunk * kLd;
   float* As = reinterpret_cast<float*>(KGs + kChunk * kLd);   // [64][64]
-  float* Gs = As + kChunk * kChunk;                            // G * log2e (inclusive cumsum)
+  float* Ps = As + kChunk * kChunk;                            // [3][16][16] block products
+  float* Gs = Ps + 3 * 256;                                    // G * log2e (inclusive cumsum)
   float* Bs = Gs + kChunk;                                     // beta
   float* EGs = Bs + kChunk;                                    // exp(G)
   float* EKs = EGs + kChunk;                                   // exp(G_L - G)
+  float* Tf = EKs + kChunk;                                    // [64][64] inverse, fp32
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KD = HK * kHD, VD = HV * kHD;
 
@@ -254,7 +260,8 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
       }
     }
   }
-  // ---- qg = q e^G scale (in place), kg = k e^(G_L - G)
+  __syncthreads();   // all warps are done reading K and Q as MMA operands
+  // ---- qg = q e^G scale (in place), kg = k e^(G_L - G); then the right-hand sides v beta and k beta e^G in place
   for (int i = tid; i < kChunk * (kHD / 8); i += kIntraThreads) {
     const int r = i >> 4, cv = (i & 15) * 8;
     float f[8];
@@ -263,47 +270,121 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] *= sq;
     *reinterpret_cast<uint4*>(Qs + r * kLd + cv) = pack8(f);
-    unpack8(*reinterpret_cast<const uint4*>(Ks + r * kLd + cv), f);
-    const float sk = EKs[r];
+    float kf[8];
+    unpack8(*reinterpret_cast<const uint4*>(Ks + r * kLd + cv), kf);
+    const float sk = EKs[r], sw = Bs[r] * EGs[r];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] *= sk;
+    for (int e = 0; e < 8; ++e) f[e] = kf[e] * sk;
     *reinterpret_cast<uint4*>(KGs + r * kLd + cv) = pack8(f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = kf[e] * sw;
+    *reinterpret_cast<uint4*>(Ks + r * kLd + cv) = pack8(f);
+    unpack8(*reinterpret_cast<const uint4*>(Vs + r * kLd + cv), f);
+    const float sv = Bs[r];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] *= sv;
+    *reinterpret_cast<uint4*>(Vs + r * kLd + cv) = pack8(f);
   }
+  // ---- T = (I + A)^-1, fp32, by 16 x 16 blocks. First the four diagonal blocks (forward substitution per column) ...
+  for (int i = tid; i < kChunk * kChunk; i += kIntraThreads) Tf[i] = 0.f;
   __syncthreads();
-
-  // ---- forward substitution, one right-hand-side column per thread: x_i = b_i - sum_{j<i} A[i][j] x_j
-  {
-    const bool is_w = tid >= kHD;
-    const int c = is_w ? tid - kHD : tid;
-    bf16_t* col = (is_w ? Ks : Vs) + c;
-    float x[kChunk];
+  if (tid < kChunk) {
+    const int base = (tid >> 4) * 16, c = tid & 15;
+    float x[16];
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
-      float b = bf2f(col[i * kLd]) * Bs[i];
-      if (is_w) b *= EGs[i];
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-      const float4* arow = reinterpret_cast<const float4*>(As + i * kChunk);
+    for (int r = 0; r < 16; ++r) {
+      float acc = r == c ? 1.f : 0.f;
+      const float* arow = As + (base + r) * kChunk + base;
 #pragma unroll
-      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-        const float4 a = arow[j4];   // entries at or right of the diagonal are zero
-        s0 += a.x * x[4 * j4];
-        if (4 * j4 + 1 < i) s1 += a.y * x[4 * j4 + 1];
-        if (4 * j4 + 2 < i) s2 += a.z * x[4 * j4 + 2];
-        if (4 * j4 + 3 < i) s3 += a.w * x[4 * j4 + 3];
-      }
-      x[i] = b - ((s0 + s1) + (s2 + s3));
+      for (int kk = 0; kk < r; ++kk) acc -= arow[kk] * x[kk];
+      x[r] = acc;
     }
-    // each thread owns its column: results replace the inputs in place
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) col[i * kLd] = f2bf(x[i]);
+    for (int r = 0; r < 16; ++r) Tf[(base + r) * kChunk + base + c] = x[r];
   }
   __syncthreads();
-  // ---- copy w (Ks), u (Vs), qg (Qs), kg (KGs) to the scratch item, 16 bytes per thread
-  for (int i = tid; i < 4 * kChunk * (kHD / 8); i += kIntraThreads) {
+  // ... then the blocks below the diagonal, one block diagonal at a time: T_ij = -T_ii * sum_{k=j}^{i-1} A_ik T_kj
+  {
+    const int r = tid >> 4, c = tid & 15;   // one element of a 16 x 16 block per thread
+#pragma unroll
+    for (int d = 1; d < 4; ++d) {
+#pragma unroll
+      for (int j = 0; j + d < 4; ++j) {
+        const int i = j + d;
+        float acc = 0.f;
+        for (int kb = j; kb < i; ++kb) {
+          const float* arow = As + (16 * i + r) * kChunk + 16 * kb;
+          const float* tcol = Tf + (16 * kb) * kChunk + 16 * j + c;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) acc += arow[e] * tcol[e * kChunk];
+        }
+        Ps[j * 256 + r * 16 + c] = acc;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j + d < 4; ++j) {
+        const int i = j + d;
+        const float* trow = Tf + (16 * i + r) * kChunk + 16 * i;
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc += trow[e] * Ps[j * 256 + e * 16 + c];
+        Tf[(16 * i + r) * kChunk + 16 * j + c] = -acc;
+      }
+      __syncthreads();
+    }
+  }
+  // ---- T as a pair of bf16 matrices (value and rounding remainder) over the memory of A, which is no longer needed
+  bf16_t* Thi = reinterpret_cast<bf16_t*>(As);
+  bf16_t* Tlo = Thi + kChunk * kLdT;
+  for (int i = tid; i < kChunk * kChunk; i += kIntraThreads) {
+    const int r = i >> 6, c = i & 63;
+    const float t = Tf[i];
+    const bf16_t hi = f2bf(t);
+    Thi[r * kLdT + c] = hi;
+    Tlo[r * kLdT + c] = f2bf(t - bf2f(hi));
+  }
+  __syncthreads();
+  // ---- u = T (v beta) (warps 0-3) and w = T (k beta e^G) (warps 4-7) on the tensor cores: 16 rows x 128 columns per warp;
+  //      T is lower triangular, so row block m only needs the k-steps 0..m
+  {
+    const int mt = warp & 3;
+    const bool is_w = warp >= 4;
+    const bf16_t* Bm = is_w ? Ks : Vs;
+    float acc[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+    const int a_row = mt * 16 + (lane & 15), a_col = (lane >> 4) * 8;
+    const int bt_row = lane & 15, bt_col = (lane >> 4) * 8;
+    for (int kk = 0; kk <= mt; ++kk) {
+      uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+      ldsm_x4(smem_u32(Thi + a_row * kLdT + kk * 16 + a_col), h0, h1, h2, h3);
+      ldsm_x4(smem_u32(Tlo + a_row * kLdT + kk * 16 + a_col), l0, l1, l2, l3);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(smem_u32(Bm + (kk * 16 + bt_row) * kLd + np * 16 + bt_col), b0, b1, b2, b3);
+        mma_bf16(acc[2 * np], h0, h1, h2, h3, b0, b1);
+        mma_bf16(acc[2 * np + 1], h0, h1, h2, h3, b2, b3);
+        mma_bf16(acc[2 * np], l0, l1, l2, l3, b0, b1);
+        mma_bf16(acc[2 * np + 1], l0, l1, l2, l3, b2, b3);
+      }
+    }
+    bf16_t* dst = item + (is_w ? kOffW : kOffU);
+    const int gr = lane >> 2, tc = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr) * kHD + nt * 8 + tc) = pack2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr + 8) * kHD + nt * 8 + tc) = pack2(acc[nt][2], acc[nt][3]);
+    }
+  }
+  // ---- copy qg (Qs) and kg (KGs) to the scratch item, 16 bytes per thread
+  for (int i = tid; i < 2 * kChunk * (kHD / 8); i += kIntraThreads) {
     const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
     const int r = rem >> 4, cv = (rem & 15) * 8;
-    const bf16_t* srcb = which == 0 ? Ks : which == 1 ? Vs : which == 2 ? Qs : KGs;
-    *reinterpret_cast<uint4*>(item + which * (kChunk * kHD) + r * kHD + cv) = *reinterpret_cast<const uint4*>(srcb + r * kLd + cv);
+    const bf16_t* srcb = which == 0 ? Qs : KGs;
+    *reinterpret_cast<uint4*>(item + (which == 0 ? kOffQg : kOffKg) + r * kHD + cv) = *reinterpret_cast<const uint4*>(srcb + r * kLd + cv);
   }
 }
 
@@ -697,4 +778,39 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
   gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
       scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
   return launch_status(cudaGetLastError());
+}
+
+// --------------------------------------------------------------------------------------------- level-parallel tree pass
+// Same kernels, but the state pass runs once per tree level: all walks of a level (one per node of that level) start from
+// the end state that their parent's walk exported to `states` in the previous launch, so sibling nodes run side by side
+// instead of one after the other inside one CTA column. levels[l] .. levels[l+1] (host array) are the walk indices of level l.
+extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                                      const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                                      const int32_t* levels, int64_t n_levels, float* states, void* scratch, void* out,
+                                      int64_t HK, int64_t HV, float scale, ojb_stream_t stream) {
+  if (n_chunks == 0 || n_levels == 0) return OJB_OK;
+  OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && levels && states && scratch && out);
+  OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_levels > 0 && n_levels <= 16 && HV <= 65535);
+  for (int64_t l = 0; l < n_levels; ++l) OJB_REQUIRE(levels[l + 1] >= levels[l] && levels[l + 1] - levels[l] <= 65535);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
+      return OJB_ERR_LAUNCH;
+    attr = true;
+  }
+  gdn_intra_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), kIntraThreads, kIntraSmem, st>>>(
+      static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
+      static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
+  if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
+  for (int64_t l = 0; l < n_levels; ++l) {
+    const int nw = levels[l + 1] - levels[l];
+    if (nw == 0) continue;
+    gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(nw)), kStateThreads, kStateSmem, st>>>(
+        static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
+        static_cast<int>(HV));
+    if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
+  }
+  return OJB_OK;
 }

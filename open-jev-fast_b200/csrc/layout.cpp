@@ -10,6 +10,10 @@
 //                      0 = carry on, 1 = start from zero, 2 = restore slot A (root end), 3 = restore slot B (question
 //                      end); save is 0 = none, 1 = store slot A, 2 = store slot B
 //   meta   [8]         (number of chunks, number of steps, Lr, R, S, 0, walk begin = 0, walk end = number of steps)
+//   lsteps [NC_max, 4] the same chunks arranged as independent walks in three levels (root | stems | leaves) that hand
+//                      states over through an exported-state buffer: load 4 = start from state slot (aux >> 16) - 1,
+//                      (aux & 0xffff) - 1 = slot to export to after the step
+//   lwalks [2 + 2S]    step ranges of the walks: [0,1) root, [1, 1+S) stems (first R used), [1+S, 1+2S) leaves
 // The tree is: root = longest common prefix of all candidates (capped so that every candidate keeps one row), one node
 // per question = common prefix of its candidates beyond the root (same cap), one leaf per candidate.
 #include <stdint.h>
@@ -101,7 +105,7 @@ extern "C" int ojb_gtree_dims(const int64_t* tokens, const int64_t* seq_off, con
   const int64_t n32 = pad8(S * L2) + pad8(N) + pad8(N + 2) + pad8(S * L2) + pad8((N + 1) * 4) + pad8(S * L2) + pad8(N) +
                       pad8(N * (N / 32));
   const int64_t nc = chunk_bound(N, S);
-  const int64_t next = N * 8 + (1 + 2 * S) * 4 + nc * 4 + nc * 4 + 8;
+  const int64_t next = N * 8 + (1 + 2 * S) * 4 + nc * 4 + nc * 4 + 8 + nc * 4 + pad8(2 + 2 * S);
   dims[0] = N; dims[1] = S; dims[2] = t.R; dims[3] = L2; dims[4] = t.Lr; dims[5] = t.Nreal;
   dims[6] = 2 * n64 + S;   // int64 elements
   dims[7] = n32;           // int32 elements
@@ -218,7 +222,9 @@ extern "C" int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, con
   int32_t* chunks = nodes + (1 + 2 * S) * 4;
   int32_t* steps = chunks + nc_max * 4;
   int32_t* meta = steps + nc_max * 4;
-  std::fill(ext32, meta + 8, 0);
+  int32_t* lsteps = meta + 8;
+  int32_t* lwalks = lsteps + nc_max * 4;
+  std::fill(ext32, lwalks + pad8(2 + 2 * S), 0);
   for (int64_t n = 0; n < N; ++n) {
     int32_t* k = krange + n * 8;
     const int32_t nd = node[n];
@@ -280,5 +286,37 @@ extern "C" int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, con
   meta[0] = static_cast<int32_t>(nc); meta[1] = static_cast<int32_t>(ns); meta[2] = static_cast<int32_t>(Lr);
   meta[3] = static_cast<int32_t>(R); meta[4] = static_cast<int32_t>(S);
   meta[6] = 0; meta[7] = static_cast<int32_t>(ns);  // walk_ptr of the single depth-first walk
+  // ---- the same chunks as three levels of independent walks (root | question stems | leaves). A walk starts from the
+  //      exported end state of its parent node (state slot 0 = root, 1 + r = question r) and exports its own end state if
+  //      it has children. Walk w of level 1 is question w (w < R), of level 2 leaf w; unused walks are empty.
+  {
+    int64_t ls = 0;
+    auto emit_walk = [&](int64_t node_i, int64_t parent_slot, int64_t own_slot) {
+      for (int64_t j = 0; j < c_count[node_i]; ++j) {
+        lsteps[ls * 4 + 0] = static_cast<int32_t>(c_first[node_i] + j);
+        lsteps[ls * 4 + 1] = j == 0 ? (parent_slot >= 0 ? 4 : 1) : 0;
+        lsteps[ls * 4 + 2] = 0;
+        int32_t aux = 0;
+        if (j == 0 && parent_slot >= 0) aux |= static_cast<int32_t>(parent_slot + 1) << 16;
+        if (j == c_count[node_i] - 1 && own_slot >= 0) aux |= static_cast<int32_t>(own_slot + 1);
+        lsteps[ls * 4 + 3] = aux;
+        ++ls;
+      }
+    };
+    const int64_t root_slot = c_count[0] > 0 ? 0 : -1;
+    int64_t w = 0;
+    lwalks[w++] = 0;
+    emit_walk(0, -1, 0);
+    lwalks[w++] = static_cast<int32_t>(ls);                  // end of level 0
+    for (int64_t r = 0; r < S; ++r) {                         // level 1: S walk slots, the first R used
+      if (r < R) emit_walk(1 + r, root_slot, 1 + r);
+      lwalks[w++] = static_cast<int32_t>(ls);
+    }
+    for (int64_t c = 0; c < S; ++c) {                         // level 2
+      const int64_t r = groups[c];
+      emit_walk(1 + R + c, c_count[1 + r] > 0 ? 1 + r : root_slot, -1);
+      lwalks[w++] = static_cast<int32_t>(ls);
+    }
+  }
   return OJB_OK;
 }

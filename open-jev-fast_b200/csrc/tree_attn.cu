@@ -1,7 +1,8 @@
 // Ancestor-masked (prefix-tree) GQA flash attention with the sigmoid output gate fused in.
 //
-// One CTA = (kv head, group of GQ query heads, 16 query rows); one warp per query head, all warps sharing the K / V tiles
-// of their kv head. Keys are visited in blocks of 32; a block is skipped when none of the 16 rows can see any of its keys.
+// One CTA = (kv head, group of GQ query heads, 16 query rows); two warps per query head, each taking every other visible key
+// block (their partial softmax states are merged through shared memory at the end), all warps sharing the K / V tiles of
+// their kv head. Keys are visited in blocks of 32; a block is skipped when none of the 16 rows can see any of its keys.
 // The mask comes either from the packed visibility words vbits[N, N/32] of the reference layout or from three half-open
 // key ranges per row (root, own question stem, own leaf up to the row itself) — the second form needs O(N) memory instead
 // of O(N^2). Q K^T and P V run on the tensor cores (mma.sync m16n8k16 bf16, fp32 accumulate), the softmax is the online
@@ -13,6 +14,7 @@ namespace {
 
 constexpr int kRows = 16;     // query rows per CTA
 constexpr int kKeys = 32;     // keys per block = one visibility word
+constexpr int kSplit = 2;     // warps per query head, interleaved over the visible key blocks
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -42,23 +44,24 @@ __device__ __forceinline__ uint32_t range_word(int lo, int hi, int kb) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(384)
 tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, const bf16_t* __restrict__ vt,
                  const bf16_t* __restrict__ gate, const int32_t* __restrict__ vbits, const int32_t* __restrict__ krange,
                  bf16_t* __restrict__ y, int N, int HQ, int HKV, int GQ, float scale_log2e) {
   constexpr int kLd = D + 8;                    // padded shared-memory row (bf16)
-  const int nwarps = GQ;
+  const int nheads = GQ;                        // query heads of this CTA; warp = split * GQ + head
   const int G = HQ / HKV;                       // query heads per kv head
   const int groups = G / GQ;
   const int kvh = blockIdx.x / groups, grp = blockIdx.x - kvh * groups;
   const int r0 = blockIdx.y * kRows;
   const int NW = N >> 5;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nthreads = nwarps * 32;
+  const int nthreads = nheads * kSplit * 32;
+  const int head = warp % nheads, split = warp / nheads;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16_t* Qs = reinterpret_cast<bf16_t*>(smem_raw);          // [GQ][16][kLd]
-  bf16_t* KV = Qs + nwarps * kRows * kLd;                     // 2 stages x (K [32][kLd] | V [32][kLd])
-  uint32_t* words = reinterpret_cast<uint32_t*>(KV + 4 * kKeys * kLd);   // [16][NW] visibility words of the 16 rows
+  bf16_t* KV = Qs + nheads * kRows * kLd;                     // 2 stages x kSplit key blocks x (K [32][kLd] | V [32][kLd])
+  uint32_t* words = reinterpret_cast<uint32_t*>(KV + 2 * kSplit * 2 * kKeys * kLd);   // [16][NW] visibility words
   int* vis_list = reinterpret_cast<int*>(words + kRows * NW);            // visible key blocks, then their count at [NW]
 
   // ---- visibility words of this row block
@@ -75,7 +78,7 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
   }
   // ---- Q rows of the GQ heads -> shared memory
   const int hq0 = kvh * G + grp * GQ;
-  for (int i = tid; i < nwarps * kRows * (D / 8); i += nthreads) {
+  for (int i = tid; i < nheads * kRows * (D / 8); i += nthreads) {
     const int w = i / (kRows * (D / 8)), rem = i - w * (kRows * (D / 8));
     const int r = rem / (D / 8), cv = (rem - r * (D / 8)) * 8;
     *reinterpret_cast<uint4*>(Qs + (w * kRows + r) * kLd + cv) =
@@ -100,17 +103,24 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
 
   const bf16_t* kbase = kt + static_cast<int64_t>(kvh) * N * D;
   const bf16_t* vbase = vt + static_cast<int64_t>(kvh) * N * D;
-  auto prefetch = [&](int stage, int kb) {
-    bf16_t* ks = KV + stage * (2 * kKeys * kLd);
-    bf16_t* vs = ks + kKeys * kLd;
-    for (int i = tid; i < 2 * kKeys * (D / 8); i += nthreads) {
-      const int which = i / (kKeys * (D / 8)), rem = i - which * (kKeys * (D / 8));
-      const int r = rem / (D / 8), cv = (rem - r * (D / 8)) * 8;
-      const bf16_t* src = (which ? vbase : kbase) + static_cast<int64_t>(kb * kKeys + r) * D + cv;
-      cp_async16(smem_u32((which ? vs : ks) + r * kLd + cv), src);
+  // stage = kSplit consecutive entries of the visible-block list, one per split
+  auto prefetch = [&](int stage, int it) {
+    for (int sp = 0; sp < kSplit; ++sp) {
+      const int li = it * kSplit + sp;
+      if (li >= nvis) break;
+      const int kb = vis_list[li];
+      bf16_t* ks = KV + (stage * kSplit + sp) * (2 * kKeys * kLd);
+      bf16_t* vs = ks + kKeys * kLd;
+      for (int i = tid; i < 2 * kKeys * (D / 8); i += nthreads) {
+        const int which = i / (kKeys * (D / 8)), rem = i - which * (kKeys * (D / 8));
+        const int r = rem / (D / 8), cv = (rem - r * (D / 8)) * 8;
+        const bf16_t* src = (which ? vbase : kbase) + static_cast<int64_t>(kb * kKeys + r) * D + cv;
+        cp_async16(smem_u32((which ? vs : ks) + r * kLd + cv), src);
+      }
     }
   };
-  if (nvis > 0) prefetch(0, vis_list[0]);
+  const int niter = (nvis + kSplit - 1) / kSplit;
+  if (niter > 0) prefetch(0, 0);
   cp_async_commit();
 
   float o[D / 8][4];
@@ -120,18 +130,20 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
     for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
   float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
   const int gr = lane >> 2, tc = (lane & 3) * 2;
-  const bf16_t* Qw = Qs + warp * kRows * kLd;
+  const bf16_t* Qw = Qs + head * kRows * kLd;
   const int a_row = lane & 15, a_col = (lane >> 4) * 8;
   const int b_row = (lane & 7) + ((lane >> 4) << 3), b_col = ((lane >> 3) & 1) * 8;
   const int bt_row = lane & 15, bt_col = (lane >> 4) * 8;
 
-  for (int it = 0; it < nvis; ++it) {
-    const int kb = vis_list[it];
-    if (it + 1 < nvis) prefetch((it + 1) & 1, vis_list[it + 1]);
+  for (int it = 0; it < niter; ++it) {
+    if (it + 1 < niter) prefetch((it + 1) & 1, it + 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const bf16_t* ks = KV + (it & 1) * (2 * kKeys * kLd);
+    const int li = it * kSplit + split;
+    if (li < nvis) {
+    const int kb = vis_list[li];
+    const bf16_t* ks = KV + ((it & 1) * kSplit + split) * (2 * kKeys * kLd);
     const bf16_t* vs = ks + kKeys * kLd;
     // ---- S = Q K^T  (16 x 32)
     float s[4][4];
@@ -205,11 +217,41 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
         mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
       }
     }
+    }
     __syncthreads();   // the stage is free for the prefetch issued in the next iteration
   }
   cp_async_wait<0>();
+  // ---- merge the partial softmax states of the two splits of a head (split 1 hands over through the K / V buffers)
+  {
+    float* xch = reinterpret_cast<float*>(KV) + static_cast<size_t>(head) * (32 * (D / 2 + 4));
+    if (split == 1) {
+#pragma unroll
+      for (int nt = 0; nt < D / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xch[(nt * 4 + e) * 32 + lane] = o[nt][e];
+      xch[(D / 2 + 0) * 32 + lane] = m_run[0];
+      xch[(D / 2 + 1) * 32 + lane] = m_run[1];
+      xch[(D / 2 + 2) * 32 + lane] = l_run[0];
+      xch[(D / 2 + 3) * 32 + lane] = l_run[1];
+    }
+    __syncthreads();
+    if (split == 1) return;
+    float f0[2], f1[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float m1 = xch[(D / 2 + h) * 32 + lane], l1 = xch[(D / 2 + 2 + h) * 32 + lane];
+      const float m = fmaxf(m_run[h], m1);
+      f0[h] = exp2f(m_run[h] - m);
+      f1[h] = exp2f(m1 - m);
+      l_run[h] = l_run[h] * f0[h] + l1 * f1[h];
+    }
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[nt][e] = o[nt][e] * f0[e >> 1] + xch[(nt * 4 + e) * 32 + lane] * f1[e >> 1];
+  }
   // ---- y = bf16(bf16(O / l) * bf16(sigmoid(gate)))
-  const int hq = hq0 + warp;
+  const int hq = hq0 + head;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = r0 + gr + h * 8;
@@ -230,7 +272,7 @@ int launch_attn(const void* qt, const void* kt, const void* vt, const void* gate
                 void* y, int64_t N, int64_t HQ, int64_t HKV, int64_t GQ, float scale, cudaStream_t st) {
   constexpr int kLd = D + 8;
   const int NW = static_cast<int>(N / 32);
-  const size_t smem = (GQ * kRows * kLd + 4 * kKeys * kLd) * 2 + kRows * NW * 4 + (NW + 1) * 4;
+  const size_t smem = (GQ * kRows * kLd + 2 * kSplit * 2 * kKeys * kLd) * 2 + kRows * NW * 4 + (NW + 1) * 4;
   if (smem > 227 * 1024) return OJB_ERR_LIMIT;
   auto kern = tree_attn_kernel<D>;
   static size_t smem_set = 0;
@@ -241,7 +283,7 @@ int launch_attn(const void* qt, const void* kt, const void* vt, const void* gate
   }
   const int G = static_cast<int>(HQ / HKV);
   dim3 grid(static_cast<unsigned>(HKV * (G / GQ)), static_cast<unsigned>(N / kRows));
-  kern<<<grid, static_cast<unsigned>(GQ * 32), smem, st>>>(static_cast<const bf16_t*>(qt), static_cast<const bf16_t*>(kt),
+  kern<<<grid, static_cast<unsigned>(GQ * kSplit * 32), smem, st>>>(static_cast<const bf16_t*>(qt), static_cast<const bf16_t*>(kt),
                                                           static_cast<const bf16_t*>(vt), static_cast<const bf16_t*>(gate), vbits,
                                                           krange, static_cast<bf16_t*>(y), static_cast<int>(N), static_cast<int>(HQ),
                                                           static_cast<int>(HKV), static_cast<int>(GQ), scale * 1.4426950408889634f);

@@ -237,6 +237,25 @@ def gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walk_ptr, n_walks, init_
     return out
 
 
+def gdn_tree_levels(q, k, v, g, beta, scale, lay, out, states=None):
+    """Tree-native pass with the state recurrence run level by level (root, question stems, leaves as three launches whose
+    walks run side by side). q, k [N, HK, 128], v [N, HV, 128]; `out` [N, HV, 128] is written for real rows only; `states`
+    fp32 [1 + S, HV, 128, 128] receives the end state of the root (slot 0) and of question r (slot 1 + r)."""
+    _chk(q, k, v, g, beta, out, states)
+    N, HV = v.shape[0], v.shape[1]
+    HK, S = k.shape[1], lay.S
+    if states is None:
+        states = torch.empty(1 + S, HV, 128, 128, dtype=torch.float32, device=v.device)
+    nch = lay.chunks.shape[0]
+    nbytes = _lib.lib().ojb_gdn_scratch_bytes
+    nbytes.restype = _lib.ctypes.c_int64
+    scratch = torch.empty(nbytes(i64(nch), i64(HV)), dtype=torch.uint8, device=v.device)
+    levels = (_lib.ctypes.c_int32 * 4)(0, 1, 1 + S, 1 + 2 * S)
+    call("ojb_gdn_chunked_levels", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(lay.chunks), i64(nch), ptr(lay.lsteps),
+         ptr(lay.lwalks), levels, i64(3), ptr(states), ptr(scratch), ptr(out), i64(HK), i64(HV), f32(scale), stream_ptr())
+    return out, states
+
+
 def gdn_fused6(q, k, v, g, beta, scale):
     """src/ext.py:34 — q, k [B,T,HK,128], v [B,T,HV,128], g f32 / beta [B,T,HV] -> o [B,T,HV,128]; zero initial state,
     rows of the last partial chunk beyond T do not exist, pad slots inside T produce zeros only if their inputs are."""

@@ -36,6 +36,7 @@ FATTN = int(os.environ.get("OJ_FATTN", "6"))               # query heads per CTA
 FATTN_MAX = int(os.environ.get("OJ_FATTN_MAX", "1000000000"))   # kept for compatibility: the kernel serves every N
 GDN_FUSED, GDN_VER, PREP, GVA, LUT, SK2 = True, 6, "dedup", True, True, True
 TREE_NATIVE = os.environ.get("OJ_TREE_NATIVE", "1") == "1"      # 0: replicated per-candidate GDN layout of the reference
+TREE_LEVELS = os.environ.get("OJ_TREE_LEVELS", "1") == "1"      # 1: state pass per tree level (3 launches), 0: one depth-first walk
 
 
 class _Layer(SimpleNamespace):
@@ -151,8 +152,16 @@ class FastQwen35(torch.nn.Module):
         if TREE_NATIVE and hasattr(lay, "chunks"):
             q, k, v, g, beta = K.linattn_prep_rows(proj, lay.hist, d.convw, d.A_log, d.dt_bias, d.KD, d.VD, d.HV, d.HK, d.HD)
             o = self._zero_buf("gdn_o", (N, d.HV, d.HD), proj.device)
-            K.gdn_chunked(q.view(N, d.HK, d.HD), k.view(N, d.HK, d.HD), v.view(N, d.HV, d.HD), g, beta, d.HD ** -0.5,
-                          lay.chunks, lay.steps, lay.walk_ptr, lay.n_walks, None, None, o)
+            if hasattr(lay, "lsteps") and TREE_LEVELS:
+                st = self._bufs.get(("gdn_states", lay.S, d.HV))
+                if st is None:
+                    st = self._bufs[("gdn_states", lay.S, d.HV)] = torch.empty(1 + lay.S, d.HV, d.HD, d.HD, dtype=torch.float32,
+                                                                              device=proj.device)
+                K.gdn_tree_levels(q.view(N, d.HK, d.HD), k.view(N, d.HK, d.HD), v.view(N, d.HV, d.HD), g, beta, d.HD ** -0.5,
+                                  lay, o, st)
+            else:
+                K.gdn_chunked(q.view(N, d.HK, d.HD), k.view(N, d.HK, d.HD), v.view(N, d.HV, d.HD), g, beta, d.HD ** -0.5,
+                              lay.chunks, lay.steps, lay.walk_ptr, lay.n_walks, None, None, o)
             return K.gated_rmsnorm(o, proj, d.normw, d.HV, d.HD, 2 * d.KD + d.VD, d.norm_eps)
         # the reference's route: every candidate path replicated, one sequence per candidate (src/fastmodel.py:420-454)
         S, L2 = lay.S, lay.L2
@@ -196,6 +205,22 @@ class FastQwen35(torch.nn.Module):
         """Forward + scoring head: fp32 [S, A] (src/server.py:37 `head(forward_gtree(ids, lay).float())`)."""
         hn = self.forward_gtree(ids, lay, return_all=True)
         return K.score_head(hn, lay.lastidx, head_w, head_b)
+
+    # ------------------------------------------------------------------------------------------------ single-level tree
+    def tree_layout(self, pre_ids, suf_ids, suf_mask, pad=0):
+        """src/fastmodel.py:247-264: layout of [prefix | S suffixes] with `pad` left-padding rows in the prefix."""
+        return _layout.tree_layout(pre_ids, suf_ids, suf_mask, pad)
+
+    @torch.no_grad()
+    def forward_tree(self, pre_ids, suf_ids, lay, fla_mode="state"):
+        """src/fastmodel.py:266-314: long shared prefix, S suffixes -> [S, H]. Both modes of the reference ("replicate" and
+        "state") give the same result; here the prefix is always computed once and its Gated DeltaNet state handed to every
+        suffix inside the state kernel."""
+        ids = torch.zeros(lay.N32, dtype=pre_ids.dtype, device=pre_ids.device)
+        ids[:lay.N] = torch.cat([pre_ids, suf_ids.reshape(-1)])
+        inner = SimpleNamespace(N=lay.N32, S=lay.S, pos=lay.pos32, rowmask=lay.rowmask32, hist=lay.hist, krange=lay.krange,
+                                chunks=lay.chunks, steps=lay.steps, walk_ptr=lay.walk_ptr, n_walks=1, lastidx=lay.lastidx)
+        return self.forward_gtree(ids, inner)
 
     # ------------------------------------------------------------------------------------------------ batch forward
     @torch.no_grad()

@@ -56,13 +56,13 @@ def field_views(d, g64, g32, e32):
     sizes = [S * L2, N, N + 2, S * L2, (N + 1) * 4, S * L2, N, N * (N // 32)]
     o = np.cumsum([0] + [_pad8(x) for x in sizes])
     v = lambda k: g32[o[k]:o[k] + sizes[k]]
-    eo = np.cumsum([0, N * 8, (1 + 2 * S) * 4, cap * 4, cap * 4, 8])
+    eo = np.cumsum([0, N * 8, (1 + 2 * S) * 4, cap * 4, cap * 4, 8, cap * 4, _pad8(2 + 2 * S)])
     e = lambda k: e32[eo[k]:eo[k + 1]]
     return dict(ids=g64[:N], pos=g64[n64:n64 + N], lastidx=g64[2 * n64:2 * n64 + S],
                 src=v(0).view(S, L2), inv=v(1), rep_ptr=v(2), rep_pos=v(3), hist=v(4).view(N + 1, 4), canon=v(5),
                 rowmask=v(6), vbits=v(7).view(N, N // 32),
                 krange=e(0).view(N, 8), nodes=e(1).view(1 + 2 * S, 4), chunks=e(2).view(cap, 4), steps=e(3).view(cap, 4),
-                meta=e(4))
+                meta=e(4), lsteps=e(5).view(cap, 4), lwalks=e(6)[:2 + 2 * S])
 
 
 def dense_masks(vbits):
@@ -131,3 +131,71 @@ def batch_layout(attention_mask, dev):
     return SimpleNamespace(N=N, S=B, L2=T, pos=torch.as_tensor(pos).to(dev), rowmask=t32(rowmask), hist=t32(hist),
                            krange=t32(krange), chunks=t32(chunks), steps=t32(steps), walk_ptr=t32(walks), n_walks=B,
                            lastidx=torch.as_tensor(last).to(dev))
+
+
+def tree_layout(pre_ids, suf_ids, suf_mask, pad=0):
+    """Single-level tree [prefix | S suffixes of Ls rows] of FastQwen35.tree_layout (src/fastmodel.py:247-264): the same
+    fields (Lp, S, Ls, N, pos, amask, rowmask, lastidx, repidx) plus the tables the kernels here consume (hist, krange,
+    chunks, steps, walk_ptr). The first `pad` prefix rows are left padding. Rows are padded up to a multiple of 32 (N32)."""
+    dev = suf_ids.device
+    Lp = int(pre_ids.shape[0])
+    S, Ls = (int(x) for x in suf_ids.shape)
+    m = suf_mask.detach().cpu().numpy().astype(bool)
+    N = Lp + S * Ls
+    N32 = -(-N // 32) * 32
+    pos = np.zeros(N32, np.int64)
+    rowmask = np.zeros(N32, np.int32)
+    hist = np.full((N32 + 1, 4), -1, np.int32)
+    krange = np.zeros((N32, 8), np.int32)
+    for n in range(N32):
+        krange[n, 3], krange[n, 4] = n, n + 1                      # default: a row sees only itself
+    # positions follow the reference for every row, padding included: prefix t - pad, suffix t + (Lp - pad)
+    pos[:Lp] = np.arange(Lp) - pad
+    for s in range(S):
+        pos[Lp + s * Ls: Lp + (s + 1) * Ls] = np.arange(Ls) + (Lp - pad)
+    for n in range(pad, Lp):
+        rowmask[n] = 1
+        krange[n, 3], krange[n, 4] = pad, n + 1
+        for i in range(4):
+            if n - 3 + i >= pad:
+                hist[n, i] = n - 3 + i
+    lens = m.sum(1)
+    for s in range(S):
+        for t in range(int(lens[s])):
+            n = Lp + s * Ls + t
+            rowmask[n] = 1
+            krange[n, 1], krange[n, 2] = pad, Lp
+            krange[n, 3], krange[n, 4] = Lp + s * Ls, n + 1
+            path = list(range(pad, Lp)) + list(range(Lp + s * Ls, n + 1))
+            for i in range(4):
+                if len(path) - 4 + i >= 0:
+                    hist[n, i] = path[len(path) - 4 + i]
+    chunks, steps, walks = [], [], [0]
+    for j in range(pad, Lp, 64):
+        steps.append([len(chunks), 1 if j == pad else 0, 0, 0])
+        chunks.append([j, min(64, Lp - j), 0, 0])
+    if steps:
+        steps[-1][2] = 1                                            # park the prefix state in slot A
+    for s in range(S):
+        for j in range(0, int(lens[s]), 64):
+            steps.append([len(chunks), (2 if Lp > pad else 1) if j == 0 else 0, 0, 0])
+            chunks.append([Lp + s * Ls + j, min(64, int(lens[s]) - j), 0, 0])
+    walks.append(len(steps))
+    if not chunks:
+        chunks, steps = [[0, 0, 0, 0]], [[0, 1, 0, 0]]
+    # dense mask with the reference's semantics for every row (rows that are padding still see valid earlier keys of their
+    # own segment and of the prefix); the kernels read krange, where padding rows see only themselves
+    seg = np.concatenate([np.zeros(Lp, np.int64), np.repeat(np.arange(1, S + 1), Ls)])
+    tp = np.concatenate([np.arange(Lp), np.tile(np.arange(Ls), S)])
+    valid = np.concatenate([np.arange(Lp) >= pad, m.reshape(-1)])
+    earlier = tp[None, :] <= tp[:, None]
+    from_prefix = (seg[None, :] == 0) & ((seg[:, None] != 0) | earlier)
+    same_suffix = (seg[None, :] == seg[:, None]) & (seg[:, None] != 0) & earlier
+    vis = ((from_prefix | same_suffix) & valid[None, :]) | np.eye(N, dtype=bool)
+    t32 = lambda a: torch.as_tensor(np.asarray(a, np.int32)).to(dev)
+    lastidx = np.array([Lp + s * Ls + int(lens[s]) - 1 for s in range(S)], np.int64)
+    repidx = np.array([[p if p < Lp else Lp + s * Ls + (p - Lp) for p in range(Lp + Ls)] for s in range(S)], np.int64)
+    return SimpleNamespace(Lp=Lp, S=S, Ls=Ls, N=N, N32=N32, pos=torch.as_tensor(pos[:N]).to(dev), pos32=torch.as_tensor(pos).to(dev),
+                           amask=torch.as_tensor(vis).to(dev)[None, None], rowmask=t32(rowmask[:N]), rowmask32=t32(rowmask),
+                           lastidx=torch.as_tensor(lastidx).to(dev), repidx=torch.as_tensor(repidx).to(dev), hist=t32(hist),
+                           krange=t32(krange), chunks=t32(chunks), steps=t32(steps), walk_ptr=t32(walks), n_walks=1)

@@ -88,6 +88,15 @@ def test_gdn_tree_native_matches_per_path_recurrence(name):
     real = lay.rowmask.cpu().bool()
     assert _rel(o[real.cuda()], ref[real]) < 4e-3
     assert float(o[~real.cuda()].float().abs().max()) == 0.0 if (~real).any() else True
+    # the level-parallel state pass (root | stems | leaves, three launches) gives the same rows, and exports the root state
+    o_lv = torch.zeros_like(o)
+    _, states = K.gdn_tree_levels(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), scale, lay, o_lv)
+    torch.cuda.synchronize()
+    assert torch.equal(o_lv, o)
+    if lay.Lr > 0:
+        root = slice(0, lay.Lr)
+        _, ref_root = OG.recurrent(q[root], k[root], v[root], g[root], beta[root], scale)
+        assert _rel(states[0], ref_root) < 1e-2
     # the replicated-layout op on the same tree gives the same rows (two routes to one result)
     src = lay.src.cpu()
     rep = [O.scatter_slots(x, src) for x in (q, k, v, g, beta)]

@@ -81,6 +81,26 @@ def test_extension_tables(name):
             assert parent >= 0
         done_nodes.add(node)
     assert len(seen) == nc
+    # level tables: every chunk once; a walk that loads a slot finds it exported by a walk of an earlier level
+    S = d["S"]
+    lw = f["lwalks"]
+    assert lw[0] == 0 and lw[1 + 2 * S] == nc and all(lw[i] <= lw[i + 1] for i in range(1 + 2 * S))
+    exported, seen = set(), set()
+    for lo, hi in ((0, 1), (1, 1 + S), (1 + S, 1 + 2 * S)):
+        new = set()
+        for w in range(lo, hi):
+            for s_ in range(lw[w], lw[w + 1]):
+                chunk, load, save, aux = f["lsteps"][s_]
+                assert chunk not in seen and save == 0
+                seen.add(chunk)
+                first = s_ == lw[w]
+                assert load == (0 if not first else (4 if (aux >> 16) else 1))
+                if aux >> 16:
+                    assert (aux >> 16) - 1 in exported
+                if aux & 0xffff:
+                    new.add((aux & 0xffff) - 1)
+        exported |= new
+    assert len(seen) == nc
 
 
 def test_rejects_bad_requests():

@@ -106,3 +106,29 @@ def test_batch_forward_matches_reference_path():
         ref = OH.all_hidden(oracle, ids[i, :l].tolist())
         rel = ((out[i, :l] - ref).norm() / ref.norm()).item()
         assert rel < 4e-2, (i, rel)      # bf16 run of a narrow 8-layer model against fp32 (its own bf16 run loses ~3e-2)
+
+
+def test_single_level_tree_with_left_padding():
+    """FastQwen35.tree_layout / forward_tree (long shared prefix with state hand-off): layout fields against the reference's
+    goldens, hidden states against the per-candidate reference path."""
+    import numpy as np
+    import os
+    from ojb200 import fastmodel as FM
+    cfg, core = _small_model(seed=4)
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "layout_golden.npz"))
+    name = "st_small"
+    pre, suf, msk, pad = trees.state_cases()[name]
+    pre = [t % cfg.vocab_size for t in pre]
+    suf = [[t % cfg.vocab_size for t in r] for r in suf]
+    oracle = OH.prepare(core, upcast=True)
+    fast = FM.FastQwen35(core.to("cuda"))
+    pre_t, suf_t, msk_t = (torch.tensor(x).cuda() for x in (pre, suf, msk))
+    lay = fast.tree_layout(pre_t, suf_t, msk_t, pad=pad)
+    for f in ("pos", "rowmask", "lastidx", "repidx"):
+        assert np.array_equal(getattr(lay, f).cpu().numpy(), gold[f"{name}/{f}"]), f
+    assert np.array_equal(np.packbits(lay.amask[0, 0].cpu().numpy(), axis=1, bitorder="little"), gold[f"{name}/amask"])
+    out = fast.forward_tree(pre_t, suf_t, lay).float().cpu()
+    seqs = [pre[pad:] + [t for t, k in zip(r, mk) if k] for r, mk in zip(suf, msk)]
+    ref = OH.candidate_hidden(oracle, seqs)
+    rel = ((out - ref).norm() / ref.norm()).item()
+    assert rel < 4e-2, rel
