@@ -395,6 +395,8 @@ constexpr int kLdA = kChunk + 8;        // padded row (bf16) of the [64 x 64] ti
 constexpr int kStateThreads = 128;
 constexpr int kBufElems = 3 * kChunk * kLd + kChunk * kLdS + kChunk * kLdA;  // w | qg | kg | u-slice | Aqk
 constexpr int kStateSmem = 2 * kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 2 * kStateThreads * 32 * 4 + 16;
+// lean form for many short walks: one operand buffer, no parking slots -> two CTAs per SM
+constexpr int kStateSmemLean = kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 16;
 
 __device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, int dv0, int tid) {
   // w, qg, kg: [64][128] each
@@ -418,6 +420,7 @@ __device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, 
 
 // steps[s] = (chunk, load, save, aux): load 0 carry on / 1 zero / 2 slot A / 3 slot B / 4 initial state aux>>16 - 1;
 // save bit 0 slot A, bit 1 slot B; (aux & 0xffff) - 1 = index of a final-state output written after the step.
+template <bool LEAN>
 __global__ void __launch_bounds__(kStateThreads)
 gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__ chunks, const int32_t* __restrict__ steps,
                  const int32_t* __restrict__ walk_ptr, const float* __restrict__ init_state, float* __restrict__ final_state,
@@ -427,7 +430,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
   if (s_begin >= s_end) return;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16_t* bufs = reinterpret_cast<bf16_t*>(smem_raw);
-  bf16_t* Sb = bufs + 2 * kBufElems;              // bf16 copy of the state slice [128 dk][32 dv]
+  bf16_t* Sb = bufs + (LEAN ? 1 : 2) * kBufElems;  // bf16 copy of the state slice [128 dk][32 dv]
   bf16_t* Vn = Sb + kHD * kLdS;                   // v' [64][32]
   float* slots = reinterpret_cast<float*>(Vn + kChunk * kLdS);   // [2][32 regs][128 threads]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -447,15 +450,21 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     const int c = steps[s * 4];
     return scratch + (static_cast<int64_t>(c) * HV + h) * kItemElems;
   };
-  state_prefetch(bufs, item_of(s_begin), dv0, tid);
-  cp_async_commit();
+  if constexpr (!LEAN) {
+    state_prefetch(bufs, item_of(s_begin), dv0, tid);
+    cp_async_commit();
+  }
 
   for (int s = s_begin; s < s_end; ++s) {
     const int4 st = reinterpret_cast<const int4*>(steps)[s];
     const int4 ch = reinterpret_cast<const int4*>(chunks)[st.x];
-    bf16_t* buf = bufs + ((s - s_begin) & 1) * kBufElems;
+    bf16_t* buf = LEAN ? bufs : bufs + ((s - s_begin) & 1) * kBufElems;
     const bf16_t* item = item_of(s);
-    if (s + 1 < s_end) state_prefetch(bufs + ((s + 1 - s_begin) & 1) * kBufElems, item_of(s + 1), dv0, tid);
+    if constexpr (LEAN) {
+      state_prefetch(buf, item, dv0, tid);
+    } else {
+      if (s + 1 < s_end) state_prefetch(bufs + ((s + 1 - s_begin) & 1) * kBufElems, item_of(s + 1), dv0, tid);
+    }
     cp_async_commit();
 
     // ---- choose the incoming state
@@ -466,7 +475,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
         for (int b = 0; b < 4; ++b)
 #pragma unroll
           for (int e = 0; e < 4; ++e) S[a][b][e] = 0.f;
-    } else if (st.y == 2 || st.y == 3) {
+    } else if (!LEAN && (st.y == 2 || st.y == 3)) {
       const float* sl = slots + (st.y - 2) * (32 * kStateThreads);
 #pragma unroll
       for (int a = 0; a < 2; ++a)
@@ -496,7 +505,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
           const int dk = warp * 32 + a * 16 + gr + half * 8;
           *reinterpret_cast<uint32_t*>(Sb + dk * kLdS + b * 8 + tc) = pack2(S[a][b][half * 2], S[a][b][half * 2 + 1]);
         }
-    cp_async_wait<1>();   // this step's operands have landed (the prefetch of the next step may still be in flight)
+    if constexpr (LEAN) cp_async_wait<0>(); else cp_async_wait<1>();   // this step's operands have landed (a prefetch of the next step may still be in flight)
     __syncthreads();
 
     const bf16_t* Ws = buf;
@@ -596,7 +605,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
       }
     }
     // ---- park / export the state
-    if (st.z & 3) {
+    if (!LEAN && (st.z & 3)) {
 #pragma unroll
       for (int sl = 0; sl < 2; ++sl)
         if (st.z & (1 << sl)) {
@@ -706,7 +715,7 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
+        cudaFuncSetAttribute(gdn_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
       return OJB_ERR_LAUNCH;
     attr = true;
   }
@@ -714,7 +723,7 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
-  gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
+  gdn_state_kernel<false><<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
       static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out),
       static_cast<int>(HV));
   return launch_status(cudaGetLastError());
@@ -763,7 +772,7 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_gdn_static_scratch) != cudaSuccess || p == nullptr) return OJB_ERR_LAUNCH;
     if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
+        cudaFuncSetAttribute(gdn_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
       return OJB_ERR_LAUNCH;
     g_static_scratch_addr[dev] = p;
   }
@@ -775,7 +784,7 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, scratch, static_cast<int>(HK), static_cast<int>(HV), scale);
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
-  gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
+  gdn_state_kernel<false><<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
       scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
   return launch_status(cudaGetLastError());
 }
@@ -796,7 +805,8 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(gdn_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
+        cudaFuncSetAttribute(gdn_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(gdn_state_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmemLean) != cudaSuccess)
       return OJB_ERR_LAUNCH;
     attr = true;
   }
@@ -807,9 +817,15 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
   for (int64_t l = 0; l < n_levels; ++l) {
     const int nw = levels[l + 1] - levels[l];
     if (nw == 0) continue;
-    gdn_state_kernel<<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(nw)), kStateThreads, kStateSmem, st>>>(
-        static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
-        static_cast<int>(HV));
+    if (nw > 1) {   // many short walks: the lean form fits two CTAs per SM
+      gdn_state_kernel<true><<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(nw)), kStateThreads, kStateSmemLean, st>>>(
+          static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
+          static_cast<int>(HV));
+    } else {
+      gdn_state_kernel<false><<<dim3(static_cast<unsigned>(HV), kHD / kDv, 1), kStateThreads, kStateSmem, st>>>(
+          static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
+          static_cast<int>(HV));
+    }
     if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   }
   return OJB_OK;
