@@ -24,9 +24,9 @@ int dispatch(int epi, int variant, const void* x, const void* w, void* out, int6
   if (variant == 0) {
     const int64_t r = M % 256;
     const bool short_tail_on_blocks = M > 256 && r > 0 && r <= 128;
-    if (short_tail_on_blocks) {
+    if (short_tail_on_blocks && (N < 16384 || M < 512)) {
       const int64_t tiles256 = ceil_div(M, 128) * ceil_div(N, 256) * splits;
-      variant = (epi == kEpiSwiglu || tiles256 >= 100) ? 1 : 2;
+      variant = tiles256 >= 100 ? 1 : 2;
     } else {
       variant = 3;
     }

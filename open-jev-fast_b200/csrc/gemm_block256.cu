@@ -13,7 +13,11 @@
 //   tail unit   the last M mod 256 (<= 128) rows of x with the operands swapped: 256 rows of w are the M side (two MMAs
 //               with M = 128), the x tail is the N side (N = rows rounded up to 16). The tail costs what it is worth
 //               instead of a whole 128-row tile of zero padding; the epilogue writes the transposed accumulator.
-// Units run x-block fastest, then k-split, then w tile, so that CTAs running at the same time share w tiles in L2.
+// Units are ordered x-block fastest, then k-split, then the tail unit of the w tile, then the next w tile, and dealt to the
+// CTAs round-robin: the CTAs that run at the same time work on the same few w tiles, which therefore come from HBM once.
+// (Giving each CTA a contiguous run instead was measured 15-20 % slower: 136 CTAs then stream 136 different w tiles at
+// once, more than the L2 holds, and every unit reads its tile from HBM again.) The grid size is kept coprime with the
+// number of units per w tile so that long block units and short tail units are spread evenly over the CTAs.
 //
 // Every wait on an mbarrier is bounded: after kWaitLimitNs the kernel raises the CTA's abort flag, records
 // OJB_DEV_WAIT_TIMEOUT in the status word, lets copies in flight land, frees its TMEM and returns.
@@ -419,7 +423,12 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
   if (rc != OJB_OK) return rc;
   const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits + (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits : 0);
-  const int grid = static_cast<int>(units < sms ? units : sms);
+  int grid = static_cast<int>(units < sms ? units : sms);
+  if (units > grid && g.tail_rows > 0) {
+    const int group = (g.n_xblk + 1) * splits;   // units per w tile when BN = 256
+    auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
+    while (grid > 1 && gcd(grid, group) != 1) --grid;
+  }
   const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
   kern<<<grid, kGemmThreads, smem, stream>>>(map_x, map_w, map_w256, map_xt, g);
   return launch_status(cudaGetLastError());
