@@ -154,7 +154,7 @@ int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const fl
                            int64_t HV, float scale, ojb_stream_t stream);
 
 /* Scratch-free form of ojb_gdn_chunked. It has no counterpart in open-jev-fast. Same arguments without `scratch`: the
- * per-(chunk, head) work items live in a fixed 72 MiB array inside the library's device image (every GPU that loads the
+ * per-(chunk, head) work items live in a fixed 80 MiB array inside the library's device image (every GPU that loads the
  * library holds it until the process exits), so the call needs no device allocation at all. It is meant for callers that
  * cannot allocate around the call — an inference process whose memory plan is frozen after start-up, or host code that has
  * no allocator for device memory. Limits and rules:

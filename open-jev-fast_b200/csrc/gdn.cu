@@ -8,7 +8,7 @@
 //              16 x 16 blocks; u = T (v beta), w = T (k beta e^G) with T as a bf16 value + remainder pair;
 //              Aqk = tril(q k^T * exp(G_i - G_j)) * scale; qg = q e^G scale; kg = k e^(G_L - G). K K^T, Q K^T and the two
 //              products with T run on the tensor cores (mma.sync bf16, fp32 accumulate).
-//              Results go to a scratch item of 36 872 bf16 per (chunk, head).
+//              Results go to a scratch item of 40 968 bf16 per (chunk, head), laid out as the state pass reads it.
 //   gdn_state  per (value head, 32-column slice of the state, walk): walks the chunks of the tree depth first with the
 //              fp32 state slice [128 x 32] in registers; per chunk v' = u - w S, o = qg S + Aqk v', S = S e^(G_L) + kg^T v'
 //              (mma.sync). The state at the end of the root and of a question stem is parked in shared memory and restored
@@ -22,9 +22,16 @@ namespace {
 
 constexpr int kHD = 128;          // head dim of q, k and v
 constexpr int kChunk = 64;
-constexpr int kItemElems = 4 * kChunk * kHD + kChunk * kChunk + 8;  // w | u | qg | kg | Aqk | (float e^{G_L}, pad)
-constexpr int kOffW = 0, kOffU = kChunk * kHD, kOffQg = 2 * kChunk * kHD, kOffKg = 3 * kChunk * kHD,
-              kOffA = 4 * kChunk * kHD, kOffGl = 4 * kChunk * kHD + kChunk * kChunk;
+// Shared-memory tile shapes (row lengths padded by 8 bf16 = 16 bytes so that ldmatrix rows fall into distinct banks). The
+// scratch item of a (chunk, head) holds its tiles in exactly these padded shapes, so the state pass copies them as flat
+// byte ranges: w | qg | kg | u as four 32-column slices | Aqk | float e^(G_L).
+constexpr int kLd = kHD + 8;            // [64 x 128] tiles: 272-byte rows
+constexpr int kDv = 32;                 // state columns per CTA of the state pass
+constexpr int kLdS = kDv + 8;           // [* x 32] tiles: 80-byte rows
+constexpr int kLdA = kChunk + 8;        // [64 x 64] tile: 144-byte rows
+constexpr int kOffW = 0, kOffQg = kChunk * kLd, kOffKg = 2 * kChunk * kLd, kOffU = 3 * kChunk * kLd,
+              kOffA = kOffU + (kHD / kDv) * kChunk * kLdS, kOffGl = kOffA + kChunk * kLdA;
+constexpr int kItemElems = kOffGl + 8;  // 40 968 bf16 = 81 936 bytes
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
@@ -143,7 +150,6 @@ gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, 
 }
 
 // ----------------------------------------------------------------------------------------------------------- gdn_intra
-constexpr int kLd = kHD + 8;      // padded row length (bf16) of a [64 x 128] tile in shared memory: 272 bytes
 constexpr int kIntraThreads = 256;
 constexpr int kLdT = kChunk + 8;  // padded row (bf16) of the [64 x 64] inverse
 // K | Q | V | KG tiles, A (fp32; later the bf16 pair of T) with the block scratch P behind it, four vectors, T (fp32)
@@ -252,7 +258,7 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
           else o2[e] = j < i ? a * Bs[i] * exp2f(gi - Gs[j]) : 0.f;
         }
         if (is_qk) {
-          *reinterpret_cast<uint32_t*>(item + kOffA + i * kChunk + nt * 8 + tc) = pack2(o2[0], o2[1]);
+          *reinterpret_cast<uint32_t*>(item + kOffA + i * kLdA + nt * 8 + tc) = pack2(o2[0], o2[1]);
         } else {
           As[i * kChunk + nt * 8 + tc] = o2[0];
           As[i * kChunk + nt * 8 + tc + 1] = o2[1];
@@ -371,12 +377,14 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
         mma_bf16(acc[2 * np + 1], l0, l1, l2, l3, b2, b3);
       }
     }
-    bf16_t* dst = item + (is_w ? kOffW : kOffU);
     const int gr = lane >> 2, tc = (lane & 3) * 2;
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) {
-      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr) * kHD + nt * 8 + tc) = pack2(acc[nt][0], acc[nt][1]);
-      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr + 8) * kHD + nt * 8 + tc) = pack2(acc[nt][2], acc[nt][3]);
+      // w keeps its 128 columns in one padded tile, u is stored as four 32-column slices (one per CTA column of the state pass)
+      bf16_t* dst = is_w ? item + kOffW + nt * 8 + tc : item + kOffU + (nt >> 2) * (kChunk * kLdS) + (nt & 3) * 8 + tc;
+      const int ld = is_w ? kLd : kLdS;
+      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr) * ld) = pack2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr + 8) * ld) = pack2(acc[nt][2], acc[nt][3]);
     }
   }
   // ---- copy qg (Qs) and kg (KGs) to the scratch item, 16 bytes per thread
@@ -384,37 +392,39 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
     const int r = rem >> 4, cv = (rem & 15) * 8;
     const bf16_t* srcb = which == 0 ? Qs : KGs;
-    *reinterpret_cast<uint4*>(item + (which == 0 ? kOffQg : kOffKg) + r * kHD + cv) = *reinterpret_cast<const uint4*>(srcb + r * kLd + cv);
+    *reinterpret_cast<uint4*>(item + (which == 0 ? kOffQg : kOffKg) + r * kLd + cv) = *reinterpret_cast<const uint4*>(srcb + r * kLd + cv);
   }
 }
 
 // ----------------------------------------------------------------------------------------------------------- gdn_state
-constexpr int kDv = 32;                 // state columns per CTA
-constexpr int kLdS = kDv + 8;           // padded row (bf16) of [* x 32] tiles: 80 bytes
-constexpr int kLdA = kChunk + 8;        // padded row (bf16) of the [64 x 64] tile: 144 bytes
 constexpr int kStateThreads = 128;
 constexpr int kBufElems = 3 * kChunk * kLd + kChunk * kLdS + kChunk * kLdA;  // w | qg | kg | u-slice | Aqk
 constexpr int kStateSmem = 2 * kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 2 * kStateThreads * 32 * 4 + 16;
 // lean form for many short walks: one operand buffer, no parking slots -> two CTAs per SM
 constexpr int kStateSmemLean = kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 16;
 
+// The operands of one step are three flat byte ranges of the item: w | qg | kg (52 224 B), this CTA's u slice (5 120 B) and
+// Aqk (9 216 B), already in the padded shapes the MMA fragments are read from.
 __device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, int dv0, int tid) {
-  // w, qg, kg: [64][128] each
-  for (int i = tid; i < 3 * kChunk * 16; i += kStateThreads) {
-    const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
-    const int r = rem >> 4, cv = (rem & 15) * 8;
-    const int src_off = (which == 0 ? kOffW : which == 1 ? kOffQg : kOffKg) + r * kHD + cv;
-    cp_async16(smem_u32(buf + which * (kChunk * kLd) + r * kLd + cv), item + src_off);
+  constexpr int kC1 = 3 * kChunk * kLd / 8, kC2 = kChunk * kLdS / 8, kC3 = kChunk * kLdA / 8;   // 16-byte chunks
+  const uint32_t dst = smem_u32(buf);
+  const uint4* src = reinterpret_cast<const uint4*>(item);
+#pragma unroll
+  for (int j = 0; j < (kC1 + kStateThreads - 1) / kStateThreads; ++j) {
+    const int c = tid + j * kStateThreads;
+    if (c < kC1) cp_async16(dst + c * 16, src + c);
   }
-  bf16_t* us = buf + 3 * kChunk * kLd;
-  for (int i = tid; i < kChunk * (kDv / 8); i += kStateThreads) {
-    const int r = i >> 2, cv = (i & 3) * 8;
-    cp_async16(smem_u32(us + r * kLdS + cv), item + kOffU + r * kHD + dv0 + cv);
+  const uint4* usrc = reinterpret_cast<const uint4*>(item + kOffU + (dv0 / kDv) * (kChunk * kLdS));
+#pragma unroll
+  for (int j = 0; j < (kC2 + kStateThreads - 1) / kStateThreads; ++j) {
+    const int c = tid + j * kStateThreads;
+    if (c < kC2) cp_async16(dst + (kC1 + c) * 16, usrc + c);
   }
-  bf16_t* as = us + kChunk * kLdS;
-  for (int i = tid; i < kChunk * (kChunk / 8); i += kStateThreads) {
-    const int r = i >> 3, cv = (i & 7) * 8;
-    cp_async16(smem_u32(as + r * kLdA + cv), item + kOffA + r * kChunk + cv);
+  const uint4* asrc = reinterpret_cast<const uint4*>(item + kOffA);
+#pragma unroll
+  for (int j = 0; j < (kC3 + kStateThreads - 1) / kStateThreads; ++j) {
+    const int c = tid + j * kStateThreads;
+    if (c < kC3) cp_async16(dst + (kC1 + kC2 + c) * 16, asrc + c);
   }
 }
 
@@ -446,8 +456,21 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
 #pragma unroll
       for (int e = 0; e < 4; ++e) S[a][b][e] = 0.f;
 
+  // The walk's step, chunk and decay entries are staged in shared memory once: read from global inside the loop they are
+  // two dependent L2 round trips on the critical path of every step.
+  constexpr int kWin = 128;
+  __shared__ int4 sm_step[kWin];
+  __shared__ int4 sm_chunk[kWin];
+  __shared__ float sm_gl[kWin];
+  for (int i = tid; i < min(kWin, s_end - s_begin); i += kStateThreads) {
+    const int4 st = reinterpret_cast<const int4*>(steps)[s_begin + i];
+    sm_step[i] = st;
+    sm_chunk[i] = reinterpret_cast<const int4*>(chunks)[st.x];
+    sm_gl[i] = *reinterpret_cast<const float*>(scratch + (static_cast<int64_t>(st.x) * HV + h) * kItemElems + kOffGl);
+  }
+  __syncthreads();
   auto item_of = [&](int s) {
-    const int c = steps[s * 4];
+    const int c = s - s_begin < kWin ? sm_step[s - s_begin].x : steps[s * 4];
     return scratch + (static_cast<int64_t>(c) * HV + h) * kItemElems;
   };
   if constexpr (!LEAN) {
@@ -456,8 +479,9 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
   }
 
   for (int s = s_begin; s < s_end; ++s) {
-    const int4 st = reinterpret_cast<const int4*>(steps)[s];
-    const int4 ch = reinterpret_cast<const int4*>(chunks)[st.x];
+    const bool staged = s - s_begin < kWin;
+    const int4 st = staged ? sm_step[s - s_begin] : reinterpret_cast<const int4*>(steps)[s];
+    const int4 ch = staged ? sm_chunk[s - s_begin] : reinterpret_cast<const int4*>(chunks)[st.x];
     bf16_t* buf = LEAN ? bufs : bufs + ((s - s_begin) & 1) * kBufElems;
     const bf16_t* item = item_of(s);
     if constexpr (LEAN) {
@@ -576,7 +600,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     }
     // ---- (3) S = S e^(G_L) + kg^T v'   (warp owns dk rows 32*warp.., K = 64 chunk rows)
     {
-      const float gl = *reinterpret_cast<const float*>(item + kOffGl);
+      const float gl = staged ? sm_gl[s - s_begin] : *reinterpret_cast<const float*>(item + kOffGl);
 #pragma unroll
       for (int a = 0; a < 2; ++a)
 #pragma unroll
@@ -747,7 +771,7 @@ extern "C" int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* 
 // inference server whose allocator is locked after start-up) or host code without access to an allocator at all.
 namespace ojb {
 namespace {
-constexpr int64_t kStaticItems = 1024;   // (chunk-table entries) x (value heads) that fit: 1024 x 73 744 B = 72 MiB per GPU
+constexpr int64_t kStaticItems = 1024;   // (chunk-table entries) x (value heads) that fit: 1024 x 81 936 B = 80 MiB per GPU
 static __device__ __align__(256) unsigned char g_gdn_static_scratch[kStaticItems * kItemElems * 2];
 constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};
