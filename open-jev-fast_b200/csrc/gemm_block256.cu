@@ -96,7 +96,7 @@ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int tot
 
 template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt, GemmArgs g) {
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
@@ -382,7 +382,7 @@ template <int EPI>
 int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
                 int32_t* status, cudaStream_t stream) {
   static bool attr_set = false;
-  auto kern = gemm_tcgen05_kernel<EPI>;
+  auto kern = gemm_block256_kernel<EPI>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)) != cudaSuccess)
       return OJB_ERR_LAUNCH;
