@@ -35,8 +35,8 @@ int ojb_abi_version(void);
  * GEMM — replaces src/lt.cpp:43 lt_matmul / src/fastmodel.py:168 _mm (cuBLASLt) and src/fastmodel.py:158 _skmm
  * (torch.bmm split-K partials). out[M,N] = x[M,K] · w[N,K]^T, bf16 operands, fp32 accumulation in tensor memory.
  * Requirements: K % 8 == 0, x / w / out 16-byte aligned. variant: 0 = the library chooses; 1 / 2 = 128-row tile kernel with
- * 128x256 / 128x128 tiles; 3 = 256-row block kernel, automatic w-tile width; a multiple of 16 in [16, 256] = that kernel
- * with this w-tile width.
+ * 128x256 / 128x128 tiles; 3 = 256-row block kernel, automatic w-tile width; 4 = that kernel with all rows of x in
+ * swapped-operand units (M <= 512); a multiple of 16 in [16, 256] = that kernel with this w-tile width.
  * ------------------------------------------------------------------------------------------------------------------ */
 int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int variant,
                   int32_t* status, ojb_stream_t stream);
@@ -46,6 +46,9 @@ int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N,
  * matching up rows. N = 2*I must be a multiple of 256. out[M, I] = bf16(bf16(silu(bf16(g))) * bf16(u)). */
 int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
                          int32_t* status, ojb_stream_t stream);
+/* The same with the kernel variant forced (0, 1, 3 or 4 as for ojb_gemm_bf16); for tuning. */
+int ojb_gemm_bf16_swiglu_v(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K, int variant,
+                           int32_t* status, ojb_stream_t stream);
 
 /* Split-K partial products, fp32: parts[s, M, N] = x[:, range s] · w[:, range s]^T, S = splits in [1, 16]; range s covers
  * k-blocks (64 columns) [s*c, min((s+1)*c, ceil(K/64))) with c = ceil(ceil(K/64)/S); no range may be empty. Replaces src/fastmodel.py:158-166 (_skmm) — note that `w` stays [N, K] (K-major); the

@@ -10,9 +10,11 @@
 //   block unit  256 rows of x (two 128-row sub-tiles) times BN rows of w. Per 64-wide k-block the two MMAs (M = 128, N = BN)
 //               share the w tile, so a CTA pulls (256 + BN) rows from L2 for 256 x BN outputs — one third less than a
 //               128 x 256 tile. BN is chosen per shape (multiple of 16, <= 256) so that the units fill the SMs.
-//   tail unit   the last M mod 256 (<= 128) rows of x with the operands swapped: 256 rows of w are the M side (two MMAs
-//               with M = 128), the x tail is the N side (N = rows rounded up to 16). The tail costs what it is worth
-//               instead of a whole 128-row tile of zero padding; the epilogue writes the transposed accumulator.
+//   tail unit   rows of x with the operands swapped: 256 rows of w are the M side (two MMAs with M = 128), up to 256 rows
+//               of x are the N side (N = rows rounded up to 16), so these rows cost what they are worth instead of whole
+//               128-row tiles of zero padding; the epilogue writes the transposed accumulator. Used for the last
+//               M mod 256 (<= 128) rows after the blocks, or — for M <= 512 on request, always for M <= 128 — for all of
+//               x in one or two chunks (a pure swapped-operand GEMM).
 // Units are ordered x-block fastest, then k-split, then the tail unit of the w tile, then the next w tile, and dealt to the
 // CTAs round-robin: the CTAs that run at the same time work on the same few w tiles, which therefore come from HBM once.
 // (Giving each CTA a contiguous run instead was measured 15-20 % slower: 136 CTAs then stream 136 different w tiles at
@@ -38,8 +40,9 @@ struct GemmArgs {
   int M, N, K;
   int BN;          // rows of w per block unit: multiple of 16, <= 256
   int n_xblk;      // 256-row blocks of x served by block units
-  int tail_rows;   // rows of x served by tail units (<= 128), starting at row n_xblk * 256
-  int tail_box;    // tail_rows rounded up to a multiple of 16 = UMMA N of the tail units
+  int tail_rows;   // rows of x served by tail units, starting at row n_xblk * 256 (0 = none)
+  int tail_box;    // rows of x per tail unit: multiple of 16, <= 256 = UMMA N of the tail units
+  int n_xchunk;    // tail units per w tile and k-split: the tail rows are cut into n_xchunk chunks of tail_box rows
   int n_wtile;     // ceil(N / BN)
   int n_wtile256;  // ceil(N / 256)
   int splits, kb_per_split, kb_total;
@@ -54,6 +57,7 @@ struct GemmArgs {
 struct Unit {
   bool tail;
   int xb, split, wt, kb0, kb1;
+  int xc;   // x chunk of a tail unit
 };
 
 // Units are ordered by the w rows they read: w tile j contributes its block units (x-block fastest, then k-split) followed
@@ -66,14 +70,14 @@ __device__ __forceinline__ int tails_before(const GemmArgs& g, int j) {
   return t < g.n_wtile256 ? t : g.n_wtile256;
 }
 __device__ __forceinline__ int group_begin(const GemmArgs& g, int j) {
-  return (j * g.n_xblk + tails_before(g, j)) * g.splits;
+  return (j * g.n_xblk + tails_before(g, j) * g.n_xchunk) * g.splits;
 }
 
 __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int total_block) {
   (void)total_block;
   Unit u;
   const int nb = g.n_xblk * g.splits;
-  int j = static_cast<int>(unit / (nb + g.splits * (g.tail_rows > 0 ? g.BN / 256.0f : 0.0f) + 1e-6f));
+  int j = static_cast<int>(unit / (nb + g.splits * g.n_xchunk * (g.tail_rows > 0 ? g.BN / 256.0f : 0.0f) + 1e-6f));
   if (j > g.n_wtile - 1) j = g.n_wtile - 1;
   while (j > 0 && group_begin(g, j) > unit) --j;
   while (j + 1 < g.n_wtile && group_begin(g, j + 1) <= unit) ++j;
@@ -83,11 +87,13 @@ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int tot
     u.xb = off % g.n_xblk;
     u.split = off / g.n_xblk;
     u.wt = j;
+    u.xc = 0;
   } else {
     const int o2 = off - nb;
     u.xb = g.n_xblk;
-    u.split = o2 % g.splits;
-    u.wt = tails_before(g, j) + o2 / g.splits;
+    u.xc = o2 % g.n_xchunk;                       // x chunk fastest: the chunks of one w tile run side by side
+    u.split = (o2 / g.n_xchunk) % g.splits;
+    u.wt = tails_before(g, j) + o2 / (g.n_xchunk * g.splits);
   }
   u.kb0 = u.split * g.kb_per_split;
   u.kb1 = min(u.kb0 + g.kb_per_split, g.kb_total);
@@ -137,7 +143,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   const int total_block = g.n_xblk * g.n_wtile * g.splits;
-  const int total_units = total_block + (g.tail_rows > 0 ? g.n_wtile256 * g.splits : 0);
+  const int total_units = total_block + (g.tail_rows > 0 ? g.n_wtile256 * g.splits * g.n_xchunk : 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -158,7 +164,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             tma_load_2d(a_dst + kABytes, &map_w, fb, kb * kBK, u.wt * g.BN);
           } else {
             tma_load_2d(a_dst, &map_w256, fb, kb * kBK, u.wt * 256);
-            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM);
+            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM + u.xc * g.tail_box);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -293,15 +299,17 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       } else {
         // ---- tail unit (operands swapped): this thread owns one row of w = one output column, the accumulator columns
         //      are the tail rows of x. A warp writes 32 neighbouring output columns of one row per store.
-        const int m0 = g.n_xblk * kBlockM;
+        const int m0 = g.n_xblk * kBlockM + u.xc * g.tail_box;
         if constexpr (EPI == kEpiSwiglu) {
-          // accumulator 0 holds gate rows, accumulator 1 the matching up rows of the same lanes
-          if (acc_id == 0) {
+          // accumulator 0 holds gate rows, accumulator 1 the matching up rows of the same lanes; the two warp sets (both
+          // can read these lanes) share the x rows of the chunk between them
+          {
             const int j = u.wt * 128 + quarter * 32 + lane;       // output column
             const bool col_ok = j < g.N / 2;
             bf16_t* ocol = reinterpret_cast<bf16_t*>(g.out) + j;
+            const int nchunk = g.tail_box / 16;
 #pragma unroll 1
-            for (int c = 0; c < g.tail_box / 16; ++c) {
+            for (int c = acc_id; c < nchunk; c += 2) {
               uint32_t gr[16], ur[16];
               tmem_ld16(tlane + c * 16, gr);
               tmem_ld16(tlane + kAcc1Col + c * 16, ur);
@@ -394,11 +402,24 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
-  g.n_xblk = static_cast<int>(M / kBlockM);
-  int r = static_cast<int>(M % kBlockM);
-  if (r > kBM) { g.n_xblk += 1; r = 0; }   // a long remainder is cheaper as one more (zero-padded) block
-  g.tail_rows = r;
-  g.tail_box = (r + 15) / 16 * 16;
+  // bn_req < 0: every row of x goes through swapped-operand units (M <= 512: up to two chunks of <= 256 rows); otherwise full
+  // 256-row blocks plus a swapped tail of <= 128 rows (a longer remainder is cheaper as one more zero-padded block)
+  const bool all_swapped = bn_req < 0 || M <= kBM;
+  if (bn_req < 0) bn_req = 0;
+  if (all_swapped) {
+    if (M > 512) return OJB_ERR_LIMIT;
+    g.n_xblk = 0;
+    g.tail_rows = static_cast<int>(M);
+    g.n_xchunk = static_cast<int>(ceil_div(M, 256));
+    g.tail_box = static_cast<int>(ceil_div(ceil_div(M, g.n_xchunk), 16) * 16);
+  } else {
+    g.n_xblk = static_cast<int>(M / kBlockM);
+    int r = static_cast<int>(M % kBlockM);
+    if (r > kBM) { g.n_xblk += 1; r = 0; }
+    g.tail_rows = r;
+    g.tail_box = (r + 15) / 16 * 16;
+    g.n_xchunk = 1;
+  }
   g.splits = splits;
   g.kb_total = static_cast<int>(ceil_div(K, kBK));
   g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
@@ -422,10 +443,11 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256);
   if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
   if (rc != OJB_OK) return rc;
-  const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits + (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits : 0);
+  const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits +
+                        (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits * g.n_xchunk : 0);
   int grid = static_cast<int>(units < sms ? units : sms);
   if (units > grid && g.tail_rows > 0) {
-    const int group = (g.n_xblk + 1) * splits;   // units per w tile when BN = 256
+    const int group = (g.n_xblk + g.n_xchunk) * splits;   // units per w tile when BN = 256
     auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
     while (grid > 1 && gcd(grid, group) != 1) --grid;
   }

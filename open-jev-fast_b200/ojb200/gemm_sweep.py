@@ -68,7 +68,9 @@ def main():
                 print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
                                   "max_err": err}), flush=True)
-            for v in ((0, 1, 3) if want("plain") else ()):
+            for v in ((0, 1, 2, 3, 7) if want("plain") else ()):
+                if v == 7 and M > 512:
+                    continue
                 out = LT.lt_matmul(x, ws[0], v)
                 err = (out.float() - ref).abs().max().item()
                 report(f"plain v{v}", _time([lambda w=w, v=v: LT.lt_matmul(x, w, v) for w in ws]), err)
@@ -79,12 +81,18 @@ def main():
                 gg, uu = ref[:, :I].to(bf16).float(), ref[:, I:].to(bf16).float()
                 err = (out.float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
                 report("swiglu", _time([lambda w=w: LT.gemm_swiglu(x, w) for w in wb]), err)
+                for v in (1, 3, 7):
+                    if v == 7 and M > 512:
+                        continue
+                    report(f"swiglu v{v}", _time([lambda w=w, v=v: LT.gemm_swiglu(x, w, v) for w in wb]), err)
             if N == 5120 and not args.quick and want("splitk"):
                 h = torch.randn(M, N, generator=g, device=dev).to(bf16)
                 w1 = torch.ones(N, device=dev)
                 plan = LT.plan_splitk(M, N, Kd)
-                for S in sorted({1, 2, 3, 4, 7, 11, plan}):
-                    for v in (0,):
+                for S in sorted({1, 2, 3, 4, 7, plan}):
+                    for v in (0, 1, 7):
+                        if v == 7 and M > 512:
+                            continue
                         parts = LT.gemm_splitk(x, ws[0], S, v)
                         err = (parts.sum(0) - ref).abs().max().item()
                         report(f"splitk S{S}{'*' if S == plan else ''} v{v}", _time([lambda w=w, S=S, v=v: LT.gemm_splitk(x, w, S, v) for w in ws]), err)

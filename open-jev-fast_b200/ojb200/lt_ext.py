@@ -2,8 +2,8 @@
 
 The reference enumerates cuBLASLt algorithms per shape (lt_setup) and runs one by index (lt_matmul); split-K plans go
 through lt2_*. Here an "algorithm" is one of the library's GEMM variants: index 0 lets the library choose, 1 / 2 force the
-128-row tile kernel with 256 / 128-wide tiles, 3 the 256-row block kernel with automatic w-tile width, 4.. that kernel
-with w-tile width 256, 192, 128.
+128-row tile kernel with 256 / 128-wide tiles, 3 the 256-row block kernel with automatic w-tile width, 4..6 that kernel
+with w-tile width 256, 192, 128, 7 that kernel with all of x in swapped-operand units (M <= 512).
 Two entry points have no counterpart in the reference: gemm_swiglu (SwiGLU fused into the epilogue) and gemm_splitk
 (fp32 partial sums from the un-split [N, K] weight).
 """
@@ -15,7 +15,7 @@ from . import _lib
 from ._lib import call, i32, i64, ptr, stream_ptr
 
 bf16 = torch.bfloat16
-VARIANT_BN = [0, 1, 2, 3, 256, 192, 128]
+VARIANT_BN = [0, 1, 2, 3, 256, 192, 128, 4]
 N_VARIANTS = len(VARIANT_BN)
 SM_COUNT = 148
 _plans = []          # lt2 plans: dicts
@@ -53,14 +53,14 @@ def lt_matmul(x, w, idx):
     return out
 
 
-def gemm_swiglu(x, w_blk):
+def gemm_swiglu(x, w_blk, idx=0):
     """out[M, I] = silu(x @ gate^T) * (x @ up^T) with w_blk = block-interleaved [2I, K] weight (see interleave_gate_up)."""
     _check(x, w_blk)
     M, K = x.shape
     N = w_blk.shape[0]
     out = torch.empty(M, N // 2, dtype=bf16, device=x.device)
-    call("ojb_gemm_bf16_swiglu", ptr(x), ptr(w_blk), ptr(out), i64(M), i64(N), i64(K), ptr(_lib.status_word(x.device)),
-         stream_ptr())
+    call("ojb_gemm_bf16_swiglu_v", ptr(x), ptr(w_blk), ptr(out), i64(M), i64(N), i64(K), i32(VARIANT_BN[idx]),
+         ptr(_lib.status_word(x.device)), stream_ptr())
     return out
 
 
@@ -75,7 +75,9 @@ def interleave_gate_up(w_gate, w_up):
 def plan_splitk(M, N, K, sms=SM_COUNT):
     """Number of K ranges for a projection whose tile count alone cannot fill the SMs: minimises (waves of CTAs) x (k-blocks
     per range), with a small charge per range for the fp32 partials that the reduce kernel has to read."""
-    if M > 256 and 0 < M % 256 <= 128:      # served by the 128-row tile kernel: bf16 output unless the tiles are very few
+    if M <= 512 and M % 256:                 # all-swapped form of the block kernel: three k ranges fill the SMs (measured)
+        return 3 if K >= 3 * 64 * 4 else 1
+    if M > 512 and 0 < M % 256 <= 128:      # served by the 128-row tile kernel: bf16 output unless the tiles are very few
         tiles = -(-M // 128) * -(-N // 256)
         return 2 if (tiles <= 74 and K >= 8192 and K % 128 == 0) else 1
     xblk = M // 256 + (1 if M % 256 > 128 else 0)
