@@ -130,6 +130,11 @@ def run_reference(args, cfg_kwargs, seqs, n_lin, n_full):
     print(json.dumps(line), flush=True)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM from the ncu captures summarised in profiles/
+# (bytes; keyed by M). The algorithmic bytes are weights + x + out = 381.0 MB at M = 544.
+TRAFFIC_NCU = {544: 395.3e6}
+
+
 def gemm_roofline(fast, M, pk, pk_kind, dev):
     """Times the dominant kernel — the gate/up GEMM with the SwiGLU epilogue, 64 launches per forward, each streaming its own
     356 MB weight (larger than L2, so no flush is needed between launches) — with CUDA events on the launching stream."""
@@ -153,8 +158,9 @@ def gemm_roofline(fast, M, pk, pk_kind, dev):
     ach = flops / (best * 1e-3) / 1e12
     peak = pk["bf16_tflops"]
     w_gbs = N2 * Kd * 2 / (best * 1e-3) / 1e9
-    return {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<256,4,swiglu> (gate/up GEMM)", "achieved": ach, "peak": peak,
-            "unit": "TFLOP/s", "frac": ach / peak, "traffic": None, "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
+    kern = "gemm_block256_kernel<swiglu>" if (M > 512 or (M <= 512 and M % 256)) else "gemm_tile128_kernel<256,4,swiglu>"
+    return {"bound": "tensor", "kernel": kern + " (gate/up GEMM + SwiGLU, 64 launches per forward)", "achieved": ach, "peak": peak,
+            "unit": "TFLOP/s", "frac": ach / peak, "traffic": TRAFFIC_NCU.get(M), "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
             "algorithmic_flops_per_launch": flops, "weight_stream_gbs": w_gbs, "hbm_peak_gbs": pk["hbm_gbs"]}
 
 
