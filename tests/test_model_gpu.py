@@ -132,3 +132,72 @@ def test_single_level_tree_with_left_padding():
     ref = OH.candidate_hidden(oracle, seqs)
     rel = ((out - ref).norm() / ref.norm()).item()
     assert rel < 4e-2, rel
+
+
+def test_gdn_layer_full_width_config1():
+    """BASELINE.json config 1: one Gated DeltaNet layer at full width (hidden 5120, 16 key / 32 value heads of 128, conv 4,
+    chunk 64) on T = 539 tokens, bf16 N(0, 0.02) weights: layer output and final recurrent state against the Hugging Face
+    module run in fp32 on the host. Activations are N(0, 1) (what the layer sees after the input norm): with N(0, 0.02)
+    activations the layer output is ~5e-6 in magnitude and absolute bounds are vacuous."""
+    from ojb200 import ext as K, lt_ext as LT, modelgen as MG
+    from transformers.models.qwen3_5 import modeling_qwen3_5 as M
+    T = 539
+    cfg = MG.make_config(num_hidden_layers=1, layer_types=["linear_attention"])
+    torch.manual_seed(0)
+    layer = M.Qwen3_5GatedDeltaNet(cfg, 0).to(bf16)
+    g = torch.Generator().manual_seed(7)
+    with torch.no_grad():
+        for n, p in layer.named_parameters():
+            if n == "A_log":
+                p.copy_(torch.log(torch.rand(p.shape, generator=g) * 16 + 1e-3).to(bf16))
+            elif n == "dt_bias":
+                p.fill_(1.0)
+            elif n == "norm.weight":
+                p.copy_((1.0 + torch.randn(p.shape, generator=g) * 0.02).to(bf16))
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * 0.02).to(bf16))
+    x = torch.randn(1, T, cfg.hidden_size, generator=g).to(bf16)
+    # ---- reference: the module in fp32, plus its final state from the chunk function
+    ref_layer = __import__("copy").deepcopy(layer).float()
+    captured = {}
+    orig = ref_layer.chunk_gated_delta_rule
+
+    def spy(*a, **kw):
+        kw["output_final_state"] = True
+        o, s = orig(*a, **kw)
+        captured["state"] = s
+        return o, s
+    ref_layer.chunk_gated_delta_rule = spy
+    with torch.no_grad():
+        ref = ref_layer(hidden_states=x.float())[0]
+    ref_state = captured["state"][0]                                   # [HV, dk, dv]
+    # ---- ours: in-proj GEMM -> prep -> chunked GDN (final state exported) -> gated norm -> out-proj GEMM
+    dev = "cuda"
+    KD, VD, HV, HK, HD = layer.key_dim, layer.value_dim, layer.num_v_heads, layer.num_k_heads, layer.head_v_dim
+    w_in = torch.cat([layer.in_proj_qkv.weight, layer.in_proj_z.weight, layer.in_proj_b.weight, layer.in_proj_a.weight], 0).to(dev).contiguous()
+    Np = 544
+    xp = torch.zeros(Np, cfg.hidden_size, dtype=bf16, device=dev)
+    xp[:T] = x[0].to(dev)
+    proj = LT.lt_matmul(xp, w_in, 0)
+    hist = torch.full((Np + 1, 4), -1, dtype=torch.int32)
+    for n in range(T):
+        for i in range(4):
+            if n - 3 + i >= 0:
+                hist[n, i] = n - 3 + i
+    q, k, v, gg, beta = K.linattn_prep_rows(proj, hist.to(dev), layer.conv1d.weight.squeeze(1).to(dev).contiguous(),
+                                            layer.A_log.to(dev), layer.dt_bias.to(dev), KD, VD, HV, HK, HD)
+    nc = (T + 63) // 64
+    chunks = torch.tensor([[j * 64, min(64, T - j * 64), 0, 0] for j in range(nc)], dtype=torch.int32, device=dev)
+    steps = torch.tensor([[j, 1 if j == 0 else 0, 0, 1 if j == nc - 1 else 0] for j in range(nc)], dtype=torch.int32, device=dev)
+    walks = torch.tensor([0, nc], dtype=torch.int32, device=dev)
+    fin = torch.zeros(1, HV, HD, HD, device=dev)
+    o = torch.zeros(Np, HV, HD, dtype=bf16, device=dev)
+    K.gdn_chunked(q.view(Np, HK, HD), k.view(Np, HK, HD), v.view(Np, HV, HD), gg, beta, HD ** -0.5, chunks, steps, walks, 1, None, fin, o)
+    y = K.gated_rmsnorm(o, proj, layer.norm.weight.to(dev), HV, HD, 2 * KD + VD, cfg.rms_norm_eps)
+    out = LT.lt_matmul(y, layer.out_proj.weight.to(dev).contiguous(), 0)[:T].float().cpu()
+    torch.cuda.synchronize()
+    rel_out = ((out - ref).norm() / ref.norm()).item()
+    rel_state = ((fin[0].cpu() - ref_state).norm() / ref_state.norm()).item()
+    assert rel_state < 1e-2, rel_state             # BASELINE: GDN final state within a relative error of 1e-2
+    assert rel_out < 1.5e-2, rel_out               # bf16 operands and bf16 intermediate tensors against an fp32 run
+    assert (out - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
