@@ -107,12 +107,14 @@ int ojb_fullattn_prep(const void* proj, const float* qw1, const float* kw1, cons
  *   not null, ext32 = krange[N,8] | nodes[1+2S,4] | chunks[cap,4] | steps[cap,4] | meta[8] | lsteps[cap,4] |
  *   lwalks[2+2S, padded to a multiple of 8] (tables of this
  *   implementation only: key ranges for the attention kernel, node / chunk / walk tables for the tree-native
- *   Gated DeltaNet pass).
+ *   Gated DeltaNet pass). With OJB_LAYOUT_NO_VBITS in `flags` the visibility words are neither computed nor written (the
+ *   kernels of this library read the key ranges instead), which makes the build O(N).
  * ------------------------------------------------------------------------------------------------------------------ */
 int ojb_gtree_dims(const int64_t* tokens, const int64_t* seq_off, const int32_t* groups, int64_t S, int64_t NB,
                    int64_t PB, int64_t* dims);
+#define OJB_LAYOUT_NO_VBITS 1   /* flags: leave vbits (the last field of buf32, the only O(N^2) one) unwritten */
 int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, const int32_t* groups, int64_t S, int64_t pad_id,
-                   int64_t NB, int64_t PB, int64_t* buf64, int32_t* buf32, int32_t* ext32);
+                   int64_t NB, int64_t PB, int64_t* buf64, int32_t* buf32, int32_t* ext32, int32_t flags);
 
 /* ------------------------------------------------------------------------------------------------------------------
  * Gated DeltaNet (linear attention).

@@ -115,7 +115,7 @@ extern "C" int ojb_gtree_dims(const int64_t* tokens, const int64_t* seq_off, con
 }
 
 extern "C" int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, const int32_t* groups, int64_t S, int64_t pad_id,
-                              int64_t NB, int64_t PB, int64_t* buf64, int32_t* buf32, int32_t* ext32) {
+                              int64_t NB, int64_t PB, int64_t* buf64, int32_t* buf32, int32_t* ext32, int32_t flags) {
   if (!buf64 || !buf32) return OJB_ERR_ARG;
   Tree t;
   const int rc = analyse(tokens, seq_off, groups, S, NB, PB, &t);
@@ -136,7 +136,9 @@ extern "C" int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, con
   int32_t* hist = buf32 + o;    o += pad8((N + 1) * 4);
   int32_t* canon = buf32 + o;   o += pad8(S * L2);
   int32_t* rowmask = buf32 + o; o += pad8(N);
-  int32_t* vbits = buf32 + o;   o += pad8(N * W);
+  int32_t* vbits = buf32 + o;
+  const bool want_vbits = (flags & OJB_LAYOUT_NO_VBITS) == 0;   // the N x N/32 words are the only O(N^2) part
+  if (want_vbits) o += pad8(N * W);
   std::fill(buf32, buf32 + o, 0);
 
   std::vector<int32_t> node(N, static_cast<int32_t>(1 + R + S));  // end padding = last node
@@ -192,9 +194,16 @@ extern "C" int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, con
   for (int64_t n = 0; n < N; ++n)
     if (rowmask[n]) canon[inv[n]] = static_cast<int32_t>(n);
   // visibility bits: ancestors + causal inside the node, valid keys only, plus the diagonal
-  auto set_range = [&](int64_t n, int64_t a, int64_t b) {  // keys [a, b)
+  auto set_range = [&](int64_t n, int64_t a, int64_t b) {  // keys [a, b), whole words at a time
+    if (!want_vbits || a >= b) return;
     uint32_t* wrow = reinterpret_cast<uint32_t*>(vbits) + n * W;
-    for (int64_t m = a; m < b; ++m) wrow[m >> 5] |= 1u << (m & 31);
+    const int64_t wa = a >> 5, wb = (b - 1) >> 5;
+    const uint32_t first = 0xffffffffu << (a & 31);
+    const uint32_t last = 0xffffffffu >> (31 - ((b - 1) & 31));
+    if (wa == wb) { wrow[wa] |= first & last; return; }
+    wrow[wa] |= first;
+    for (int64_t w = wa + 1; w < wb; ++w) wrow[w] = 0xffffffffu;
+    wrow[wb] |= last;
   };
   for (int64_t n = 0; n < N; ++n) {
     const int32_t nd = node[n];

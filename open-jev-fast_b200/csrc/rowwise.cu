@@ -241,7 +241,7 @@ fullattn_prep_kernel(const bf16_t* __restrict__ proj, const float* __restrict__ 
 
 using namespace ojb;
 
-extern "C" int ojb_abi_version(void) { return 1; }
+extern "C" int ojb_abi_version(void) { return 2; }
 
 extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
                                void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream) {

@@ -24,8 +24,10 @@ def _flatten(seqs, groups):
     return tok, off, np.asarray(groups, np.int32)
 
 
-def gtree_host(seqs, groups, pad_id, NB=32, PB=16, pin=False):
-    """Runs the host builder. Returns (dims dict, buf64, buf32, ext32) as CPU torch tensors (pinned if asked)."""
+def gtree_host(seqs, groups, pad_id, NB=32, PB=16, pin=False, vbits=True):
+    """Runs the host builder. Returns (dims dict, buf64, buf32, ext32) as CPU torch tensors (pinned if asked). With
+    vbits=False the N x N/32 visibility words (last field of buf32) are not computed; dims["n32_used"] is the number of
+    int32 elements of buf32 that carry data."""
     if len(seqs) == 0 or len(groups) != len(seqs):
         raise RuntimeError("gtree_build: need one group index per candidate and at least one candidate")
     tok, off, grp = _flatten(seqs, groups)
@@ -42,10 +44,11 @@ def gtree_host(seqs, groups, pad_id, NB=32, PB=16, pin=False):
     ext32 = torch.empty(next_, dtype=torch.int32, pin_memory=pin)
     rc = L.ojb_gtree_fill(*args, ctypes.c_int64(pad_id), ctypes.c_int64(NB), ctypes.c_int64(PB),
                           ctypes.cast(buf64.data_ptr(), _I64P), ctypes.cast(buf32.data_ptr(), _I32P),
-                          ctypes.cast(ext32.data_ptr(), _I32P))
+                          ctypes.cast(ext32.data_ptr(), _I32P), ctypes.c_int32(0 if vbits else 1))
     if rc != 0:
         raise RuntimeError("gtree_build: layout fill failed")
     d = dict(N=N, S=S, R=R, L2=L2, Lr=Lr, Nreal=Nreal, cap=cap)
+    d["n32_used"] = n32 if vbits else n32 - _pad8(N * (N // 32))
     return d, buf64, buf32, ext32
 
 

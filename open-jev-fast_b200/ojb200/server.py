@@ -60,7 +60,8 @@ class Entry:
     def run(self, host_bufs):
         """Upload one request's tables (pinned host buffers) and replay. Returns the static fp32 [S, A] output."""
         self.g64.copy_(host_bufs[0], non_blocking=True)
-        self.g32.copy_(host_bufs[1], non_blocking=True)
+        n32 = self.dims.get("n32_used", self.g32.numel())     # without the visibility words when they were not built
+        self.g32[:n32].copy_(host_bufs[1][:n32], non_blocking=True)
         self.ge.copy_(host_bufs[2], non_blocking=True)
         return self.replay()
 
@@ -102,13 +103,14 @@ class Scorer:
     def score_tokens(self, seqs, groups):
         """Candidate token lists + question index per candidate -> fp32 [S, A] scores on the GPU (not synchronised)."""
         t0 = time.perf_counter()
-        dims, b64, b32, e32 = _layout.gtree_host(seqs, groups, self.pad_id, NB, PB, pin=True)
+        # the kernels read key ranges, not the N x N/32 visibility words: those are neither built nor uploaded
+        dims, b64, b32, e32 = _layout.gtree_host(seqs, groups, self.pad_id, NB, PB, pin=True, vbits=False)
         t1 = time.perf_counter()
         with self.lock, torch.cuda.device(self.device):
             ent, captured = self.entry_for(dims, (b64, b32, e32))
             out = ent.run((b64, b32, e32))
         self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=ent.lay.key, rows=dims["Nreal"],
-                         h2d_bytes=b64.numel() * 8 + b32.numel() * 4 + e32.numel() * 4, launches=ent.launches)
+                         h2d_bytes=b64.numel() * 8 + dims["n32_used"] * 4 + e32.numel() * 4, launches=ent.launches)
         return out
 
     def forward(self, records):
