@@ -56,6 +56,14 @@ int ojb_gemm_bf16_swiglu_v(const void* x, const void* w_blk, void* out, int64_t 
 int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, int64_t N, int64_t K, int splits,
                          int variant, int32_t* status, ojb_stream_t stream);
 
+/* Measurement hook of the 256-row block GEMM kernel (no counterpart in the reference). `records` = null switches it off;
+ * otherwise a device buffer of 1 + 4*capacity uint64 words, word 0 = record counter (zero it before a launch). Every work
+ * unit appends {CTA << 32 | tail flag << 31 | unit, ns when its epilogue began to wait, ns when its accumulators were
+ * complete, ns when its epilogue ended} (%globaltimer). mma_repeat > 1 issues the MMAs of every shared-memory stage that
+ * many times (results are then meaningless): the slope against mma_repeat is the pure tensor-pipe cost of a stage.
+ * stage_cols = 32 or 64 forces the width of a shared-memory stage of that kernel, 0 restores its default. */
+int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t stage_cols);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Row-wise and element-wise kernels.
  * ------------------------------------------------------------------------------------------------------------------ */

@@ -70,3 +70,9 @@ extern "C" int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, 
   OJB_REQUIRE(aligned16(x) && aligned16(w) && aligned16(parts));
   return dispatch(kEpiPartialF32, variant, x, w, parts, M, N, K, splits, N, status, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t stage_cols) {
+  OJB_REQUIRE(capacity >= 0 && mma_repeat >= 1 && mma_repeat <= 64 && (stage_cols == 0 || stage_cols == 32 || stage_cols == 64));
+  gemm_block256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity, mma_repeat, stage_cols);
+  return OJB_OK;
+}

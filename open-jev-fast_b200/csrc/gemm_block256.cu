@@ -23,82 +23,22 @@
 //
 // Every wait on an mbarrier is bounded: after kWaitLimitNs the kernel raises the CTA's abort flag, records
 // OJB_DEV_WAIT_TIMEOUT in the status word, lets copies in flight land, frees its TMEM and returns.
-#include "gemm_common.cuh"
+#include "gemm_units.cuh"
 
 namespace ojb {
 namespace {
 
-constexpr int kBlockM = 256;       // rows of x per block unit (two UMMA M sub-tiles)
 constexpr int kGemmThreads = 320;
 constexpr int kEpiWarps = 8;
-constexpr int kMaxStages = 8;
-constexpr uint32_t kABytes = kBlockM * kBK * 2;   // 32 KB: 256 rows of x (block unit) or 256 rows of w (tail unit)
-constexpr uint32_t kSubBytes = kBM * kBK * 2;     // 16 KB: one 128-row sub-tile
+constexpr int kMaxStages = 12;
 constexpr uint32_t kAcc1Col = 256;                // TMEM column of the second accumulator
 
-struct GemmArgs {
-  int M, N, K;
-  int BN;          // rows of w per block unit: multiple of 16, <= 256
-  int n_xblk;      // 256-row blocks of x served by block units
-  int tail_rows;   // rows of x served by tail units, starting at row n_xblk * 256 (0 = none)
-  int tail_box;    // rows of x per tail unit: multiple of 16, <= 256 = UMMA N of the tail units
-  int n_xchunk;    // tail units per w tile and k-split: the tail rows are cut into n_xchunk chunks of tail_box rows
-  int n_wtile;     // ceil(N / BN)
-  int n_wtile256;  // ceil(N / 256)
-  int splits, kb_per_split, kb_total;
-  int stages;
-  uint32_t stage_bytes;
-  void* out;
-  int64_t ldo;           // leading dimension of out in elements
-  int64_t split_stride;  // elements between split planes (fp32 partials)
-  int32_t* status;
-};
-
-struct Unit {
-  bool tail;
-  int xb, split, wt, kb0, kb1;
-  int xc;   // x chunk of a tail unit
-};
-
-// Units are ordered by the w rows they read: w tile j contributes its block units (x-block fastest, then k-split) followed
-// by the tail units that start inside it, so a tail unit finds its w rows in L2 instead of streaming them from HBM again.
-// group_begin(j) = position of the first unit of tile j; tails_before(j) = tail tiles (256 w rows each) that start before
-// row j * BN.
-__device__ __forceinline__ int tails_before(const GemmArgs& g, int j) {
-  if (g.tail_rows == 0) return 0;
-  const int t = (j * g.BN + 255) / 256;
-  return t < g.n_wtile256 ? t : g.n_wtile256;
-}
-__device__ __forceinline__ int group_begin(const GemmArgs& g, int j) {
-  return (j * g.n_xblk + tails_before(g, j) * g.n_xchunk) * g.splits;
-}
-
-__device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int total_block) {
-  (void)total_block;
-  Unit u;
-  const int nb = g.n_xblk * g.splits;
-  int j = static_cast<int>(unit / (nb + g.splits * g.n_xchunk * (g.tail_rows > 0 ? g.BN / 256.0f : 0.0f) + 1e-6f));
-  if (j > g.n_wtile - 1) j = g.n_wtile - 1;
-  while (j > 0 && group_begin(g, j) > unit) --j;
-  while (j + 1 < g.n_wtile && group_begin(g, j + 1) <= unit) ++j;
-  const int off = unit - group_begin(g, j);
-  u.tail = off >= nb;
-  if (!u.tail) {
-    u.xb = off % g.n_xblk;
-    u.split = off / g.n_xblk;
-    u.wt = j;
-    u.xc = 0;
-  } else {
-    const int o2 = off - nb;
-    u.xb = g.n_xblk;
-    u.xc = o2 % g.n_xchunk;                       // x chunk fastest: the chunks of one w tile run side by side
-    u.split = (o2 / g.n_xchunk) % g.splits;
-    u.wt = tails_before(g, j) + o2 / (g.n_xchunk * g.splits);
-  }
-  u.kb0 = u.split * g.kb_per_split;
-  u.kb1 = min(u.kb0 + g.kb_per_split, g.kb_total);
-  return u;
-}
+// Measurement hooks (process-wide, set by ojb_gemm_set_trace): where the kernel records unit timelines, and how often it
+// repeats the MMAs of a stage.
+unsigned long long* g_trace = nullptr;
+int g_trace_cap = 0;
+int g_mma_repeat = 1;
+int g_bk = 0;   // 0 = the default of launch_gemm
 
 template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -153,18 +93,18 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
         const Unit u = decode_unit(g, unit, total_block);
-        const uint32_t tx = kABytes + static_cast<uint32_t>(u.tail ? g.tail_box : g.BN) * (kBK * 2);
+        const uint32_t tx = g.a_bytes + static_cast<uint32_t>(u.tail ? g.tail_box : g.BN) * (g.bk * 2);
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = tiles0 + stage * g.stage_bytes;
           const uint32_t fb = full0 + 8 * stage;
           mbar_expect_tx(fb, tx);
           if (!u.tail) {
-            tma_load_2d(a_dst, &map_x, fb, kb * kBK, u.xb * kBlockM);
-            tma_load_2d(a_dst + kABytes, &map_w, fb, kb * kBK, u.wt * g.BN);
+            tma_load_2d(a_dst, &map_x, fb, kb * g.bk, u.xb * kBlockM);
+            tma_load_2d(a_dst + g.a_bytes, &map_w, fb, kb * g.bk, u.wt * g.BN);
           } else {
-            tma_load_2d(a_dst, &map_w256, fb, kb * kBK, u.wt * 256);
-            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM + u.xc * g.tail_box);
+            tma_load_2d(a_dst, &map_w256, fb, kb * g.bk, u.wt * 256);
+            tma_load_2d(a_dst + g.a_bytes, &map_xt, fb, kb * g.bk, g.n_xblk * kBlockM + u.xc * g.tail_box);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -185,15 +125,19 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = tiles0 + stage * g.stage_bytes;
-          const uint64_t adesc0 = smem_desc_sw128(a_addr);
-          const uint64_t adesc1 = smem_desc_sw128(a_addr + kSubBytes);
-          const uint64_t bdesc = smem_desc_sw128(a_addr + kABytes);
-#pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
-            const uint32_t accum = (kb > u.kb0 || k > 0) ? 1u : 0u;
-            umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
-            umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
+          const bool wide = g.bk == 64;
+          const uint64_t adesc0 = wide ? smem_desc_sw128(a_addr) : smem_desc_sw64(a_addr);
+          const uint64_t adesc1 = wide ? smem_desc_sw128(a_addr + g.a_bytes / 2) : smem_desc_sw64(a_addr + g.a_bytes / 2);
+          const uint64_t bdesc = wide ? smem_desc_sw128(a_addr + g.a_bytes) : smem_desc_sw64(a_addr + g.a_bytes);
+          const int ksteps = g.bk / kUmmaK;
+          for (int rep = 0; rep < g.mma_repeat; ++rep) {
+#pragma unroll 4
+            for (int k = 0; k < ksteps; ++k) {
+              // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
+              const uint32_t accum = (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u;
+              umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
+              umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
+            }
           }
           umma_commit(empty0 + 8 * stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -211,88 +155,109 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     bool ok = true;
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
       const Unit u = decode_unit(g, unit, total_block);
+      const bool tracing = g.trace != nullptr && warp == 2 && lane == 0;
+      const unsigned long long t_begin = tracing ? global_timer_ns() : 0ull;
       if (!mbar_wait(accfull, acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      const unsigned long long t_full = tracing ? global_timer_ns() : 0ull;
       const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t taddr = tlane + static_cast<uint32_t>(acc_id) * kAcc1Col;
       if (!u.tail) {
         // ---- block unit: this thread owns one row of x, the accumulator columns are output columns
         const int row = u.xb * kBlockM + acc_id * kBM + quarter * 32 + lane;
         const bool row_ok = row < g.M;
+        // TMEM loads are issued one chunk ahead of the chunk being converted and stored, so their latency overlaps the
+        // stores instead of adding up once per chunk.
         if constexpr (EPI == kEpiSwiglu) {
           // BN = 256: columns [0,128) of the tile are gate_j, columns [128,256) the matching up_j
           bf16_t* orow = reinterpret_cast<bf16_t*>(g.out) + static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * 128;
           const int ncols = g.N / 2 - u.wt * 128;
-#pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
-            uint32_t gr[16], ur[16];
-            tmem_ld16(taddr + c * 16, gr);
-            tmem_ld16(taddr + 128 + c * 16, ur);
-            tmem_ld_wait();
-            if (row_ok) {
+          auto emit = [&](int c, const uint32_t (&gr)[16], const uint32_t (&ur)[16]) {
+            if (!row_ok) return;
 #pragma unroll
-              for (int j = 0; j < 16; j += 8) {
-                if (c * 16 + j < ncols) {
-                  float o[8];
+            for (int j = 0; j < 16; j += 8) {
+              if (c * 16 + j < ncols) {
+                float o[8];
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) {
-                    const float gv = round_bf(__uint_as_float(gr[j + e]));
-                    const float uv = round_bf(__uint_as_float(ur[j + e]));
-                    o[e] = round_bf(silu_f(gv)) * uv;
-                  }
-                  *reinterpret_cast<uint4*>(orow + c * 16 + j) = pack8(o);
+                for (int e = 0; e < 8; ++e) {
+                  const float gv = round_bf(__uint_as_float(gr[j + e]));
+                  const float uv = round_bf(__uint_as_float(ur[j + e]));
+                  o[e] = round_bf(silu_f(gv)) * uv;
                 }
+                *reinterpret_cast<uint4*>(orow + c * 16 + j) = pack8(o);
               }
             }
-          }
-        } else if constexpr (EPI == kEpiBf16) {
-          bf16_t* orow = reinterpret_cast<bf16_t*>(g.out) + static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * g.BN;
-          const int ncols = g.N - u.wt * g.BN;
-          const bool vec_ok = (g.ldo % 8) == 0 && (g.BN % 8) == 0;
+          };
+          uint32_t ga[16], ua[16], gb[16], ub[16];
+          tmem_ld16(taddr, ga);
+          tmem_ld16(taddr + 128, ua);
+          tmem_ld_wait();
 #pragma unroll 1
-          for (int c = 0; c < g.BN / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(taddr + c * 16, r);
+          for (int c = 0; c < 8; c += 2) {
+            tmem_ld16(taddr + (c + 1) * 16, gb);
+            tmem_ld16(taddr + 128 + (c + 1) * 16, ub);
+            emit(c, ga, ua);
             tmem_ld_wait();
-            if (row_ok) {
+            if (c + 2 < 8) {
+              tmem_ld16(taddr + (c + 2) * 16, ga);
+              tmem_ld16(taddr + 128 + (c + 2) * 16, ua);
+            }
+            emit(c + 1, gb, ub);
+            tmem_ld_wait();
+          }
+        } else {
+          constexpr bool kF32 = EPI == kEpiPartialF32;
+          const int64_t off = static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * g.BN +
+                              (kF32 ? static_cast<int64_t>(u.split) * g.split_stride : 0);
+          bf16_t* orow_h = reinterpret_cast<bf16_t*>(g.out) + off;
+          float* orow_f = reinterpret_cast<float*>(g.out) + off;
+          const int ncols = min(g.N - u.wt * g.BN, g.BN);      // columns of this tile that exist
+          const bool vec_ok = (g.ldo % 8) == 0 && (g.BN % 8) == 0;
+          auto emit = [&](int c, const uint32_t (&r)[32]) {
+            if (!row_ok) return;
+            if constexpr (kF32) {
 #pragma unroll
-              for (int j = 0; j < 16; j += 8) {
-                const int col = c * 16 + j;
+              for (int j = 0; j < 32; j += 4) {
+                const int col = c * 32 + j;
+                if (col + 4 <= ncols && vec_ok) {
+                  *reinterpret_cast<uint4*>(orow_f + col) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    if (col + e < ncols) orow_f[col + e] = __uint_as_float(r[j + e]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                const int col = c * 32 + j;
                 if (col + 8 <= ncols && vec_ok) {
                   float o[8];
 #pragma unroll
                   for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
-                  *reinterpret_cast<uint4*>(orow + col) = pack8(o);
+                  *reinterpret_cast<uint4*>(orow_h + col) = pack8(o);
                 } else {
 #pragma unroll
                   for (int e = 0; e < 8; ++e)
-                    if (col + e < ncols) orow[col + e] = f2bf(__uint_as_float(r[j + e]));
+                    if (col + e < ncols) orow_h[col + e] = f2bf(__uint_as_float(r[j + e]));
                 }
               }
             }
-          }
-        } else {
-          float* orow = reinterpret_cast<float*>(g.out) + static_cast<int64_t>(u.split) * g.split_stride +
-                        static_cast<int64_t>(row) * g.ldo + static_cast<int64_t>(u.wt) * g.BN;
-          const int ncols = g.N - u.wt * g.BN;
-          const bool vec_ok = (g.ldo % 4) == 0 && (g.BN % 4) == 0;
+          };
+          // chunks of 32 columns; the last one may reach past BN into unused columns of this accumulator's 256
+          const int nch = (g.BN + 31) / 32;
+          uint32_t ra[32], rb[32];
+          tmem_ld32(taddr, ra);
+          tmem_ld_wait();
 #pragma unroll 1
-          for (int c = 0; c < g.BN / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(taddr + c * 16, r);
+          for (int c = 0; c < nch; c += 2) {
+            if (c + 1 < nch) tmem_ld32(taddr + (c + 1) * 32, rb);
+            emit(c, ra);
             tmem_ld_wait();
-            if (row_ok) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4) {
-                const int col = c * 16 + j;
-                if (col + 4 <= ncols && vec_ok) {
-                  *reinterpret_cast<uint4*>(orow + col) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                } else {
-#pragma unroll
-                  for (int e = 0; e < 4; ++e)
-                    if (col + e < ncols) orow[col + e] = __uint_as_float(r[j + e]);
-                }
-              }
+            if (c + 1 < nch) {
+              if (c + 2 < nch) tmem_ld32(taddr + (c + 2) * 32, ra);
+              emit(c + 1, rb);
+              tmem_ld_wait();
             }
           }
         }
@@ -351,6 +316,16 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(accempty);
       acc_phase ^= 1u;
+      if (tracing) {
+        const unsigned long long slot = atomicAdd(g.trace, 1ull);
+        if (slot < static_cast<unsigned long long>(g.trace_cap)) {
+          unsigned long long* rec = g.trace + 1 + 4 * slot;
+          rec[0] = (static_cast<unsigned long long>(blockIdx.x) << 32) | static_cast<unsigned>(unit) | (u.tail ? 1ull << 31 : 0ull);
+          rec[1] = t_begin;
+          rec[2] = t_full;
+          rec[3] = global_timer_ns();
+        }
+      }
     }
   }
 
@@ -369,22 +344,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   }
 }
 
-// Width of the w tile of the block units: the multiple of 16 that needs the fewest waves of CTAs, wider tiles preferred
-// (they pull less from L2 per flop); tail units are short and fill the gaps.
-int choose_bn(int64_t N, int n_xblk, int splits, int sms) {
-  if (n_xblk == 0) return 256;
-  int best = 256;
-  double best_cost = 1e30;
-  for (int bn = 256; bn >= 64; bn -= 16) {
-    const int64_t units = ceil_div(N, bn) * n_xblk * splits;
-    const int64_t waves = ceil_div(units, sms);
-    const double cost = static_cast<double>(waves) * bn * (1.0 + 0.15 * (256 - bn) / 256.0);
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
-  }
-  return best;
-}
-
 constexpr size_t kSmemBudget = 227 * 1024;
+constexpr int kDefaultBk = 64;
 
 template <int EPI>
 int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
@@ -421,14 +382,23 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.n_xchunk = 1;
   }
   g.splits = splits;
-  g.kb_total = static_cast<int>(ceil_div(K, kBK));
-  g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
-  if (static_cast<int64_t>(splits - 1) * g.kb_per_split >= g.kb_total) return OJB_ERR_ARG;   // an empty split
+  // 32-column stages: twice as many stages fit, so more bytes are on their way from L2 while one stage is being consumed
+  // (the main loop is bound by the latency of these copies, not by their bandwidth)
+  g.bk = (g_bk == 32 || g_bk == 64) ? g_bk : kDefaultBk;
+  {
+    // K ranges are defined in blocks of 64 columns whatever the stage width, so partial sums do not depend on it
+    const int64_t kb64 = ceil_div(K, 64);
+    const int64_t per64 = ceil_div(kb64, splits);
+    if (static_cast<int64_t>(splits - 1) * per64 >= kb64) return OJB_ERR_ARG;   // an empty split
+    g.kb_total = static_cast<int>(ceil_div(K, g.bk));
+    g.kb_per_split = static_cast<int>(per64 * (64 / g.bk));
+  }
+  g.a_bytes = static_cast<uint32_t>(kBlockM) * g.bk * 2;
   g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, splits, sms));
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
   const int b_rows = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) : g.tail_box;
-  g.stage_bytes = kABytes + static_cast<uint32_t>(b_rows) * (kBK * 2);
+  g.stage_bytes = g.a_bytes + static_cast<uint32_t>(b_rows) * (g.bk * 2);
   const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16;
   g.stages = static_cast<int>((kSmemBudget - fixed) / g.stage_bytes);
   if (g.stages > kMaxStages) g.stages = kMaxStages;
@@ -437,11 +407,14 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.ldo = ldo;
   g.split_stride = M * N;
   g.status = status;
+  g.trace = g_trace;
+  g.trace_cap = g_trace_cap;
+  g.mma_repeat = g_mma_repeat;
   CUtensorMap map_x, map_w, map_w256, map_xt;
-  int rc = make_map(&map_x, x, M, K, kBlockM);
-  if (rc == OJB_OK) rc = make_map(&map_w, w, N, K, g.BN);
-  if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256);
-  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
+  int rc = make_map(&map_x, x, M, K, kBlockM, g.bk);
+  if (rc == OJB_OK) rc = make_map(&map_w, w, N, K, g.BN, g.bk);
+  if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256, g.bk);
+  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16, g.bk);
   if (rc != OJB_OK) return rc;
   const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits +
                         (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits * g.n_xchunk : 0);
@@ -457,6 +430,13 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
 }
 
 }  // namespace
+
+void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int bk) {
+  g_trace = buf;
+  g_trace_cap = buf ? cap : 0;
+  g_mma_repeat = repeat >= 1 ? repeat : 1;
+  g_bk = bk;
+}
 
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream) {

@@ -114,6 +114,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
+// The same for tiles whose rows are 64 bytes (32 elements), written by TMA with the 64-byte swizzle: 8-row groups are
+// 512 bytes apart, swizzle mode 4.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;
+  return d;
+}
 
 // Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = BN.
 __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
@@ -155,16 +166,18 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle, zero fill.
-int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows) {
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix, zero fill; box = [box_rows, 64 columns] with the 128-byte
+// swizzle, or [box_rows, 32 columns] with the 64-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows, int box_cols = kBK) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return OJB_ERR_DRIVER;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
 }
@@ -188,5 +201,6 @@ int gemm_tile128_launch(int epi, int bn, const void* x, const void* w, void* out
                         int64_t ldo, int32_t* status, cudaStream_t stream);
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
+void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int bk);
 
 }  // namespace ojb
