@@ -143,13 +143,13 @@ def gemm_roofline(fast, M, pk, pk_kind, dev):
     x = torch.randn(M, H, device=dev).to(torch.bfloat16)
     layers = [d for d in fast.L if getattr(d, "fused_mlp", False)]
     for d in layers[:4]:
-        LT.gemm_swiglu(x, d.w_gu_blk)
+        fast._mlp_in(x, d)
     best = float("inf")
     for _ in range(3):
         a, b = torch.cuda.Event(True), torch.cuda.Event(True)
         a.record()
         for d in layers:
-            LT.gemm_swiglu(x, d.w_gu_blk)
+            fast._mlp_in(x, d)               # the kernel variant the model uses for this row count (FastQwen35.tune)
         b.record()
         torch.cuda.synchronize()
         best = min(best, a.elapsed_time(b) / len(layers))
@@ -158,7 +158,10 @@ def gemm_roofline(fast, M, pk, pk_kind, dev):
     ach = flops / (best * 1e-3) / 1e12
     peak = pk["bf16_tflops"]
     w_gbs = N2 * Kd * 2 / (best * 1e-3) / 1e9
-    kern = "gemm_block256_kernel<swiglu>" if (M > 512 or (M <= 512 and M % 256)) else "gemm_tile128_kernel<256,4,swiglu>"
+    N2_, Kd_ = layers[0].w_gu_blk.shape
+    idx = fast._plan.get(("gu", M, N2_, Kd_), 0)
+    code = LT.VARIANT_BN[idx] if idx else LT.gemm_plan(M, N2_, Kd_, 1)[0]
+    kern = {1: "gemm_tile128_kernel<256,4,swiglu>", 2: "gemm_tile128_kernel<128,6,swiglu>"}.get(code, "gemm_block256_kernel<swiglu>")
     return {"bound": "tensor", "kernel": kern + " (gate/up GEMM + SwiGLU, 64 launches per forward)", "achieved": ach, "peak": peak,
             "unit": "TFLOP/s", "frac": ach / peak, "traffic": TRAFFIC_NCU.get(M), "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
             "algorithmic_flops_per_launch": flops, "weight_stream_gbs": w_gbs, "hbm_peak_gbs": pk["hbm_gbs"]}

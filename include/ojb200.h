@@ -56,13 +56,21 @@ int ojb_gemm_bf16_swiglu_v(const void* x, const void* w_blk, void* out, int64_t 
 int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, int64_t N, int64_t K, int splits,
                          int variant, int32_t* status, ojb_stream_t stream);
 
+/* Host-side plan (no GPU work): which kernel variant and how many K ranges the library's cost model picks for a shape.
+ * kind = 0 bf16 output, 1 SwiGLU-fused, 2 fp32 split-K partials (the only kind that may use more than one range, up to
+ * max_splits). *microseconds (optional) receives the modelled time. Takes the place of the algorithm search of
+ * src/lt.cpp:93 (lt2_search), which times cuBLASLt candidates on the device. */
+int ojb_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t kind, int32_t max_splits, int32_t* variant, int32_t* splits,
+                  float* microseconds);
+
 /* Measurement hook of the 256-row block GEMM kernel (no counterpart in the reference). `records` = null switches it off;
  * otherwise a device buffer of 1 + 4*capacity uint64 words, word 0 = record counter (zero it before a launch). Every work
  * unit appends {CTA << 32 | tail flag << 31 | unit, ns when its epilogue began to wait, ns when its accumulators were
  * complete, ns when its epilogue ended} (%globaltimer). mma_repeat > 1 issues the MMAs of every shared-memory stage that
  * many times (results are then meaningless): the slope against mma_repeat is the pure tensor-pipe cost of a stage.
- * stage_cols = 32 or 64 forces the width of a shared-memory stage of that kernel, 0 restores its default. */
-int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t stage_cols);
+ * mma_repeat = 0 issues none (pure copy rate). knob: 0 = nothing, 2..12 = cap on the number of pipeline stages, 100 / 101 =
+ * the block epilogue skips its global stores / its TMEM loads. The CTA-pair kernel records the same timelines. */
+int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t knob);
 
 /* ------------------------------------------------------------------------------------------------------------------
  * Row-wise and element-wise kernels.

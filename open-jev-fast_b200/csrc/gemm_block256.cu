@@ -31,23 +31,29 @@ namespace {
 constexpr int kGemmThreads = 320;
 constexpr int kEpiWarps = 8;
 constexpr int kMaxStages = 12;
-constexpr uint32_t kAcc1Col = 256;                // TMEM column of the second accumulator
+constexpr uint32_t kABytes = kBlockM * kBK * 2;   // 32 KB: 256 rows of x (block unit) or 256 rows of w (tail unit)
+constexpr uint32_t kSubBytes = kBM * kBK * 2;     // 16 KB: one 128-row sub-tile
+constexpr uint32_t kAcc1Col = 256;
+constexpr uint32_t kStagingBytes = kEpiWarps * 4096;                // TMEM column of the second accumulator
 
 // Measurement hooks (process-wide, set by ojb_gemm_set_trace): where the kernel records unit timelines, and how often it
 // repeats the MMAs of a stage.
 unsigned long long* g_trace = nullptr;
 int g_trace_cap = 0;
 int g_mma_repeat = 1;
-int g_bk = 0;   // 0 = the default of launch_gemm
+int g_bk = 0;   // 2..12: cap on the number of pipeline stages (measurement only)
+int g_dbg = 0;
 
 template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt, GemmArgs g) {
+                    const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt,
+                    const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_w128, GemmArgs g) {
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(g.stages) * g.stage_bytes);
+  uint8_t* staging = smem + static_cast<size_t>(g.stages) * g.stage_bytes;       // [8 warps][32 rows][128 bytes] when tma_out
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + (g.tma_out ? kStagingBytes : 0));
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -72,6 +78,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w256) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xt) : "memory");
+    if (g.tma_out) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
+    if (g.tail_sub) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w128) : "memory");
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -93,18 +101,38 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
         const Unit u = decode_unit(g, unit, total_block);
-        const uint32_t tx = g.a_bytes + static_cast<uint32_t>(u.tail ? g.tail_box : g.BN) * (g.bk * 2);
+        const uint32_t tx = kABytes + static_cast<uint32_t>(u.tail ? g.tail_box : g.BN) * (kBK * 2);
+        if (u.tail && g.tail_sub) {
+          // A short tail next to full blocks: its own k-block (36 KB) would leave most of the 64 KB stage empty and too few
+          // bytes in flight, so a stage carries three sub-stages instead — (k-block, half of the w tile) pairs, each 128 rows
+          // of w plus the x rows — in the order gate half, up half, next k-block ...
+          const int nh = 2 * (u.kb1 - u.kb0);
+          for (int h0 = 0; h0 < nh; h0 += 3) {
+            const int cnt = nh - h0 < 3 ? nh - h0 : 3;
+            if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+            const uint32_t a_dst = tiles0 + stage * g.stage_bytes;
+            const uint32_t fb = full0 + 8 * stage;
+            mbar_expect_tx(fb, static_cast<uint32_t>(cnt * g.tail_sub));
+            for (int j = 0; j < cnt; ++j) {
+              const int h = h0 + j, kb = u.kb0 + (h >> 1);
+              tma_load_2d(a_dst + j * g.tail_sub, &map_w128, fb, kb * kBK, u.wt * 256 + (h & 1) * kBM);
+              tma_load_2d(a_dst + j * g.tail_sub + kSubBytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM + u.xc * g.tail_box);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          continue;
+        }
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = tiles0 + stage * g.stage_bytes;
           const uint32_t fb = full0 + 8 * stage;
           mbar_expect_tx(fb, tx);
           if (!u.tail) {
-            tma_load_2d(a_dst, &map_x, fb, kb * g.bk, u.xb * kBlockM);
-            tma_load_2d(a_dst + g.a_bytes, &map_w, fb, kb * g.bk, u.wt * g.BN);
+            tma_load_2d(a_dst, &map_x, fb, kb * kBK, u.xb * kBlockM);
+            tma_load_2d(a_dst + kABytes, &map_w, fb, kb * kBK, u.wt * g.BN);
           } else {
-            tma_load_2d(a_dst, &map_w256, fb, kb * g.bk, u.wt * 256);
-            tma_load_2d(a_dst + g.a_bytes, &map_xt, fb, kb * g.bk, g.n_xblk * kBlockM + u.xc * g.tail_box);
+            tma_load_2d(a_dst, &map_w256, fb, kb * kBK, u.wt * 256);
+            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM + u.xc * g.tail_box);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -121,23 +149,51 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const uint32_t idesc = umma_idesc(u.tail ? g.tail_box : g.BN);
         if (!mbar_wait(accempty, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (u.tail && g.tail_sub) {
+          const int nh = 2 * (u.kb1 - u.kb0);
+          for (int h0 = 0; h0 < nh; h0 += 3) {
+            const int cnt = nh - h0 < 3 ? nh - h0 : 3;
+            if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_addr = tiles0 + stage * g.stage_bytes;
+            for (int j = 0; j < cnt; ++j) {
+              const int h = h0 + j;
+              const uint32_t acc = tmem_base + ((h & 1) ? kAcc1Col : 0u);
+              const uint64_t adesc = smem_desc_sw128(a_addr + j * g.tail_sub);
+              const uint64_t bdesc = smem_desc_sw128(a_addr + j * g.tail_sub + kSubBytes);
+#pragma unroll
+              for (int k = 0; k < kBK / kUmmaK; ++k) umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (h >= 2 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(empty0 + 8 * stage);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          umma_commit(accfull);
+          acc_phase ^= 1u;
+          continue;
+        }
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = tiles0 + stage * g.stage_bytes;
-          const bool wide = g.bk == 64;
-          const uint64_t adesc0 = wide ? smem_desc_sw128(a_addr) : smem_desc_sw64(a_addr);
-          const uint64_t adesc1 = wide ? smem_desc_sw128(a_addr + g.a_bytes / 2) : smem_desc_sw64(a_addr + g.a_bytes / 2);
-          const uint64_t bdesc = wide ? smem_desc_sw128(a_addr + g.a_bytes) : smem_desc_sw64(a_addr + g.a_bytes);
-          const int ksteps = g.bk / kUmmaK;
-          for (int rep = 0; rep < g.mma_repeat; ++rep) {
-#pragma unroll 4
-            for (int k = 0; k < ksteps; ++k) {
+          const uint64_t adesc0 = smem_desc_sw128(a_addr);
+          const uint64_t adesc1 = smem_desc_sw128(a_addr + kSubBytes);
+          const uint64_t bdesc = smem_desc_sw128(a_addr + kABytes);
+          if (g.mma_repeat == 1) {
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
               // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
-              const uint32_t accum = (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u;
+              const uint32_t accum = (kb > u.kb0 || k > 0) ? 1u : 0u;
               umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
               umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
             }
+          } else {                                   // measurement only (ojb_gemm_set_trace)
+            for (int rep = 0; rep < g.mma_repeat; ++rep)
+              for (int k = 0; k < kBK / kUmmaK; ++k) {
+                const uint32_t accum = (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u;
+                umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
+                umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
+              }
           }
           umma_commit(empty0 + 8 * stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -166,6 +222,85 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         // ---- block unit: this thread owns one row of x, the accumulator columns are output columns
         const int row = u.xb * kBlockM + acc_id * kBM + quarter * 32 + lane;
         const bool row_ok = row < g.M;
+        if (g.tma_out) {
+          // ---- through shared memory: the warp's 32 rows x 128 bytes go into a swizzled tile (16-byte piece j of row r at
+          //      slot j ^ (r & 7), the layout of the 128-byte swizzle) and one lane hands the tile to the bulk-copy engine,
+          //      which clips it at the edges of out. Stores issued by the threads themselves reach only ~17 GB/s per SM.
+          uint8_t* tile = staging + (warp - 2) * 4096;
+          const uint32_t tile_s = smem_u32(tile);
+          const int row0 = u.xb * kBlockM + acc_id * kBM + quarter * 32;
+          auto put = [&](int j, const uint4& v) { *reinterpret_cast<uint4*>(tile + lane * 128 + ((j ^ (lane & 7)) << 4)) = v; };
+          auto flush = [&](int col) {     // col = first output column of the tile
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && row0 < g.M) {
+              tma_store_3d(&map_out, tile_s, col, row0, EPI == kEpiPartialF32 ? u.split : 0);
+              bulk_commit();
+            }
+          };
+          auto reuse = [&]() {            // the previous store of this warp has read the tile
+            if (lane == 0) bulk_wait_read();
+            __syncwarp();
+          };
+          if constexpr (EPI == kEpiSwiglu) {
+#pragma unroll 1
+            for (int t = 0; t < 2; ++t) {          // two tiles of 64 output columns
+              uint32_t gr[32], ur[32];
+#pragma unroll 1
+              for (int c = 0; c < 2; ++c) {
+                tmem_ld32(taddr + t * 64 + c * 32, gr);
+                tmem_ld32(taddr + 128 + t * 64 + c * 32, ur);
+                tmem_ld_wait();
+                if (c == 0) reuse();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float o[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const float gv = round_bf(__uint_as_float(gr[8 * j + e]));
+                    const float uv = round_bf(__uint_as_float(ur[8 * j + e]));
+                    o[e] = round_bf(silu_f(gv)) * uv;
+                  }
+                  put(c * 4 + j, pack8(o));
+                }
+              }
+              if (u.wt * 128 + t * 64 < g.N / 2) flush(u.wt * 128 + t * 64);
+            }
+          } else if constexpr (EPI == kEpiBf16) {
+            const int nt = g.BN / 64;              // BN is a multiple of 64 on this path
+#pragma unroll 1
+            for (int t = 0; t < nt; ++t) {
+              uint32_t ra[32], rb[32];
+              tmem_ld32(taddr + t * 64, ra);
+              tmem_ld32(taddr + t * 64 + 32, rb);
+              tmem_ld_wait();
+              reuse();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(ra[8 * j + e]);
+                put(j, pack8(o));
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(rb[8 * j + e]);
+                put(j + 4, pack8(o));
+              }
+              if (u.wt * g.BN + t * 64 < g.N) flush(u.wt * g.BN + t * 64);
+            }
+          } else {
+            const int nt = g.BN / 32;              // BN is a multiple of 32 on this path
+#pragma unroll 1
+            for (int t = 0; t < nt; ++t) {
+              uint32_t r[32];
+              tmem_ld32(taddr + t * 32, r);
+              tmem_ld_wait();
+              reuse();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) put(j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+              if (u.wt * g.BN + t * 32 < g.N) flush(u.wt * g.BN + t * 32);
+            }
+          }
+        } else
         // TMEM loads are issued one chunk ahead of the chunk being converted and stored, so their latency overlaps the
         // stores instead of adding up once per chunk.
         if constexpr (EPI == kEpiSwiglu) {
@@ -214,7 +349,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           const int ncols = min(g.N - u.wt * g.BN, g.BN);      // columns of this tile that exist
           const bool vec_ok = (g.ldo % 8) == 0 && (g.BN % 8) == 0;
           auto emit = [&](int c, const uint32_t (&r)[32]) {
-            if (!row_ok) return;
+            if (!row_ok || g.dbg == 100) return;
             if constexpr (kF32) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
@@ -247,15 +382,16 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           // chunks of 32 columns; the last one may reach past BN into unused columns of this accumulator's 256
           const int nch = (g.BN + 31) / 32;
           uint32_t ra[32], rb[32];
-          tmem_ld32(taddr, ra);
+          const bool ld = g.dbg != 101;
+          if (ld) tmem_ld32(taddr, ra);
           tmem_ld_wait();
 #pragma unroll 1
           for (int c = 0; c < nch; c += 2) {
-            if (c + 1 < nch) tmem_ld32(taddr + (c + 1) * 32, rb);
+            if (c + 1 < nch && ld) tmem_ld32(taddr + (c + 1) * 32, rb);
             emit(c, ra);
             tmem_ld_wait();
             if (c + 1 < nch) {
-              if (c + 2 < nch) tmem_ld32(taddr + (c + 2) * 32, ra);
+              if (c + 2 < nch && ld) tmem_ld32(taddr + (c + 2) * 32, ra);
               emit(c + 1, rb);
               tmem_ld_wait();
             }
@@ -327,6 +463,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         }
       }
     }
+    if (g.tma_out && lane == 0) bulk_wait_all();     // the shared-memory tiles must outlive the stores that read them
   }
 
   // ------------------------------------------------------------------ teardown
@@ -345,7 +482,6 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 }
 
 constexpr size_t kSmemBudget = 227 * 1024;
-constexpr int kDefaultBk = 64;
 
 template <int EPI>
 int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
@@ -382,26 +518,28 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.n_xchunk = 1;
   }
   g.splits = splits;
-  // 32-column stages: twice as many stages fit, so more bytes are on their way from L2 while one stage is being consumed
-  // (the main loop is bound by the latency of these copies, not by their bandwidth)
-  g.bk = (g_bk == 32 || g_bk == 64) ? g_bk : kDefaultBk;
-  {
-    // K ranges are defined in blocks of 64 columns whatever the stage width, so partial sums do not depend on it
-    const int64_t kb64 = ceil_div(K, 64);
-    const int64_t per64 = ceil_div(kb64, splits);
-    if (static_cast<int64_t>(splits - 1) * per64 >= kb64) return OJB_ERR_ARG;   // an empty split
-    g.kb_total = static_cast<int>(ceil_div(K, g.bk));
-    g.kb_per_split = static_cast<int>(per64 * (64 / g.bk));
-  }
-  g.a_bytes = static_cast<uint32_t>(kBlockM) * g.bk * 2;
-  g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, splits, sms));
+  g.bk = kBK;
+  g.kb_total = static_cast<int>(ceil_div(K, kBK));
+  g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
+  if (static_cast<int64_t>(splits - 1) * g.kb_per_split >= g.kb_total) return OJB_ERR_ARG;   // an empty split
+  g.a_bytes = kABytes;
+  g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, g.tail_box, g.n_xchunk, g.tail_rows > 0, splits, g.kb_total, sms, EPI));
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
   const int b_rows = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) : g.tail_box;
-  g.stage_bytes = g.a_bytes + static_cast<uint32_t>(b_rows) * (g.bk * 2);
-  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16;
+  g.stage_bytes = kABytes + static_cast<uint32_t>(b_rows) * (kBK * 2);
+  {
+    const uint32_t sub = kSubBytes + static_cast<uint32_t>(g.tail_box) * (kBK * 2);
+    g.tail_sub = (g.n_xblk > 0 && g.tail_rows > 0 && g.tail_box <= 32 && 3 * sub <= g.stage_bytes && g_mma_repeat == 1) ? static_cast<int>(sub) : 0;
+  }
+  // bulk tensor stores need 16-byte aligned rows and whole 128-byte tiles inside every w tile
+  const int64_t out_cols = EPI == kEpiSwiglu ? N / 2 : N;
+  const int out_elt = EPI == kEpiPartialF32 ? 4 : 2;
+  g.tma_out = g.n_xblk > 0 && (ldo * out_elt) % 16 == 0 && g.BN % (128 / out_elt) == 0 ? 1 : 0;
+  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16 + (g.tma_out ? kStagingBytes : 0);
   g.stages = static_cast<int>((kSmemBudget - fixed) / g.stage_bytes);
   if (g.stages > kMaxStages) g.stages = kMaxStages;
+  if (g_bk >= 2 && g_bk <= 12 && g.stages > g_bk) g.stages = g_bk;
   if (g.stages < 2) return OJB_ERR_LIMIT;
   g.out = out;
   g.ldo = ldo;
@@ -410,11 +548,17 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.trace = g_trace;
   g.trace_cap = g_trace_cap;
   g.mma_repeat = g_mma_repeat;
+  g.dbg = g_dbg;
   CUtensorMap map_x, map_w, map_w256, map_xt;
-  int rc = make_map(&map_x, x, M, K, kBlockM, g.bk);
-  if (rc == OJB_OK) rc = make_map(&map_w, w, N, K, g.BN, g.bk);
-  if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256, g.bk);
-  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16, g.bk);
+  int rc = make_map(&map_x, x, M, K, kBlockM);
+  if (rc == OJB_OK) rc = make_map(&map_w, w, N, K, g.BN);
+  if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256);
+  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
+  CUtensorMap map_w128;
+  if (rc == OJB_OK) rc = make_map(&map_w128, w, N, K, kBM);
+  CUtensorMap map_out = map_xt;
+  if (rc == OJB_OK && g.tma_out)
+    rc = make_out_map(&map_out, out, out_elt, M, out_cols, ldo, EPI == kEpiPartialF32 ? splits : 1, g.split_stride);
   if (rc != OJB_OK) return rc;
   const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits +
                         (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits * g.n_xchunk : 0);
@@ -425,7 +569,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     while (grid > 1 && gcd(grid, group) != 1) --grid;
   }
   const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
-  kern<<<grid, kGemmThreads, smem, stream>>>(map_x, map_w, map_w256, map_xt, g);
+  kern<<<grid, kGemmThreads, smem, stream>>>(map_x, map_w, map_w256, map_xt, map_out, map_w128, g);
   return launch_status(cudaGetLastError());
 }
 
@@ -434,8 +578,9 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
 void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int bk) {
   g_trace = buf;
   g_trace_cap = buf ? cap : 0;
-  g_mma_repeat = repeat >= 1 ? repeat : 1;
-  g_bk = bk;
+  g_mma_repeat = repeat >= 0 ? repeat : 1;
+  g_bk = bk >= 100 ? 0 : bk;
+  g_dbg = bk >= 100 ? bk : 0;
 }
 
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,

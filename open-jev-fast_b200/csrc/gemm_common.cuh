@@ -60,6 +60,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// Bulk tensor store of one shared-memory tile (box of the map) to global memory; x = column, y = row, z = plane.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x),
+               "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all bulk stores of this thread have finished reading their shared-memory source
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all bulk stores of this thread are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make shared-memory writes of this thread visible to the bulk-copy engine
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
 }
@@ -114,18 +128,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
-// The same for tiles whose rows are 64 bytes (32 elements), written by TMA with the 64-byte swizzle: 8-row groups are
-// 512 bytes apart, swizzle mode 4.
-__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(512 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(4) << 61;
-  return d;
-}
-
 // Instruction descriptor of tcgen05.mma.kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = BN.
 __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
@@ -144,7 +146,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+// SiLU of the fused epilogues: approximate exponential and division (about 2 ulp in fp32, far below the bf16 rounding that
+// follows); the full-precision forms cost more issue slots than the rest of the epilogue together.
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 enum Epilogue { kEpiBf16 = 0, kEpiSwiglu = 1, kEpiPartialF32 = 2 };
 
@@ -166,18 +170,35 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map over a row-major [rows, cols] matrix, zero fill; box = [box_rows, 64 columns] with the 128-byte
-// swizzle, or [box_rows, 32 columns] with the 64-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows, int box_cols = kBK) {
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle, zero fill.
+// (32-column boxes with the 64-byte swizzle give twice the stages but were measured 30 % slower: the copy engine moves
+// whole 128-byte lines.)
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return OJB_ERR_DRIVER;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
+}
+
+// Tensor map of an output matrix for bulk tensor stores from [32 rows][128 bytes] shared-memory tiles written with the
+// 128-byte swizzle: rows x cols elements of elt bytes (2 = bf16, 4 = fp32), row pitch ld elements, `planes` matrices
+// plane_stride elements apart. Stores are clipped at the matrix edges.
+int make_out_map(CUtensorMap* map, void* base, int elt, int64_t rows, int64_t cols, int64_t ld, int64_t planes,
+                 int64_t plane_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return OJB_ERR_DRIVER;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * elt, static_cast<cuuint64_t>(plane_stride) * elt};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / elt), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
 }
@@ -202,5 +223,8 @@ int gemm_tile128_launch(int epi, int bn, const void* x, const void* w, void* out
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int bk);
+int gemm_pair256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
+                        int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
+void gemm_pair256_set_trace(unsigned long long* buf, int cap, int repeat, int max_stages);
 
 }  // namespace ojb

@@ -29,6 +29,9 @@ struct GemmArgs {
   int32_t* status;
   unsigned long long* trace;   // null, or [0] = record counter followed by records of 4 words (see ojb_gemm_set_trace)
   int trace_cap;
+  int tail_sub;                // bytes of a tail sub-stage (128 rows of w + the x rows), 0 = one k-block per stage
+  int tma_out;                 // the block epilogue stores through shared-memory tiles and bulk tensor stores
+  int dbg;                     // measurement only: 100 = the block epilogue skips its global stores, 101 = its TMEM loads
   int mma_repeat;              // 1; > 1 only for measurements: every stage's MMAs are issued this many times
 };
 
@@ -78,17 +81,73 @@ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int tot
   return u;
 }
 
-// Width of the w tile of the block units: the multiple of 16 that needs the fewest waves of CTAs, wider tiles preferred
-// (they pull less from L2 per flop); tail units are short and fill the gaps.
-inline int choose_bn(int64_t N, int n_xblk, int splits, int sms) {
+// ---- Cost model (host). Times are SM clocks; the constants come from unit timelines measured on B200 (ojb_gemm_set_trace):
+// the main loops are bound by shared-memory bandwidth (128 bytes per clock per SM shared between the TMA fill of a stage
+// and the operand reads of its MMAs), an MMA with M = 128 never takes less than 64 clocks, a swapped-operand unit keeps
+// too few bytes in flight to run faster than about 1200 clocks per k-block, and the epilogue of a block unit costs about 19
+// (bf16), 33 (fp32) or 40 (SwiGLU) clocks per accumulator column.
+struct UnitCost {
+  double block_kb, block_epi, tail_kb, tail_epi;
+};
+inline UnitCost unit_cost(int bn, int tail_box, int epi) {
+  UnitCost c;
+  const double smem = 512.0 + 3.0 * bn, mma = 4.0 * bn;
+  c.block_kb = smem > mma ? smem : mma;
+  c.block_epi = 900.0 + bn * (epi == kEpiPartialF32 ? 33.0 : (epi == kEpiSwiglu ? 40.0 : 19.0));
+  const double tsm = 512.0 + 3.0 * tail_box;
+  c.tail_kb = tsm > 1200.0 ? tsm : 1200.0;
+  c.tail_epi = 3200.0 + 24.0 * tail_box;
+  return c;
+}
+
+// Longest per-worker sum when the units of the block kernels (order of decode_unit) are dealt round-robin to `workers`
+// CTAs (or CTA pairs). n_xblk == 0: swapped-operand units only.
+inline double block_kernel_clocks(int64_t N, int bn, int n_xblk, int tail_box, int n_xchunk, bool has_tail, int splits,
+                                  int kb_total, int workers, int epi, int* grid_out = nullptr) {
+  const int n_wtile = n_xblk > 0 ? static_cast<int>(ceil_div(N, bn)) : static_cast<int>(ceil_div(N, 256));
+  const int n_wtile256 = static_cast<int>(ceil_div(N, 256));
+  const int per = static_cast<int>(ceil_div(kb_total, splits));
+  const UnitCost c = unit_cost(bn, tail_box, epi);
+  const int64_t units = static_cast<int64_t>(n_xblk) * n_wtile * splits + (has_tail ? static_cast<int64_t>(n_wtile256) * splits * n_xchunk : 0);
+  int grid = static_cast<int>(units < workers ? units : workers);
+  if (units > grid && has_tail && n_xblk > 0) {
+    const int group = (n_xblk + n_xchunk) * splits;
+    auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
+    while (grid > 1 && gcd(grid, group) != 1) --grid;
+  }
+  if (grid_out) *grid_out = grid;
+  if (grid <= 0) return 0.0;
+  double load[160] = {0.0};
+  if (grid > 160) return 1e30;
+  int64_t i = 0;
+  auto kbs = [&](int s) { const int k1 = (s + 1) * per < kb_total ? (s + 1) * per : kb_total; return k1 - s * per; };
+  auto tails_before = [&](int j) {
+    if (!has_tail) return 0;
+    const int t = n_xblk > 0 ? (j * bn + 255) / 256 : j;
+    return t < n_wtile256 ? t : n_wtile256;
+  };
+  for (int j = 0; j < n_wtile; ++j) {
+    for (int s = 0; s < splits; ++s)
+      for (int xb = 0; xb < n_xblk; ++xb) load[i++ % grid] += kbs(s) * c.block_kb + c.block_epi;
+    const int nt = (j + 1 < n_wtile ? tails_before(j + 1) : (has_tail ? n_wtile256 : 0)) - tails_before(j);
+    for (int t = 0; t < nt; ++t)
+      for (int s = 0; s < splits; ++s)
+        for (int xc = 0; xc < n_xchunk; ++xc) load[i++ % grid] += kbs(s) * c.tail_kb + c.tail_epi;
+  }
+  double worst = 0.0;
+  for (int k = 0; k < grid; ++k) worst = load[k] > worst ? load[k] : worst;
+  return worst + 5000.0;      // launch, TMEM allocation, first stages
+}
+
+// Width of the w tile of the block units: the multiple of 16 with the smallest modelled time, wider tiles preferred.
+inline int choose_bn(int64_t N, int n_xblk, int tail_box, int n_xchunk, bool has_tail, int splits, int kb_total, int workers,
+                     int epi) {
   if (n_xblk == 0) return 256;
   int best = 256;
   double best_cost = 1e30;
   for (int bn = 256; bn >= 64; bn -= 16) {
-    const int64_t units = ceil_div(N, bn) * n_xblk * splits;
-    const int64_t waves = ceil_div(units, sms);
-    const double cost = static_cast<double>(waves) * bn * (1.0 + 0.15 * (256 - bn) / 256.0);
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+    const double cost = block_kernel_clocks(N, bn, n_xblk, tail_box, n_xchunk, has_tail, splits, kb_total, workers, epi);
+    if (cost < best_cost * 0.98) { best_cost = cost; best = bn; }
   }
   return best;
 }

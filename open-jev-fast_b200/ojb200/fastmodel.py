@@ -62,6 +62,7 @@ class FastQwen35(torch.nn.Module):
         self.embed, self.rotary = core.embed_tokens, core.rotary_emb
         self.v2, self.fuse_l2 = v2, fuse_l2
         self._bufs = {}
+        self._plan, self._tuned = {}, set()     # (op, M, N, K) -> kernel choice, filled by tune()
         w1 = lambda norm: (1.0 + norm.weight.float()).contiguous()
         self.in_w1 = [w1(L.input_layernorm) for L in core.layers]
         self.post_w1 = [w1(L.post_attention_layernorm) for L in core.layers]
@@ -103,12 +104,13 @@ class FastQwen35(torch.nn.Module):
                 self.L.append(d)
 
     # ------------------------------------------------------------------------------------------------ GEMM dispatch
-    # The reference times every cuBLASLt candidate per shape (src/fastmodel.py:114-156). Here one kernel serves all shapes;
-    # its tile width is chosen inside the library from the work-unit count, and the K split of the two projections onto the
-    # hidden size (too few tiles for 148 SMs) by lt_ext.plan_splitk.
+    # The reference times every cuBLASLt candidate per shape (src/fastmodel.py:114-156). Here the library's cost model picks
+    # kernel, tile width and K split for any shape (lt_ext.gemm_plan); `tune(M)` refines that choice for one row count by
+    # timing the candidates on this model's own weights, back to back over all layers (so under the power cap and with the
+    # weights coming from HBM, as in the real forward).
     def _mm(self, x, w):
         """out = x @ w^T, bf16 (src/fastmodel.py:168 _mm)."""
-        return LT.lt_matmul(x, w, 0)
+        return LT.lt_matmul(x, w, self._plan.get(("mm", x.shape[0], w.shape[0], w.shape[1]), 0))
 
     @staticmethod
     def _split(W, S):
@@ -118,20 +120,91 @@ class FastQwen35(torch.nn.Module):
 
     def _res(self, h, y, w, S, w1, mask):
         """Output projection + residual + RMSNorm (src/fastmodel.py:196 _res): fp32 partial products over S ranges of K, then
-        one kernel for partial sum + residual + norm. S = 0 lets plan_splitk choose; S = 1 is a plain bf16 GEMM followed by
+        one kernel for partial sum + residual + norm. S = 0 lets the plan choose; S = 1 is a plain bf16 GEMM followed by
         the fused add + norm (delta = bf16 of the fp32 accumulator, the rounding point of the reference's bf16(sum))."""
         M, Kd = y.shape
+        idx = 0
         if S == 0:
-            S = LT.plan_splitk(M, w.shape[0], Kd)
+            idx, S = self._plan.get(("res", M, w.shape[0], Kd), (0, 0))
+            if S == 0:
+                S = LT.plan_splitk(M, w.shape[0], Kd)
         if S == 1:
-            return K.add_rmsnorm(h, self._mm(y, w), w1, mask, self.eps)
-        parts = LT.gemm_splitk(y, w, S, 0)
+            return K.add_rmsnorm(h, LT.lt_matmul(y, w, idx), w1, mask, self.eps)
+        parts = LT.gemm_splitk(y, w, S, idx)
         return K.add_rmsnorm_sk2(h, parts, w1, mask, self.eps)
 
     def _mlp_in(self, hn, d):
         if d.fused_mlp:
-            return LT.gemm_swiglu(hn, d.w_gu_blk)
+            return LT.gemm_swiglu(hn, d.w_gu_blk, self._plan.get(("gu", hn.shape[0]) + tuple(d.w_gu_blk.shape), 0))
         return K.silu_mul(self._mm(hn, d.w_gu_cat))
+
+    TUNE_MAX_ROWS = int(os.environ.get("OJ_TUNE_MAX_ROWS", "1024"))
+
+    def tune(self, M, force=False, report=None):
+        """Choose kernel variant (and K split) of every projection for M packed rows by timing (src/fastmodel.py:114-156
+        _tune). Each candidate runs over all layers that have the shape, twice, between CUDA events. Above TUNE_MAX_ROWS the
+        cost model is kept (every shape then has many units per SM and the 256-row block kernel wins throughout)."""
+        if (M in self._tuned or M > self.TUNE_MAX_ROWS) and not force:
+            return
+        self._tuned.add(M)
+        dev = self.L[0].w_down.device
+        g = torch.Generator(device=dev).manual_seed(1234)
+        rnd = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+
+        def clock(fn, layers):
+            for d in layers[:2]:
+                fn(d)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(2):
+                for d in layers:
+                    fn(d)
+            b.record()
+            b.synchronize()
+            return a.elapsed_time(b) * 1e3 / (2 * len(layers))
+
+        def groups(attr):
+            out = {}
+            for d in self.L:
+                w = getattr(d, attr, None)
+                if w is not None:
+                    out.setdefault(tuple(w.shape), []).append(d)
+            return out
+
+        kernels = [1, 3] + ([7] if M <= 512 else [])
+        for (N, Kd), layers in groups("w_in").items():
+            x = rnd(M, Kd)
+            res = {i: clock(lambda d, i=i: LT.lt_matmul(x, d.w_in, i), layers) for i in kernels + [2]}
+            best = min(res, key=res.get)
+            self._plan[("mm", M, N, Kd)] = best
+            if report is not None:
+                report.append(dict(op="in-proj", M=M, N=N, K=Kd, us=res, best=best))
+        for (N, Kd), layers in groups("w_gu_blk").items():
+            x = rnd(M, Kd)
+            res = {i: clock(lambda d, i=i: LT.gemm_swiglu(x, d.w_gu_blk, i), layers) for i in kernels}
+            best = min(res, key=res.get)
+            self._plan[("gu", M, N, Kd)] = best
+            if report is not None:
+                report.append(dict(op="gate/up", M=M, N=N, K=Kd, us=res, best=best))
+        for attr, norms in (("w_out", self.post_w1), ("w_down", self.in_w1)):
+            for (N, Kd), layers in groups(attr).items():
+                y, h, w1 = rnd(M, Kd), rnd(M, N), norms[0]
+                kb = -(-Kd // 64)
+                res = {}
+                for S in (1, 2, 3, 4, 6, 8):
+                    if (S - 1) * -(-kb // S) >= kb:
+                        continue
+                    for i in kernels:
+                        if S == 1:
+                            fn = lambda d, i=i: K.add_rmsnorm(h, LT.lt_matmul(y, getattr(d, attr), i), w1, None, self.eps)
+                        else:
+                            fn = lambda d, i=i, S=S: K.add_rmsnorm_sk2(h, LT.gemm_splitk(y, getattr(d, attr), S, i), w1, None, self.eps)
+                        res[(i, S)] = clock(fn, layers)
+                best = min(res, key=res.get)
+                self._plan[("res", M, N, Kd)] = best
+                if report is not None:
+                    report.append(dict(op=attr, M=M, N=N, K=Kd, us={f"v{i} S{S}": round(t, 1) for (i, S), t in res.items()}, best=best))
+        torch.cuda.synchronize(dev)
 
     gtree_build = staticmethod(_layout.gtree_build)
 

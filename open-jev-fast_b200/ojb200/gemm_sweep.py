@@ -68,7 +68,7 @@ def main():
                 print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
                                   "max_err": err}), flush=True)
-            for v in ((0, 1, 2, 3, 7) if want("plain") else ()):
+            for v in ((0, 1, 2, 3, 7, 8) if want("plain") else ()):
                 if v == 7 and M > 512:
                     continue
                 out = LT.lt_matmul(x, ws[0], v)
@@ -85,12 +85,16 @@ def main():
                     if v == 7 and M > 512:
                         continue
                     report(f"swiglu v{v}", _time([lambda w=w, v=v: LT.gemm_swiglu(x, w, v) for w in wb]), err)
+                wb64 = [LT.interleave_gate_up(w[:I], w[I:], 64) for w in ws]      # layout of the CTA-pair kernel
+                err64 = (LT.gemm_swiglu(x, wb64[0], 8).float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
+                report("swiglu v8", _time([lambda w=w: LT.gemm_swiglu(x, w, 8) for w in wb64]), err64)
+                del wb64
             if N == 5120 and not args.quick and want("splitk"):
                 h = torch.randn(M, N, generator=g, device=dev).to(bf16)
                 w1 = torch.ones(N, device=dev)
                 plan = LT.plan_splitk(M, N, Kd)
-                for S in sorted({1, 2, 3, 4, 7, plan}):
-                    for v in (0, 1, 7):
+                for S in sorted({1, 2, 3, 4, 6, plan}):
+                    for v in (0, 1, 3, 7, 8):
                         if v == 7 and M > 512:
                             continue
                         parts = LT.gemm_splitk(x, ws[0], S, v)

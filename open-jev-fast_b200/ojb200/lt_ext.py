@@ -3,10 +3,12 @@
 The reference enumerates cuBLASLt algorithms per shape (lt_setup) and runs one by index (lt_matmul); split-K plans go
 through lt2_*. Here an "algorithm" is one of the library's GEMM variants: index 0 lets the library choose, 1 / 2 force the
 128-row tile kernel with 256 / 128-wide tiles, 3 the 256-row block kernel with automatic w-tile width, 4..6 that kernel
-with w-tile width 256, 192, 128, 7 that kernel with all of x in swapped-operand units (M <= 512).
+with w-tile width 256, 192, 128, 7 that kernel with all of x in swapped-operand units (M <= 512), 8 / 9 the CTA-pair
+kernel (tcgen05.mma.cta_group::2) with automatic width / all of x in swapped-operand units.
 Two entry points have no counterpart in the reference: gemm_swiglu (SwiGLU fused into the epilogue) and gemm_splitk
 (fp32 partial sums from the un-split [N, K] weight).
 """
+import ctypes
 import sys
 
 import torch
@@ -15,7 +17,7 @@ from . import _lib
 from ._lib import call, i32, i64, ptr, stream_ptr
 
 bf16 = torch.bfloat16
-VARIANT_BN = [0, 1, 2, 3, 256, 192, 128, 4]
+VARIANT_BN = [0, 1, 2, 3, 256, 192, 128, 4, 5, 6]
 N_VARIANTS = len(VARIANT_BN)
 SM_COUNT = 148
 _plans = []          # lt2 plans: dicts
@@ -64,36 +66,25 @@ def gemm_swiglu(x, w_blk, idx=0):
     return out
 
 
-def interleave_gate_up(w_gate, w_up):
-    """[I, K] gate and up weights -> [2I, K] in blocks of 128 gate rows followed by their 128 up rows (I % 128 == 0)."""
+def interleave_gate_up(w_gate, w_up, block=128):
+    """[I, K] gate and up weights -> [2I, K] in blocks of `block` gate rows followed by their up rows (I % 128 == 0)."""
     I, K = w_gate.shape
     if I % 128:
         raise RuntimeError("interleave_gate_up: I must be a multiple of 128")
-    return torch.stack([w_gate.view(I // 128, 128, K), w_up.view(I // 128, 128, K)], 1).reshape(2 * I, K).contiguous()
+    return torch.stack([w_gate.view(I // block, block, K), w_up.view(I // block, block, K)], 1).reshape(2 * I, K).contiguous()
+
+
+def gemm_plan(M, N, K, kind, max_splits=16):
+    """(variant code, K ranges, modelled microseconds) that the library's cost model picks for a shape; kind = 0 bf16
+    output, 1 SwiGLU-fused, 2 fp32 split-K partials. Host arithmetic only."""
+    v, s, us = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_float()
+    call("ojb_gemm_plan", i64(M), i64(N), i64(K), i32(kind), i32(max_splits), ctypes.byref(v), ctypes.byref(s), ctypes.byref(us))
+    return v.value, s.value, us.value
 
 
 def plan_splitk(M, N, K, sms=SM_COUNT):
-    """Number of K ranges for a projection whose tile count alone cannot fill the SMs: minimises (waves of CTAs) x (k-blocks
-    per range), with a small charge per range for the fp32 partials that the reduce kernel has to read."""
-    if M <= 512 and M % 256:                 # all-swapped form of the block kernel: three k ranges fill the SMs (measured)
-        return 3 if K >= 3 * 64 * 4 else 1
-    if M > 512 and 0 < M % 256 <= 128:      # served by the 128-row tile kernel: bf16 output unless the tiles are very few
-        tiles = -(-M // 128) * -(-N // 256)
-        return 2 if (tiles <= 74 and K >= 8192 and K % 128 == 0) else 1
-    xblk = M // 256 + (1 if M % 256 > 128 else 0)
-    tail = 1 if 0 < M % 256 <= 128 else 0
-    kb = -(-K // 64)
-    best, best_cost = 1, float("inf")
-    for S in range(1, 17):
-        per = -(-kb // S)
-        if (S - 1) * per >= kb or per < 4:
-            continue
-        tiles = -(-N // 256)
-        units = xblk * tiles * S + tail * tiles * S * (M % 256) / 512.0
-        cost = -(-int(units + 0.999) // sms) * per * (1.0 + 0.03 * S)
-        if cost < best_cost:
-            best, best_cost = S, cost
-    return best
+    """Number of K ranges for a projection whose output goes through the partial-sum reduction (residual + RMSNorm kernel)."""
+    return gemm_plan(M, N, K, 2)[1]
 
 
 def gemm_splitk(x, w, S, idx=0):

@@ -35,11 +35,12 @@ class Entry:
         self.ids = f.pop("ids")
         self.lay = _layout.SimpleNamespace(N=dims["N"], S=dims["S"], L2=dims["L2"], key=(dims["N"], dims["S"], dims["L2"]), **f)
         self.lay.walk_ptr, self.lay.n_walks = self.lay.meta[6:8], 1
+        fast.tune(dims["N"])            # per-shape choice of GEMM kernel and K split, timed on the model's own weights
         body = lambda: fast.score_gtree(self.ids, self.lay, scorer.head_w, scorer.head_b)
         st = torch.cuda.Stream(device=dev)
         st.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(st):
-            for _ in range(2):          # warm-up: also lets the GEMM dispatcher time its candidates for these shapes
+            for _ in range(2):          # warm-up
                 body()
         torch.cuda.current_stream(dev).wait_stream(st)
         torch.cuda.synchronize(dev)
