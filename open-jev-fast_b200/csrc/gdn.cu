@@ -195,8 +195,10 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
   // ---- cumulative log-decay (warp 0): two elements per lane
   if (warp == 0) {
     const int r0 = lane * 2, r1 = r0 + 1;
-    float g0 = r0 < nrows ? g[static_cast<int64_t>(row0 + r0) * HV + h] : 0.f;
-    float g1 = r1 < nrows ? g[static_cast<int64_t>(row0 + r1) * HV + h] : 0.f;
+    // log-decays below -1e4 are clamped: e^-1e4 is zero in fp32 either way, and -inf would turn the differences of the
+    // cumulative sums into NaN
+    float g0 = r0 < nrows ? fmaxf(g[static_cast<int64_t>(row0 + r0) * HV + h], -1e4f) : 0.f;
+    float g1 = r1 < nrows ? fmaxf(g[static_cast<int64_t>(row0 + r1) * HV + h], -1e4f) : 0.f;
     Bs[r0] = r0 < nrows ? bf2f(beta[static_cast<int64_t>(row0 + r0) * HV + h]) : 0.f;
     Bs[r1] = r1 < nrows ? bf2f(beta[static_cast<int64_t>(row0 + r1) * HV + h]) : 0.f;
     float s = g0 + g1;

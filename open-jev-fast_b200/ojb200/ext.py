@@ -155,6 +155,10 @@ def _prep(proj, hist, rep_ptr, rep_pos, n_out, convw, A_log, dt_bias, KD, VD, HV
     _chk(proj, hist, rep_ptr, rep_pos, convw, A_log, dt_bias)
     if HD != 128 or HK * HD != KD or HV * HD != VD or convw.shape[1] != 4:
         raise RuntimeError("linattn_prep: head dim must be 128 and the conv width 4")
+    if any(t.dtype != bf16 for t in (proj, convw, A_log, dt_bias)) or A_log.numel() != HV or dt_bias.numel() != HV:
+        # the reference reads these through bf16 pointers without a check (src/kernels.cu:1173-1283); fp32 parameters would
+        # be misread silently
+        raise RuntimeError("linattn_prep: proj, convw, A_log [HV] and dt_bias [HV] must be bf16")
     N = proj.shape[0]
     if proj.shape[1] != 2 * KD + 2 * VD + 2 * HV or hist.shape != (N + 1, 4) or hist.dtype != torch.int32:
         raise RuntimeError("linattn_prep: proj must be [N, 2KD+2VD+2HV] and hist int32 [N+1, 4]")

@@ -42,3 +42,19 @@ def test_argument_checks_need_no_gpu():
     rc = lib.ojb_tree_attn(one, one, one, one, one, None, one, ctypes.c_int64(33), ctypes.c_int64(4), ctypes.c_int64(2),
                            ctypes.c_int64(256), ctypes.c_int64(2), ctypes.c_float(1.0), None)
     assert rc == -1      # N must be a multiple of 32
+
+
+def test_gemm_plan_is_host_arithmetic():
+    """ojb_gemm_plan needs no GPU: it returns a valid variant, a split count within bounds, and a finite time."""
+    from ojb200 import lt_ext
+    for M, N, K, kind in [(544, 12352, 5120, 0), (544, 34816, 5120, 1), (544, 5120, 17408, 2), (64, 5120, 4096, 2), (16384, 5120, 17408, 2),
+                          (1, 16, 8, 0)]:
+        v, s, us = lt_ext.gemm_plan(M, N, K, kind)
+        assert v in (1, 2, 3, 4) and 1 <= s <= 16 and 0 < us < 1e6
+        if kind != 2:
+            assert s == 1
+        kb = -(-K // 64)
+        assert (s - 1) * -(-kb // s) < kb          # no empty K range
+    # more rows never make the modelled time shorter
+    t = [lt_ext.gemm_plan(M, 34816, 5120, 1)[2] for M in (256, 512, 1024, 2048, 4096)]
+    assert all(a <= b for a, b in zip(t, t[1:]))

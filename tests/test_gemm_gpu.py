@@ -24,12 +24,14 @@ def _close(out, ref):
     assert err <= tol, (err, tol)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 3, 5, 7])
+# lt_matmul indices: 0 planner, 1 / 2 tile128, 3 block256, 4-6 block256 with forced width, 7 block256 all swapped,
+# 8 / 9 CTA-pair kernel (automatic width / all swapped)
+@pytest.mark.parametrize("variant", [0, 1, 3, 4, 5, 7, 8, 9])
 @pytest.mark.parametrize("M,N,K", [(64, 512, 256), (16, 48, 64), (257, 300, 136), (400, 1000, 512), (1000, 520, 192), (128, 256, 64), (288, 1280, 5120), (539, 12352, 5120), (100, 200, 72),
                                    (1024, 5120, 6144), (544, 5120, 4096)])
 def test_gemm_plain(M, N, K, variant):
     from ojb200 import lt_ext, _lib
-    if variant == 7 and M > 512:
+    if variant in (7, 9) and M > 512:
         pytest.skip("the all-swapped form serves M <= 512")
     x, w = _mk(M, N, K, 1)
     out = lt_ext.lt_matmul(x, w, variant)
@@ -38,17 +40,18 @@ def test_gemm_plain(M, N, K, variant):
     _close(out, _ref(x, w))
 
 
-@pytest.mark.parametrize("variant", [0, 1, 3, 7])
-@pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120), (256, 256, 320), (700, 384, 512)])
+@pytest.mark.parametrize("variant", [0, 1, 3, 7, 8, 9])
+@pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120), (256, 256, 320), (700, 384, 512), (539, 2048, 1024)])
 def test_gemm_swiglu(M, I, K, variant):
     from ojb200 import lt_ext, _lib
-    if variant == 7 and M > 512:
+    if variant in (7, 9) and M > 512:
         pytest.skip("the all-swapped form serves M <= 512")
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(M, K, generator=g, device="cuda").to(bf16)
     wg = (torch.randn(I, K, generator=g, device="cuda") * 0.02).to(bf16)
     wu = (torch.randn(I, K, generator=g, device="cuda") * 0.02).to(bf16)
-    out = lt_ext.gemm_swiglu(x, lt_ext.interleave_gate_up(wg, wu), variant)
+    # the CTA-pair kernel reads gate / up interleaved in blocks of 64 rows, the other two in blocks of 128
+    out = lt_ext.gemm_swiglu(x, lt_ext.interleave_gate_up(wg, wu, 64 if variant in (8, 9) else 128), variant)
     torch.cuda.synchronize()
     _lib.check_status()
     gg = _ref(x, wg).to(bf16).float()
@@ -60,7 +63,7 @@ def test_gemm_swiglu(M, I, K, variant):
     assert err <= tol, (err, tol)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 7])
+@pytest.mark.parametrize("variant", [0, 1, 3, 7, 8])
 @pytest.mark.parametrize("M,N,K,S", [(64, 256, 256, 2), (288, 5120, 6144, 2), (544, 5120, 17408, 4), (539, 5120, 4096, 2),
                                      (544, 5120, 17408, 7), (64, 5120, 4096, 16), (300, 520, 1000, 3)])
 def test_gemm_splitk(M, N, K, S, variant):
@@ -78,3 +81,25 @@ def test_gemm_splitk(M, N, K, S, variant):
         ref = x[:, s * ks:(s + 1) * ks].float() @ w[:, s * ks:(s + 1) * ks].float().t()
         err = (parts[s] - ref).abs().max().item()
         assert err <= ref.abs().max().item() * 1e-4 + 1e-4, (s, err)
+
+
+def test_trace_hook_records_every_unit():
+    """The measurement hook appends one timeline record per work unit and leaves the result untouched."""
+    import ctypes
+    from ojb200 import lt_ext, _lib
+    x, w = _mk(544, 1024, 512, 4)
+    ref = lt_ext.lt_matmul(x, w, 4)
+    cap = 64
+    rec = torch.zeros(1 + 4 * cap, dtype=torch.int64, device="cuda")
+    _lib.call("ojb_gemm_set_trace", _lib.ptr(rec), _lib.i32(cap), _lib.i32(1), _lib.i32(0))
+    try:
+        out = lt_ext.lt_matmul(x, w, 4)
+        torch.cuda.synchronize()
+    finally:
+        _lib.call("ojb_gemm_set_trace", None, _lib.i32(0), _lib.i32(1), _lib.i32(0))
+    _lib.check_status()
+    assert torch.equal(out, ref)
+    r = rec.cpu()
+    assert int(r[0]) == 2 * 4 + 4            # two 256-row blocks and one tail unit per 256-wide w tile
+    t = r[1:1 + 4 * int(r[0])].view(-1, 4)
+    assert bool((t[:, 1] <= t[:, 2]).all()) and bool((t[:, 2] <= t[:, 3]).all())

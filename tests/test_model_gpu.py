@@ -89,6 +89,32 @@ def test_forward_gtree_matches_reference_path(case, tree_native):
     assert torch.equal(sc.argmax(0)[clear], ref_s.argmax(0)[clear])   # ... with identical argmax over the candidates
 
 
+def test_tune_picks_a_kernel_per_shape_and_keeps_the_result():
+    """FastQwen35.tune times the GEMM candidates per projection shape (the reference's _tune, src/fastmodel.py:114-156): it
+    must fill a plan for every shape of the row count, and the forward with the tuned kernels must agree with the untuned
+    forward to bf16 noise (different kernels differ only in fp32 summation order and split-K rounding points)."""
+    from ojb200 import fastmodel as FM
+    cfg, core = _small_model()
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()["example"]
+    seqs = [[t % cfg.vocab_size for t in s] for s in seqs]
+    fast = FM.FastQwen35(core.to("cuda"))
+    ids, lay = fast.gtree_build(seqs, groups, pad_id % cfg.vocab_size, NB, PB)
+    h0 = fast.forward_gtree(ids, lay).float()
+    rep = []
+    fast.tune(lay.N, report=rep)
+    assert lay.N in fast._tuned and {r["op"] for r in rep} == {"in-proj", "gate/up", "w_out", "w_down"}
+    for d in fast.L:
+        assert ("mm", lay.N) + tuple(d.w_in.shape) in fast._plan
+        assert ("res", lay.N) + tuple(d.w_out.shape) in fast._plan and ("res", lay.N) + tuple(d.w_down.shape) in fast._plan
+    n_plan = len(fast._plan)
+    fast.tune(lay.N)                       # second call is a no-op
+    assert len(fast._plan) == n_plan
+    h1 = fast.forward_gtree(ids, lay).float()
+    from ojb200 import _lib
+    _lib.check_status()
+    assert ((h1 - h0).norm() / h0.norm()).item() < 2.5e-2      # the bf16 noise of an 8-layer forward (see the test above)
+
+
 def test_batch_forward_matches_reference_path():
     from ojb200 import fastmodel as FM
     cfg, core = _small_model(seed=2)

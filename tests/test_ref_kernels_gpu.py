@@ -1,0 +1,200 @@
+"""Operator-for-operator comparison with the reference's own CUDA kernels, rebuilt for sm_100a (oracle/build_ref_kernels.py
+compiles open-jev-fast's src/kernels.cu where it lies; only the built module travels). Every operator of the hot loop
+(src/fastmodel.py:400-482) gets the same seeded inputs on both sides, on the 539-row benchmark tree and the example-shaped
+tree. Skipped when the reference module has not been built."""
+import json
+import os
+
+import pytest
+import torch
+
+import trees
+
+pytestmark = pytest.mark.gpu
+bf16 = torch.bfloat16
+DIMS = dict(H=5120, KD=2048, VD=4096, HV=32, HK=16, HD=128, HQ=24, HKV=4, D=256, RD=64, I=17408)
+_times = {}
+
+
+@pytest.fixture(scope="module")
+def R():
+    from oracle import build_ref_kernels
+    mod = build_ref_kernels.load()
+    if mod is None:
+        pytest.skip("reference operators not built (python oracle/build_ref_kernels.py)")
+    return mod
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ojb200 import ext
+    return ext.load()
+
+
+@pytest.fixture(scope="module", params=["baseline", "example"])
+def lay(request):
+    from ojb200 import layout as PL
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()[request.param]
+    ids, lay = PL.gtree_build(seqs, groups, pad_id, NB, PB, dev="cuda", dense=True)
+    lay.case = request.param
+    return lay
+
+
+def _rand(gen, *shape, std=1.0, dtype=bf16):
+    return (torch.randn(*shape, generator=gen, device="cuda") * std).to(dtype)
+
+
+def _time(fn, reps=10):
+    """Microseconds per call from a CUDA graph of `reps` calls (host launch overhead excluded on both sides)."""
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        fn()
+    torch.cuda.current_stream().wait_stream(st)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    graph.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(3):
+        graph.replay()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) * 1e3 / (3 * reps)
+
+
+def _both(name, case, ref_fn, our_fn):
+    """Run both sides, record their times (microseconds, back-to-back graph launches, inputs L2-resident)."""
+    r, o = ref_fn(), our_fn()
+    torch.cuda.synchronize()
+    _times[f"{name} [{case}]"] = dict(reference_us=round(_time(ref_fn), 2), ours_us=round(_time(our_fn), 2))
+    return r, o
+
+
+def _ulps(a, b):
+    """Largest difference in units of the bf16 spacing at the larger magnitude, and the fraction of unequal elements."""
+    a32, b32 = a.float(), b.float()
+    d = (a32 - b32).abs()
+    mag = torch.maximum(a32.abs(), b32.abs()).clamp_min(2.0 ** -126)
+    spacing = torch.exp2(torch.floor(torch.log2(mag)) - 7)
+    return (d / spacing).max().item(), (d > 0).float().mean().item()
+
+
+def teardown_module(module):
+    out = os.environ.get("OJ_REF_TIMES")
+    if out and _times:
+        with open(out, "w") as f:
+            json.dump(_times, f, indent=1, sort_keys=True)
+
+
+def test_add_rmsnorm_and_splitk_reduce(R, K, lay):
+    g = torch.Generator(device="cuda").manual_seed(11)
+    N, H = lay.N, DIMS["H"]
+    x, delta = _rand(g, N, H), _rand(g, N, H)
+    w1 = (1.0 + torch.randn(H, generator=g, device="cuda") * 0.02).float()
+    for mask in (None, lay.rowmask):
+        (rh, rhn), (oh, ohn) = _both("add_rmsnorm", lay.case, lambda: R.add_rmsnorm(x.clone(), delta, w1, mask, 1e-6),
+                                     lambda: K.add_rmsnorm(x.clone(), delta, w1, mask, 1e-6))
+        assert torch.equal(rh, oh)                       # h = bf16(x + delta): no freedom
+        u, frac = _ulps(rhn, ohn)
+        assert u <= 1.0 and frac < 2e-3, (u, frac)       # hn: the row's fp32 sum of squares may be added in another order
+    parts = torch.randn(2, N, H, generator=g, device="cuda")
+    (rh, rhn), (oh, ohn) = _both("add_rmsnorm_sk2", lay.case, lambda: R.add_rmsnorm_sk2(x.clone(), parts, w1, lay.rowmask, 1e-6),
+                                 lambda: K.add_rmsnorm_sk2(x.clone(), parts, w1, lay.rowmask, 1e-6))
+    assert torch.equal(rh, oh)
+    u, frac = _ulps(rhn, ohn)
+    assert u <= 1.0 and frac < 2e-3, (u, frac)
+
+
+def test_activation_tables_and_silu_mul(R, K, lay):
+    g = torch.Generator(device="cuda").manual_seed(12)
+    like = _rand(g, 8, 8)
+    rt, ot = R.act_tables(like), K.act_tables(like)
+    same = lambda a, b: bool(((a == b) | (a.isnan() & b.isnan())).all())     # the entries of NaN inputs are NaN on both sides
+    assert len(rt) == len(ot) == 2 and all(a.dtype == b.dtype and a.shape == b.shape and same(a, b) for a, b in zip(rt, ot))
+    gu = _rand(g, lay.N, 2 * DIMS["I"], std=2.0)
+    r, o = _both("silu_mul_lut", lay.case, lambda: R.silu_mul_lut(gu, rt[0]), lambda: K.silu_mul_lut(gu, ot[0]))
+    assert torch.equal(r, o)
+
+
+def test_pack_bits_and_gate_mul(R, K, lay):
+    g = torch.Generator(device="cuda").manual_seed(13)
+    vis = lay.amask[0, 0].contiguous()
+    assert torch.equal(R.pack_bits(vis), K.pack_bits(vis))
+    assert torch.equal(R.pack_bits(vis).view(-1), lay.vbits.view(-1))
+    N, HQ, D = lay.N, DIMS["HQ"], DIMS["D"]
+    att, gate = _rand(g, 1, HQ, N, D), _rand(g, N, HQ * D)
+    sig = R.act_tables(att)[1]
+    r, o = _both("gate_mul3", lay.case, lambda: R.gate_mul3(att, gate, sig, N, HQ, D), lambda: K.gate_mul3(att, gate, sig, N, HQ, D))
+    assert torch.equal(r, o)
+
+
+def test_gdn_prep_core_and_gated_norm(R, K, lay):
+    g = torch.Generator(device="cuda").manual_seed(14)
+    d = DIMS
+    N, S, L2 = lay.N, lay.S, lay.L2
+    C = 2 * d["KD"] + d["VD"]
+    proj = _rand(g, N, C + d["VD"] + 2 * d["HV"])
+    convw = _rand(g, C, 4, std=0.5)
+    A_log = torch.log(torch.rand(d["HV"], generator=g, device="cuda") * 16.0).to(bf16)      # Hugging Face initialisation
+    dt_bias = torch.ones(d["HV"], device="cuda", dtype=bf16)
+    args = (proj, lay.hist, lay.rep_ptr, lay.rep_pos, L2, convw, A_log, dt_bias, d["KD"], d["VD"], d["HV"], d["HK"], d["HD"], False)
+    rp, op = _both("linattn_prep_dedup2", lay.case, lambda: R.linattn_prep_dedup2(*args), lambda: K.linattn_prep_dedup2(*args))
+    for name, a, b in zip("q k v g beta".split(), rp, op):
+        assert a.shape == b.shape and a.dtype == b.dtype, name
+        if a.dtype == bf16:
+            u, frac = _ulps(a, b)
+            assert u <= 1.0 and frac < 5e-3, (name, u, frac)     # conv / L2-norm sums in fp32, one bf16 rounding at the end
+        else:
+            assert bool(a.isfinite().all()) and torch.allclose(a, b, rtol=2e-6, atol=1e-7), name
+    q, k, v, gg, beta = rp
+    ga = (q.view(S, L2, d["HK"], d["HD"]), k.view(S, L2, d["HK"], d["HD"]), v.view(S, L2, d["HV"], d["HD"]), gg.view(S, L2, d["HV"]),
+          beta.view(S, L2, d["HV"]), d["HD"] ** -0.5)
+    ro, oo = _both("gdn_fused6", lay.case, lambda: R.gdn_fused6(*ga), lambda: K.gdn_fused6(*ga))
+    real = lay.src.view(S, L2) >= 0                    # slots that hold a real packed row
+    rr, orr = ro[real].float(), oo[real].float()
+    assert not orr.isnan().any(), ("ours", int(orr.isnan().sum()))
+    assert not rr.isnan().any(), ("reference", int(rr.isnan().sum()))
+    rel = ((rr - orr).norm() / rr.norm()).item()
+    # two different blockings of the same chunked recurrence, both with bf16 operands on the tensor cores: the reference
+    # reports 3-6e-3 relative for its own kernel against FLA
+    assert rel < 6e-3, rel
+    normw = (1.0 + torch.randn(d["HD"], generator=g, device="cuda") * 0.02).to(bf16)
+    sig = R.act_tables(proj)[1]
+    zoff = 2 * d["KD"] + d["VD"]
+    ry, oy = _both("gated_rmsnorm_inv2", lay.case, lambda: R.gated_rmsnorm_inv2(ro, lay.inv, proj, normw, sig, d["HV"], d["HD"], zoff, 1e-6),
+                   lambda: K.gated_rmsnorm_inv2(ro, lay.inv, proj, normw, sig, d["HV"], d["HD"], zoff, 1e-6))
+    u, frac = _ulps(ry, oy)
+    assert u <= 1.0 and frac < 5e-3, (u, frac)
+
+
+def test_attention_prep_and_tree_attention(R, K, lay):
+    g = torch.Generator(device="cuda").manual_seed(15)
+    d = DIMS
+    N, HQ, HKV, D, RD = lay.N, d["HQ"], d["HKV"], d["D"], d["RD"]
+    proj = _rand(g, N, 2 * HQ * D + 2 * HKV * D)
+    qw1 = (1.0 + torch.randn(D, generator=g, device="cuda") * 0.02).float()
+    kw1 = (1.0 + torch.randn(D, generator=g, device="cuda") * 0.02).float()
+    inv_freq = 1.0 / (10000 ** (torch.arange(0, RD, 2, device="cuda").float() / RD))
+    ang = lay.pos.float()[:, None] * inv_freq[None]
+    cosb, sinb = torch.cat([ang.cos()] * 2, -1).to(bf16).contiguous(), torch.cat([ang.sin()] * 2, -1).to(bf16).contiguous()
+    args = (proj, qw1, kw1, cosb, sinb, 1, N, HQ, HKV, D, 1e-6)
+    rp, op = _both("fullattn_prep2", lay.case, lambda: R.fullattn_prep2(*args), lambda: K.fullattn_prep2(*args))
+    for name, a, b in zip("qt kt vt gate".split(), rp, op):
+        assert a.shape == b.shape, name
+        u, frac = _ulps(a, b)
+        assert u <= 1.0 and frac < 5e-3, (name, u, frac)
+    qt, kt, vt, gate = rp
+    sig = R.act_tables(proj)[1]
+    scale = D ** -0.5
+    for gq in (3, 6):
+        ry, oy = _both(f"fattn_tree gq={gq}", lay.case, lambda: R.fattn_tree(qt, kt, vt, gate, sig, lay.vbits, scale, gq),
+                       lambda: K.fattn_tree(qt, kt, vt, gate, sig, lay.vbits, scale, gq))
+        real = lay.rowmask.bool()
+        rel = ((ry[real].float() - oy[real].float()).norm() / ry[real].float().norm()).item()
+        assert rel < 3e-3, rel                            # same online softmax with bf16 P; block order differs
+        assert (ry[real].float() - oy[real].float()).abs().max().item() < 3e-2
