@@ -1,5 +1,6 @@
 // Shared device/host helpers for the ojb200 kernels (sm_100a only).
 #pragma once
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -55,6 +56,44 @@ __device__ __forceinline__ void report_status(int32_t* status, int32_t code) {
 }
 
 static inline int launch_status(cudaError_t e) { return e == cudaSuccess ? OJB_OK : OJB_ERR_LAUNCH; }
+
+// ---- Programmatic dependent launch (off unless OJB_PDL=1 is in the environment). Every kernel of the hot loop goes through
+// launch_kernel() and begins with pdl_begin(): with the stream-serialisation attribute set, the next kernel of the stream
+// may be scheduled as soon as all CTAs of this one have started (its CTAs fill SMs that this grid leaves idle, set up their
+// shared memory / barriers / TMEM, and park at their own pdl_wait), and pdl_wait() blocks until the previous kernel has
+// completed and its writes are visible. No global memory may be read or written before pdl_wait(). Measured on the 539-row
+// tree: 32.9 ms with the attribute against 32.6 ms without, at 1650 against 1695 MHz — the forward runs against the power
+// cap, so closing the gaps between kernels only lowers the clock; without the attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_begin() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("OJB_PDL");
+    on = (e && e[0] == '1') ? 1 : 0;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 #define OJB_REQUIRE(cond)             \
   do {                                \

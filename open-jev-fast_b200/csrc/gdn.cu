@@ -65,6 +65,7 @@ gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, 
                 const int32_t* __restrict__ rep_pos, const bf16_t* __restrict__ convw, const bf16_t* __restrict__ A_log,
                 const bf16_t* __restrict__ dt_bias, bf16_t* __restrict__ q, bf16_t* __restrict__ k, bf16_t* __restrict__ v,
                 float* __restrict__ g, bf16_t* __restrict__ beta, int N, int KD, int VD, int HV) {
+  pdl_begin();
   const int C = 2 * KD + VD, P = C + VD + 2 * HV;
   const int n = blockIdx.y;
   int4 hr = make_int4(-1, -1, -1, -1);
@@ -160,6 +161,7 @@ __global__ void __launch_bounds__(kIntraThreads)
 gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, const bf16_t* __restrict__ v,
                  const float* __restrict__ g, const bf16_t* __restrict__ beta, const int32_t* __restrict__ chunks,
                  bf16_t* __restrict__ scratch, int HK, int HV, float scale) {
+  pdl_begin();
   const int4 ch = reinterpret_cast<const int4*>(chunks)[blockIdx.x];
   const int row0 = ch.x, nrows = ch.y;
   if (nrows <= 0) return;
@@ -437,6 +439,7 @@ __global__ void __launch_bounds__(kStateThreads)
 gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__ chunks, const int32_t* __restrict__ steps,
                  const int32_t* __restrict__ walk_ptr, const float* __restrict__ init_state, float* __restrict__ final_state,
                  bf16_t* __restrict__ out, int HV) {
+  pdl_begin();
   const int h = blockIdx.x, dv0 = blockIdx.y * kDv;
   const int s_begin = walk_ptr[blockIdx.z], s_end = walk_ptr[blockIdx.z + 1];
   if (s_begin >= s_end) return;
@@ -666,6 +669,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_kernel(const bf16_t* __restrict__ x, const int32_t* __restrict__ inv, const bf16_t* __restrict__ proj,
                      const bf16_t* __restrict__ w, bf16_t* __restrict__ out, int64_t items, int HV, int zoff, int P, float eps) {
+  pdl_begin();
   const int64_t it = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (it >= items) return;
   const int lane = threadIdx.x & 31;
@@ -712,14 +716,14 @@ extern "C" int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t
   if (rep_ptr != nullptr) {
     OJB_REQUIRE(rep_pos != nullptr && n_slots > 0);
     dim3 grid(gx, static_cast<unsigned>(N + ceil_div(n_slots, 16)));
-    gdn_prep_kernel<true><<<grid, 256, 0, st>>>(static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), rep_ptr, rep_pos,
+    launch_kernel(gdn_prep_kernel<true>, dim3(grid), dim3(256), 0, st, static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), rep_ptr, rep_pos,
                                                 static_cast<const bf16_t*>(convw), static_cast<const bf16_t*>(A_log),
                                                 static_cast<const bf16_t*>(dt_bias), static_cast<bf16_t*>(q), static_cast<bf16_t*>(k),
                                                 static_cast<bf16_t*>(v), g, static_cast<bf16_t*>(beta), static_cast<int>(N),
                                                 static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV));
   } else {
     dim3 grid(gx, static_cast<unsigned>(N));
-    gdn_prep_kernel<false><<<grid, 256, 0, st>>>(static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), nullptr, nullptr,
+    launch_kernel(gdn_prep_kernel<false>, dim3(grid), dim3(256), 0, st, static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), nullptr, nullptr,
                                                  static_cast<const bf16_t*>(convw), static_cast<const bf16_t*>(A_log),
                                                  static_cast<const bf16_t*>(dt_bias), static_cast<bf16_t*>(q), static_cast<bf16_t*>(k),
                                                  static_cast<bf16_t*>(v), g, static_cast<bf16_t*>(beta), static_cast<int>(N),
@@ -745,11 +749,11 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
       return OJB_ERR_LAUNCH;
     attr = true;
   }
-  gdn_intra_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), kIntraThreads, kIntraSmem, st>>>(
+  launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
-  gdn_state_kernel<false><<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
+  launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out),
       static_cast<int>(HV));
   return launch_status(cudaGetLastError());
@@ -760,7 +764,7 @@ extern "C" int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* 
   if (N == 0) return OJB_OK;
   OJB_REQUIRE(x && proj && w && out && N > 0 && HV > 0 && HD == kHD && zoff >= 0 && zoff + HV * HD <= P && zoff % 4 == 0 && P % 4 == 0);
   const int64_t items = N * HV;
-  gated_rmsnorm_kernel<<<static_cast<unsigned>(ceil_div(items, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(gated_rmsnorm_kernel, dim3(static_cast<unsigned>(ceil_div(items, 8))), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const bf16_t*>(x), inv, static_cast<const bf16_t*>(proj), static_cast<const bf16_t*>(w), static_cast<bf16_t*>(out),
       items, static_cast<int>(HV), static_cast<int>(zoff), static_cast<int>(P), eps);
   return launch_status(cudaGetLastError());
@@ -806,11 +810,11 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // Nothing in the array has to start at zero: the first kernel overwrites every byte of every item that the second one
   // reads (items of unused chunk-table entries are neither written nor read).
-  gdn_intra_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), kIntraThreads, kIntraSmem, st>>>(
+  launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, scratch, static_cast<int>(HK), static_cast<int>(HV), scale);
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
-  gdn_state_kernel<false><<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)), kStateThreads, kStateSmem, st>>>(
+  launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
   return launch_status(cudaGetLastError());
 }
@@ -836,7 +840,7 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
       return OJB_ERR_LAUNCH;
     attr = true;
   }
-  gdn_intra_kernel<<<dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), kIntraThreads, kIntraSmem, st>>>(
+  launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
@@ -844,11 +848,11 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
     const int nw = levels[l + 1] - levels[l];
     if (nw == 0) continue;
     if (nw > 1) {   // many short walks: the lean form fits two CTAs per SM
-      gdn_state_kernel<true><<<dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(nw)), kStateThreads, kStateSmemLean, st>>>(
+      launch_kernel(gdn_state_kernel<true>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(nw))), dim3(kStateThreads), kStateSmemLean, st, 
           static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
           static_cast<int>(HV));
     } else {
-      gdn_state_kernel<false><<<dim3(static_cast<unsigned>(HV), kHD / kDv, 1), kStateThreads, kStateSmem, st>>>(
+      launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, 1)), dim3(kStateThreads), kStateSmem, st, 
           static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
           static_cast<int>(HV));
     }

@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt,
                     const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_w128, GemmArgs g) {
+  pdl_launch_dependents();
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -89,6 +90,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();      // from here on the previous kernel of the stream has completed
 
   const int total_block = g.n_xblk * g.n_wtile * g.splits;
   const int total_units = total_block + (g.tail_rows > 0 ? g.n_wtile256 * g.splits * g.n_xchunk : 0);
@@ -569,7 +571,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     while (grid > 1 && gcd(grid, group) != 1) --grid;
   }
   const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
-  kern<<<grid, kGemmThreads, smem, stream>>>(map_x, map_w, map_w256, map_xt, map_out, map_w128, g);
+  launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, stream, map_x, map_w, map_w256, map_xt, map_out, map_w128, g);
   return launch_status(cudaGetLastError());
 }
 

@@ -133,6 +133,7 @@ template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_wh,
                     const __grid_constant__ CUtensorMap map_w128, const __grid_constant__ CUtensorMap map_xt, GemmArgs g) {
+  pdl_launch_dependents();
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -177,6 +178,7 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
   cluster_sync_all();      // the barriers of both CTAs exist before any remote arrive or copy completion reaches them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();      // from here on the previous kernel of the stream has completed
 
   const int total_block = g.n_xblk * g.n_wtile * g.splits;
   const int total_units = total_block + (g.tail_rows > 0 ? g.n_wtile256 * g.splits * g.n_xchunk : 0);
@@ -500,7 +502,7 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     while (n_pairs > 1 && gcd(n_pairs, group) != 1) --n_pairs;
   }
   const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
-  kern<<<2 * n_pairs, kPairThreads, smem, stream>>>(map_xh, map_wh, map_w128, map_xt, g);
+  launch_kernel(kern, dim3(2 * n_pairs), dim3(kPairThreads), smem, stream, map_xh, map_wh, map_w128, map_xt, g);
   return launch_status(cudaGetLastError());
 }
 

@@ -42,6 +42,7 @@ struct SmemPlan {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tile128_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, GemmArgs g) {
+  pdl_launch_dependents();
   using Plan = SmemPlan<BN, STAGES>;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns (256 or 512: both powers of two)
   extern __shared__ uint8_t smem_raw[];
@@ -80,6 +81,7 @@ gemm_tile128_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();      // from here on the previous kernel of the stream has completed
 
   const int total_units = g.num_m * g.num_n * g.splits;
 
@@ -290,7 +292,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   if (sms <= 0) return OJB_ERR_LAUNCH;
   const int64_t units = static_cast<int64_t>(g.num_m) * g.num_n * splits;
   const int grid = static_cast<int>(units < sms ? units : sms);
-  kern<<<grid, kGemmThreads, Plan::kTotal, stream>>>(map_x, map_w, g);
+  launch_kernel(kern, dim3(grid), dim3(kGemmThreads), Plan::kTotal, stream, map_x, map_w, g);
   return launch_status(cudaGetLastError());
 }
 

@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(kRowThreads)
 add_rmsnorm_kernel(const bf16_t* __restrict__ x, const bf16_t* __restrict__ delta, const float* __restrict__ parts,
                    int64_t part_stride, const float* __restrict__ w1, const int32_t* __restrict__ rowmask,
                    bf16_t* __restrict__ h_out, bf16_t* __restrict__ hn_out, int H, float eps) {
+  pdl_begin();
   __shared__ float red[kRowThreads / 32];
   const int64_t row = blockIdx.x;
   const int nvec = H >> 3;
@@ -102,6 +103,7 @@ __global__ void act_tables_kernel(bf16_t* __restrict__ silu_tab, float* __restri
 // 8 outputs per thread; gate at column c, up at column I + c of the same row.
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const bf16_t* __restrict__ gu, const bf16_t* __restrict__ tab, bf16_t* __restrict__ out, int I, int64_t nvec) {
+  pdl_begin();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= nvec) return;
   const int vec_per_row = I >> 3;
@@ -127,6 +129,7 @@ silu_mul_kernel(const bf16_t* __restrict__ gu, const bf16_t* __restrict__ tab, b
 __global__ void __launch_bounds__(256)
 gate_mul_kernel(const bf16_t* __restrict__ att, int64_t stride_t, int64_t stride_h, const bf16_t* __restrict__ gate,
                 bf16_t* __restrict__ y, int HQ, int D, int64_t nvec) {
+  pdl_begin();
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= nvec) return;
   const int64_t e0 = i * 8;
@@ -162,6 +165,7 @@ fullattn_prep_kernel(const bf16_t* __restrict__ proj, const float* __restrict__ 
                      const bf16_t* __restrict__ cosb, const bf16_t* __restrict__ sinb, bf16_t* __restrict__ qt,
                      bf16_t* __restrict__ kt, bf16_t* __restrict__ vt, bf16_t* __restrict__ gate, int64_t N, int HQ, int HKV,
                      int D, int RD, float eps) {
+  pdl_begin();
   const int ntask = HQ + 2 * HKV;
   const int64_t wid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= N * ntask) return;
@@ -249,7 +253,7 @@ extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1
   OJB_REQUIRE(x && w1 && hn_out && rows > 0 && H > 0 && H % 8 == 0);
   OJB_REQUIRE(delta == nullptr || h_out != nullptr);
   if (H > kRowThreads * kRowVecs * 8) return OJB_ERR_LIMIT;
-  add_rmsnorm_kernel<0><<<static_cast<unsigned>(rows), kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(add_rmsnorm_kernel<0>, dim3(static_cast<unsigned>(rows)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const bf16_t*>(x), static_cast<const bf16_t*>(delta), nullptr, 0, w1, rowmask,
       static_cast<bf16_t*>(h_out), static_cast<bf16_t*>(hn_out), static_cast<int>(H), eps);
   return launch_status(cudaGetLastError());
@@ -264,7 +268,7 @@ extern "C" int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits,
   const int64_t ps = rows * H;
 #define OJB_SK(S)                                                                                                     \
   case S:                                                                                                             \
-    add_rmsnorm_kernel<S><<<static_cast<unsigned>(rows), kRowThreads, 0, st>>>(                                       \
+    launch_kernel(add_rmsnorm_kernel<S>, dim3(static_cast<unsigned>(rows)), dim3(kRowThreads), 0, st,                                        \
         static_cast<const bf16_t*>(x), nullptr, parts, ps, w1, rowmask, static_cast<bf16_t*>(h_out),                  \
         static_cast<bf16_t*>(hn_out), static_cast<int>(H), eps);                                                      \
     break;
@@ -286,7 +290,7 @@ extern "C" int ojb_silu_mul(const void* gu, const void* silu_tab, void* out, int
   OJB_REQUIRE(gu && out && rows >= 0 && I > 0 && I % 8 == 0);
   const int64_t nvec = rows * I / 8;
   if (nvec == 0) return OJB_OK;
-  silu_mul_kernel<<<static_cast<unsigned>(ceil_div(nvec, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(silu_mul_kernel, dim3(static_cast<unsigned>(ceil_div(nvec, 256))), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const bf16_t*>(gu), static_cast<const bf16_t*>(silu_tab), static_cast<bf16_t*>(out), static_cast<int>(I), nvec);
   return launch_status(cudaGetLastError());
 }
@@ -296,7 +300,7 @@ extern "C" int ojb_gate_mul(const void* att, int64_t att_stride_t, int64_t att_s
   OJB_REQUIRE(att && gate && y && T >= 0 && HQ > 0 && D > 0 && D % 8 == 0 && att_stride_t % 8 == 0 && att_stride_h % 8 == 0);
   const int64_t nvec = T * HQ * D / 8;
   if (nvec == 0) return OJB_OK;
-  gate_mul_kernel<<<static_cast<unsigned>(ceil_div(nvec, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(gate_mul_kernel, dim3(static_cast<unsigned>(ceil_div(nvec, 256))), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const bf16_t*>(att), att_stride_t, att_stride_h, static_cast<const bf16_t*>(gate), static_cast<bf16_t*>(y),
       static_cast<int>(HQ), static_cast<int>(D), nvec);
   return launch_status(cudaGetLastError());
@@ -322,7 +326,7 @@ extern "C" int ojb_fullattn_prep(const void* proj, const float* qw1, const float
   const unsigned grid = static_cast<unsigned>(ceil_div(warps, 8));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define OJB_PREP(P)                                                                                                     \
-  fullattn_prep_kernel<P><<<grid, 256, 0, st>>>(static_cast<const bf16_t*>(proj), qw1, kw1,                             \
+  launch_kernel(fullattn_prep_kernel<P>, dim3(grid), dim3(256), 0, st, static_cast<const bf16_t*>(proj), qw1, kw1,                             \
                                                 static_cast<const bf16_t*>(cosb), static_cast<const bf16_t*>(sinb),     \
                                                 static_cast<bf16_t*>(qt), static_cast<bf16_t*>(kt),                     \
                                                 static_cast<bf16_t*>(vt), static_cast<bf16_t*>(gate), N,                \
@@ -340,6 +344,7 @@ namespace {
 __global__ void __launch_bounds__(256)
 score_head_kernel(const bf16_t* __restrict__ hn, const int64_t* __restrict__ rows, const float* __restrict__ W,
                   const float* __restrict__ bias, float* __restrict__ out, int S, int A, int H) {
+  pdl_begin();
   const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= S * A) return;
   const int lane = threadIdx.x & 31;
@@ -364,7 +369,7 @@ extern "C" int ojb_score_head(const void* hn, const int64_t* rows, const float* 
   if (S == 0 || A == 0) return OJB_OK;
   OJB_REQUIRE(hn && rows && W && out && S > 0 && A > 0 && H > 0 && H % 8 == 0);
   const int64_t warps = S * A;
-  ojb::score_head_kernel<<<static_cast<unsigned>(ojb::ceil_div(warps, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(ojb::score_head_kernel, dim3(static_cast<unsigned>(ojb::ceil_div(warps, 8))), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const ojb::bf16_t*>(hn), rows, W, bias, out, static_cast<int>(S), static_cast<int>(A), static_cast<int>(H));
   return ojb::launch_status(cudaGetLastError());
 }

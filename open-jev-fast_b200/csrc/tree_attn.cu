@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(384)
 tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, const bf16_t* __restrict__ vt,
                  const bf16_t* __restrict__ gate, const int32_t* __restrict__ vbits, const int32_t* __restrict__ krange,
                  bf16_t* __restrict__ y, int N, int HQ, int HKV, int GQ, float scale_log2e) {
+  pdl_begin();
   constexpr int kLd = D + 8;                    // padded shared-memory row (bf16)
   const int nheads = GQ;                        // query heads of this CTA; warp = split * GQ + head
   const int G = HQ / HKV;                       // query heads per kv head
@@ -283,7 +284,7 @@ int launch_attn(const void* qt, const void* kt, const void* vt, const void* gate
   }
   const int G = static_cast<int>(HQ / HKV);
   dim3 grid(static_cast<unsigned>(HKV * (G / GQ)), static_cast<unsigned>(N / kRows));
-  kern<<<grid, static_cast<unsigned>(GQ * kSplit * 32), smem, st>>>(static_cast<const bf16_t*>(qt), static_cast<const bf16_t*>(kt),
+  launch_kernel(kern, dim3(grid), dim3(static_cast<unsigned>(GQ * kSplit * 32)), smem, st, static_cast<const bf16_t*>(qt), static_cast<const bf16_t*>(kt),
                                                           static_cast<const bf16_t*>(vt), static_cast<const bf16_t*>(gate), vbits,
                                                           krange, static_cast<bf16_t*>(y), static_cast<int>(N), static_cast<int>(HQ),
                                                           static_cast<int>(HKV), static_cast<int>(GQ), scale * 1.4426950408889634f);
