@@ -147,6 +147,14 @@ class FastQwen35(torch.nn.Module):
         if (M in self._tuned or M > self.TUNE_MAX_ROWS) and not force:
             return
         self._tuned.add(M)
+        cache = os.environ.get("OJ_TUNE_CACHE")      # optional file that pins the choices across processes (profiling runs)
+        if cache and os.path.exists(cache) and not force:
+            import json
+            saved = json.load(open(cache)).get(str(M))
+            if saved is not None:
+                for k, v in saved:
+                    self._plan[tuple(k)] = tuple(v) if isinstance(v, list) else v
+                return
         dev = self.L[0].w_down.device
         g = torch.Generator(device=dev).manual_seed(1234)
         rnd = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.5).to(torch.bfloat16)
@@ -205,6 +213,11 @@ class FastQwen35(torch.nn.Module):
                 if report is not None:
                     report.append(dict(op=attr, M=M, N=N, K=Kd, us={f"v{i} S{S}": round(t, 1) for (i, S), t in res.items()}, best=best))
         torch.cuda.synchronize(dev)
+        if cache:
+            import json
+            allp = json.load(open(cache)) if os.path.exists(cache) else {}
+            allp[str(M)] = [[list(k), list(v) if isinstance(v, tuple) else v] for k, v in self._plan.items() if k[1] == M]
+            json.dump(allp, open(cache, "w"))
 
     gtree_build = staticmethod(_layout.gtree_build)
 
