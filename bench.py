@@ -132,7 +132,8 @@ def run_reference(args, cfg_kwargs, seqs, n_lin, n_full):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM from the ncu captures summarised in profiles/
 # (bytes; keyed by M). The algorithmic bytes are weights + x + out = 381.0 MB at M = 544.
-TRAFFIC_NCU = {544: 395.3e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM at M = 544 (profiles/gemm_swiglu_m544_ncu_full.md)
+TRAFFIC_NCU = {("gemm_block256", 544): 394.8e6, ("gemm_tile128", 544): 389.1e6}
 
 
 def gemm_roofline(fast, M, pk, pk_kind, dev):
@@ -163,7 +164,7 @@ def gemm_roofline(fast, M, pk, pk_kind, dev):
     code = LT.VARIANT_BN[idx] if idx else LT.gemm_plan(M, N2_, Kd_, 1)[0]
     kern = {1: "gemm_tile128_kernel<256,4,swiglu>", 2: "gemm_tile128_kernel<128,6,swiglu>"}.get(code, "gemm_block256_kernel<swiglu>")
     return {"bound": "tensor", "kernel": kern + " (gate/up GEMM + SwiGLU, 64 launches per forward)", "achieved": ach, "peak": peak,
-            "unit": "TFLOP/s", "frac": ach / peak, "traffic": TRAFFIC_NCU.get(M), "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
+            "unit": "TFLOP/s", "frac": ach / peak, "traffic": TRAFFIC_NCU.get((kern.split("_kernel")[0], M)), "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
             "algorithmic_flops_per_launch": flops, "weight_stream_gbs": w_gbs, "hbm_peak_gbs": pk["hbm_gbs"]}
 
 
