@@ -6,7 +6,9 @@
 // The mask comes either from the packed visibility words vbits[N, N/32] of the reference layout or from three half-open
 // key ranges per row (root, own question stem, own leaf up to the row itself) — the second form needs O(N) memory instead
 // of O(N^2). Q K^T and P V run on the tensor cores (mma.sync m16n8k16 bf16, fp32 accumulate), the softmax is the online
-// form in the exp2 domain; K / V tiles are double-buffered with cp.async.
+// form in the exp2 domain (ex2.approx); K / V tiles are double-buffered with cp.async. OJB_ATTN_SPLIT=1 in the environment
+// selects one warp per head (half the shared memory, two CTAs per SM); measured slower than the default of two on both
+// benchmark trees (57 vs 47 us at 544 rows, 22 vs 19 us at 288).
 #include "common.cuh"
 
 namespace ojb {
@@ -14,7 +16,6 @@ namespace {
 
 constexpr int kRows = 16;     // query rows per CTA
 constexpr int kKeys = 32;     // keys per block = one visibility word
-constexpr int kSplit = 2;     // warps per query head, interleaved over the visible key blocks
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -35,6 +36,12 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // bits of keys [32*kb, 32*kb+32) that fall in [lo, hi)
 __device__ __forceinline__ uint32_t range_word(int lo, int hi, int kb) {
   const int a = max(lo - kb * 32, 0), b = min(hi - kb * 32, 32);
@@ -43,8 +50,9 @@ __device__ __forceinline__ uint32_t range_word(int lo, int hi, int kb) {
   return upto_b & ~((1u << a) - 1u);
 }
 
-template <int D>
-__global__ void __launch_bounds__(384)
+// kSplit = warps per query head, interleaved over the visible key blocks (1 or 2)
+template <int D, int kSplit>
+__global__ void __launch_bounds__(192 * kSplit)
 tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, const bf16_t* __restrict__ vt,
                  const bf16_t* __restrict__ gate, const int32_t* __restrict__ vbits, const int32_t* __restrict__ krange,
                  bf16_t* __restrict__ y, int N, int HQ, int HKV, int GQ, float scale_log2e) {
@@ -181,31 +189,30 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
     }
-    float alpha[2], rs[2] = {0.f, 0.f};
+    float alpha[2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) { alpha[h] = exp2f(m_run[h] - mx[h]); m_run[h] = mx[h]; }
+    for (int h = 0; h < 2; ++h) {
+      alpha[h] = ex2_approx(m_run[h] - mx[h]);
+      m_run[h] = mx[h];
+      l_run[h] *= alpha[h];          // per-thread partial row sums: the four lanes of a row are added once, at the end
+    }
     uint32_t pa[2][4];   // P as A fragments of the two 16-key steps
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       float p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        p[e] = exp2f(s[nt][e] - mx[e >> 1]);
-        p[e] = round_bf(p[e]);          // the row sum uses the same rounded values that multiply V
-        rs[e >> 1] += p[e];
+        p[e] = ex2_approx(s[nt][e] - mx[e >> 1]);
+        l_run[e >> 1] += p[e];
       }
       pa[nt >> 1][(nt & 1) * 2 + 0] = pack2(p[0], p[1]);
       pa[nt >> 1][(nt & 1) * 2 + 1] = pack2(p[2], p[3]);
     }
+    if (alpha[0] != 1.f || alpha[1] != 1.f) {      // the running maxima settle after the first blocks
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
-      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
-      l_run[h] = l_run[h] * alpha[h] + rs[h];
-    }
-#pragma unroll
-    for (int nt = 0; nt < D / 8; ++nt) {
-      o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+      for (int nt = 0; nt < D / 8; ++nt) {
+        o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
+      }
     }
     // ---- O += P V  (K = 32 keys in two steps, N = D)
 #pragma unroll
@@ -222,8 +229,13 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
     __syncthreads();   // the stage is free for the prefetch issued in the next iteration
   }
   cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
   // ---- merge the partial softmax states of the two splits of a head (split 1 hands over through the K / V buffers)
-  {
+  if constexpr (kSplit == 2) {
     float* xch = reinterpret_cast<float*>(KV) + static_cast<size_t>(head) * (32 * (D / 2 + 4));
     if (split == 1) {
 #pragma unroll
@@ -242,8 +254,8 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
     for (int h = 0; h < 2; ++h) {
       const float m1 = xch[(D / 2 + h) * 32 + lane], l1 = xch[(D / 2 + 2 + h) * 32 + lane];
       const float m = fmaxf(m_run[h], m1);
-      f0[h] = exp2f(m_run[h] - m);
-      f1[h] = exp2f(m1 - m);
+      f0[h] = ex2_approx(m_run[h] - m);
+      f1[h] = ex2_approx(m1 - m);
       l_run[h] = l_run[h] * f0[h] + l1 * f1[h];
     }
 #pragma unroll
@@ -262,20 +274,20 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
     for (int nt = 0; nt < D / 8; ++nt) {
       const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + off + nt * 8 + tc));
       const float a0 = round_bf(o[nt][h * 2] * inv_l), a1 = round_bf(o[nt][h * 2 + 1] * inv_l);
-      const float s0 = round_bf(1.0f / (1.0f + expf(-gv.x))), s1 = round_bf(1.0f / (1.0f + expf(-gv.y)));
+      const float s0 = round_bf(__fdividef(1.0f, 1.0f + __expf(-gv.x))), s1 = round_bf(__fdividef(1.0f, 1.0f + __expf(-gv.y)));
       *reinterpret_cast<uint32_t*>(y + off + nt * 8 + tc) = pack2(a0 * s0, a1 * s1);
     }
   }
 }
 
-template <int D>
+template <int D, int kSplit>
 int launch_attn(const void* qt, const void* kt, const void* vt, const void* gate, const int32_t* vbits, const int32_t* krange,
                 void* y, int64_t N, int64_t HQ, int64_t HKV, int64_t GQ, float scale, cudaStream_t st) {
   constexpr int kLd = D + 8;
   const int NW = static_cast<int>(N / 32);
   const size_t smem = (GQ * kRows * kLd + 2 * kSplit * 2 * kKeys * kLd) * 2 + kRows * NW * 4 + (NW + 1) * 4;
   if (smem > 227 * 1024) return OJB_ERR_LIMIT;
-  auto kern = tree_attn_kernel<D>;
+  auto kern = tree_attn_kernel<D, kSplit>;
   static size_t smem_set = 0;
   if (smem > smem_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
@@ -303,8 +315,20 @@ extern "C" int ojb_tree_attn(const void* qt, const void* kt, const void* vt, con
   OJB_REQUIRE(qt && kt && vt && gate && y && (vbits || krange) && N > 0 && N % 32 == 0);
   OJB_REQUIRE(HQ > 0 && HKV > 0 && HQ % HKV == 0 && gq >= 1 && gq <= 6 && (HQ / HKV) % gq == 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (D == 256) return launch_attn<256>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
-  if (D == 128) return launch_attn<128>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
-  if (D == 64) return launch_attn<64>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
+  static int split_env = -1;
+  if (split_env < 0) {
+    const char* e = getenv("OJB_ATTN_SPLIT");
+    split_env = e ? atoi(e) : 0;
+  }
+  const int split = split_env == 1 || split_env == 2 ? split_env : 2;
+  if (split == 1) {
+    if (D == 256) return launch_attn<256, 1>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
+    if (D == 128) return launch_attn<128, 1>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
+    if (D == 64) return launch_attn<64, 1>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
+    return OJB_ERR_ARG;
+  }
+  if (D == 256) return launch_attn<256, 2>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
+  if (D == 128) return launch_attn<128, 2>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
+  if (D == 64) return launch_attn<64, 2>(qt, kt, vt, gate, vbits, krange, y, N, HQ, HKV, gq, scale, st);
   return OJB_ERR_ARG;
 }

@@ -32,7 +32,7 @@ LT = _lt.load()
 SK_LIN_OUT = int(os.environ.get("OJ_SK_LIN_OUT", "0"))     # split-K of the GDN out-projection; 0 = choose by timing
 SK_FULL_OUT = int(os.environ.get("OJ_SK_FULL_OUT", "0"))   # split-K of the attention o-projection
 SK_DOWN = int(os.environ.get("OJ_SK_DOWN", "0"))           # split-K of the MLP down-projection
-FATTN = int(os.environ.get("OJ_FATTN", "6"))               # query heads per CTA of the tree attention (3 or 6)
+FATTN = int(os.environ.get("OJ_FATTN", "0"))               # query heads per CTA of the tree attention (3 or 6); 0 = by row count
 FATTN_MAX = int(os.environ.get("OJ_FATTN_MAX", "1000000000"))   # kept for compatibility: the kernel serves every N
 GDN_FUSED, GDN_VER, PREP, GVA, LUT, SK2 = True, 6, "dedup", True, True, True
 TREE_NATIVE = os.environ.get("OJ_TREE_NATIVE", "1") == "1"      # 0: replicated per-candidate GDN layout of the reference
@@ -159,17 +159,26 @@ class FastQwen35(torch.nn.Module):
         g = torch.Generator(device=dev).manual_seed(1234)
         rnd = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.5).to(torch.bfloat16)
 
-        def clock(fn, layers):
-            for d in layers[:2]:
-                fn(d)
+        def clock_once(fn, layers):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            for _ in range(2):
-                for d in layers:
-                    fn(d)
+            for d in layers:
+                fn(d)
             b.record()
             b.synchronize()
-            return a.elapsed_time(b) * 1e3 / (2 * len(layers))
+            return a.elapsed_time(b) * 1e3 / len(layers)
+
+        def race(cands, layers):
+            """cands: {key: fn(layer)}. Three interleaved rounds over all layers, best round per candidate: a candidate is not
+            judged by the clock the GPU happened to run at during its turn."""
+            for fn in cands.values():
+                for d in layers[:2]:
+                    fn(d)
+            best = {k: float("inf") for k in cands}
+            for _ in range(3):
+                for k, fn in cands.items():
+                    best[k] = min(best[k], clock_once(fn, layers))
+            return best
 
         def groups(attr):
             out = {}
@@ -182,14 +191,14 @@ class FastQwen35(torch.nn.Module):
         kernels = [1, 3] + ([7] if M <= 512 else [])
         for (N, Kd), layers in groups("w_in").items():
             x = rnd(M, Kd)
-            res = {i: clock(lambda d, i=i: LT.lt_matmul(x, d.w_in, i), layers) for i in kernels + [2]}
+            res = race({i: (lambda d, i=i: LT.lt_matmul(x, d.w_in, i)) for i in kernels + [2]}, layers)
             best = min(res, key=res.get)
             self._plan[("mm", M, N, Kd)] = best
             if report is not None:
                 report.append(dict(op="in-proj", M=M, N=N, K=Kd, us=res, best=best))
         for (N, Kd), layers in groups("w_gu_blk").items():
             x = rnd(M, Kd)
-            res = {i: clock(lambda d, i=i: LT.gemm_swiglu(x, d.w_gu_blk, i), layers) for i in kernels}
+            res = race({i: (lambda d, i=i: LT.gemm_swiglu(x, d.w_gu_blk, i)) for i in kernels}, layers)
             best = min(res, key=res.get)
             self._plan[("gu", M, N, Kd)] = best
             if report is not None:
@@ -198,7 +207,7 @@ class FastQwen35(torch.nn.Module):
             for (N, Kd), layers in groups(attr).items():
                 y, h, w1 = rnd(M, Kd), rnd(M, N), norms[0]
                 kb = -(-Kd // 64)
-                res = {}
+                cands = {}
                 for S in (1, 2, 3, 4, 6, 8):
                     if (S - 1) * -(-kb // S) >= kb:
                         continue
@@ -207,7 +216,8 @@ class FastQwen35(torch.nn.Module):
                             fn = lambda d, i=i: K.add_rmsnorm(h, LT.lt_matmul(y, getattr(d, attr), i), w1, None, self.eps)
                         else:
                             fn = lambda d, i=i, S=S: K.add_rmsnorm_sk2(h, LT.gemm_splitk(y, getattr(d, attr), S, i), w1, None, self.eps)
-                        res[(i, S)] = clock(fn, layers)
+                        cands[(i, S)] = fn
+                res = race(cands, layers)
                 best = min(res, key=res.get)
                 self._plan[("res", M, N, Kd)] = best
                 if report is not None:
@@ -263,7 +273,10 @@ class FastQwen35(torch.nn.Module):
         N = proj.shape[0]
         qt, kt, vt, gate = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps)
         G = d.HQ // d.HKV
-        gq = FATTN if FATTN in (1, 2, 3, 6) and G % FATTN == 0 else 1
+        # measured: 3 heads per CTA (twice the CTAs) is faster up to a few hundred rows (19 vs 23 us at 288), 6 heads per CTA
+        # (each K / V tile loaded once per kv head) above (47 vs 63 us at 544)
+        want = FATTN if FATTN else (3 if N <= 384 else 6)
+        gq = want if want in (1, 2, 3, 6) and G % want == 0 else 1
         if hasattr(lay, "krange"):
             return K.fattn_tree_ranges(qt, kt, vt, gate, lay.krange, d.scale, gq)
         return K.fattn_tree(qt, kt, vt, gate, None, lay.vbits, d.scale, gq)
