@@ -185,6 +185,12 @@ int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const fl
  *   - all calls on one GPU share the array: calls that may overlap on the GPU (different streams, no ordering) race;
  *     the array keeps the previous call's contents, and nothing in it needs clearing between calls. */
 int64_t ojb_gdn_static_max_items(void);
+
+/* Measurement hook of the state pass (no counterpart in the reference): `records` = null switches it off; otherwise a device
+ * buffer of 12 uint64 words per walk step. The CTA of head 0 / column slice 0 / walk 0 stores %globaltimer at six points of
+ * every step (step begin, operands ready, phase 1 done, v' visible, phase 2 done, step end), words 0-5 from its state-chain
+ * warp and 6-11 from its output warp. Synchronises the device (it writes a device variable). */
+int ojb_gdn_set_trace(uint64_t* records);
 int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
                            const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                            int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK, int64_t HV,

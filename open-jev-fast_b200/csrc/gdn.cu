@@ -401,11 +401,14 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
 }
 
 // ----------------------------------------------------------------------------------------------------------- gdn_state
-constexpr int kStateThreads = 128;
+// 8 warps: warps 0-3 carry the state (the sequential chain: w S -> v' -> S update), warps 4-7 compute the outputs
+// (qg S + Aqk v') beside them, so the outputs are off the chain that the next step waits for.
+constexpr int kStateThreads = 256;
+constexpr int kChainThreads = 128;
 constexpr int kBufElems = 3 * kChunk * kLd + kChunk * kLdS + kChunk * kLdA;  // w | qg | kg | u-slice | Aqk
-constexpr int kStateSmem = 2 * kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 2 * kStateThreads * 32 * 4 + 16;
+constexpr int kStateSmem = 2 * kBufElems * 2 + 2 * kHD * kLdS * 2 + kChunk * kLdS * 2 + 2 * kChainThreads * 32 * 4 + 16;
 // lean form for many short walks: one operand buffer, no parking slots -> two CTAs per SM
-constexpr int kStateSmemLean = kBufElems * 2 + kHD * kLdS * 2 + kChunk * kLdS * 2 + 16;
+constexpr int kStateSmemLean = kBufElems * 2 + 2 * kHD * kLdS * 2 + kChunk * kLdS * 2 + 16;
 
 // The operands of one step are three flat byte ranges of the item: w | qg | kg (52 224 B), this CTA's u slice (5 120 B) and
 // Aqk (9 216 B), already in the padded shapes the MMA fragments are read from.
@@ -432,6 +435,11 @@ __device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, 
   }
 }
 
+// Measurement hook (ojb_gdn_set_trace): when non-null, the CTA of head 0 / column slice 0 / walk 0 records six %globaltimer
+// stamps per step — step begin, operands + state copy ready, phase 1 done, v' visible, phase 2 done, step end — from its
+// chain warp 0 (words 0-5 of the step's record) and its output warp 0 (words 6-11).
+__device__ unsigned long long* g_state_trace = nullptr;
+
 // steps[s] = (chunk, load, save, aux): load 0 carry on / 1 zero / 2 slot A / 3 slot B / 4 initial state aux>>16 - 1;
 // save bit 0 slot A, bit 1 slot B; (aux & 0xffff) - 1 = index of a final-state output written after the step.
 template <bool LEAN>
@@ -445,10 +453,12 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
   if (s_begin >= s_end) return;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16_t* bufs = reinterpret_cast<bf16_t*>(smem_raw);
-  bf16_t* Sb = bufs + (LEAN ? 1 : 2) * kBufElems;  // bf16 copy of the state slice [128 dk][32 dv]
-  bf16_t* Vn = Sb + kHD * kLdS;                   // v' [64][32]
-  float* slots = reinterpret_cast<float*>(Vn + kChunk * kLdS);   // [2][32 regs][128 threads]
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  bf16_t* Sb2 = bufs + (LEAN ? 1 : 2) * kBufElems;  // two bf16 copies of the state slice [128 dk][32 dv], alternating by step
+  bf16_t* Vn = Sb2 + 2 * kHD * kLdS;               // v' [64][32]
+  float* slots = reinterpret_cast<float*>(Vn + kChunk * kLdS);   // [2][32 regs][128 chain threads]
+  const int tid = threadIdx.x, lane = tid & 31;
+  const bool chain = tid < kChainThreads;           // warps 0-3: state chain; warps 4-7: outputs
+  const int warp = (tid >> 5) & 3;                   // index inside the group: 16 chunk rows / 32 dk rows each
   const int gr = lane >> 2, tc = (lane & 3) * 2;
   const int64_t VD = static_cast<int64_t>(HV) * kHD;
 
@@ -483,7 +493,11 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     cp_async_commit();
   }
 
+  unsigned long long* trace = g_state_trace;
+  const bool tracer = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == kChainThreads);
   for (int s = s_begin; s < s_end; ++s) {
+    unsigned long long* rec = tracer ? trace + (static_cast<size_t>(s - s_begin) * 12 + (tid ? 6 : 0)) : nullptr;
+    if (rec) rec[0] = global_timer_ns();
     const bool staged = s - s_begin < kWin;
     const int4 st = staged ? sm_step[s - s_begin] : reinterpret_cast<const int4*>(steps)[s];
     const int4 ch = staged ? sm_chunk[s - s_begin] : reinterpret_cast<const int4*>(chunks)[st.x];
@@ -496,6 +510,8 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     }
     cp_async_commit();
 
+    bf16_t* Sb = Sb2 + ((s - s_begin) & 1) * (kHD * kLdS);
+    if (chain) {
     // ---- choose the incoming state
     if (st.y == 1) {
 #pragma unroll
@@ -505,13 +521,13 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
 #pragma unroll
           for (int e = 0; e < 4; ++e) S[a][b][e] = 0.f;
     } else if (!LEAN && (st.y == 2 || st.y == 3)) {
-      const float* sl = slots + (st.y - 2) * (32 * kStateThreads);
+      const float* sl = slots + (st.y - 2) * (32 * kChainThreads);
 #pragma unroll
       for (int a = 0; a < 2; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) S[a][b][e] = sl[((a * 4 + b) * 4 + e) * kStateThreads + tid];
+          for (int e = 0; e < 4; ++e) S[a][b][e] = sl[((a * 4 + b) * 4 + e) * kChainThreads + tid];
     } else if (st.y == 4) {
       const float* is = init_state + (static_cast<int64_t>((st.w >> 16) - 1) * HV + h) * (kHD * kHD);
 #pragma unroll
@@ -534,8 +550,10 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
           const int dk = warp * 32 + a * 16 + gr + half * 8;
           *reinterpret_cast<uint32_t*>(Sb + dk * kLdS + b * 8 + tc) = pack2(S[a][b][half * 2], S[a][b][half * 2 + 1]);
         }
+    }
     if constexpr (LEAN) cp_async_wait<0>(); else cp_async_wait<1>();   // this step's operands have landed (a prefetch of the next step may still be in flight)
     __syncthreads();
+    if (rec) rec[1] = global_timer_ns();
 
     const bf16_t* Ws = buf;
     const bf16_t* Qg = buf + kChunk * kLd;
@@ -547,40 +565,45 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     // B operand from [k][n] storage through ldmatrix.trans: lanes 0-15 rows k0..k0+15 at column n0, lanes 16-31 at n0+8
     const int bt_row = lane & 15, bt_col = (lane >> 4) * 8;
 
-    // ---- (1) acc_w = w S ; acc_o = qg S   (16 rows x 32 columns per warp, K = 128)
-    float accw[4][4], acco[4][4];
+    // ---- (1) chain warps: acc_w = w S, v' = u - acc_w -> shared memory; output warps: acc_o = qg S
+    //      (16 rows x 32 columns per warp, K = 128)
+    float acc[4][4];
 #pragma unroll
     for (int b = 0; b < 4; ++b)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { accw[b][e] = 0.f; acco[b][e] = 0.f; }
+      for (int e = 0; e < 4; ++e) acc[b][e] = 0.f;
+    {
+      const bf16_t* Am = chain ? Ws : Qg;
 #pragma unroll
-    for (int ks = 0; ks < kHD / 16; ++ks) {
-      uint32_t w0, w1, w2, w3, q0, q1, q2, q3;
-      ldsm_x4(smem_u32(Ws + a_row * kLd + ks * 16 + a_col), w0, w1, w2, w3);
-      ldsm_x4(smem_u32(Qg + a_row * kLd + ks * 16 + a_col), q0, q1, q2, q3);
+      for (int ks = 0; ks < kHD / 16; ++ks) {
+        uint32_t w0, w1, w2, w3;
+        ldsm_x4(smem_u32(Am + a_row * kLd + ks * 16 + a_col), w0, w1, w2, w3);
 #pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        uint32_t b0, b1, b2, b3;
-        ldsm_x4_t(smem_u32(Sb + (ks * 16 + bt_row) * kLdS + np * 16 + bt_col), b0, b1, b2, b3);
-        mma_bf16(accw[2 * np], w0, w1, w2, w3, b0, b1);
-        mma_bf16(accw[2 * np + 1], w0, w1, w2, w3, b2, b3);
-        mma_bf16(acco[2 * np], q0, q1, q2, q3, b0, b1);
-        mma_bf16(acco[2 * np + 1], q0, q1, q2, q3, b2, b3);
+        for (int np = 0; np < 2; ++np) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(smem_u32(Sb + (ks * 16 + bt_row) * kLdS + np * 16 + bt_col), b0, b1, b2, b3);
+          mma_bf16(acc[2 * np], w0, w1, w2, w3, b0, b1);
+          mma_bf16(acc[2 * np + 1], w0, w1, w2, w3, b2, b3);
+        }
       }
     }
-    // v' = u - w S  -> shared memory (bf16) for the two products that follow
+    if (chain) {
 #pragma unroll
-    for (int b = 0; b < 4; ++b)
+      for (int b = 0; b < 4; ++b)
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int r = m0 + gr + half * 8;
-        const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(Us + r * kLdS + b * 8 + tc);
-        const float2 uf = __bfloat1622float2(u2);
-        *reinterpret_cast<uint32_t*>(Vn + r * kLdS + b * 8 + tc) = pack2(uf.x - accw[b][half * 2], uf.y - accw[b][half * 2 + 1]);
-      }
+        for (int half = 0; half < 2; ++half) {
+          const int r = m0 + gr + half * 8;
+          const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(Us + r * kLdS + b * 8 + tc);
+          const float2 uf = __bfloat1622float2(u2);
+          *reinterpret_cast<uint32_t*>(Vn + r * kLdS + b * 8 + tc) = pack2(uf.x - acc[b][half * 2], uf.y - acc[b][half * 2 + 1]);
+        }
+    }
+    if (rec) rec[2] = global_timer_ns();
     __syncthreads();
+    if (rec) rec[3] = global_timer_ns();
 
-    // ---- (2) o = qg S + Aqk v'   (K = 64)
+    if (!chain) {
+    // ---- (2) output warps: o = qg S + Aqk v'   (K = 64)
 #pragma unroll
     for (int ks = 0; ks < kChunk / 16; ++ks) {
       uint32_t a0, a1, a2, a3;
@@ -589,8 +612,8 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
       for (int np = 0; np < 2; ++np) {
         uint32_t b0, b1, b2, b3;
         ldsm_x4_t(smem_u32(Vn + (ks * 16 + bt_row) * kLdS + np * 16 + bt_col), b0, b1, b2, b3);
-        mma_bf16(acco[2 * np], a0, a1, a2, a3, b0, b1);
-        mma_bf16(acco[2 * np + 1], a0, a1, a2, a3, b2, b3);
+        mma_bf16(acc[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
       }
     }
 #pragma unroll
@@ -600,10 +623,11 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
         bf16_t* orow = out + static_cast<int64_t>(ch.x + r) * VD + h * kHD + dv0;
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-          *reinterpret_cast<uint32_t*>(orow + b * 8 + tc) = pack2(acco[b][half * 2], acco[b][half * 2 + 1]);
+          *reinterpret_cast<uint32_t*>(orow + b * 8 + tc) = pack2(acc[b][half * 2], acc[b][half * 2 + 1]);
       }
     }
-    // ---- (3) S = S e^(G_L) + kg^T v'   (warp owns dk rows 32*warp.., K = 64 chunk rows)
+    } else {
+    // ---- (3) chain warps: S = S e^(G_L) + kg^T v'   (warp owns dk rows 32*warp.., K = 64 chunk rows)
     {
       const float gl = staged ? sm_gl[s - s_begin] : *reinterpret_cast<const float*>(item + kOffGl);
 #pragma unroll
@@ -638,13 +662,13 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
 #pragma unroll
       for (int sl = 0; sl < 2; ++sl)
         if (st.z & (1 << sl)) {
-          float* dst = slots + sl * (32 * kStateThreads);
+          float* dst = slots + sl * (32 * kChainThreads);
 #pragma unroll
           for (int a = 0; a < 2; ++a)
 #pragma unroll
             for (int b = 0; b < 4; ++b)
 #pragma unroll
-              for (int e = 0; e < 4; ++e) dst[((a * 4 + b) * 4 + e) * kStateThreads + tid] = S[a][b][e];
+              for (int e = 0; e < 4; ++e) dst[((a * 4 + b) * 4 + e) * kChainThreads + tid] = S[a][b][e];
         }
     }
     if ((st.w & 0xffff) != 0 && final_state != nullptr) {
@@ -659,7 +683,10 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
             fs[dk * kHD + dv] = S[a][b][e];
           }
     }
-    __syncthreads();   // everyone is done with Sb, Vn and this buffer before they are overwritten
+    }
+    if (rec) rec[4] = global_timer_ns();
+    __syncthreads();   // everyone is done with Vn and this operand buffer before they are overwritten
+    if (rec) rec[5] = global_timer_ns();
   }
   cp_async_wait<0>();
 }
@@ -730,6 +757,11 @@ extern "C" int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t
                                                  static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV));
   }
   return launch_status(cudaGetLastError());
+}
+
+extern "C" int ojb_gdn_set_trace(uint64_t* records) {
+  unsigned long long* p = reinterpret_cast<unsigned long long*>(records);
+  return launch_status(cudaMemcpyToSymbol(ojb::g_state_trace, &p, sizeof(p)));
 }
 
 extern "C" int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV) { return n_chunks * HV * kItemElems * 2; }
