@@ -258,10 +258,11 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 for (int j = 0; j < 4; ++j) {
                   float o[8];
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) {
-                    const float gv = round_bf(__uint_as_float(gr[8 * j + e]));
-                    const float uv = round_bf(__uint_as_float(ur[8 * j + e]));
-                    o[e] = round_bf(silu_f(gv)) * uv;
+                  for (int e = 0; e < 8; e += 2) {
+                    float s0, s1;
+                    silu2_f(round_bf(__uint_as_float(gr[8 * j + e])), round_bf(__uint_as_float(gr[8 * j + e + 1])), s0, s1);
+                    o[e] = round_bf(s0) * round_bf(__uint_as_float(ur[8 * j + e]));
+                    o[e + 1] = round_bf(s1) * round_bf(__uint_as_float(ur[8 * j + e + 1]));
                   }
                   put(c * 4 + j, pack8(o));
                 }
