@@ -1,6 +1,8 @@
 """Test infrastructure: builds the reference's own CUDA operators for sm_100a so that GPU tests can compare against them.
 
-    python oracle/build_ref_kernels.py [reference root, default /root/reference]
+    python oracle/build_ref_kernels.py [reference root]
+
+(default: $OJ_REFERENCE, else the directory `reference` next to this repository)
 
 Nothing of the reference is copied: its `src/kernels.cu` and the prototype string of its `src/ext.py` are read where they
 lie and handed to torch's inline-extension builder, exactly as `src/ext.py:47-56` does, except for the target architecture
@@ -16,7 +18,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref", "ojref")
 
 
-def build(ref_root="/root/reference", verbose=False):
+def default_ref_root():
+    return os.environ.get("OJ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
+
+
+def build(ref_root=None, verbose=False):
+    ref_root = ref_root or default_ref_root()
     src_dir = os.path.join(ref_root, "src")
     cu = os.path.join(src_dir, "kernels.cu")
     if not os.path.exists(cu):

@@ -1,6 +1,6 @@
 """Generates tests/golden/layout_golden.npz from the reference's own `gtree_build` and `tree_layout`.
 
-Run in a container that mounts open-jev-fast (default /root/reference, override with OJ_REFERENCE):
+Run in a container that mounts open-jev-fast ($OJ_REFERENCE, else the directory `reference` next to this repository):
     python tests/golden/make_layout_golden.py
 The two functions are lifted out of src/fastmodel.py by AST (the module itself cannot be imported without a GPU because it
 builds its CUDA extension at import) and executed unmodified with dev="cpu". The inputs are the seeded synthetic trees of
@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 import trees  # noqa: E402
 
-REF = os.environ.get("OJ_REFERENCE", "/root/reference")
+REF = os.environ.get("OJ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
 
 
 def reference_functions():
