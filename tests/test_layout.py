@@ -124,3 +124,31 @@ def test_state_layout_oracle_matches_reference_golden(name):
     for f in ("pos", "rowmask", "lastidx", "repidx"):
         assert np.array_equal(lay[f], GOLD[f"{name}/{f}"]), f
     assert np.array_equal(np.packbits(lay["vis"], axis=1, bitorder="little"), GOLD[f"{name}/amask"])
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_build_without_visibility_words(name):
+    """OJB_LAYOUT_NO_VBITS: every other field and both other buffers are identical, the N x N/32 words are left untouched
+    (the scorer neither builds nor uploads them: the attention kernel works from the O(N) key ranges)."""
+    from ojb200 import layout as PL
+    seqs, groups, pad_id, NB, PB = CASES[name]
+    d1, a64, a32, ae = PL.gtree_host(seqs, groups, pad_id, NB, PB)
+    d0, b64, b32, be = PL.gtree_host(seqs, groups, pad_id, NB, PB, vbits=False)
+    N = d1["N"]
+    assert d1["n32_used"] == a32.numel() and d0["n32_used"] == a32.numel() - (N * (N // 32) + 7) // 8 * 8
+    assert {k: v for k, v in d0.items() if k != "n32_used"} == {k: v for k, v in d1.items() if k != "n32_used"}
+    assert torch.equal(a64, b64) and torch.equal(ae, be)
+    assert torch.equal(a32[:d0["n32_used"]], b32[:d0["n32_used"]])
+
+
+def test_long_prefix_layout_is_linear_in_rows():
+    """A 16 384-token shared prefix (the top of the length sweep): the O(N) build succeeds and its key ranges are causal."""
+    from ojb200 import layout as PL
+    seqs, groups = trees.make_tree(7, 16384, [12, 9], [5, 8, 3, 6], [0, 0, 1, 1], 4096)
+    d, b64, b32, e32 = PL.gtree_host(seqs, groups, 0, 32, 16, vbits=False)
+    assert d["N"] % 32 == 0 and d["Nreal"] == 16384 + 21 + 22 and d["n32_used"] < 40 * d["N"]
+    f = PL.field_views(d, b64, b32, e32)
+    kr = f["krange"].numpy()
+    n = np.arange(d["Nreal"])
+    assert np.all(kr[:16384, 0] == n[:16384] + 1)          # root rows: causal prefix
+    assert np.all(kr[16384:d["Nreal"], 0] == 16384)        # every other row sees the whole root
