@@ -153,11 +153,13 @@ gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, 
 // ----------------------------------------------------------------------------------------------------------- gdn_intra
 constexpr int kIntraThreads = 256;
 constexpr int kLdT = kChunk + 8;  // padded row (bf16) of the [64 x 64] inverse
-// K | Q | V | KG tiles, A (fp32; later the bf16 pair of T) with the block scratch P behind it, four vectors, T (fp32)
-constexpr int kIntraSmem = 4 * kChunk * kLd * 2 + kChunk * kChunk * 4 + 3 * 256 * 4 + 4 * kChunk * 4 + kChunk * kChunk * 4;
+// K | Q | V tiles (the Q tile holds the fp32 inverse T once q is no longer needed), A (fp32; later the bf16 pair of T) with
+// the block scratch P behind it, four vectors: 74 KB, three CTAs per SM
+constexpr int kIntraSmem = 3 * kChunk * kLd * 2 + kChunk * kChunk * 4 + 3 * 256 * 4 + 4 * kChunk * 4;
+static_assert(kChunk * kChunk * 4 <= kChunk * kLd * 2, "the fp32 inverse must fit over the Q tile");
 static_assert(2 * kChunk * kLdT * 2 <= kChunk * kChunk * 4 + 3 * 256 * 4, "the bf16 pair of T must fit over A and P");
 
-__global__ void __launch_bounds__(kIntraThreads)
+__global__ void __launch_bounds__(kIntraThreads, 3)
 gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, const bf16_t* __restrict__ v,
                  const float* __restrict__ g, const bf16_t* __restrict__ beta, const int32_t* __restrict__ chunks,
                  bf16_t* __restrict__ scratch, int HK, int HV, float scale) {
@@ -170,14 +172,13 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
   bf16_t* Ks = reinterpret_cast<bf16_t*>(smem_raw);
   bf16_t* Qs = Ks + kChunk * kLd;
   bf16_t* Vs = Qs + kChunk * kLd;
-  bf16_t* KGs = Vs + kChunk * kLd;
-  float* As = reinterpret_cast<float*>(KGs + kChunk * kLd);   // [64][64]
+  float* As = reinterpret_cast<float*>(Vs + kChunk * kLd);    // [64][64]
   float* Ps = As + kChunk * kChunk;                            // [3][16][16] block products
   float* Gs = Ps + 3 * 256;                                    // G * log2e (inclusive cumsum)
   float* Bs = Gs + kChunk;                                     // beta
   float* EGs = Bs + kChunk;                                    // exp(G)
   float* EKs = EGs + kChunk;                                   // exp(G_L - G)
-  float* Tf = EKs + kChunk;                                    // [64][64] inverse, fp32
+  float* Tf = reinterpret_cast<float*>(Qs);                    // [64][64] inverse, fp32 (after the elementwise phase)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KD = HK * kHD, VD = HV * kHD;
 
@@ -271,7 +272,8 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     }
   }
   __syncthreads();   // all warps are done reading K and Q as MMA operands
-  // ---- qg = q e^G scale (in place), kg = k e^(G_L - G); then the right-hand sides v beta and k beta e^G in place
+  // ---- qg = q e^G scale and kg = k e^(G_L - G) go straight to the item; the right-hand sides v beta and k beta e^G
+  //      replace v and k in shared memory
   for (int i = tid; i < kChunk * (kHD / 8); i += kIntraThreads) {
     const int r = i >> 4, cv = (i & 15) * 8;
     float f[8];
@@ -279,13 +281,13 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     const float sq = EGs[r] * scale;
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] *= sq;
-    *reinterpret_cast<uint4*>(Qs + r * kLd + cv) = pack8(f);
+    *reinterpret_cast<uint4*>(item + kOffQg + r * kLd + cv) = pack8(f);
     float kf[8];
     unpack8(*reinterpret_cast<const uint4*>(Ks + r * kLd + cv), kf);
     const float sk = EKs[r], sw = Bs[r] * EGs[r];
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = kf[e] * sk;
-    *reinterpret_cast<uint4*>(KGs + r * kLd + cv) = pack8(f);
+    *reinterpret_cast<uint4*>(item + kOffKg + r * kLd + cv) = pack8(f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = kf[e] * sw;
     *reinterpret_cast<uint4*>(Ks + r * kLd + cv) = pack8(f);
@@ -295,6 +297,7 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     for (int e = 0; e < 8; ++e) f[e] *= sv;
     *reinterpret_cast<uint4*>(Vs + r * kLd + cv) = pack8(f);
   }
+  __syncthreads();   // q has been consumed: its tile becomes the fp32 inverse
   // ---- T = (I + A)^-1, fp32, by 16 x 16 blocks. First the four diagonal blocks (forward substitution per column) ...
   for (int i = tid; i < kChunk * kChunk; i += kIntraThreads) Tf[i] = 0.f;
   __syncthreads();
@@ -390,13 +393,6 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
       *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr) * ld) = pack2(acc[nt][0], acc[nt][1]);
       *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr + 8) * ld) = pack2(acc[nt][2], acc[nt][3]);
     }
-  }
-  // ---- copy qg (Qs) and kg (KGs) to the scratch item, 16 bytes per thread
-  for (int i = tid; i < 2 * kChunk * (kHD / 8); i += kIntraThreads) {
-    const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
-    const int r = rem >> 4, cv = (rem & 15) * 8;
-    const bf16_t* srcb = which == 0 ? Qs : KGs;
-    *reinterpret_cast<uint4*>(item + (which == 0 ? kOffQg : kOffKg) + r * kLd + cv) = *reinterpret_cast<const uint4*>(srcb + r * kLd + cv);
   }
 }
 
