@@ -8,7 +8,7 @@
 // of O(N^2). Q K^T and P V run on the tensor cores (mma.sync m16n8k16 bf16, fp32 accumulate), the softmax is the online
 // form in the exp2 domain (ex2.approx); K / V tiles are double-buffered with cp.async. OJB_ATTN_SPLIT=1 in the environment
 // selects one warp per head (half the shared memory, two CTAs per SM); measured slower than the default of two on both
-// benchmark trees (57 vs 47 us at 544 rows, 22 vs 19 us at 288).
+// benchmark trees (45 vs 44 us at 544 rows with 3 / 6 heads per CTA, 18.6 vs 17.7 us at 288).
 #include "common.cuh"
 
 namespace ojb {
@@ -120,11 +120,12 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
       const int kb = vis_list[li];
       bf16_t* ks = KV + (stage * kSplit + sp) * (2 * kKeys * kLd);
       bf16_t* vs = ks + kKeys * kLd;
-      for (int i = tid; i < 2 * kKeys * (D / 8); i += nthreads) {
-        const int which = i / (kKeys * (D / 8)), rem = i - which * (kKeys * (D / 8));
-        const int r = rem / (D / 8), cv = (rem - r * (D / 8)) * 8;
-        const bf16_t* src = (which ? vbase : kbase) + static_cast<int64_t>(kb * kKeys + r) * D + cv;
-        cp_async16(smem_u32((which ? vs : ks) + r * kLd + cv), src);
+      const bf16_t* ksrc = kbase + static_cast<int64_t>(kb) * (kKeys * D);
+      const bf16_t* vsrc = vbase + static_cast<int64_t>(kb) * (kKeys * D);
+      for (int i = tid; i < kKeys * (D / 8); i += nthreads) {      // the K and the V piece at the same (row, column)
+        const int r = i / (D / 8), cv = (i - r * (D / 8)) * 8;
+        cp_async16(smem_u32(ks + r * kLd + cv), ksrc + r * D + cv);
+        cp_async16(smem_u32(vs + r * kLd + cv), vsrc + r * D + cv);
       }
     }
   };
@@ -162,7 +163,7 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
       for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      uint32_t a0, a1, a2, a3;
+      uint32_t a0, a1, a2, a3;     // (keeping the Q fragments in registers across key blocks was measured: no gain)
       ldsm_x4(smem_u32(Qw + a_row * kLd + kk * 16 + a_col), a0, a1, a2, a3);
 #pragma unroll
       for (int np = 0; np < 2; ++np) {

@@ -273,8 +273,8 @@ class FastQwen35(torch.nn.Module):
         N = proj.shape[0]
         qt, kt, vt, gate = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps)
         G = d.HQ // d.HKV
-        # measured: 3 heads per CTA (twice the CTAs) is faster up to a few hundred rows (19 vs 23 us at 288), 6 heads per CTA
-        # (each K / V tile loaded once per kv head) above (47 vs 63 us at 544)
+        # measured: 3 heads per CTA (twice the CTAs) is faster up to a few hundred rows (17.7 vs 21.5 us at 288), 6 heads per
+        # CTA (each K / V tile loaded once per kv head) above (44 vs 54 us at 544)
         want = FATTN if FATTN else (3 if N <= 384 else 6)
         gq = want if want in (1, 2, 3, 6) and G % want == 0 else 1
         if hasattr(lay, "krange"):
