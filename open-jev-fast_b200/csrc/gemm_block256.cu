@@ -41,7 +41,7 @@ constexpr uint32_t kStagingBytes = kEpiWarps * 4096;                // TMEM colu
 unsigned long long* g_trace = nullptr;
 int g_trace_cap = 0;
 int g_mma_repeat = 1;
-int g_bk = 0;   // 2..12: cap on the number of pipeline stages (measurement only)
+int g_max_stages = 0;   // 2..12: cap on the number of pipeline stages (measurement only)
 int g_dbg = 0;
 
 template <int EPI>
@@ -521,11 +521,9 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.n_xchunk = 1;
   }
   g.splits = splits;
-  g.bk = kBK;
   g.kb_total = static_cast<int>(ceil_div(K, kBK));
   g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
   if (static_cast<int64_t>(splits - 1) * g.kb_per_split >= g.kb_total) return OJB_ERR_ARG;   // an empty split
-  g.a_bytes = kABytes;
   g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, g.tail_box, g.n_xchunk, g.tail_rows > 0, splits, g.kb_total, sms, EPI));
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
@@ -542,7 +540,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16 + (g.tma_out ? kStagingBytes : 0);
   g.stages = static_cast<int>((kSmemBudget - fixed) / g.stage_bytes);
   if (g.stages > kMaxStages) g.stages = kMaxStages;
-  if (g_bk >= 2 && g_bk <= 12 && g.stages > g_bk) g.stages = g_bk;
+  if (g_max_stages >= 2 && g_max_stages <= 12 && g.stages > g_max_stages) g.stages = g_max_stages;
   if (g.stages < 2) return OJB_ERR_LIMIT;
   g.out = out;
   g.ldo = ldo;
@@ -578,12 +576,12 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
 
 }  // namespace
 
-void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int bk) {
+void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int knob) {
   g_trace = buf;
   g_trace_cap = buf ? cap : 0;
   g_mma_repeat = repeat >= 0 ? repeat : 1;
-  g_bk = bk >= 100 ? 0 : bk;
-  g_dbg = bk >= 100 ? bk : 0;
+  g_max_stages = knob >= 100 ? 0 : knob;
+  g_dbg = knob >= 100 ? knob : 0;
 }
 
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,

@@ -237,7 +237,7 @@ int gemm_tile128_launch(int epi, int bn, const void* x, const void* w, void* out
                         int64_t ldo, int32_t* status, cudaStream_t stream);
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
-void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int bk);
+void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int knob);
 int gemm_pair256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                         int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 void gemm_pair256_set_trace(unsigned long long* buf, int cap, int repeat, int max_stages);

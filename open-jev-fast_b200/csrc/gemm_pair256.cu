@@ -461,7 +461,6 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.n_xchunk = 1;
   }
   g.splits = splits;
-  g.bk = kBK;
   g.kb_total = static_cast<int>(ceil_div(K, kBK));
   g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
   if (static_cast<int64_t>(splits - 1) * g.kb_per_split >= g.kb_total) return OJB_ERR_ARG;   // an empty split
@@ -469,7 +468,6 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
   const int half_b = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) / 2 : g.tail_box / 2;
-  g.a_bytes = kHalfABytes;
   g.stage_bytes = kHalfABytes + static_cast<uint32_t>(half_b) * (kBK * 2);
   g.stage_bytes = (g.stage_bytes + 1023u) & ~1023u;      // every stage starts on a swizzle-atom boundary
   const size_t fixed = 1024 + kStagingBytes + (2 * kPairMaxStages + 4) * 8 + 16;

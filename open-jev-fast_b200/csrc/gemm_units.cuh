@@ -18,11 +18,9 @@ struct GemmArgs {
   int n_xchunk;    // tail units per w tile and k-split: the tail rows are cut into n_xchunk chunks of tail_box rows
   int n_wtile;     // ceil(N / BN)
   int n_wtile256;  // ceil(N / 256)
-  int splits, kb_per_split, kb_total;   // in k-blocks of bk columns
-  int bk;                // columns of x and w per shared-memory stage: 64 (128-byte swizzle) or 32 (64-byte swizzle)
+  int splits, kb_per_split, kb_total;   // in k-blocks of 64 columns
   int stages;
   uint32_t stage_bytes;
-  uint32_t a_bytes;      // 256 rows x bk columns: the x rows of a block unit or the w rows of a tail unit
   void* out;
   int64_t ldo;           // leading dimension of out in elements
   int64_t split_stride;  // elements between split planes (fp32 partials)
