@@ -144,6 +144,9 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
   const int a_row = lane & 15, a_col = (lane >> 4) * 8;
   const int b_row = (lane & 7) + ((lane >> 4) << 3), b_col = ((lane >> 3) & 1) * 8;
   const int bt_row = lane & 15, bt_col = (lane >> 4) * 8;
+  // shared-memory byte addresses of this lane's fragment rows, converted once: inside the loops only constants are added
+  const uint32_t q_lane = smem_u32(Qw + a_row * kLd + a_col);
+  const uint32_t k_lane_off = static_cast<uint32_t>(b_row * kLd + b_col) * 2u, v_lane_off = static_cast<uint32_t>(bt_row * kLd + bt_col) * 2u;
 
   for (int it = 0; it < niter; ++it) {
     if (it + 1 < niter) prefetch((it + 1) & 1, it + 1);
@@ -155,6 +158,7 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
     const int kb = vis_list[li];
     const bf16_t* ks = KV + ((it & 1) * kSplit + split) * (2 * kKeys * kLd);
     const bf16_t* vs = ks + kKeys * kLd;
+    const uint32_t k_lane = smem_u32(ks) + k_lane_off, v_lane = smem_u32(vs) + v_lane_off;
     // ---- S = Q K^T  (16 x 32)
     float s[4][4];
 #pragma unroll
@@ -164,11 +168,11 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       uint32_t a0, a1, a2, a3;     // (keeping the Q fragments in registers across key blocks was measured: no gain)
-      ldsm_x4(smem_u32(Qw + a_row * kLd + kk * 16 + a_col), a0, a1, a2, a3);
+      ldsm_x4(q_lane + kk * 32, a0, a1, a2, a3);
 #pragma unroll
       for (int np = 0; np < 2; ++np) {
         uint32_t b0, b1, b2, b3;
-        ldsm_x4(smem_u32(ks + (np * 16 + b_row) * kLd + kk * 16 + b_col), b0, b1, b2, b3);
+        ldsm_x4(k_lane + (np * 16 * kLd + kk * 16) * 2, b0, b1, b2, b3);
         mma_bf16(s[2 * np], a0, a1, a2, a3, b0, b1);
         mma_bf16(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
       }
@@ -221,7 +225,7 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {
         uint32_t b0, b1, b2, b3;
-        ldsm_x4_t(smem_u32(vs + (kk * 16 + bt_row) * kLd + np * 16 + bt_col), b0, b1, b2, b3);
+        ldsm_x4_t(v_lane + (kk * 16 * kLd + np * 16) * 2, b0, b1, b2, b3);
         mma_bf16(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
         mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
       }
