@@ -178,6 +178,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", type=int, default=0, help="run this many eager (graph-free) forwards between "
                     "cudaProfilerStart/Stop and exit: for `ncu --profile-from-start off`")
+    ap.add_argument("--pack", type=int, default=0, help="also time this many requests packed into one forward (extra key "
+                    "`packed` of the JSON line; the headline numbers stay one request per forward)")
     ap.add_argument("--layers", type=int, default=64, help="debugging only: a run with fewer than 64 layers is not a result")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -265,6 +267,22 @@ def main():
         total_ms, e2e_s = float(t[0]), float(t[1])
     ms_per_step = total_ms / args.steps
 
+    packed = None
+    if args.pack > 1 and rank == 0:
+        # several requests per forward (Scorer.score_packed): end to end, host layout + H2D + replay + D2H inside the region
+        group = [reqs[i % len(reqs)] for i in range(args.pack)]
+        for _ in range(max(args.warmup, 2)):
+            [o.cpu() for o in scorer.score_packed(group)]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            outs = [o.cpu() for o in scorer.score_packed(group)]
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        packed = {"requests_per_forward": args.pack, "rows": scorer.last["rows"], "ms_per_forward": dt / args.steps * 1e3,
+                  "value": args.pack * args.steps / dt, "unit": "requests/s", "h2d_bytes_per_forward": scorer.last["h2d_bytes"]}
+        _lib.check_status(dev)
+
     roof = gemm_roofline(fast, key[0], pk, pk_kind, dev) if rank == 0 else None
     P = matmul_params(cfg)
     line = {"metric": METRIC, "value": world * 1e3 / ms_per_step, "unit": "requests/s", "n_gpus": world, "steps": args.steps,
@@ -294,6 +312,8 @@ def main():
                                               f"x({n_lin},{n_full}); {sec:.1f} s per request"}
         else:
             line["cpu_baseline"] = None
+        if packed is not None:
+            line["packed"] = packed
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -211,7 +211,8 @@ int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* proj, const
  * F.scaled_dot_product_attention + gate_mul3 of src/fastmodel.py:470-473).
  * qt bf16 [HQ, N, D], kt / vt bf16 [HKV, N, D] (head-major, from ojb_fullattn_prep), gate bf16 [N, HQ*D].
  * Mask: vbits int32 [N, N/32] (bit b of word w of row n = key 32w+b visible), or, when vbits is null,
- * krange int32 [N, 8] = (e0, a1, e1, a2, e2, -, -, -): row n sees keys [0,e0) + [a1,e1) + [a2,e2).
+ * krange int32 [N, 8] = (e0, a1, e1, a2, e2, a0, -, -): row n sees keys [a0,e0) + [a1,e1) + [a2,e2) (a0 = 0 in the layout of
+ * one request; a request packed behind others has its root start there).
  * y[N, HQ*D] = bf16(bf16(softmax(scale * q k^T + mask) v) * bf16(sigmoid(gate))). N % 32 == 0; D in {64, 128, 256};
  * gq = query heads per CTA, a divisor of HQ/HKV, at most 6. Every row must see at least one key.
  * ------------------------------------------------------------------------------------------------------------------ */

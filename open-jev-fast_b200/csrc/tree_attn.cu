@@ -81,7 +81,7 @@ tree_attn_kernel(const bf16_t* __restrict__ qt, const bf16_t* __restrict__ kt, c
       w = static_cast<uint32_t>(vbits[static_cast<int64_t>(r0 + r) * NW + kb]);
     } else {
       const int* kr = krange + static_cast<int64_t>(r0 + r) * 8;
-      w = range_word(0, kr[0], kb) | range_word(kr[1], kr[2], kb) | range_word(kr[3], kr[4], kb);
+      w = range_word(kr[5], kr[0], kb) | range_word(kr[1], kr[2], kb) | range_word(kr[3], kr[4], kb);
     }
     words[r * NW + kb] = w;
   }

@@ -98,6 +98,52 @@ def gtree_build(seqs, groups, pad_id, NB=32, PB=16, dev="cuda", dense=True):
     return ids, lay
 
 
+def pack_requests(requests, pad_id=0, NB=32, PB=16, dev="cuda", pin=False):
+    """Several requests in one forward (not in the reference, which scores one request at a time): every request keeps
+    its own packed tree, the trees follow one another in the row dimension, and every table of the tree kernels is shifted
+    accordingly — history and key ranges by the row offset of the request, walk steps by its chunk offset; each tree is
+    one walk of the state pass. `requests` = list of (seqs, groups). Returns (ids, lay, host) where lay has the fields the
+    tree forward reads (pos, rowmask, hist, krange, chunks, steps, walk_ptr, n_walks, lastidx, N, S) and `host` is the
+    dict of host tensors behind them (for re-upload into static buffers), plus `counts` = candidates per request."""
+    ids, pos, rowmask, hist, krange, chunks, steps, last, walks, counts, keys = [], [], [], [], [], [], [], [], [0], [], []
+    base = cbase = 0
+    for seqs, groups in requests:
+        d, b64, b32, e32 = gtree_host(seqs, groups, pad_id, NB, PB, vbits=False)
+        f = {k: v.numpy() for k, v in field_views(d, b64, b32, e32).items() if k != "vbits"}
+        N = d["N"]
+        ids.append(f["ids"]); pos.append(f["pos"]); rowmask.append(f["rowmask"])
+        h = f["hist"][:N].copy()
+        h[h >= 0] += base
+        hist.append(h)
+        kr = f["krange"].copy()
+        kr[:, 5] = np.where(kr[:, 0] > 0, base, 0)
+        kr[:, 0] = np.where(kr[:, 0] > 0, kr[:, 0] + base, 0)
+        kr[:, 1:5] += base
+        krange.append(kr)
+        ch = f["chunks"].copy()
+        ch[:, 0] += base
+        chunks.append(ch)
+        w0, w1 = int(f["meta"][6]), int(f["meta"][7])
+        st = f["steps"][w0:w1].copy()
+        st[:, 0] += cbase
+        steps.append(st)
+        walks.append(walks[-1] + (w1 - w0))
+        last.append(f["lastidx"] + base)
+        counts.append(d["S"])
+        keys.append((d["N"], d["S"], d["L2"]))
+        base += N
+        cbase += ch.shape[0]
+    hist.append(np.full((1, 4), -1, np.int32))
+    host = dict(ids=np.concatenate(ids), pos=np.concatenate(pos), rowmask=np.concatenate(rowmask), hist=np.concatenate(hist),
+                krange=np.concatenate(krange), chunks=np.concatenate(chunks), steps=np.concatenate(steps),
+                walk_ptr=np.asarray(walks, np.int32), lastidx=np.concatenate(last))
+    host = {k: (torch.as_tensor(np.ascontiguousarray(v)).pin_memory() if pin else torch.as_tensor(np.ascontiguousarray(v)))
+            for k, v in host.items()}
+    lay = SimpleNamespace(N=base, S=int(sum(counts)), L2=max(k[2] for k in keys), n_walks=len(requests), counts=counts,
+                          key=tuple(keys), **{k: v.to(dev) for k, v in host.items() if k != "ids"})
+    return host["ids"].to(dev), lay, host
+
+
 def batch_layout(attention_mask, dev):
     """Layout of a right-padded batch [B, T] of independent sequences (the non-tree forward of src/fastmodel.py:205-241)
     in the vocabulary of the tree kernels: every sequence is its own path, rows are b*T + t, padded up to a multiple of 32

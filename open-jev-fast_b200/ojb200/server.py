@@ -74,6 +74,46 @@ class Entry:
         return self.out
 
 
+class PackedEntry:
+    """Static tables + CUDA graph of `score_gtree` for several requests packed into one forward (layout.pack_requests).
+    Keyed by the tuple of the requests' (N, S, L2) keys; replay = one small copy per table, then the graph."""
+
+    def __init__(self, scorer, ids, lay):
+        fast, dev = scorer.fast, scorer.device
+        self.ids, self.lay = ids, lay
+        self.tables = dict(ids=ids, **{k: getattr(lay, k) for k in ("pos", "rowmask", "hist", "krange", "chunks", "steps", "walk_ptr",
+                                                                   "lastidx")})
+        fast.tune(lay.N)
+        body = lambda: fast.score_gtree(self.ids, self.lay, scorer.head_w, scorer.head_b)
+        st = torch.cuda.Stream(device=dev)
+        st.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(st):
+            for _ in range(2):
+                body()
+        torch.cuda.current_stream(dev).wait_stream(st)
+        torch.cuda.synchronize(dev)
+        self.g = None
+        n0 = _lib.launch_count()
+        if scorer.use_graph:
+            self.g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g, pool=scorer.pool):
+                self.out = body()
+            torch.cuda.synchronize(dev)
+        else:
+            self.out = body()
+        self.launches = _lib.launch_count() - n0
+        self._body = body
+
+    def run(self, host):
+        for k, t in self.tables.items():
+            t.copy_(host[k], non_blocking=True)
+        if self.g is not None:
+            self.g.replay()
+        else:
+            self.out = self._body()
+        return self.out
+
+
 class Scorer:
     """One GPU's worth of the service: model + head + graph cache + lock (one request at a time per GPU, src/server.py:97)."""
 
@@ -113,6 +153,29 @@ class Scorer:
         self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=ent.lay.key, rows=dims["Nreal"],
                          h2d_bytes=b64.numel() * 8 + dims["n32_used"] * 4 + e32.numel() * 4, launches=ent.launches)
         return out
+
+    def score_packed(self, requests):
+        """Several requests in one forward (raises the row count of every GEMM; not in the reference, which scores one
+        request at a time). requests = list of (seqs, groups); returns one fp32 [S_r, A] tensor per request (GPU, not
+        synchronised). The requests of later calls with the same keys in the same order reuse the captured graph."""
+        t0 = time.perf_counter()
+        ids, lay, host = _layout.pack_requests(requests, self.pad_id, NB, PB, dev="cpu", pin=True)
+        t1 = time.perf_counter()
+        key = ("packed",) + lay.key
+        with self.lock, torch.cuda.device(self.device):
+            ent = self.graphs.get(key)
+            captured = ent is None
+            if captured:
+                dlay = _layout.SimpleNamespace(**{k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in vars(lay).items()})
+                ent = self.graphs[key] = PackedEntry(self, ids.to(self.device), dlay)
+                while len(self.graphs) > self.max_graphs:
+                    self.graphs.popitem(last=False)
+            else:
+                self.graphs.move_to_end(key)
+            out = ent.run(host)
+        self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=key, rows=lay.N,
+                         h2d_bytes=sum(v.numel() * v.element_size() for v in host.values()), launches=ent.launches)
+        return list(out.split(lay.counts))
 
     def forward(self, records):
         """src/server.py:86-142 on token ids: list of per-record score tensors (CPU, fp32)."""

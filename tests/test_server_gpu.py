@@ -60,3 +60,34 @@ def test_score_head_matches_oracle():
     got = K.score_head(hn.cuda(), rows.cuda(), W.cuda(), b.cuda()).cpu()
     want = OH.scores(hn[rows].float(), W, b)
     assert torch.allclose(got, want, rtol=1e-5, atol=1e-4)
+
+
+def test_packed_requests_match_separate_forwards():
+    """Several requests in one forward: every request's scores and hidden rows equal those of its own forward up to the
+    bf16 noise of differently blocked GEMMs (the row count of a GEMM decides its kernel and K split), the packed layout
+    shifts the tables correctly (three different tree shapes, the second and third start at non-zero rows), and a second
+    call with the same keys replays the captured graph."""
+    cfg, fast, sc, W, b = _scorer(A=3)
+    V = cfg.vocab_size
+    reqs = [trees.make_tree(11, 40, [5, 9], [3, 6, 2, 8], [0, 0, 1, 1], V),
+            trees.make_tree(12, 70, [4], [3, 5, 7], [0, 0, 0], V),
+            trees.make_tree(13, 9, [0, 6], [2, 4, 3], [0, 1, 1], V)]
+    packed = [o.clone() for o in sc.score_packed(reqs)]
+    from ojb200 import layout as PL, _lib
+    ids, lay, host = PL.pack_requests(reqs, 0, dev="cuda")
+    hid = fast.forward_gtree(ids, lay, return_all=True).float()
+    base = 0
+    for (seqs, groups), got in zip(reqs, packed):
+        i1, l1 = fast.gtree_build(seqs, groups, 0)
+        want = fast.score_gtree(i1, l1, W, b)
+        h1 = fast.forward_gtree(i1, l1, return_all=True).float()
+        real = l1.rowmask.bool()
+        rel = ((hid[base:base + l1.N][real] - h1[real]).norm() / h1[real].norm()).item()
+        assert rel < 2.5e-2, rel
+        assert got.shape == want.shape and (got - want).abs().max().item() < 6e-2
+        base += l1.N
+    _lib.check_status()
+    n_graphs = len(sc.graphs)
+    again = sc.score_packed(reqs)
+    assert len(sc.graphs) == n_graphs and not sc.last["captured"]
+    assert all(torch.equal(a, p) for a, p in zip(again, packed))
