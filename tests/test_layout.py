@@ -152,3 +152,39 @@ def test_long_prefix_layout_is_linear_in_rows():
     n = np.arange(d["Nreal"])
     assert np.all(kr[:16384, 0] == n[:16384] + 1)          # root rows: causal prefix
     assert np.all(kr[16384:d["Nreal"], 0] == 16384)        # every other row sees the whole root
+
+
+def test_packed_requests_tables():
+    """layout.pack_requests: the visibility implied by the shifted key ranges is block diagonal with each request's own
+    visibility on the diagonal; histories, chunks and walk steps point into the request's own rows; one walk per request."""
+    from ojb200 import layout as PL
+    names = ["example", "doc", "ragged"]
+    reqs = [(CASES[n][0], CASES[n][1]) for n in names]
+    ids, lay, host = PL.pack_requests(reqs, 0, 32, 16, dev="cpu")
+    refs = [OL.gtree_layout(s, g, 0, 32, 16) for s, g in reqs]
+    assert lay.N == sum(r["N"] for r in refs) and lay.n_walks == 3 and lay.counts == [r["S"] for r in refs]
+    kr = host["krange"].numpy()
+    N = lay.N
+    vis = np.zeros((N, N), bool)
+    for n in range(N):
+        a0, e0, a1, e1, a2, e2 = kr[n, 5], kr[n, 0], kr[n, 1], kr[n, 2], kr[n, 3], kr[n, 4]
+        vis[n, a0:e0] = True
+        vis[n, a1:e1] = True
+        vis[n, a2:e2] = True
+    base = 0
+    hist, chunks, steps, walks = host["hist"].numpy(), host["chunks"].numpy(), host["steps"].numpy(), host["walk_ptr"].numpy()
+    for i, r in enumerate(refs):
+        n = r["N"]
+        blk = vis[base:base + n, base:base + n]
+        real = r["rowmask"].astype(bool)
+        assert np.array_equal(blk[real], r["vis"][real])
+        assert not vis[base:base + n, :base].any() and not vis[base:base + n, base + n:].any()
+        h = hist[base:base + n]
+        assert ((h == -1) | ((h >= base) & (h < base + n))).all()
+        assert np.array_equal(np.where(h >= 0, h - base, -1), r["hist"][:n])
+        st = steps[walks[i]:walks[i + 1]]
+        rows = chunks[st[:, 0]]
+        assert ((rows[:, 0] >= base) & (rows[:, 0] + rows[:, 1] <= base + n)).all()
+        assert rows[:, 1].sum() == real.sum()                     # the walk of a request covers each of its real rows once
+        assert np.array_equal(host["lastidx"].numpy()[sum(lay.counts[:i]):sum(lay.counts[:i + 1])], r["lastidx"] + base)
+        base += n
