@@ -308,12 +308,12 @@ class FastQwen35(torch.nn.Module):
         return K.score_head(hn, lay.lastidx, head_w, head_b)
 
     # ------------------------------------------------------------------------------------------------ single-level tree
-    def tree_layout(self, pre_ids, suf_ids, suf_mask, pad=0):
+    def tree_layout(self, pre_ids, suf_ids, suf_mask, pad=0, dense=True, cap=None):
         """src/fastmodel.py:247-264: layout of [prefix | S suffixes] with `pad` left-padding rows in the prefix."""
-        return _layout.tree_layout(pre_ids, suf_ids, suf_mask, pad)
+        return _layout.tree_layout(pre_ids, suf_ids, suf_mask, pad, dense, cap)
 
     @torch.no_grad()
-    def forward_tree(self, pre_ids, suf_ids, lay, fla_mode="state"):
+    def forward_tree(self, pre_ids, suf_ids, lay, fla_mode="state", return_all=False):
         """src/fastmodel.py:266-314: long shared prefix, S suffixes -> [S, H]. Both modes of the reference ("replicate" and
         "state") give the same result; here the prefix is always computed once and its Gated DeltaNet state handed to every
         suffix inside the state kernel."""
@@ -321,7 +321,7 @@ class FastQwen35(torch.nn.Module):
         ids[:lay.N] = torch.cat([pre_ids, suf_ids.reshape(-1)])
         inner = SimpleNamespace(N=lay.N32, S=lay.S, pos=lay.pos32, rowmask=lay.rowmask32, hist=lay.hist, krange=lay.krange,
                                 chunks=lay.chunks, steps=lay.steps, walk_ptr=lay.walk_ptr, n_walks=1, lastidx=lay.lastidx)
-        return self.forward_gtree(ids, inner)
+        return self.forward_gtree(ids, inner, return_all)
 
     # ------------------------------------------------------------------------------------------------ batch forward
     @torch.no_grad()

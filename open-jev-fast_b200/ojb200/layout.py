@@ -182,10 +182,12 @@ def batch_layout(attention_mask, dev):
                            lastidx=torch.as_tensor(last).to(dev))
 
 
-def tree_layout(pre_ids, suf_ids, suf_mask, pad=0):
+def tree_layout(pre_ids, suf_ids, suf_mask, pad=0, dense=True, cap=None):
     """Single-level tree [prefix | S suffixes of Ls rows] of FastQwen35.tree_layout (src/fastmodel.py:247-264): the same
     fields (Lp, S, Ls, N, pos, amask, rowmask, lastidx, repidx) plus the tables the kernels here consume (hist, krange,
-    chunks, steps, walk_ptr). The first `pad` prefix rows are left padding. Rows are padded up to a multiple of 32 (N32)."""
+    chunks, steps, walk_ptr). The first `pad` prefix rows are left padding. Rows are padded up to a multiple of 32 (N32).
+    dense=False leaves out the O(N^2) mask and the replication index (the kernels do not read them); cap pads the chunk and
+    step tables to a fixed number of entries so that one CUDA graph serves every request of a (Lp, S, Ls) key."""
     dev = suf_ids.device
     Lp = int(pre_ids.shape[0])
     S, Ls = (int(x) for x in suf_ids.shape)
@@ -202,12 +204,12 @@ def tree_layout(pre_ids, suf_ids, suf_mask, pad=0):
     pos[:Lp] = np.arange(Lp) - pad
     for s in range(S):
         pos[Lp + s * Ls: Lp + (s + 1) * Ls] = np.arange(Ls) + (Lp - pad)
-    for n in range(pad, Lp):
-        rowmask[n] = 1
-        krange[n, 3], krange[n, 4] = pad, n + 1
-        for i in range(4):
-            if n - 3 + i >= pad:
-                hist[n, i] = n - 3 + i
+    if Lp > pad:
+        pr = np.arange(pad, Lp)
+        rowmask[pad:Lp] = 1
+        krange[pad:Lp, 3], krange[pad:Lp, 4] = pad, pr + 1
+        hp = pr[:, None] - 3 + np.arange(4)[None, :]
+        hist[pad:Lp] = np.where(hp >= pad, hp, -1)
     lens = m.sum(1)
     for s in range(S):
         for t in range(int(lens[s])):
@@ -215,10 +217,10 @@ def tree_layout(pre_ids, suf_ids, suf_mask, pad=0):
             rowmask[n] = 1
             krange[n, 1], krange[n, 2] = pad, Lp
             krange[n, 3], krange[n, 4] = Lp + s * Ls, n + 1
-            path = list(range(pad, Lp)) + list(range(Lp + s * Ls, n + 1))
+            tail = list(range(max(pad, Lp - 3), Lp)) + list(range(Lp + s * Ls, n + 1))     # the last rows of this path
             for i in range(4):
-                if len(path) - 4 + i >= 0:
-                    hist[n, i] = path[len(path) - 4 + i]
+                if len(tail) - 4 + i >= 0:
+                    hist[n, i] = tail[len(tail) - 4 + i]
     chunks, steps, walks = [], [], [0]
     for j in range(pad, Lp, 64):
         steps.append([len(chunks), 1 if j == pad else 0, 0, 0])
@@ -232,6 +234,17 @@ def tree_layout(pre_ids, suf_ids, suf_mask, pad=0):
     walks.append(len(steps))
     if not chunks:
         chunks, steps = [[0, 0, 0, 0]], [[0, 1, 0, 0]]
+    if cap is not None:
+        if len(chunks) > cap:
+            raise RuntimeError("tree_layout: more chunks than the table capacity")
+        chunks += [[0, 0, 0, 0]] * (cap - len(chunks))
+        steps += [[0, 0, 0, 0]] * (cap - len(steps))
+    t32 = lambda a: torch.as_tensor(np.asarray(a, np.int32)).to(dev)
+    lastidx = np.array([Lp + s * Ls + max(int(lens[s]) - 1, 0) for s in range(S)], np.int64)
+    if not dense:
+        return SimpleNamespace(Lp=Lp, S=S, Ls=Ls, N=N, N32=N32, pos=torch.as_tensor(pos[:N]).to(dev), pos32=torch.as_tensor(pos).to(dev),
+                               rowmask=t32(rowmask[:N]), rowmask32=t32(rowmask), lastidx=torch.as_tensor(lastidx).to(dev),
+                               hist=t32(hist), krange=t32(krange), chunks=t32(chunks), steps=t32(steps), walk_ptr=t32(walks), n_walks=1)
     # dense mask with the reference's semantics for every row (rows that are padding still see valid earlier keys of their
     # own segment and of the prefix); the kernels read krange, where padding rows see only themselves
     seg = np.concatenate([np.zeros(Lp, np.int64), np.repeat(np.arange(1, S + 1), Ls)])
@@ -241,8 +254,6 @@ def tree_layout(pre_ids, suf_ids, suf_mask, pad=0):
     from_prefix = (seg[None, :] == 0) & ((seg[:, None] != 0) | earlier)
     same_suffix = (seg[None, :] == seg[:, None]) & (seg[:, None] != 0) & earlier
     vis = ((from_prefix | same_suffix) & valid[None, :]) | np.eye(N, dtype=bool)
-    t32 = lambda a: torch.as_tensor(np.asarray(a, np.int32)).to(dev)
-    lastidx = np.array([Lp + s * Ls + int(lens[s]) - 1 for s in range(S)], np.int64)
     repidx = np.array([[p if p < Lp else Lp + s * Ls + (p - Lp) for p in range(Lp + Ls)] for s in range(S)], np.int64)
     return SimpleNamespace(Lp=Lp, S=S, Ls=Ls, N=N, N32=N32, pos=torch.as_tensor(pos[:N]).to(dev), pos32=torch.as_tensor(pos).to(dev),
                            amask=torch.as_tensor(vis).to(dev)[None, None], rowmask=t32(rowmask[:N]), rowmask32=t32(rowmask),

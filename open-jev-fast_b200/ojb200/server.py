@@ -18,6 +18,9 @@ from . import _lib
 from . import layout as _layout
 
 NB, PB = int(os.environ.get("ROW_BUCKET", "32")), int(os.environ.get("PATH_BUCKET", "16"))
+PRE_B, SUF_B = int(os.environ.get("PRE_BUCKET", "64")), int(os.environ.get("SUF_BUCKET", "16"))
+REP_MAX = int(os.environ.get("REP_MAX", "4096"))
+STATE_PATH = os.environ.get("OJ_STATE_PATH", "0") == "1"
 MAX_GRAPHS = int(os.environ.get("MAX_GRAPHS", "512"))
 USE_GRAPH = os.environ.get("USE_GRAPH", "1") == "1"
 
@@ -67,6 +70,56 @@ class Entry:
         return self.replay()
 
     def replay(self):
+        if self.g is not None:
+            self.g.replay()
+        else:
+            self.out = self._body()
+        return self.out
+
+
+class EntryState:
+    """Single-level prefix tree with prefix-state hand-off (long shared context, one question): src/server.py:50-70. Static
+    prefix / suffix / mask buffers and one CUDA graph per key (Lp bucket, S, Ls bucket); `run` rebuilds the layout on the
+    host (tables padded to the key's capacity) and copies it over the static tables."""
+    FIELDS = ("pos32", "rowmask32", "hist", "krange", "chunks", "steps", "walk_ptr", "lastidx")
+
+    def __init__(self, scorer, Lpb, S, Lsb):
+        from . import ext as K
+        fast, dev = scorer.fast, scorer.device
+        self.pre = torch.zeros(Lpb, dtype=torch.long, device=dev)
+        self.suf = torch.zeros(S, Lsb, dtype=torch.long, device=dev)
+        self.msk = torch.ones(S, Lsb, dtype=torch.long, device=dev)
+        self.cap = -(-Lpb // 64) + S * -(-Lsb // 64)
+        self.lay = fast.tree_layout(self.pre, self.suf, self.msk, pad=0, dense=False, cap=self.cap)
+        fast.tune(self.lay.N32)
+        body = lambda: K.score_head(fast.forward_tree(self.pre, self.suf, self.lay, "state", return_all=True), self.lay.lastidx,
+                                    scorer.head_w, scorer.head_b)
+        st = torch.cuda.Stream(device=dev)
+        st.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(st):
+            for _ in range(2):
+                body()
+        torch.cuda.current_stream(dev).wait_stream(st)
+        torch.cuda.synchronize(dev)
+        self.g = None
+        n0 = _lib.launch_count()
+        if scorer.use_graph:
+            self.g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g, pool=scorer.pool):
+                self.out = body()
+            torch.cuda.synchronize(dev)
+        else:
+            self.out = body()
+        self.launches = _lib.launch_count() - n0
+        self._body, self._fast = body, fast
+
+    def run(self, pre, suf, msk, pad):
+        self.pre.copy_(pre, non_blocking=True)
+        self.suf.copy_(suf, non_blocking=True)
+        self.msk.copy_(msk, non_blocking=True)
+        L = self._fast.tree_layout(pre, suf, msk, pad=pad, dense=False, cap=self.cap)          # host tensors
+        for name in self.FIELDS:
+            getattr(self.lay, name).copy_(getattr(L, name), non_blocking=True)
         if self.g is not None:
             self.g.replay()
         else:
@@ -154,6 +207,43 @@ class Scorer:
                          h2d_bytes=b64.numel() * 8 + dims["n32_used"] * 4 + e32.numel() * 4, launches=ent.launches)
         return out
 
+    def score_state(self, seqs):
+        """The reference's route for one question over a long shared context (src/server.py:100-115): the common prefix of
+        the candidates is cut off (left-padded to a bucket), the rest of each candidate is one suffix row block. Returns
+        fp32 [S, A] (GPU, not synchronised). The general tree route (score_tokens) serves the same requests; this one keeps
+        the reference's key (Lp bucket, S, Ls bucket) and its `tree_layout` / `forward_tree` entry points."""
+        t0 = time.perf_counter()
+        mn = min(len(q) for q in seqs)
+        Lp = 0
+        while Lp < mn - 1 and all(q[Lp] == seqs[0][Lp] for q in seqs):
+            Lp += 1
+        S = len(seqs)
+        Ls = max(len(q) - Lp for q in seqs)
+        ceil_ = lambda x, b: -(-x // b) * b
+        Lpb, Lsb = ceil_(Lp, PRE_B), ceil_(Ls, SUF_B)
+        pad = Lpb - Lp
+        pre = torch.tensor([self.pad_id] * pad + list(seqs[0][:Lp]), dtype=torch.long)
+        suf = torch.full((S, Lsb), self.pad_id, dtype=torch.long)
+        msk = torch.zeros(S, Lsb, dtype=torch.long)
+        for i, q in enumerate(seqs):
+            suf[i, :len(q) - Lp] = torch.tensor(q[Lp:])
+            msk[i, :len(q) - Lp] = 1
+        key = ("state", Lpb, S, Lsb)
+        t1 = time.perf_counter()
+        with self.lock, torch.cuda.device(self.device):
+            ent = self.graphs.get(key)
+            captured = ent is None
+            if captured:
+                ent = self.graphs[key] = EntryState(self, Lpb, S, Lsb)
+                while len(self.graphs) > self.max_graphs:
+                    self.graphs.popitem(last=False)
+            else:
+                self.graphs.move_to_end(key)
+            out = ent.run(pre, suf, msk, pad)
+        self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=key, rows=Lp + sum(len(q) - Lp for q in seqs),
+                         h2d_bytes=0, launches=ent.launches)
+        return out
+
     def score_packed(self, requests):
         """Several requests in one forward (raises the row count of every GEMM; not in the reference, which scores one
         request at a time). requests = list of (seqs, groups); returns one fp32 [S_r, A] tensor per request (GPU, not
@@ -186,12 +276,20 @@ class Scorer:
             counts.append(len(c))
             seqs += c
             groups += [ri] * len(c)
-        scores = self.score_tokens(seqs, groups).cpu()      # device-to-host read = the synchronisation point
+        Lp = 0
+        if STATE_PATH and len(records) == 1 and len(seqs) > 1:
+            mn = min(len(q) for q in seqs)
+            while Lp < mn - 1 and all(q[Lp] == seqs[0][Lp] for q in seqs):
+                Lp += 1
+        if STATE_PATH and len(records) == 1 and (len(seqs) - 1) * Lp > REP_MAX:        # src/server.py:102
+            scores = self.score_state(seqs).cpu()
+        else:
+            scores = self.score_tokens(seqs, groups).cpu()      # device-to-host read = the synchronisation point
         _lib.check_status(self.device)
         t1 = time.perf_counter()
         self.nreq += 1
         if self.log:
-            rec = dict(ts=time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), req=self.nreq, path="tree2", gpu=self.device.index,
+            rec = dict(ts=time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), req=self.nreq, path="state" if self.last["key"][0] == "state" else "tree2", gpu=self.device.index,
                        questions=len(records), candidates=len(seqs), tokens=sum(map(len, seqs)), rows=self.last["rows"],
                        key=self.last["key"], captured=int(self.last["captured"]), build_ms=round(self.last["build_ms"], 3),
                        ms=round((t1 - t0) * 1e3, 3))

@@ -91,3 +91,20 @@ def test_packed_requests_match_separate_forwards():
     again = sc.score_packed(reqs)
     assert len(sc.graphs) == n_graphs and not sc.last["captured"]
     assert all(torch.equal(a, p) for a, p in zip(again, packed))
+
+
+def test_state_route_matches_tree_route():
+    """One question over a long shared context through EntryState (tree_layout / forward_tree, src/server.py:50-70,100-115)
+    gives the scores of the general tree route; a second request of the same key (other tokens, other suffix lengths)
+    replays the graph."""
+    cfg, fast, sc, W, b = _scorer(A=2)
+    V = cfg.vocab_size
+    for seed, leaf in ((21, [3, 6, 2, 8, 5]), (22, [7, 1, 4, 8, 2])):
+        seqs, groups = trees.make_tree(seed, 150, [0], leaf, [0] * 5, V)
+        got = sc.score_state(seqs).clone()
+        want = sc.score_tokens(seqs, groups).clone()
+        assert got.shape == want.shape == (5, 2)
+        assert (got - want).abs().max().item() < 6e-2, (got, want)
+    from ojb200 import _lib
+    _lib.check_status()
+    assert sum(1 for k in sc.graphs if k[0] == "state") == 1
