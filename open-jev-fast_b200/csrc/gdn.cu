@@ -162,11 +162,47 @@ static_assert(2 * kChunk * kLdT * 2 <= kChunk * kChunk * 4 + 3 * 256 * 4, "the b
 __global__ void __launch_bounds__(kIntraThreads, 3)
 gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, const bf16_t* __restrict__ v,
                  const float* __restrict__ g, const bf16_t* __restrict__ beta, const int32_t* __restrict__ chunks,
-                 bf16_t* __restrict__ scratch, int HK, int HV, float scale) {
+                 bf16_t* __restrict__ scratch, int HK, int HV, float scale, int pair) {
   pdl_begin();
   const int4 ch = reinterpret_cast<const int4*>(chunks)[blockIdx.x];
   const int row0 = ch.x, nrows = ch.y;
   if (nrows <= 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Short chunks (at most 32 rows: question stems, candidate tails) are done two to a CTA: the second one occupies local rows
+  // 32-63, the cross terms of the two are masked out, so the 64 x 64 algebra is block diagonal and each half is exactly what
+  // the chunk alone would give. The short chunks pair up in table order: the even-ranked one takes the next short chunk
+  // with it, the odd-ranked CTA has nothing to do. (Any two chunks are independent in this pass.)
+  __shared__ int s_rank, s_next;
+  int partner = -1;
+  if (pair && nrows <= 32) {
+    if (tid == 0) { s_rank = 0; s_next = 0x7fffffff; }
+    __syncthreads();
+    int cnt = 0, nxt = 0x7fffffff;
+    for (int j = tid; j < static_cast<int>(gridDim.x); j += kIntraThreads) {
+      const int nj = chunks[j * 4 + 1];
+      if (nj > 0 && nj <= 32) {
+        if (j < static_cast<int>(blockIdx.x)) ++cnt;
+        else if (j > static_cast<int>(blockIdx.x)) nxt = min(nxt, j);
+      }
+    }
+    if (cnt) atomicAdd(&s_rank, cnt);
+    if (nxt != 0x7fffffff) atomicMin(&s_next, nxt);
+    __syncthreads();
+    if (s_rank & 1) return;
+    partner = s_next == 0x7fffffff ? -1 : s_next;
+  }
+  const bool paired = partner >= 0;
+  int rowB0 = 0, nB = 0;
+  if (paired) {
+    const int4 cb = reinterpret_cast<const int4*>(chunks)[partner];
+    rowB0 = cb.x;
+    nB = cb.y;
+  }
+  // global row of local row r, or -1 for padding
+  auto grow = [&](int r) -> int64_t {
+    if (!paired) return r < nrows ? row0 + r : -1;
+    return r < 32 ? (r < nrows ? row0 + r : -1) : (r - 32 < nB ? rowB0 + r - 32 : -1);
+  };
   const int h = blockIdx.y, hk = h / (HV / HK);
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16_t* Ks = reinterpret_cast<bf16_t*>(smem_raw);
@@ -179,16 +215,37 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
   float* EGs = Bs + kChunk;                                    // exp(G)
   float* EKs = EGs + kChunk;                                   // exp(G_L - G)
   float* Tf = reinterpret_cast<float*>(Qs);                    // [64][64] inverse, fp32 (after the elementwise phase)
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KD = HK * kHD, VD = HV * kHD;
+  bf16_t* item = scratch + (static_cast<int64_t>(blockIdx.x) * HV + h) * kItemElems;
+  bf16_t* itemB = paired ? scratch + (static_cast<int64_t>(partner) * HV + h) * kItemElems : item;
+  // local row i of the tile -> (item, row inside the item)
+  auto out_item = [&](int i) { return (paired && i >= 32) ? itemB : item; };
+  auto out_row = [&](int i) { return (paired && i >= 32) ? i - 32 : i; };
+  if (paired) {
+    // rows 32-63 of both items belong to no chunk row: the state pass multiplies all 64 rows, so they must be zero
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    for (int which = 0; which < 2; ++which) {
+      bf16_t* it = which ? itemB : item;
+      for (int i = tid; i < 3 * 32 * (kLd / 8); i += kIntraThreads) {          // w | qg | kg tiles [64][kLd]
+        const int t = i / (32 * (kLd / 8)), rem = i - t * (32 * (kLd / 8));
+        *reinterpret_cast<uint4*>(it + t * (kChunk * kLd) + 32 * kLd + rem * 8) = z;
+      }
+      for (int i = tid; i < 4 * 32 * (kLdS / 8); i += kIntraThreads) {         // four u slices [64][kLdS]
+        const int t = i / (32 * (kLdS / 8)), rem = i - t * (32 * (kLdS / 8));
+        *reinterpret_cast<uint4*>(it + kOffU + t * (kChunk * kLdS) + 32 * kLdS + rem * 8) = z;
+      }
+      for (int i = tid; i < 32 * (kLdA / 8); i += kIntraThreads)               // Aqk rows 32-63
+        *reinterpret_cast<uint4*>(it + kOffA + 32 * kLdA + i * 8) = z;
+    }
+  }
 
   // ---- load K, Q, V rows (zero rows past the end of the chunk)
   for (int i = tid; i < 3 * kChunk * (kHD / 8); i += kIntraThreads) {
     const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
     const int r = rem >> 4, cv = (rem & 15) * 8;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (r < nrows) {
-      const int64_t row = row0 + r;
+    const int64_t row = grow(r);
+    if (row >= 0) {
       const bf16_t* src = which == 0 ? k + row * KD + hk * kHD : which == 1 ? q + row * KD + hk * kHD : v + row * VD + h * kHD;
       val = *reinterpret_cast<const uint4*>(src + cv);
     }
@@ -200,29 +257,31 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     const int r0 = lane * 2, r1 = r0 + 1;
     // log-decays below -1e4 are clamped: e^-1e4 is zero in fp32 either way, and -inf would turn the differences of the
     // cumulative sums into NaN
-    float g0 = r0 < nrows ? fmaxf(g[static_cast<int64_t>(row0 + r0) * HV + h], -1e4f) : 0.f;
-    float g1 = r1 < nrows ? fmaxf(g[static_cast<int64_t>(row0 + r1) * HV + h], -1e4f) : 0.f;
-    Bs[r0] = r0 < nrows ? bf2f(beta[static_cast<int64_t>(row0 + r0) * HV + h]) : 0.f;
-    Bs[r1] = r1 < nrows ? bf2f(beta[static_cast<int64_t>(row0 + r1) * HV + h]) : 0.f;
+    const int64_t gr0 = grow(r0), gr1 = grow(r1);
+    float g0 = gr0 >= 0 ? fmaxf(g[gr0 * HV + h], -1e4f) : 0.f;
+    float g1 = gr1 >= 0 ? fmaxf(g[gr1 * HV + h], -1e4f) : 0.f;
+    Bs[r0] = gr0 >= 0 ? bf2f(beta[gr0 * HV + h]) : 0.f;
+    Bs[r1] = gr1 >= 0 ? bf2f(beta[gr1 * HV + h]) : 0.f;
     float s = g0 + g1;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const float t = __shfl_up_sync(0xffffffffu, s, o);
-      if (lane >= o) s += t;
+      // with two chunks in the tile the sum restarts at local row 32 (lane 16)
+      if (lane >= o && (!paired || ((lane ^ (lane - o)) & 16) == 0)) s += t;
     }
     const float c1 = s, c0 = s - g1;      // inclusive sums at r1 and r0
-    const float total = __shfl_sync(0xffffffffu, s, 31);
+    const float total_hi = __shfl_sync(0xffffffffu, s, 31), total_lo = __shfl_sync(0xffffffffu, s, 15);
+    const float total = (paired && lane < 16) ? total_lo : total_hi;     // the sum over this row's own chunk
     Gs[r0] = c0 * kLog2e; Gs[r1] = c1 * kLog2e;
     EGs[r0] = exp2f(c0 * kLog2e); EGs[r1] = exp2f(c1 * kLog2e);
     EKs[r0] = exp2f((total - c0) * kLog2e); EKs[r1] = exp2f((total - c1) * kLog2e);
     if (lane == 0) {
-      float* gl = reinterpret_cast<float*>(scratch + (static_cast<int64_t>(blockIdx.x) * HV + h) * kItemElems + kOffGl);
-      gl[0] = exp2f(total * kLog2e);
+      *reinterpret_cast<float*>(item + kOffGl) = exp2f((paired ? total_lo : total_hi) * kLog2e);
+      if (paired) *reinterpret_cast<float*>(itemB + kOffGl) = exp2f(total_hi * kLog2e);
     }
   }
   __syncthreads();
 
-  bf16_t* item = scratch + (static_cast<int64_t>(blockIdx.x) * HV + h) * kItemElems;
   // ---- K K^T (warps 0-3) and Q K^T (warps 4-7): 16 rows x 64 columns per warp
   {
     const bool is_qk = warp >= 4;
@@ -259,11 +318,15 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
         for (int e = 0; e < 2; ++e) {
           const int j = nt * 8 + tc + e;
           const float a = acc[nt][half * 2 + e];
-          if (is_qk) o2[e] = j <= i ? a * exp2f(gi - Gs[j]) * scale : 0.f;
-          else o2[e] = j < i ? a * Bs[i] * exp2f(gi - Gs[j]) : 0.f;
+          const bool same = !paired || ((i ^ j) & 32) == 0;      // both rows in the same chunk of the tile
+          if (is_qk) o2[e] = (same && j <= i) ? a * exp2f(gi - Gs[j]) * scale : 0.f;
+          else o2[e] = (same && j < i) ? a * Bs[i] * exp2f(gi - Gs[j]) : 0.f;
         }
         if (is_qk) {
-          *reinterpret_cast<uint32_t*>(item + kOffA + i * kLdA + nt * 8 + tc) = pack2(o2[0], o2[1]);
+          // second chunk of a pair: its own block moves to columns 0-31 of its item, the (zero) cross block to 32-63
+          const int col = nt * 8 + tc;
+          *reinterpret_cast<uint32_t*>(out_item(i) + kOffA + out_row(i) * kLdA + ((paired && i >= 32) ? (col ^ 32) : col)) =
+              pack2(o2[0], o2[1]);
         } else {
           As[i * kChunk + nt * 8 + tc] = o2[0];
           As[i * kChunk + nt * 8 + tc + 1] = o2[1];
@@ -281,13 +344,13 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     const float sq = EGs[r] * scale;
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] *= sq;
-    *reinterpret_cast<uint4*>(item + kOffQg + r * kLd + cv) = pack8(f);
+    *reinterpret_cast<uint4*>(out_item(r) + kOffQg + out_row(r) * kLd + cv) = pack8(f);
     float kf[8];
     unpack8(*reinterpret_cast<const uint4*>(Ks + r * kLd + cv), kf);
     const float sk = EKs[r], sw = Bs[r] * EGs[r];
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = kf[e] * sk;
-    *reinterpret_cast<uint4*>(item + kOffKg + r * kLd + cv) = pack8(f);
+    *reinterpret_cast<uint4*>(out_item(r) + kOffKg + out_row(r) * kLd + cv) = pack8(f);
 #pragma unroll
     for (int e = 0; e < 8; ++e) f[e] = kf[e] * sw;
     *reinterpret_cast<uint4*>(Ks + r * kLd + cv) = pack8(f);
@@ -388,10 +451,12 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt) {
       // w keeps its 128 columns in one padded tile, u is stored as four 32-column slices (one per CTA column of the state pass)
-      bf16_t* dst = is_w ? item + kOffW + nt * 8 + tc : item + kOffU + (nt >> 2) * (kChunk * kLdS) + (nt & 3) * 8 + tc;
+      bf16_t* it = out_item(mt * 16);                   // the 16 rows of a warp lie in one chunk of the tile
+      bf16_t* dst = is_w ? it + kOffW + nt * 8 + tc : it + kOffU + (nt >> 2) * (kChunk * kLdS) + (nt & 3) * 8 + tc;
       const int ld = is_w ? kLd : kLdS;
-      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr) * ld) = pack2(acc[nt][0], acc[nt][1]);
-      *reinterpret_cast<uint32_t*>(dst + (mt * 16 + gr + 8) * ld) = pack2(acc[nt][2], acc[nt][3]);
+      const int orow = out_row(mt * 16) + gr;
+      *reinterpret_cast<uint32_t*>(dst + orow * ld) = pack2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<uint32_t*>(dst + (orow + 8) * ld) = pack2(acc[nt][2], acc[nt][3]);
     }
   }
 }
@@ -760,6 +825,24 @@ extern "C" int ojb_gdn_set_trace(uint64_t* records) {
   return launch_status(cudaMemcpyToSymbol(ojb::g_state_trace, &p, sizeof(p)));
 }
 
+namespace ojb {
+namespace {
+// Two short chunks per CTA only when one CTA per chunk would not fit the GPU in a single wave (three CTAs per SM):
+// with room to spare the chunks finish sooner side by side. OJB_GDN_PAIR = 0 / 1 forces the choice (measurements).
+int intra_pairing(int64_t n_chunks, int64_t HV) {
+  static const int forced = [] { const char* e = getenv("OJB_GDN_PAIR"); return e ? atoi(e) : -1; }();
+  if (forced >= 0) return forced != 0;
+  static const int slots = [] {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return 3 * sms;
+  }();
+  return n_chunks * HV > slots;
+}
+}  // namespace
+}  // namespace ojb
+
 extern "C" int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV) { return n_chunks * HV * kItemElems * 2; }
 
 extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const void* beta,
@@ -779,7 +862,8 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
   }
   launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
-      static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
+      static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale,
+      intra_pairing(n_chunks, HV));
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out),
@@ -840,7 +924,8 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
   // reads (items of unused chunk-table entries are neither written nor read).
   launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
-      static_cast<const bf16_t*>(beta), chunks, scratch, static_cast<int>(HK), static_cast<int>(HV), scale);
+      static_cast<const bf16_t*>(beta), chunks, scratch, static_cast<int>(HK), static_cast<int>(HV), scale,
+      intra_pairing(n_chunks, HV));
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
@@ -870,7 +955,8 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
   }
   launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
-      static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale);
+      static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale,
+      intra_pairing(n_chunks, HV));
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   for (int64_t l = 0; l < n_levels; ++l) {
     const int nw = levels[l + 1] - levels[l];
