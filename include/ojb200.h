@@ -37,7 +37,8 @@ int ojb_abi_version(void);
  * Requirements: K % 8 == 0, x / w / out 16-byte aligned. variant: 0 = the library chooses (cost model, see ojb_gemm_plan);
  * 1 / 2 = 128-row tile kernel with 128x256 / 128x128 tiles; 3 = 256-row block kernel, automatic w-tile width; 4 = that
  * kernel with all rows of x in swapped-operand units (M <= 512); a multiple of 16 in [16, 256] = that kernel with this
- * w-tile width; 5 / 6 = CTA-pair kernel (tcgen05.mma.cta_group::2) with automatic width / all rows swapped (M <= 512);
+ * w-tile width; 5 = CTA-pair kernel (tcgen05.mma.cta_group::2) with automatic width; 6 = CTA-pair kernel with all rows of
+ * x in swapped-operand units (any M: one pass over w per 512 rows of x, up to 512 accumulator columns per unit);
  * 512 + a multiple of 16 in [16, 256] = the pair kernel with that width.
  * ------------------------------------------------------------------------------------------------------------------ */
 int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int variant,
@@ -47,7 +48,8 @@ int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N,
  * re-laid in blocks of 256 rows: rows [256b, 256b+128) = gate rows [128b, 128b+128), rows [256b+128, 256b+256) = the
  * matching up rows. N = 2*I must be a multiple of 256. out[M, I] = bf16(bf16(silu(bf16(g))) * bf16(u)); the SiLU uses the
  * approximate exponential and reciprocal of the device (about 2 ulp in fp32 before the bf16 rounding). The CTA-pair kernel
- * (variants 5 / 6) reads a different interleave: blocks of 64 gate rows followed by their 64 up rows. */
+ * with block units (variant 5) reads a different interleave: blocks of 64 gate rows followed by their 64 up rows; with all
+ * rows swapped (variant 6) it reads the layout above. */
 int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
                          int32_t* status, ojb_stream_t stream);
 /* The same with the kernel variant forced (0, 1, 3, 4, 5 or 6 as for ojb_gemm_bf16); for tuning. */

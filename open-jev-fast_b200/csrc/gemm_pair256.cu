@@ -17,7 +17,10 @@
 //                               global stores are whole 128-byte rows; then arrives on the leader's "accumulator free" barrier
 // Work units, their order and the K ranges are those of the one-CTA block kernel (gemm_units.cuh), dealt to the CTA pairs
 // round-robin: block units of 256 rows of x times BN rows of w, and swapped-operand units (256 rows of w as the M side,
-// up to 256 rows of x as the N side) for the last M mod 256 <= 128 rows or, on request, for all of x when M <= 512.
+// rows of x as the N side) for the last M mod 256 <= 128 rows or, on request, for all of x. In the latter mode a unit
+// covers up to 512 rows of x with one pass over its 256 rows of w: its accumulator columns are filled by up to two MMAs per
+// k-step (N <= 256 each), so w crosses the memory system once per 512 rows of x; a unit wider than 256 columns uses the
+// whole tensor memory and the MMAs of the next unit wait for its epilogue.
 //
 // Every wait on an mbarrier is bounded (2 s): the CTA then raises its abort flag, records OJB_DEV_WAIT_TIMEOUT, lets copies
 // in flight land, and both CTAs still meet at the closing cluster barrier before freeing their TMEM.
@@ -132,7 +135,8 @@ __device__ __forceinline__ void stage_flush(const uint8_t* tile, int lane, T* ou
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_constant__ CUtensorMap map_wh,
-                    const __grid_constant__ CUtensorMap map_w128, const __grid_constant__ CUtensorMap map_xt, GemmArgs g) {
+                    const __grid_constant__ CUtensorMap map_w128, const __grid_constant__ CUtensorMap map_xt,
+                    const __grid_constant__ CUtensorMap map_w64, GemmArgs g) {
   pdl_launch_dependents();
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
@@ -168,6 +172,7 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_wh) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w128) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xt) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w64) : "memory");
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
@@ -182,7 +187,10 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
 
   const int total_block = g.n_xblk * g.n_wtile * g.splits;
   const int total_units = total_block + (g.tail_rows > 0 ? g.n_wtile256 * g.splits * g.n_xchunk : 0);
-  const int half_bn = g.BN / 2, half_tb = g.tail_box / 2;
+  const int half_bn = g.BN / 2, half_cw = g.chunk_w / 2;
+  // accumulator buffers: two of 256 columns, or, when a swapped unit needs more than 256 columns, one of up to 512 (the
+  // MMAs of a unit then wait for the epilogue of the previous one)
+  const int nbuf = g.tail_box > static_cast<int>(kAccCols) ? 1 : 2;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -192,7 +200,7 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
       bool ok = true;
       for (int unit = pair_id; unit < total_units && ok; unit += n_pairs) {
         const Unit u = decode_unit(g, unit, total_block);
-        const uint32_t my_bytes = kHalfABytes + static_cast<uint32_t>(u.tail ? half_tb : half_bn) * (kBK * 2);
+        const uint32_t my_bytes = kHalfABytes + static_cast<uint32_t>(u.tail ? g.n_chunk * half_cw : half_bn) * (kBK * 2);
         for (int kb = u.kb0; kb < u.kb1; ++kb) {
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = tiles0 + stage * g.stage_bytes;
@@ -202,9 +210,19 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
             tma_load_2d_pair(a_dst, &map_xh, fb_leader, kb * kBK, u.xb * kBlockM + static_cast<int>(rank) * kBM);
             tma_load_2d_pair(a_dst + kHalfABytes, &map_wh, fb_leader, kb * kBK, u.wt * g.BN + static_cast<int>(rank) * half_bn);
           } else {
-            tma_load_2d_pair(a_dst, &map_w128, fb_leader, kb * kBK, u.wt * 256 + static_cast<int>(rank) * kBM);
-            tma_load_2d_pair(a_dst + kHalfABytes, &map_xt, fb_leader, kb * kBK,
-                             g.n_xblk * kBlockM + u.xc * g.tail_box + static_cast<int>(rank) * half_tb);
+            if (g.w_split64) {
+              tma_load_2d_pair(a_dst, &map_w64, fb_leader, kb * kBK, u.wt * 256 + static_cast<int>(rank) * 64);
+              tma_load_2d_pair(a_dst + kHalfABytes / 2, &map_w64, fb_leader, kb * kBK, u.wt * 256 + 128 + static_cast<int>(rank) * 64);
+            } else {
+              tma_load_2d_pair(a_dst, &map_w128, fb_leader, kb * kBK, u.wt * 256 + static_cast<int>(rank) * kBM);
+            }
+            const int xrow0 = g.n_xblk * kBlockM + u.xc * g.tail_box;
+            for (int c = 0; c < g.n_chunk; ++c) {
+              const int wc = min(g.chunk_w, g.tail_box - c * g.chunk_w);
+              // (the box always has chunk_w / 2 rows: behind a narrower last chunk it fetches rows no MMA reads)
+              tma_load_2d_pair(a_dst + kHalfABytes + static_cast<uint32_t>(c * half_cw) * (kBK * 2), &map_xt, fb_leader, kb * kBK,
+                               xrow0 + c * g.chunk_w + static_cast<int>(rank) * (wc / 2));
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -219,9 +237,9 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
       bool ok = true;
       for (int unit = pair_id; unit < total_units && ok; unit += n_pairs, ++it) {
         const Unit u = decode_unit(g, unit, total_block);
-        const uint32_t idesc = umma_idesc_m256(u.tail ? g.tail_box : g.BN);
-        const int buf = it & 1;
-        const uint32_t use = static_cast<uint32_t>(it >> 1);
+        const uint32_t idesc = umma_idesc_m256(g.BN);
+        const int buf = nbuf == 2 ? (it & 1) : 0;
+        const uint32_t use = static_cast<uint32_t>(nbuf == 2 ? (it >> 1) : it);
         if (!mbar_wait(accempty0 + 8 * buf, (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem_base + static_cast<uint32_t>(buf) * kAccCols;
@@ -231,7 +249,19 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
           const uint32_t a_addr = tiles0 + stage * g.stage_bytes;
           const uint64_t adesc = smem_desc_sw128(a_addr);
           const uint64_t bdesc = smem_desc_sw128(a_addr + kHalfABytes);
-          if (g.mma_repeat == 1) {
+          if (u.tail) {
+            for (int rep = 0; rep < g.mma_repeat; ++rep) {      // (repeat > 1 only for measurements)
+              for (int c = 0; c < g.n_chunk; ++c) {
+                const int wc = min(g.chunk_w, g.tail_box - c * g.chunk_w);
+                const uint32_t idesc_c = umma_idesc_m256(wc);
+                const uint64_t bdesc_c = smem_desc_sw128(a_addr + kHalfABytes + static_cast<uint32_t>(c * half_cw) * (kBK * 2));
+#pragma unroll
+                for (int k = 0; k < kBK / kUmmaK; ++k)
+                  umma_bf16_pair(acc + static_cast<uint32_t>(c * g.chunk_w), adesc + 2 * k, bdesc_c + 2 * k, idesc_c,
+                                 (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u);
+              }
+            }
+          } else if (g.mma_repeat == 1) {
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k)
               umma_bf16_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
@@ -257,8 +287,8 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
     bool ok = true;
     for (int unit = pair_id; unit < total_units && ok; unit += n_pairs, ++it) {
       const Unit u = decode_unit(g, unit, total_block);
-      const int buf = it & 1;
-      const uint32_t use = static_cast<uint32_t>(it >> 1);
+      const int buf = nbuf == 2 ? (it & 1) : 0;
+      const uint32_t use = static_cast<uint32_t>(nbuf == 2 ? (it >> 1) : it);
       const bool tracing = g.trace != nullptr && warp == 2 && lane == 0 && leader;
       const unsigned long long t_begin = tracing ? global_timer_ns() : 0ull;
       if (!mbar_wait(accfull0 + 8 * buf, use & 1u, abort_flag)) { ok = false; break; }
@@ -444,14 +474,16 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
-  const bool all_swapped = bn_req < 0 || M <= kBM;
+  const bool forced_swapped = bn_req < 0;      // variant 6: the SwiGLU weight is then read in the 128-row interleave
+  const bool all_swapped = forced_swapped || M <= kBM;
   if (bn_req < 0) bn_req = 0;
   if (all_swapped) {
-    if (M > 512) return OJB_ERR_LIMIT;
+    // every row of x through swapped-operand units: passes of at most 512 rows, each the accumulator columns of one unit
+    const int64_t m16 = ceil_div(M, 16) * 16;
     g.n_xblk = 0;
     g.tail_rows = static_cast<int>(M);
-    g.n_xchunk = static_cast<int>(ceil_div(M, 256));
-    g.tail_box = static_cast<int>(ceil_div(ceil_div(M, g.n_xchunk), 16) * 16);
+    g.n_xchunk = static_cast<int>(ceil_div(m16, 512));
+    g.tail_box = static_cast<int>(ceil_div(ceil_div(m16, g.n_xchunk), 16) * 16);
   } else {
     g.n_xblk = static_cast<int>(M / kBlockM);
     int r = static_cast<int>(M % kBlockM);
@@ -460,6 +492,9 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.tail_box = (r + 15) / 16 * 16;
     g.n_xchunk = 1;
   }
+  g.n_chunk = g.tail_box > 0 ? static_cast<int>(ceil_div(g.tail_box, 256)) : 1;
+  g.chunk_w = g.tail_box > 0 ? static_cast<int>(ceil_div(ceil_div(g.tail_box, g.n_chunk), 16) * 16) : 16;
+  g.w_split64 = (EPI == kEpiSwiglu && forced_swapped) ? 1 : 0;
   g.splits = splits;
   g.kb_total = static_cast<int>(ceil_div(K, kBK));
   g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
@@ -467,7 +502,8 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, g.tail_box, g.n_xchunk, g.tail_rows > 0, splits, g.kb_total, pairs, EPI));
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
-  const int half_b = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) / 2 : g.tail_box / 2;
+  const int tail_half = g.n_chunk * g.chunk_w / 2;      // rows of x per CTA and stage of a swapped unit
+  const int half_b = g.n_xblk > 0 ? (g.BN / 2 > tail_half ? g.BN / 2 : tail_half) : tail_half;
   g.stage_bytes = kHalfABytes + static_cast<uint32_t>(half_b) * (kBK * 2);
   g.stage_bytes = (g.stage_bytes + 1023u) & ~1023u;      // every stage starts on a swizzle-atom boundary
   const size_t fixed = 1024 + kStagingBytes + (2 * kPairMaxStages + 4) * 8 + 16;
@@ -485,11 +521,12 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.dbg = 0;
   g.tail_sub = 0;
   g.tma_out = 0;
-  CUtensorMap map_xh, map_wh, map_w128, map_xt;
+  CUtensorMap map_xh, map_wh, map_w128, map_xt, map_w64;
   int rc = make_map(&map_xh, x, M, K, kBM);
   if (rc == OJB_OK) rc = make_map(&map_wh, w, N, K, g.BN / 2);
   if (rc == OJB_OK) rc = make_map(&map_w128, w, N, K, kBM);
-  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box / 2 : 8);
+  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.chunk_w / 2 : 8);
+  if (rc == OJB_OK) rc = make_map(&map_w64, w, N, K, 64);
   if (rc != OJB_OK) return rc;
   const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits +
                         (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits * g.n_xchunk : 0);
@@ -500,7 +537,7 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     while (n_pairs > 1 && gcd(n_pairs, group) != 1) --n_pairs;
   }
   const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
-  launch_kernel(kern, dim3(2 * n_pairs), dim3(kPairThreads), smem, stream, map_xh, map_wh, map_w128, map_xt, g);
+  launch_kernel(kern, dim3(2 * n_pairs), dim3(kPairThreads), smem, stream, map_xh, map_wh, map_w128, map_xt, map_w64, g);
   return launch_status(cudaGetLastError());
 }
 

@@ -31,6 +31,11 @@ struct GemmArgs {
   int tma_out;                 // the block epilogue stores through shared-memory tiles and bulk tensor stores
   int dbg;                     // measurement only: 100 = the block epilogue skips its global stores, 101 = its TMEM loads
   int mma_repeat;              // 1; > 1 only for measurements: every stage's MMAs are issued this many times
+  // CTA-pair kernel, swapped-operand units: the tail_box accumulator columns (= rows of x) of a unit are produced by
+  // n_chunk MMAs per k-step of chunk_w columns each (the last one narrower), so one pass over 256 rows of w serves up to
+  // 512 rows of x; w_split64: the 128 rows of w of a CTA are fetched as rows [64r, 64r+64) and [128+64r, 128+64r+64) of the
+  // tile (gate and up rows of the same 64 outputs of a SwiGLU weight interleaved in blocks of 128 rows).
+  int n_chunk, chunk_w, w_split64;
 };
 
 struct Unit {

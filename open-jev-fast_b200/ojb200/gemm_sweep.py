@@ -50,6 +50,8 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--shape", type=int, nargs=2, default=None, metavar=("K", "N"), help="only this weight shape")
     ap.add_argument("--only", default=None, help="only kernels whose name starts with this (plain, swiglu, splitk)")
+    ap.add_argument("--library", action="store_true",
+                    help="also time torch.nn.functional.linear (cuBLASLt, the GEMM path of the reference) on the same operands: a comparator only")
     ap.add_argument("--copies", type=int, default=0, help="distinct weight copies to cycle through (default: enough to exceed L2)")
     args = ap.parse_args()
     dev = torch.device("cuda")
@@ -68,12 +70,16 @@ def main():
                 print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
                                   "max_err": err}), flush=True)
-            for v in ((0, 1, 2, 3, 7, 8) if want("plain") else ()):
+            for v in ((0, 1, 2, 3, 7, 8, 9) if want("plain") else ()):
                 if v == 7 and M > 512:
                     continue
                 out = LT.lt_matmul(x, ws[0], v)
                 err = (out.float() - ref).abs().max().item()
                 report(f"plain v{v}", _time([lambda w=w, v=v: LT.lt_matmul(x, w, v) for w in ws]), err)
+            if args.library:
+                out = torch.nn.functional.linear(x, ws[0])
+                report("library F.linear", _time([lambda w=w: torch.nn.functional.linear(x, w) for w in ws]),
+                       (out.float() - ref).abs().max().item())
             if N % 256 == 0 and Kd == 5120 and N > 20000 and want("swiglu"):
                 I = N // 2
                 wb = [LT.interleave_gate_up(w[:I], w[I:]) for w in ws]
@@ -89,12 +95,14 @@ def main():
                 err64 = (LT.gemm_swiglu(x, wb64[0], 8).float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
                 report("swiglu v8", _time([lambda w=w: LT.gemm_swiglu(x, w, 8) for w in wb64]), err64)
                 del wb64
+                err9 = (LT.gemm_swiglu(x, wb[0], 9).float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
+                report("swiglu v9", _time([lambda w=w: LT.gemm_swiglu(x, w, 9) for w in wb]), err9)
             if N == 5120 and not args.quick and want("splitk"):
                 h = torch.randn(M, N, generator=g, device=dev).to(bf16)
                 w1 = torch.ones(N, device=dev)
                 plan = LT.plan_splitk(M, N, Kd)
                 for S in sorted({1, 2, 3, 4, 6, plan}):
-                    for v in (0, 1, 3, 7, 8):
+                    for v in (0, 1, 3, 7, 8, 9):
                         if v == 7 and M > 512:
                             continue
                         parts = LT.gemm_splitk(x, ws[0], S, v)

@@ -41,7 +41,7 @@ def main():
     x = torch.randn(M, K, generator=g, device=dev).to(bf16)
     ws = [(torch.randn(N, K, generator=g, device=dev) * 0.02).to(bf16) for _ in range(2)]
     if args.kind == "swiglu":
-        blk = 64 if args.variant in (5, 6) or args.variant >= 512 else 128
+        blk = 64 if args.variant == 5 or args.variant >= 512 else 128
         ws = [LT.interleave_gate_up(w[:N // 2].contiguous(), w[N // 2:].contiguous(), blk) for w in ws]
     rec = torch.zeros(1 + 4 * CAP, dtype=torch.int64, device=dev)
     st = ptr(_lib.status_word(dev))

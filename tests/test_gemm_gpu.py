@@ -31,7 +31,7 @@ def _close(out, ref):
                                    (1024, 5120, 6144), (544, 5120, 4096)])
 def test_gemm_plain(M, N, K, variant):
     from ojb200 import lt_ext, _lib
-    if variant in (7, 9) and M > 512:
+    if variant == 7 and M > 512:
         pytest.skip("the all-swapped form serves M <= 512")
     x, w = _mk(M, N, K, 1)
     out = lt_ext.lt_matmul(x, w, variant)
@@ -44,14 +44,14 @@ def test_gemm_plain(M, N, K, variant):
 @pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120), (256, 256, 320), (700, 384, 512), (539, 2048, 1024)])
 def test_gemm_swiglu(M, I, K, variant):
     from ojb200 import lt_ext, _lib
-    if variant in (7, 9) and M > 512:
+    if variant == 7 and M > 512:
         pytest.skip("the all-swapped form serves M <= 512")
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(M, K, generator=g, device="cuda").to(bf16)
     wg = (torch.randn(I, K, generator=g, device="cuda") * 0.02).to(bf16)
     wu = (torch.randn(I, K, generator=g, device="cuda") * 0.02).to(bf16)
-    # the CTA-pair kernel reads gate / up interleaved in blocks of 64 rows, the other two in blocks of 128
-    out = lt_ext.gemm_swiglu(x, lt_ext.interleave_gate_up(wg, wu, 64 if variant in (8, 9) else 128), variant)
+    # the CTA-pair kernel with block units reads gate / up interleaved in blocks of 64 rows, all others in blocks of 128
+    out = lt_ext.gemm_swiglu(x, lt_ext.interleave_gate_up(wg, wu, 64 if variant == 8 else 128), variant)
     torch.cuda.synchronize()
     _lib.check_status()
     gg = _ref(x, wg).to(bf16).float()
