@@ -75,7 +75,8 @@ int ojb_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t kind, int32_t max_spl
  * complete, ns when its epilogue ended} (%globaltimer). mma_repeat > 1 issues the MMAs of every shared-memory stage that
  * many times (results are then meaningless): the slope against mma_repeat is the pure tensor-pipe cost of a stage.
  * mma_repeat = 0 issues none (pure copy rate). knob: 0 = nothing, 2..12 = cap on the number of pipeline stages, 100 / 101 =
- * the block epilogue skips its global stores / its TMEM loads. The CTA-pair kernel records the same timelines. */
+ * the block epilogue skips its global stores / its TMEM loads, 102 = with mma_repeat > 1 the MMAs of block units are issued
+ * with M = 64 instead of 128 (the cost of a half-height MMA). The CTA-pair kernel records the same timelines. */
 int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t knob);
 
 /* ------------------------------------------------------------------------------------------------------------------

@@ -108,7 +108,7 @@ extern "C" int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, 
 }
 
 extern "C" int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t stage_cols) {
-  OJB_REQUIRE(capacity >= 0 && mma_repeat >= 0 && mma_repeat <= 64 && (stage_cols == 0 || (stage_cols >= 2 && stage_cols <= 12) || stage_cols == 100 || stage_cols == 101));
+  OJB_REQUIRE(capacity >= 0 && mma_repeat >= 0 && mma_repeat <= 64 && (stage_cols == 0 || (stage_cols >= 2 && stage_cols <= 12) || stage_cols == 100 || stage_cols == 101 || stage_cols == 102));
   gemm_block256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity, mma_repeat, stage_cols);
   gemm_pair256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity, mma_repeat, stage_cols);
   return OJB_OK;

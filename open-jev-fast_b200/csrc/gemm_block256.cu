@@ -190,11 +190,13 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
               umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
             }
           } else {                                   // measurement only (ojb_gemm_set_trace)
+            // knob 102: the same MMAs with M = 64 in the instruction descriptor (what does a half-height MMA cost?)
+            const uint32_t idesc_m = g.dbg == 102 ? ((idesc & ~(0x1fu << 24)) | (static_cast<uint32_t>(64 >> 4) << 24)) : idesc;
             for (int rep = 0; rep < g.mma_repeat; ++rep)
               for (int k = 0; k < kBK / kUmmaK; ++k) {
                 const uint32_t accum = (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u;
-                umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
-                umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
+                umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc_m, accum);
+                umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc_m, accum);
               }
           }
           umma_commit(empty0 + 8 * stage);
