@@ -500,7 +500,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   }
   const int sms = sm_count();
   if (sms <= 0) return OJB_ERR_LAUNCH;
-  GemmArgs g;
+  GemmArgs g{};
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);

@@ -470,7 +470,7 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   }
   const int pairs = sm_count() / 2;
   if (pairs <= 0) return OJB_ERR_LAUNCH;
-  GemmArgs g;
+  GemmArgs g{};
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);

@@ -275,7 +275,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   if (rc != OJB_OK) return rc;
   rc = make_map(&map_w, w, N, K, BN);
   if (rc != OJB_OK) return rc;
-  GemmArgs g;
+  GemmArgs g{};
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
