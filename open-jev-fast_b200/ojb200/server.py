@@ -4,7 +4,9 @@ Follows open-jev-fast's src/server.py: `Entry` (src/server.py:32-49) owns static
 key (N, S, L2); `Scorer.forward(records)` keeps the contract of `_forward(records)` (src/server.py:86-142): one score per
 candidate, `noul` questions answered as [0, score], an LRU of at most MAX_GRAPHS graphs, one access-log record per request.
 What is outside this repository's scope (HTTP, tokenizer, chat template: the un-vendored `jev` package) is replaced by
-token-id lists: a record is {"kind": "noul" | "choice" | "score", "candidates": [[token ids], ...]}.
+token-id lists: a record is {"kind": "noul" | "choice" | "score", "candidates": [[token ids], ...]}. `prompt_ids` is the
+tokenisation step of src/server.py:72-85 for callers that bring a Hugging Face tokenizer: the chat template is rendered
+once around a marker, split into a fixed head and tail, and all prompts of a request go through one batched encode.
 """
 import collections
 import json
@@ -23,6 +25,44 @@ REP_MAX = int(os.environ.get("REP_MAX", "4096"))
 STATE_PATH = os.environ.get("OJ_STATE_PATH", "0") == "1"
 MAX_GRAPHS = int(os.environ.get("MAX_GRAPHS", "512"))
 USE_GRAPH = os.environ.get("USE_GRAPH", "1") == "1"
+
+
+_TEMPLATE_PARTS = {}
+_MARK = "\x00OJB\x00"
+
+
+def prompt_ids(tok, prompts):
+    """Token ids of every prompt wrapped in the tokenizer's chat template (one user message, generation prompt, thinking
+    off), as src/server.py:72-85 does: the template text is rendered once per tokenizer around a marker and cut at the
+    marker; each prompt is then head + prompt + tail and the whole list is encoded by one call of the backend tokenizer.
+    A template in which the marker does not appear exactly once falls back to rendering and encoding prompt by prompt."""
+    parts = _TEMPLATE_PARTS.get(id(tok))
+    if parts is None:
+        text = tok.apply_chat_template([{"role": "user", "content": _MARK}], tokenize=False, add_generation_prompt=True,
+                                       enable_thinking=False)
+        parts = _TEMPLATE_PARTS[id(tok)] = tuple(text.split(_MARK)) if text.count(_MARK) == 1 else ()
+    if not parts:
+        return [tok(tok.apply_chat_template([{"role": "user", "content": p}], tokenize=False, add_generation_prompt=True,
+                                            enable_thinking=False))["input_ids"] for p in prompts]
+    enc = tok.backend_tokenizer.encode_batch([parts[0] + p + parts[1] for p in prompts], add_special_tokens=True)
+    return [list(e.ids) for e in enc]
+
+
+def token_records(records, tok, candidate_prompts):
+    """Text records -> the token-id records `Scorer.forward` takes. `candidate_prompts(record)` returns the prompt of every
+    candidate of a record (the un-vendored jev.candidate_prompts in the reference, src/server.py:91); all prompts of the
+    request are tokenised by one `prompt_ids` call."""
+    prompts, counts = [], []
+    for r in records:
+        c = candidate_prompts(r)
+        counts.append(len(c))
+        prompts += c
+    ids = prompt_ids(tok, prompts)
+    out, off = [], 0
+    for r, c in zip(records, counts):
+        out.append({"kind": r.get("kind", "score"), "candidates": ids[off:off + c]})
+        off += c
+    return out
 
 
 class Entry:
