@@ -62,6 +62,19 @@ int ojb_gemm_bf16_swiglu_v(const void* x, const void* w_blk, void* out, int64_t 
 int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, int64_t M, int64_t N, int64_t K, int splits,
                          int variant, int32_t* status, ojb_stream_t stream);
 
+/* 8-bit variant of the three GEMM forms (the FP8 path the reference measured, README.md:131 / bench/logs/peak_fp8_bench.log,
+ * and did not ship): operands are e4m3 bytes with one fp32 scale per row, out = (xq · wq^T) * sx[m] * sw[n], fp32
+ * accumulation in tensor memory (tcgen05.mma.kind::f8f6f4, 256-row block kernel). kind 0: out = bf16 [M, N]; kind 1:
+ * SwiGLU as in ojb_gemm_bf16_swiglu (wq = the re-laid gate/up weight, sw in the same row order, N % 256 == 0), out = bf16
+ * [M, N/2]; kind 2: fp32 partials [splits, M, N] over K ranges of whole 128-column k-blocks. K % 16 == 0; splits = 1
+ * unless kind 2. Off by default in the Python layer (OJ_FP8=1): scores move by more than the bf16 tolerance. */
+int ojb_gemm_e4m3(const void* xq, const float* sx, const void* wq, const float* sw, void* out, int64_t M, int64_t N, int64_t K,
+                  int32_t kind, int32_t splits, int32_t* status, ojb_stream_t stream);
+
+/* Per-row e4m3 quantisation of a bf16 matrix [rows, K] (K % 8 == 0) for ojb_gemm_e4m3: scale[m] = max|x[m,:]| / 448 (1 for
+ * an all-zero row), q[m,k] = e4m3(x[m,k] / scale[m]), round to nearest, saturating. */
+int ojb_quantize_rows_e4m3(const void* x, void* q, float* scale, int64_t rows, int64_t K, ojb_stream_t stream);
+
 /* Host-side plan (no GPU work): which kernel variant and how many K ranges the library's cost model picks for a shape.
  * kind = 0 bf16 output, 1 SwiGLU-fused, 2 fp32 split-K partials (the only kind that may use more than one range, up to
  * max_splits). *microseconds (optional) receives the modelled time. Takes the place of the algorithm search of

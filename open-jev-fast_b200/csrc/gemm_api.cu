@@ -133,3 +133,15 @@ extern "C" int ojb_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t kind, int3
   if (microseconds) *microseconds = static_cast<float>(best.clocks / 1800.0);
   return OJB_OK;
 }
+
+extern "C" int ojb_gemm_e4m3(const void* xq, const float* sx, const void* wq, const float* sw, void* out, int64_t M, int64_t N,
+                             int64_t K, int32_t kind, int32_t splits, int32_t* status, ojb_stream_t stream) {
+  if (M == 0 || N == 0) return OJB_OK;
+  OJB_REQUIRE(xq && sx && wq && sw && out && M > 0 && N > 0 && K > 0 && K % 16 == 0 && kind >= 0 && kind <= 2);
+  OJB_REQUIRE(aligned16(xq) && aligned16(wq) && aligned16(out));
+  OJB_REQUIRE(kind == 2 ? (splits >= 1 && splits <= 16) : splits == 1);
+  OJB_REQUIRE(kind != 1 || N % 256 == 0);
+  const int epi = kind == 0 ? kEpiBf16 : (kind == 1 ? kEpiSwiglu : kEpiPartialF32);
+  return gemm_block256_launch_e4m3(epi, xq, sx, wq, sw, out, M, N, K, splits, kind == 1 ? N / 2 : N, status,
+                                   static_cast<cudaStream_t>(stream));
+}

@@ -44,13 +44,20 @@ int g_mma_repeat = 1;
 int g_max_stages = 0;   // 2..12: cap on the number of pipeline stages (measurement only)
 int g_dbg = 0;
 
-template <int EPI>
+// FP8: the operands are e4m3 bytes (a k-block of 128 bytes is then 128 elements of K and an MMA covers 32 of them); the
+// epilogue multiplies the accumulator by the scale of its row of x and of its row of w. Everything counted in bytes (stages,
+// swizzle, descriptors) is the same for both operand types.
+template <int EPI, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt,
                     const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_w128, GemmArgs g) {
   pdl_launch_dependents();
   constexpr uint32_t kTmemCols = 512;
+  constexpr int kKE = FP8 ? 128 : kBK;      // elements of K per k-block (the coordinate step of the copies)
+  auto mma = [](uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    if constexpr (FP8) umma_f8(d, a, b, idesc, acc); else umma_bf16(d, a, b, idesc, acc);
+  };
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* staging = smem + static_cast<size_t>(g.stages) * g.stage_bytes;       // [8 warps][32 rows][128 bytes] when tma_out
@@ -117,8 +124,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             mbar_expect_tx(fb, static_cast<uint32_t>(cnt * g.tail_sub));
             for (int j = 0; j < cnt; ++j) {
               const int h = h0 + j, kb = u.kb0 + (h >> 1);
-              tma_load_2d(a_dst + j * g.tail_sub, &map_w128, fb, kb * kBK, u.wt * 256 + (h & 1) * kBM);
-              tma_load_2d(a_dst + j * g.tail_sub + kSubBytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM + u.xc * g.tail_box);
+              tma_load_2d(a_dst + j * g.tail_sub, &map_w128, fb, kb * kKE, u.wt * 256 + (h & 1) * kBM);
+              tma_load_2d(a_dst + j * g.tail_sub + kSubBytes, &map_xt, fb, kb * kKE, g.n_xblk * kBlockM + u.xc * g.tail_box);
             }
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -130,11 +137,11 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           const uint32_t fb = full0 + 8 * stage;
           mbar_expect_tx(fb, tx);
           if (!u.tail) {
-            tma_load_2d(a_dst, &map_x, fb, kb * kBK, u.xb * kBlockM);
-            tma_load_2d(a_dst + kABytes, &map_w, fb, kb * kBK, u.wt * g.BN);
+            tma_load_2d(a_dst, &map_x, fb, kb * kKE, u.xb * kBlockM);
+            tma_load_2d(a_dst + kABytes, &map_w, fb, kb * kKE, u.wt * g.BN);
           } else {
-            tma_load_2d(a_dst, &map_w256, fb, kb * kBK, u.wt * 256);
-            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kBK, g.n_xblk * kBlockM + u.xc * g.tail_box);
+            tma_load_2d(a_dst, &map_w256, fb, kb * kKE, u.wt * 256);
+            tma_load_2d(a_dst + kABytes, &map_xt, fb, kb * kKE, g.n_xblk * kBlockM + u.xc * g.tail_box);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -148,7 +155,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
         const Unit u = decode_unit(g, unit, total_block);
-        const uint32_t idesc = umma_idesc(u.tail ? g.tail_box : g.BN);
+        const uint32_t idesc = FP8 ? umma_idesc_e4m3(u.tail ? g.tail_box : g.BN) : umma_idesc(u.tail ? g.tail_box : g.BN);
         if (!mbar_wait(accempty, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (u.tail && g.tail_sub) {
@@ -164,7 +171,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
               const uint64_t adesc = smem_desc_sw128(a_addr + j * g.tail_sub);
               const uint64_t bdesc = smem_desc_sw128(a_addr + j * g.tail_sub + kSubBytes);
 #pragma unroll
-              for (int k = 0; k < kBK / kUmmaK; ++k) umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (h >= 2 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < kBK / kUmmaK; ++k) mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (h >= 2 || k > 0) ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * stage);
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -186,8 +193,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             for (int k = 0; k < kBK / kUmmaK; ++k) {
               // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
               const uint32_t accum = (kb > u.kb0 || k > 0) ? 1u : 0u;
-              umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
-              umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
+              mma(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
+              mma(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
             }
           } else {                                   // measurement only (ojb_gemm_set_trace)
             // knob 102: the same MMAs with M = 64 in the instruction descriptor (what does a half-height MMA cost?)
@@ -195,8 +202,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             for (int rep = 0; rep < g.mma_repeat; ++rep)
               for (int k = 0; k < kBK / kUmmaK; ++k) {
                 const uint32_t accum = (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u;
-                umma_bf16(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc_m, accum);
-                umma_bf16(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc_m, accum);
+                mma(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc_m, accum);
+                mma(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc_m, accum);
               }
           }
           umma_commit(empty0 + 8 * stage);
@@ -211,6 +218,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter+32) are the ones this warp may read
     const int acc_id = (warp - 2) >> 2;     // warps 2-5 read accumulator 0, warps 6-9 accumulator 1
+    // e4m3 operands: scale of row n of w / row m of x (indices clamped: tiles may reach past the matrix)
+    auto sw_at = [&](int n) -> float { if constexpr (FP8) return __ldg(g.sw + min(n, g.N - 1)); else return 1.f; };
+    auto sx_at = [&](int m) -> float { if constexpr (FP8) return __ldg(g.sx + min(m, g.M - 1)); else return 1.f; };
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
@@ -226,6 +236,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         // ---- block unit: this thread owns one row of x, the accumulator columns are output columns
         const int row = u.xb * kBlockM + acc_id * kBM + quarter * 32 + lane;
         const bool row_ok = row < g.M;
+        const float rs = sx_at(row);
         if (g.tma_out) {
           // ---- through shared memory: the warp's 32 rows x 128 bytes go into a swizzled tile (16-byte piece j of row r at
           //      slot j ^ (r & 7), the layout of the 128-byte swizzle) and one lane hands the tile to the bulk-copy engine,
@@ -261,10 +272,17 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                   float o[8];
 #pragma unroll
                   for (int e = 0; e < 8; e += 2) {
+                    float g0 = __uint_as_float(gr[8 * j + e]), g1 = __uint_as_float(gr[8 * j + e + 1]);
+                    float u0 = __uint_as_float(ur[8 * j + e]), u1 = __uint_as_float(ur[8 * j + e + 1]);
+                    if constexpr (FP8) {
+                      const int wr = u.wt * 256 + t * 64 + c * 32 + 8 * j + e;      // gate row of w; its up row is 128 further
+                      g0 *= rs * sw_at(wr); g1 *= rs * sw_at(wr + 1);
+                      u0 *= rs * sw_at(wr + 128); u1 *= rs * sw_at(wr + 129);
+                    }
                     float s0, s1;
-                    silu2_f(round_bf(__uint_as_float(gr[8 * j + e])), round_bf(__uint_as_float(gr[8 * j + e + 1])), s0, s1);
-                    o[e] = round_bf(s0) * round_bf(__uint_as_float(ur[8 * j + e]));
-                    o[e + 1] = round_bf(s1) * round_bf(__uint_as_float(ur[8 * j + e + 1]));
+                    silu2_f(round_bf(g0), round_bf(g1), s0, s1);
+                    o[e] = round_bf(s0) * round_bf(u0);
+                    o[e + 1] = round_bf(s1) * round_bf(u1);
                   }
                   put(c * 4 + j, pack8(o));
                 }
@@ -283,11 +301,12 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 float o[8];
+                const int wr = u.wt * g.BN + t * 64 + 8 * j;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(ra[8 * j + e]);
+                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(ra[8 * j + e]) * (FP8 ? rs * sw_at(wr + e) : 1.f);
                 put(j, pack8(o));
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(rb[8 * j + e]);
+                for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(rb[8 * j + e]) * (FP8 ? rs * sw_at(wr + 32 + e) : 1.f);
                 put(j + 4, pack8(o));
               }
               if (u.wt * g.BN + t * 64 < g.N) flush(u.wt * g.BN + t * 64);
@@ -301,7 +320,14 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
               tmem_ld_wait();
               reuse();
 #pragma unroll
-              for (int j = 0; j < 8; ++j) put(j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+              for (int j = 0; j < 8; ++j) {
+                if constexpr (FP8) {
+                  const int wr = u.wt * g.BN + t * 32 + 4 * j;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) r[4 * j + e] = __float_as_uint(__uint_as_float(r[4 * j + e]) * rs * sw_at(wr + e));
+                }
+                put(j, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+              }
               if (u.wt * g.BN + t * 32 < g.N) flush(u.wt * g.BN + t * 32);
             }
           }
@@ -414,6 +440,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             const bool col_ok = j < g.N / 2;
             bf16_t* ocol = reinterpret_cast<bf16_t*>(g.out) + j;
             const int nchunk = g.tail_box / 16;
+            const float swg = sw_at(u.wt * 256 + quarter * 32 + lane), swu = sw_at(u.wt * 256 + 128 + quarter * 32 + lane);
 #pragma unroll 1
             for (int c = acc_id; c < nchunk; c += 2) {
               uint32_t gr[16], ur[16];
@@ -424,7 +451,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
               for (int e = 0; e < 16; ++e) {
                 const int m = m0 + c * 16 + e;
                 if (col_ok && m < g.M) {
-                  const float gv = round_bf(__uint_as_float(gr[e])), uv = round_bf(__uint_as_float(ur[e]));
+                  const float xs = sx_at(m);
+                  const float gv = round_bf(__uint_as_float(gr[e]) * (FP8 ? xs * swg : 1.f));
+                  const float uv = round_bf(__uint_as_float(ur[e]) * (FP8 ? xs * swu : 1.f));
                   ocol[static_cast<int64_t>(m) * g.ldo] = f2bf(round_bf(silu_f(gv)) * uv);
                 }
               }
@@ -433,6 +462,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         } else {
           const int col = u.wt * 256 + acc_id * kBM + quarter * 32 + lane;
           const bool col_ok = col < g.N;
+          const float swc = sw_at(col);
 #pragma unroll 1
           for (int c = 0; c < g.tail_box / 16; ++c) {
             uint32_t r[16];
@@ -442,11 +472,11 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             for (int e = 0; e < 16; ++e) {
               const int m = m0 + c * 16 + e;
               if (col_ok && m < g.M) {
+                const float v = __uint_as_float(r[e]) * (FP8 ? swc * sx_at(m) : 1.f);
                 if constexpr (EPI == kEpiBf16) {
-                  reinterpret_cast<bf16_t*>(g.out)[static_cast<int64_t>(m) * g.ldo + col] = f2bf(__uint_as_float(r[e]));
+                  reinterpret_cast<bf16_t*>(g.out)[static_cast<int64_t>(m) * g.ldo + col] = f2bf(v);
                 } else {
-                  reinterpret_cast<float*>(g.out)[static_cast<int64_t>(u.split) * g.split_stride + static_cast<int64_t>(m) * g.ldo + col] =
-                      __uint_as_float(r[e]);
+                  reinterpret_cast<float*>(g.out)[static_cast<int64_t>(u.split) * g.split_stride + static_cast<int64_t>(m) * g.ldo + col] = v;
                 }
               }
             }
@@ -488,11 +518,11 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 
 constexpr size_t kSmemBudget = 227 * 1024;
 
-template <int EPI>
+template <int EPI, bool FP8 = false>
 int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
-                int32_t* status, cudaStream_t stream) {
+                int32_t* status, cudaStream_t stream, const float* sx = nullptr, const float* sw = nullptr) {
   static bool attr_set = false;
-  auto kern = gemm_block256_kernel<EPI>;
+  auto kern = gemm_block256_kernel<EPI, FP8>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)) != cudaSuccess)
       return OJB_ERR_LAUNCH;
@@ -523,10 +553,11 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.n_xchunk = 1;
   }
   g.splits = splits;
-  g.kb_total = static_cast<int>(ceil_div(K, kBK));
+  g.kb_total = static_cast<int>(ceil_div(K, FP8 ? 128 : kBK));
   g.kb_per_split = static_cast<int>(ceil_div(g.kb_total, splits));
   if (static_cast<int64_t>(splits - 1) * g.kb_per_split >= g.kb_total) return OJB_ERR_ARG;   // an empty split
   g.BN = EPI == kEpiSwiglu ? 256 : (bn_req > 0 ? bn_req : choose_bn(N, g.n_xblk, g.tail_box, g.n_xchunk, g.tail_rows > 0, splits, g.kb_total, sms, EPI));
+  if (FP8 && g.BN % 64 != 0) g.BN = (g.BN + 63) / 64 * 64;      // whole 128-byte store tiles (the scaled epilogue needs them)
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
   const int b_rows = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) : g.tail_box;
@@ -552,13 +583,17 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.trace_cap = g_trace_cap;
   g.mma_repeat = g_mma_repeat;
   g.dbg = g_dbg;
+  g.sx = sx;
+  g.sw = sw;
+  if (FP8 && g.n_xblk > 0 && !g.tma_out) return OJB_ERR_ARG;      // the scaled block epilogue exists on the bulk-store path only
+  auto mk = FP8 ? make_map_u8 : make_map;
   CUtensorMap map_x, map_w, map_w256, map_xt;
-  int rc = make_map(&map_x, x, M, K, kBlockM);
-  if (rc == OJB_OK) rc = make_map(&map_w, w, N, K, g.BN);
-  if (rc == OJB_OK) rc = make_map(&map_w256, w, N, K, 256);
-  if (rc == OJB_OK) rc = make_map(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
+  int rc = mk(&map_x, x, M, K, kBlockM);
+  if (rc == OJB_OK) rc = mk(&map_w, w, N, K, g.BN);
+  if (rc == OJB_OK) rc = mk(&map_w256, w, N, K, 256);
+  if (rc == OJB_OK) rc = mk(&map_xt, x, M, K, g.tail_box > 0 ? g.tail_box : 16);
   CUtensorMap map_w128;
-  if (rc == OJB_OK) rc = make_map(&map_w128, w, N, K, kBM);
+  if (rc == OJB_OK) rc = mk(&map_w128, w, N, K, kBM);
   CUtensorMap map_out = map_xt;
   if (rc == OJB_OK && g.tma_out)
     rc = make_out_map(&map_out, out, out_elt, M, out_cols, ldo, EPI == kEpiPartialF32 ? splits : 1, g.split_stride);
@@ -591,6 +626,13 @@ int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void
   if (epi == kEpiBf16) return launch_gemm<kEpiBf16>(x, w, out, M, N, K, splits, bn_req, ldo, status, stream);
   if (epi == kEpiSwiglu) return launch_gemm<kEpiSwiglu>(x, w, out, M, N, K, splits, bn_req, ldo, status, stream);
   return launch_gemm<kEpiPartialF32>(x, w, out, M, N, K, splits, bn_req, ldo, status, stream);
+}
+
+int gemm_block256_launch_e4m3(int epi, const void* xq, const float* sx, const void* wq, const float* sw, void* out, int64_t M,
+                              int64_t N, int64_t K, int splits, int64_t ldo, int32_t* status, cudaStream_t stream) {
+  if (epi == kEpiBf16) return launch_gemm<kEpiBf16, true>(xq, wq, out, M, N, K, splits, 0, ldo, status, stream, sx, sw);
+  if (epi == kEpiSwiglu) return launch_gemm<kEpiSwiglu, true>(xq, wq, out, M, N, K, splits, 0, ldo, status, stream, sx, sw);
+  return launch_gemm<kEpiPartialF32, true>(xq, wq, out, M, N, K, splits, 0, ldo, status, stream, sx, sw);
 }
 
 }  // namespace ojb

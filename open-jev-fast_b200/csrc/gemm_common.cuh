@@ -96,6 +96,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
+// The same MMA on 8-bit floating-point operands (kind::f8f6f4; K = 32 elements = 32 bytes per instruction).
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -134,6 +145,11 @@ __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
          (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
+
+// Instruction descriptor of tcgen05.mma.kind::f8f6f4: fp32 accumulator, e4m3 A and B (format code 0), both K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int bn) {
+  return (1u << 4) | (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
 
 // 32 lanes x 16 consecutive fp32 columns
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -201,6 +217,20 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
   return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
 }
 
+// The same for a row-major matrix of bytes (e4m3 operands): a box is box_rows rows of 128 bytes = 128 elements of K.
+int make_map_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return OJB_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols)};
+  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
+}
+
 // Tensor map of an output matrix for bulk tensor stores from [32 rows][128 bytes] shared-memory tiles written with the
 // 128-byte swizzle: rows x cols elements of elt bytes (2 = bf16, 4 = fp32), row pitch ld elements, `planes` matrices
 // plane_stride elements apart. Stores are clipped at the matrix edges.
@@ -238,6 +268,9 @@ int gemm_tile128_launch(int epi, int bn, const void* x, const void* w, void* out
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int knob);
+// e4m3 operands with one fp32 scale per row of x (sx) and per row of w (sw): out = (xq . wq^T) * sx[m] * sw[n]
+int gemm_block256_launch_e4m3(int epi, const void* xq, const float* sx, const void* wq, const float* sw, void* out, int64_t M,
+                              int64_t N, int64_t K, int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 int gemm_pair256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                         int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 void gemm_pair256_set_trace(unsigned long long* buf, int cap, int repeat, int max_stages);

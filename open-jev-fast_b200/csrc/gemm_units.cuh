@@ -36,6 +36,9 @@ struct GemmArgs {
   // 512 rows of x; w_split64: the 128 rows of w of a CTA are fetched as rows [64r, 64r+64) and [128+64r, 128+64r+64) of the
   // tile (gate and up rows of the same 64 outputs of a SwiGLU weight interleaved in blocks of 128 rows).
   int n_chunk, chunk_w, w_split64;
+  // e4m3 operands (block kernel): fp32 scale per row of x and per row of w, applied to the accumulator in the epilogue
+  const float* sx;
+  const float* sw;
 };
 
 struct Unit {

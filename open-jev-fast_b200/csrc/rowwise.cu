@@ -2,6 +2,7 @@
 // SwiGLU product, activation tables, sigmoid gate product, visibility bit packing, attention q/k/v preparation.
 // All of them are HBM-bound streaming kernels: 16-byte accesses, one pass over the data, rows held in registers.
 #include "common.cuh"
+#include <cuda_fp8.h>
 
 namespace ojb {
 namespace {
@@ -240,6 +241,50 @@ fullattn_prep_kernel(const bf16_t* __restrict__ proj, const float* __restrict__ 
   store(dst + (static_cast<int64_t>(hh) * N + n) * D + d0, ov);
 }
 
+// Per-row e4m3 quantisation for the 8-bit GEMM: scale[m] = max|x[m,:]| / 448 (1 for an all-zero row), q = x / scale rounded
+// to e4m3 (saturating). One CTA per row, two passes over the row (the second one hits L1 / L2).
+__global__ void __launch_bounds__(kRowThreads)
+quantize_rows_e4m3_kernel(const bf16_t* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, int K) {
+  pdl_begin();
+  __shared__ float red[kRowThreads / 32];
+  const int64_t row = blockIdx.x;
+  const bf16_t* xr = x + row * K;
+  float amax = 0.f;
+  for (int i = threadIdx.x * 8; i < K; i += kRowThreads * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < kRowThreads / 32; ++w) amax = fmaxf(amax, red[w]);
+  const float sc = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+  const float inv = 1.0f / sc;
+  if (threadIdx.x == 0) scale[row] = sc;
+  uint8_t* qr = q + row * K;
+  for (int i = threadIdx.x * 8; i < K; i += kRowThreads * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint32_t out[2];
+#pragma unroll
+    for (int e = 0; e < 4; e += 2) {
+      const float2 a = __bfloat1622float2(h[e]), b = __bfloat1622float2(h[e + 1]);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv, a.y * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv, b.y * inv), __NV_SATFINITE, __NV_E4M3);
+      out[e >> 1] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint2*>(qr + i) = make_uint2(out[0], out[1]);
+  }
+}
+
 }  // namespace
 }  // namespace ojb
 
@@ -372,4 +417,12 @@ extern "C" int ojb_score_head(const void* hn, const int64_t* rows, const float* 
   launch_kernel(ojb::score_head_kernel, dim3(static_cast<unsigned>(ojb::ceil_div(warps, 8))), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const ojb::bf16_t*>(hn), rows, W, bias, out, static_cast<int>(S), static_cast<int>(A), static_cast<int>(H));
   return ojb::launch_status(cudaGetLastError());
+}
+
+extern "C" int ojb_quantize_rows_e4m3(const void* x, void* q, float* scale, int64_t rows, int64_t K, ojb_stream_t stream) {
+  if (rows == 0) return OJB_OK;
+  OJB_REQUIRE(x && q && scale && rows > 0 && K > 0 && K % 8 == 0);
+  launch_kernel(quantize_rows_e4m3_kernel, dim3(static_cast<unsigned>(rows)), dim3(kRowThreads), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const bf16_t*>(x), static_cast<uint8_t*>(q), scale, static_cast<int>(K));
+  return launch_status(cudaGetLastError());
 }

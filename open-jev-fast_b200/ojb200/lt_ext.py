@@ -99,6 +99,47 @@ def gemm_splitk(x, w, S, idx=0):
 
 
 # ---------------------------------------------------------------------------------------------- lt2_* (src/lt.cpp:64-190)
+def quantize_weight_e4m3(w):
+    """Offline weight preparation of the 8-bit path: w [N, K] bf16 -> (e4m3 bytes [N, K] as uint8, fp32 scale per row), scale =
+    max|row| / 448. Plain torch: this runs once per weight, not in the forward."""
+    wf = w.float()
+    s = wf.abs().amax(dim=1).clamp_min(1e-30) / 448.0
+    q = (wf / s[:, None]).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).contiguous(), s.contiguous()
+
+
+def quantize_rows_e4m3(x):
+    """x [M, K] bf16 -> (e4m3 bytes [M, K] uint8, fp32 scale [M]) through ojb_quantize_rows_e4m3 (one kernel)."""
+    if not (x.is_cuda and x.is_contiguous() and x.dtype == bf16 and x.dim() == 2):
+        raise RuntimeError("quantize_rows_e4m3: contiguous CUDA bf16 [M, K] expected")
+    M, K = x.shape
+    q = torch.empty(M, K, dtype=torch.uint8, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    call("ojb_quantize_rows_e4m3", ptr(x), ptr(q), ptr(s), i64(M), i64(K), stream_ptr())
+    return q, s
+
+
+def gemm_e4m3(xq, sx, wq, sw, kind=0, splits=1):
+    """out = (xq @ wq^T) * sx[:, None] * sw[None, :] on e4m3 operands (ojb_gemm_e4m3). kind 0: bf16 [M, N]; 1: SwiGLU on the
+    re-laid gate/up weight -> bf16 [M, N/2]; 2: fp32 partials [splits, M, N]."""
+    for t, dt in ((xq, torch.uint8), (wq, torch.uint8), (sx, torch.float32), (sw, torch.float32)):
+        if not (t.is_cuda and t.is_contiguous() and t.dtype == dt):
+            raise RuntimeError("gemm_e4m3: contiguous CUDA uint8 operands and fp32 scales expected")
+    M, K = xq.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K or sx.numel() != M or sw.numel() != N:
+        raise RuntimeError("gemm_e4m3: shapes do not match")
+    if kind == 0:
+        out = torch.empty(M, N, dtype=bf16, device=xq.device)
+    elif kind == 1:
+        out = torch.empty(M, N // 2, dtype=bf16, device=xq.device)
+    else:
+        out = torch.empty(splits, M, N, dtype=torch.float32, device=xq.device)
+    call("ojb_gemm_e4m3", ptr(xq), ptr(sx), ptr(wq), ptr(sw), ptr(out), i64(M), i64(N), i64(K), i32(kind), i32(splits),
+         ptr(_lib.status_word(xq.device)), stream_ptr())
+    return out
+
+
 def lt2_plan(M, N, K, S, f32, wl):
     """src/lt.cpp:64 — plan handle. wl = 0: w [N, K]; wl = 1: w [S, K/S, N] (the reference's pre-split layout)."""
     if wl not in (0, 1) or (wl == 0 and S != 1 and False):

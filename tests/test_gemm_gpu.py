@@ -103,3 +103,77 @@ def test_trace_hook_records_every_unit():
     assert int(r[0]) == 2 * 4 + 4            # two 256-row blocks and one tail unit per 256-wide w tile
     t = r[1:1 + 4 * int(r[0])].view(-1, 4)
     assert bool((t[:, 1] <= t[:, 2]).all()) and bool((t[:, 2] <= t[:, 3]).all())
+
+
+def _deq(q, s):
+    return q.view(torch.float8_e4m3fn).float() * s[:, None]
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (37, 520), (544, 5120)])
+def test_quantize_rows_e4m3(M, K):
+    """ojb_quantize_rows_e4m3 against torch's own e4m3 conversion of x / scale."""
+    from ojb200 import lt_ext, _lib
+    x = (torch.randn(M, K, device="cuda") * 3).to(bf16)
+    if M > 1:
+        x[1].zero_()
+    q, s = lt_ext.quantize_rows_e4m3(x)
+    amax = x.float().abs().amax(dim=1)
+    ref_s = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    assert torch.allclose(s, ref_s, rtol=1e-6, atol=0)
+    ref_q = (x.float() * (1.0 / s)[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert (q != ref_q).float().mean().item() < 1e-3      # the reciprocal of the scale may tip a tie
+    assert (_deq(q, s) - x.float()).abs().max().item() <= amax.max().item() * 2 ** -4 + 1e-6
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 512, 256), (256, 256, 128), (544, 1024, 640), (539, 12352, 5120), (288, 1280, 5120), (300, 520, 1008)])
+def test_gemm_e4m3_plain(M, N, K):
+    """8-bit GEMM against fp32 matmul of the same dequantised operands: only the accumulation order differs."""
+    from ojb200 import lt_ext, _lib
+    x = torch.randn(M, K, device="cuda").to(bf16)
+    w = (torch.randn(N, K, device="cuda") * 0.02).to(bf16)
+    xq, sx = lt_ext.quantize_rows_e4m3(x)
+    wq, sw = lt_ext.quantize_weight_e4m3(w)
+    ref = _deq(xq, sx) @ _deq(wq, sw).t()
+    out = lt_ext.gemm_e4m3(xq, sx, wq, sw, 0)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert (out.float() - ref).abs().max().item() <= ref.abs().max().item() * 2 ** -8 + 1e-4
+    # and the quantisation itself stays within a few per cent of the bf16 product
+    full = x.float() @ w.float().t()
+    assert ((out.float() - full).norm() / full.norm()).item() < 6e-2
+
+
+@pytest.mark.parametrize("M,N,K,S", [(544, 5120, 17408, 2), (288, 5120, 4096, 3), (64, 512, 1024, 2), (539, 520, 1008, 1)])
+def test_gemm_e4m3_splitk(M, N, K, S):
+    from ojb200 import lt_ext, _lib
+    x = torch.randn(M, K, device="cuda").to(bf16)
+    w = (torch.randn(N, K, device="cuda") * 0.02).to(bf16)
+    xq, sx = lt_ext.quantize_rows_e4m3(x)
+    wq, sw = lt_ext.quantize_weight_e4m3(w)
+    ref = _deq(xq, sx) @ _deq(wq, sw).t()
+    parts = lt_ext.gemm_e4m3(xq, sx, wq, sw, 2, S)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert parts.shape == (S, M, N)
+    assert (parts.sum(0) - ref).abs().max().item() <= ref.abs().max().item() * 1e-5 + 1e-5
+
+
+@pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120), (539, 2048, 1024)])
+def test_gemm_e4m3_swiglu(M, I, K):
+    from ojb200 import lt_ext, _lib
+    x = torch.randn(M, K, device="cuda").to(bf16)
+    wg = (torch.randn(I, K, device="cuda") * 0.02).to(bf16)
+    wu = (torch.randn(I, K, device="cuda") * 0.02).to(bf16)
+    xq, sx = lt_ext.quantize_rows_e4m3(x)
+    wq, sw = lt_ext.quantize_weight_e4m3(lt_ext.interleave_gate_up(wg, wu, 128))
+    out = lt_ext.gemm_e4m3(xq, sx, wq, sw, 1)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    wd = _deq(wq, sw).view(-1, 2, 128, K)
+    xd = _deq(xq, sx)
+    g = (xd @ wd[:, 0].reshape(-1, K).t()).to(bf16).float()
+    u = (xd @ wd[:, 1].reshape(-1, K).t()).to(bf16).float()
+    ref = torch.nn.functional.silu(g).to(bf16).float() * u
+    assert out.shape == (M, I)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= ref.abs().max().item() * 2 ** -6 + 1e-3, err
