@@ -180,6 +180,8 @@ def main():
                     "cudaProfilerStart/Stop and exit: for `ncu --profile-from-start off`")
     ap.add_argument("--pack", type=int, default=0, help="also time this many requests packed into one forward (extra key "
                     "`packed` of the JSON line; the headline numbers stay one request per forward)")
+    ap.add_argument("--fp8", action="store_true", help="run the projections on e4m3 operands (ojb_gemm_e4m3): not the parity "
+                    "path, reported with its own dtype and without a roofline entry")
     ap.add_argument("--layers", type=int, default=64, help="debugging only: a run with fewer than 64 layers is not a result")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -207,7 +209,7 @@ def main():
     pk, pk_kind = peaks()
 
     core = MG.build_core(cfg, device=dev, seed=0)
-    fast = FM.FastQwen35(core, free_original=True)
+    fast = FM.FastQwen35(core, free_original=True, fp8=args.fp8)
     W, b = MG.make_head(cfg.hidden_size, A=1, seed=1, device=dev)
     scorer = SV.Scorer(fast, W, b, pad_id=0, device=dev)
     # every rank serves its own requests: different seeds, same shape (weak scaling: fixed work per GPU)
@@ -283,11 +285,12 @@ def main():
                   "value": args.pack * args.steps / dt, "unit": "requests/s", "h2d_bytes_per_forward": scorer.last["h2d_bytes"]}
         _lib.check_status(dev)
 
-    roof = gemm_roofline(fast, key[0], pk, pk_kind, dev) if rank == 0 else None
+    roof = gemm_roofline(fast, key[0], pk, pk_kind, dev) if rank == 0 and not args.fp8 else None
     P = matmul_params(cfg)
     line = {"metric": METRIC, "value": world * 1e3 / ms_per_step, "unit": "requests/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
+            "dtype": "e4m3 projections with per-row scales, bf16 elsewhere (outside the bf16 parity tolerance)" if args.fp8 else "bf16",
+            "data": "synthetic",
             "config": {"workload": f"{args.workload} tree: key (N,S,L2)={key}, real rows {scorer.last['rows']}, 64-layer hybrid "
                                    "(48 GDN + 16 gated GQA), hidden 5120, MLP 17408, HV=32",
                        "layers": args.layers, "parallelism": f"dp{world}", "l2": "inputs larger than L2 (46 GB of weights per step)",

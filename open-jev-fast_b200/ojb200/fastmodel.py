@@ -53,8 +53,12 @@ class _Layer(SimpleNamespace):
 
 
 class FastQwen35(torch.nn.Module):
-    def __init__(self, core, free_original=False, v2=True, fuse_l2=True):
+    def __init__(self, core, free_original=False, v2=True, fuse_l2=True, fp8=None):
         super().__init__()
+        # 8-bit projections (e4m3 operands, per-row scales; README.md:131 of the reference: measured there, not shipped).
+        # Off unless asked for: the scores then differ from the bf16 path by more than its tolerance.
+        self.fp8 = (os.environ.get("OJ_FP8", "0") == "1") if fp8 is None else bool(fp8)
+        self._q8 = {}       # data_ptr of a bf16 weight -> (e4m3 bytes, fp32 row scales)
         cfg = core.config
         self.cfg, self.core = cfg, core
         self.H, self.eps = cfg.hidden_size, cfg.rms_norm_eps
@@ -95,6 +99,9 @@ class FastQwen35(torch.nn.Module):
                     d.w_out, d.sk_out = sa.o_proj.weight, SK_FULL_OUT
                     d.qw1, d.kw1 = w1(sa.q_norm), w1(sa.k_norm)
                     d.HQ, d.HKV, d.D, d.scale = cfg.num_attention_heads, cfg.num_key_value_heads, sa.head_dim, sa.scaling
+                if self.fp8:
+                    for w in ([d.w_gu_blk] if d.fused_mlp else [d.w_gu_cat]) + [d.w_down, d.w_in, d.w_out]:
+                        self._q8[w.data_ptr()] = LT.quantize_weight_e4m3(w)
                 if free_original:   # the merged copies replace the originals: release q/k/v, in_proj_* and gate/up storage
                     mods = [L.mlp.gate_proj, L.mlp.up_proj]
                     mods += [la.in_proj_qkv, la.in_proj_z, la.in_proj_b, la.in_proj_a] if self.layer_types[i] == "linear_attention" \
@@ -110,6 +117,10 @@ class FastQwen35(torch.nn.Module):
     # weights coming from HBM, as in the real forward).
     def _mm(self, x, w):
         """out = x @ w^T, bf16 (src/fastmodel.py:168 _mm)."""
+        q8 = self._q8.get(w.data_ptr()) if self.fp8 else None
+        if q8 is not None:
+            xq, sx = LT.quantize_rows_e4m3(x)
+            return LT.gemm_e4m3(xq, sx, q8[0], q8[1], 0)
         return LT.lt_matmul(x, w, self._plan.get(("mm", x.shape[0], w.shape[0], w.shape[1]), 0))
 
     @staticmethod
@@ -124,6 +135,13 @@ class FastQwen35(torch.nn.Module):
         the fused add + norm (delta = bf16 of the fp32 accumulator, the rounding point of the reference's bf16(sum))."""
         M, Kd = y.shape
         idx = 0
+        q8 = self._q8.get(w.data_ptr()) if self.fp8 else None
+        if q8 is not None:
+            yq, sy = LT.quantize_rows_e4m3(y)
+            S8 = S if S > 0 else LT.plan_splitk(M, w.shape[0], Kd // 2)      # a 128-byte k-block holds twice the elements
+            if S8 == 1:
+                return K.add_rmsnorm(h, LT.gemm_e4m3(yq, sy, q8[0], q8[1], 0), w1, mask, self.eps)
+            return K.add_rmsnorm_sk2(h, LT.gemm_e4m3(yq, sy, q8[0], q8[1], 2, S8), w1, mask, self.eps)
         if S == 0:
             idx, S = self._plan.get(("res", M, w.shape[0], Kd), (0, 0))
             if S == 0:
@@ -134,6 +152,10 @@ class FastQwen35(torch.nn.Module):
         return K.add_rmsnorm_sk2(h, parts, w1, mask, self.eps)
 
     def _mlp_in(self, hn, d):
+        if d.fused_mlp and self.fp8:
+            q8 = self._q8[d.w_gu_blk.data_ptr()]
+            xq, sx = LT.quantize_rows_e4m3(hn)
+            return LT.gemm_e4m3(xq, sx, q8[0], q8[1], 1)
         if d.fused_mlp:
             return LT.gemm_swiglu(hn, d.w_gu_blk, self._plan.get(("gu", hn.shape[0]) + tuple(d.w_gu_blk.shape), 0))
         return K.silu_mul(self._mm(hn, d.w_gu_cat))
@@ -144,7 +166,7 @@ class FastQwen35(torch.nn.Module):
         """Choose kernel variant (and K split) of every projection for M packed rows by timing (src/fastmodel.py:114-156
         _tune). Each candidate runs over all layers that have the shape, twice, between CUDA events. Above TUNE_MAX_ROWS the
         cost model is kept (every shape then has many units per SM and the 256-row block kernel wins throughout)."""
-        if (M in self._tuned or M > self.TUNE_MAX_ROWS) and not force:
+        if (M in self._tuned or M > self.TUNE_MAX_ROWS or self.fp8) and not force:
             return
         self._tuned.add(M)
         cache = os.environ.get("OJ_TUNE_CACHE")      # optional file that pins the choices across processes (profiling runs)
