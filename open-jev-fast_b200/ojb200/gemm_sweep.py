@@ -52,6 +52,9 @@ def main():
     ap.add_argument("--only", default=None, help="only kernels whose name starts with this (plain, swiglu, splitk)")
     ap.add_argument("--library", action="store_true",
                     help="also time torch.nn.functional.linear (cuBLASLt, the GEMM path of the reference) on the same operands: a comparator only")
+    ap.add_argument("--e4m3", action="store_true",
+                    help="also time the 8-bit form (ojb_gemm_e4m3: bf16 out, SwiGLU where N is a gate/up width, fp32 partials where N is "
+                         "the hidden size) and the row quantisation kernel")
     ap.add_argument("--copies", type=int, default=0, help="distinct weight copies to cycle through (default: enough to exceed L2)")
     args = ap.parse_args()
     dev = torch.device("cuda")
@@ -80,6 +83,24 @@ def main():
                 out = torch.nn.functional.linear(x, ws[0])
                 report("library F.linear", _time([lambda w=w: torch.nn.functional.linear(x, w) for w in ws]),
                        (out.float() - ref).abs().max().item())
+            if args.e4m3 and want("e4m3"):
+                xq, sx = LT.quantize_rows_e4m3(x)
+                q8 = [LT.quantize_weight_e4m3(w) for w in ws]
+                deq = xq.view(torch.float8_e4m3fn).float() * sx[:, None]
+                ref8 = deq @ (q8[0][0].view(torch.float8_e4m3fn).float() * q8[0][1][:, None]).t()
+                out = LT.gemm_e4m3(xq, sx, q8[0][0], q8[0][1], 0)
+                report("e4m3 plain", _time([lambda q=q: LT.gemm_e4m3(xq, sx, q[0], q[1], 0) for q in q8]),
+                       (out.float() - ref8).abs().max().item())
+                if N == 5120:
+                    for S in (2, 3, 4):
+                        parts = LT.gemm_e4m3(xq, sx, q8[0][0], q8[0][1], 2, S)
+                        report(f"e4m3 splitk S{S}", _time([lambda q=q, S=S: LT.gemm_e4m3(xq, sx, q[0], q[1], 2, S) for q in q8]),
+                               (parts.sum(0) - ref8).abs().max().item())
+                if N % 256 == 0 and Kd == 5120 and N > 20000:
+                    # (timing only: the rows are not interleaved here; tests/test_gemm_gpu.py checks the SwiGLU values)
+                    report("e4m3 swiglu", _time([lambda q=q: LT.gemm_e4m3(xq, sx, q[0], q[1], 1) for q in q8]), None)
+                report("e4m3 quantize rows", _time([lambda: LT.quantize_rows_e4m3(x) for _ in range(8)]), None)
+                del q8, deq, ref8
             if N % 256 == 0 and Kd == 5120 and N > 20000 and want("swiglu"):
                 I = N // 2
                 wb = [LT.interleave_gate_up(w[:I], w[I:]) for w in ws]
