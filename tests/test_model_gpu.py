@@ -144,6 +144,43 @@ def test_e4m3_projections_stay_close_to_the_bf16_forward():
     assert c > 0.8, c
 
 
+def test_full_width_tree_forward_equals_its_candidates_scored_alone():
+    """Size-independent property at the model's full width (hidden 5120, MLP 17408, 32 / 16 GDN heads, 24 / 4 attention
+    heads; 4 layers = 3 Gated DeltaNet + 1 attention) on the 539-row benchmark tree: packing candidates into a prefix tree
+    must not change what each candidate sees, so the tree forward equals every candidate pushed through alone as a
+    single-path tree; and the candidates in another order give the same scores in that order."""
+    from ojb200 import fastmodel as FM, modelgen as MG, _lib
+    cfg = MG.make_config(num_hidden_layers=4, vocab_size=4096)
+    core = MG.build_core(cfg, device="cuda", seed=3)
+    W, b = MG.make_head(cfg.hidden_size, A=1, seed=1, device="cuda")
+    fast = FM.FastQwen35(core)
+    seqs, groups = trees.baseline_tree(seed=0, vocab=cfg.vocab_size)
+    ids, lay = fast.gtree_build(seqs, groups, 0, 32, 16)
+    assert lay.key[0] == 544
+    tree_h = fast.forward_gtree(ids, lay).float()
+    tree_s = fast.score_gtree(ids, lay, W, b)
+    alone = []
+    for q in seqs:
+        i1, l1 = fast.gtree_build([q], [0], 0, 32, 16)
+        alone.append(fast.forward_gtree(i1, l1).float()[0])
+    alone = torch.stack(alone)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    rel = ((tree_h - alone).norm() / alone.norm()).item()
+    # Same bf16 operators on the same values; chunk boundaries, summation order and kernel choice per row count differ. Two
+    # bf16 evaluations of this random-weight network sit about 1 % per 4 layers apart (measured here: 1.5e-2; the 8-layer test
+    # model above is 2e-2 away from its own fp32 run), so the bound is that noise, and the scores must agree to BASELINE's
+    # logit tolerance.
+    assert rel < 3e-2, rel
+    alone_s = (alone @ W.float().t() + b.float())
+    assert (tree_s.float() - alone_s).abs().max().item() <= 3e-2
+    perm = [3, 0, 6, 1, 5, 2, 4]
+    ids2, lay2 = fast.gtree_build([seqs[i] for i in perm], [groups[i] for i in perm], 0, 32, 16)
+    s2 = fast.score_gtree(ids2, lay2, W, b)
+    torch.cuda.synchronize()
+    assert (s2 - tree_s[perm]).abs().max().item() <= 3e-2
+
+
 def test_batch_forward_matches_reference_path():
     from ojb200 import fastmodel as FM
     cfg, core = _small_model(seed=2)
