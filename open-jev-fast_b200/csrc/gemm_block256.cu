@@ -51,7 +51,8 @@ template <int EPI, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w256, const __grid_constant__ CUtensorMap map_xt,
-                    const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_w128, GemmArgs g) {
+                    const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_w128,
+                    const __grid_constant__ CUtensorMap map_tail, GemmArgs g) {
   pdl_launch_dependents();
   constexpr uint32_t kTmemCols = 512;
   constexpr int kKE = FP8 ? 128 : kBK;      // elements of K per k-block (the coordinate step of the copies)
@@ -61,7 +62,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* staging = smem + static_cast<size_t>(g.stages) * g.stage_bytes;       // [8 warps][32 rows][128 bytes] when tma_out
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + (g.tma_out ? kStagingBytes : 0));
+  // staging: 4 KB per epilogue warp when block units store through it, 2 KB when only swapped units do
+  const uint32_t stg_warp = g.tma_out ? 4096u : (g.tail_tma ? 2048u : 0u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * stg_warp);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -88,6 +91,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xt) : "memory");
     if (g.tma_out) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
     if (g.tail_sub) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w128) : "memory");
+    if (g.tail_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_tail) : "memory");
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -441,12 +445,39 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             bf16_t* ocol = reinterpret_cast<bf16_t*>(g.out) + j;
             const int nchunk = g.tail_box / 16;
             const float swg = sw_at(u.wt * 256 + quarter * 32 + lane), swu = sw_at(u.wt * 256 + 128 + quarter * 32 + lane);
+            uint8_t* tile0 = staging + (warp - 2) * stg_warp;
+            if (g.tail_tma) {          // the stores of this warp's previous unit have read its tiles
+              if (lane == 0) bulk_wait_read();
+              __syncwarp();
+            }
 #pragma unroll 1
             for (int c = acc_id; c < nchunk; c += 2) {
               uint32_t gr[16], ur[16];
               tmem_ld16(tlane + c * 16, gr);
               tmem_ld16(tlane + kAcc1Col + c * 16, ur);
               tmem_ld_wait();
+              if (g.tail_tma) {
+                // [16 rows of x][32 output columns] tile, one bulk tensor store per chunk (clipped at the edges of out)
+                bf16_t* t = reinterpret_cast<bf16_t*>(tile0 + ((c >> 1) & 1) * 1024);
+                if (c >= acc_id + 4) {
+                  if (lane == 0) bulk_wait_read1();
+                  __syncwarp();
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                  const float xs = sx_at(m0 + c * 16 + e);
+                  const float gv = round_bf(__uint_as_float(gr[e]) * (FP8 ? xs * swg : 1.f));
+                  const float uv = round_bf(__uint_as_float(ur[e]) * (FP8 ? xs * swu : 1.f));
+                  t[e * 32 + lane] = f2bf(round_bf(silu_f(gv)) * uv);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0 && u.wt * 128 + quarter * 32 < g.N / 2) {
+                  tma_store_3d(&map_tail, smem_u32(t), u.wt * 128 + quarter * 32, m0 + c * 16, 0);
+                  bulk_commit();
+                }
+                continue;
+              }
 #pragma unroll
               for (int e = 0; e < 16; ++e) {
                 const int m = m0 + c * 16 + e;
@@ -463,11 +494,39 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           const int col = u.wt * 256 + acc_id * kBM + quarter * 32 + lane;
           const bool col_ok = col < g.N;
           const float swc = sw_at(col);
+          uint8_t* tile0 = staging + (warp - 2) * stg_warp;
+          // two tiles per warp where they fit (bf16: 1 KB each; fp32: 2 KB each, only beside the 4 KB block-unit tiles)
+          const bool two = EPI != kEpiPartialF32 || stg_warp == 4096u;
+          if (g.tail_tma) {          // the stores of this warp's previous unit have read its tiles
+            if (lane == 0) bulk_wait_read();
+            __syncwarp();
+          }
 #pragma unroll 1
           for (int c = 0; c < g.tail_box / 16; ++c) {
             uint32_t r[16];
             tmem_ld16(taddr + c * 16, r);
             tmem_ld_wait();
+            if (g.tail_tma) {
+              uint8_t* t = tile0 + (two ? (c & 1) * (EPI == kEpiPartialF32 ? 2048 : 1024) : 0);
+              if (two ? c >= 2 : c >= 1) {
+                if (lane == 0) { if (two) bulk_wait_read1(); else bulk_wait_read(); }
+                __syncwarp();
+              }
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                const float v = __uint_as_float(r[e]) * (FP8 ? swc * sx_at(m0 + c * 16 + e) : 1.f);
+                if constexpr (EPI == kEpiBf16) reinterpret_cast<bf16_t*>(t)[e * 32 + lane] = f2bf(v);
+                else reinterpret_cast<float*>(t)[e * 32 + lane] = v;
+              }
+              fence_proxy_async();
+              __syncwarp();
+              const int col0 = u.wt * 256 + acc_id * kBM + quarter * 32;
+              if (lane == 0 && col0 < g.N) {
+                tma_store_3d(&map_tail, smem_u32(t), col0, m0 + c * 16, EPI == kEpiPartialF32 ? u.split : 0);
+                bulk_commit();
+              }
+              continue;
+            }
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               const int m = m0 + c * 16 + e;
@@ -498,7 +557,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         }
       }
     }
-    if (g.tma_out && lane == 0) bulk_wait_all();     // the shared-memory tiles must outlive the stores that read them
+    if ((g.tma_out || g.tail_tma) && lane == 0) bulk_wait_all();     // the shared-memory tiles must outlive the stores that read them
   }
 
   // ------------------------------------------------------------------ teardown
@@ -570,7 +629,8 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   const int64_t out_cols = EPI == kEpiSwiglu ? N / 2 : N;
   const int out_elt = EPI == kEpiPartialF32 ? 4 : 2;
   g.tma_out = g.n_xblk > 0 && (ldo * out_elt) % 16 == 0 && g.BN % (128 / out_elt) == 0 ? 1 : 0;
-  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16 + (g.tma_out ? kStagingBytes : 0);
+  g.tail_tma = (g.tail_rows > 0 && (ldo * out_elt) % 16 == 0 && (EPI != kEpiPartialF32 || (M * N * 4) % 16 == 0)) ? 1 : 0;
+  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16 + (g.tma_out ? kStagingBytes : (g.tail_tma ? kStagingBytes / 2 : 0));
   g.stages = static_cast<int>((kSmemBudget - fixed) / g.stage_bytes);
   if (g.stages > kMaxStages) g.stages = kMaxStages;
   if (g_max_stages >= 2 && g_max_stages <= 12 && g.stages > g_max_stages) g.stages = g_max_stages;
@@ -597,6 +657,9 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   CUtensorMap map_out = map_xt;
   if (rc == OJB_OK && g.tma_out)
     rc = make_out_map(&map_out, out, out_elt, M, out_cols, ldo, EPI == kEpiPartialF32 ? splits : 1, g.split_stride);
+  CUtensorMap map_tail = map_xt;
+  if (rc == OJB_OK && g.tail_tma)
+    rc = make_tail_out_map(&map_tail, out, out_elt, M, out_cols, ldo, EPI == kEpiPartialF32 ? splits : 1, g.split_stride);
   if (rc != OJB_OK) return rc;
   const int64_t units = static_cast<int64_t>(g.n_xblk) * g.n_wtile * splits +
                         (g.tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits * g.n_xchunk : 0);
@@ -607,7 +670,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     while (grid > 1 && gcd(grid, group) != 1) --grid;
   }
   const size_t smem = static_cast<size_t>(g.stages) * g.stage_bytes + fixed;
-  launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, stream, map_x, map_w, map_w256, map_xt, map_out, map_w128, g);
+  launch_kernel(kern, dim3(grid), dim3(kGemmThreads), smem, stream, map_x, map_w, map_w256, map_xt, map_out, map_w128, map_tail, g);
   return launch_status(cudaGetLastError());
 }
 

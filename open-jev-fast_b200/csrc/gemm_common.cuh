@@ -69,6 +69,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all bulk stores of this thread have finished reading their shared-memory source
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the most recent bulk group of this thread have read their shared-memory source
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // all bulk stores of this thread are complete
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // make shared-memory writes of this thread visible to the bulk-copy engine
@@ -244,6 +246,22 @@ int make_out_map(CUtensorMap* map, void* base, int elt, int64_t rows, int64_t co
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box,
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
+}
+
+// Tensor map of an output matrix for bulk tensor stores of the swapped-operand units: boxes of 16 rows x 32 columns from
+// plain (unswizzled) [16][32] shared-memory tiles.
+int make_tail_out_map(CUtensorMap* map, void* base, int elt, int64_t rows, int64_t cols, int64_t ld, int64_t planes,
+                      int64_t plane_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return OJB_ERR_DRIVER;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * elt, static_cast<cuuint64_t>(plane_stride) * elt};
+  cuuint32_t box[3] = {32, 16, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
 }

@@ -39,6 +39,7 @@ struct GemmArgs {
   // e4m3 operands (block kernel): fp32 scale per row of x and per row of w, applied to the accumulator in the epilogue
   const float* sx;
   const float* sw;
+  int tail_tma;                // block kernel: swapped-operand units store through [16][32] shared-memory tiles and bulk tensor stores
 };
 
 struct Unit {
