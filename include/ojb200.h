@@ -36,7 +36,7 @@ int ojb_abi_version(void);
  * (torch.bmm split-K partials). out[M,N] = x[M,K] · w[N,K]^T, bf16 operands, fp32 accumulation in tensor memory.
  * Requirements: K % 8 == 0, x / w / out 16-byte aligned. variant: 0 = the library chooses (cost model, see ojb_gemm_plan);
  * 1 / 2 = 128-row tile kernel with 128x256 / 128x128 tiles; 3 = 256-row block kernel, automatic w-tile width; 4 = that
- * kernel with all rows of x in swapped-operand units (M <= 512); a multiple of 16 in [16, 256] = that kernel with this
+ * kernel with all rows of x in swapped-operand units (M <= 2048); a multiple of 16 in [16, 256] = that kernel with this
  * w-tile width; 5 = CTA-pair kernel (tcgen05.mma.cta_group::2) with automatic width; 6 = CTA-pair kernel with all rows of
  * x in swapped-operand units (any M: one pass over w per 512 rows of x, up to 512 accumulator columns per unit);
  * 512 + a multiple of 16 in [16, 256] = the pair kernel with that width.

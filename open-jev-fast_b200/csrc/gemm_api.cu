@@ -3,7 +3,7 @@
 //   tile128   (gemm_tile128.cu)   128 x 256 (or 128 x 128) output tiles, two TMEM accumulators so that the epilogue of one
 //             tile overlaps the MMAs of the next. M is padded to a multiple of 128.
 //   block256  (gemm_block256.cu)  256 rows of x share each w tile between two MMAs (one third less shared-memory fill per
-//             flop), w-tile width chosen per shape, the last M mod 256 <= 128 rows (or all rows when M <= 512) run with
+//             flop), w-tile width chosen per shape, the last M mod 256 <= 128 rows (or all rows when M <= 2048, on request) run with
 //             swapped operands at their true cost.
 //   pair256   (gemm_pair256.cu)   the same units on CTA pairs with tcgen05.mma.cta_group::2; measured on par with block256
 //             (both are bound by shared-memory bandwidth), kept as variants 5 / 6.
@@ -17,9 +17,9 @@ namespace {
 
 // variant: 0 = automatic; 1 = tile128 with 128x256 tiles; 2 = tile128 with 128x128 tiles; a multiple of 16 in [16, 256] =
 // block256 with that w-tile width; 3 = block256 with automatic width; 4 = block256 with every row of x in swapped-operand
-// units (M <= 512).
+// units (M <= 2048).
 // 5 = pair256 (CTA pairs, cta_group::2) with automatic width; 6 = pair256 with every row of x in swapped-operand units
-// (M <= 512); 512 + a multiple of 16 in [16, 256] = pair256 with that w-tile width.
+// (any M); 512 + a multiple of 16 in [16, 256] = pair256 with that w-tile width.
 bool variant_ok(int v) {
   return (v >= 0 && v <= 6) || (v >= 16 && v <= 256 && v % 16 == 0) || (v >= 528 && v <= 768 && v % 16 == 0);
 }
@@ -59,7 +59,7 @@ Plan plan_kernel(int epi, int64_t M, int64_t N, int64_t K, int splits) {
       consider(3, block_kernel_clocks(N, bn, n_xblk, tail_box, 1, r > 0, splits, kb_total, sms, epi));
     }
   }
-  if (M <= 512) {  // block256 with every row in swapped-operand units
+  if (M <= 2048) {  // block256 with every row in swapped-operand units
     const int n_xchunk = static_cast<int>(ceil_div(M, 256));
     const int tail_box = static_cast<int>(ceil_div(ceil_div(M, n_xchunk), 16) * 16);
     consider(4, block_kernel_clocks(N, 256, 0, tail_box, n_xchunk, true, splits, kb_total, sms, epi));

@@ -13,7 +13,7 @@
 //   tail unit   rows of x with the operands swapped: 256 rows of w are the M side (two MMAs with M = 128), up to 256 rows
 //               of x are the N side (N = rows rounded up to 16), so these rows cost what they are worth instead of whole
 //               128-row tiles of zero padding; the epilogue writes the transposed accumulator. Used for the last
-//               M mod 256 (<= 128) rows after the blocks, or — for M <= 512 on request, always for M <= 128 — for all of
+//               M mod 256 (<= 128) rows after the blocks, or — for M <= 2048 on request, always for M <= 128 — for all of
 //               x in one or two chunks (a pure swapped-operand GEMM).
 // Units are ordered x-block fastest, then k-split, then the tail unit of the w tile, then the next w tile, and dealt to the
 // CTAs round-robin: the CTAs that run at the same time work on the same few w tiles, which therefore come from HBM once.
@@ -593,12 +593,12 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
-  // bn_req < 0: every row of x goes through swapped-operand units (M <= 512: up to two chunks of <= 256 rows); otherwise full
+  // bn_req < 0: every row of x goes through swapped-operand units (M <= 2048: chunks of <= 256 rows); otherwise full
   // 256-row blocks plus a swapped tail of <= 128 rows (a longer remainder is cheaper as one more zero-padded block)
   const bool all_swapped = bn_req < 0 || M <= kBM;
   if (bn_req < 0) bn_req = 0;
   if (all_swapped) {
-    if (M > 512) return OJB_ERR_LIMIT;
+    if (M > 2048) return OJB_ERR_LIMIT;
     g.n_xblk = 0;
     g.tail_rows = static_cast<int>(M);
     g.n_xchunk = static_cast<int>(ceil_div(M, 256));

@@ -210,7 +210,7 @@ class FastQwen35(torch.nn.Module):
                     out.setdefault(tuple(w.shape), []).append(d)
             return out
 
-        kernels = [1, 3] + ([7] if M <= 512 else [])
+        kernels = [1, 3] + ([7] if M <= 2048 else [])
         for (N, Kd), layers in groups("w_in").items():
             x = rnd(M, Kd)
             res = race({i: (lambda d, i=i: LT.lt_matmul(x, d.w_in, i)) for i in kernels + [2]}, layers)

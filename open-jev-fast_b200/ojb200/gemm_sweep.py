@@ -74,7 +74,7 @@ def main():
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
                                   "max_err": err}), flush=True)
             for v in ((0, 1, 2, 3, 7, 8, 9) if want("plain") else ()):
-                if v == 7 and M > 512:
+                if v == 7 and M > 2048:
                     continue
                 out = LT.lt_matmul(x, ws[0], v)
                 err = (out.float() - ref).abs().max().item()
@@ -109,7 +109,7 @@ def main():
                 err = (out.float() - torch.nn.functional.silu(gg).to(bf16).float() * uu).abs().max().item()
                 report("swiglu", _time([lambda w=w: LT.gemm_swiglu(x, w) for w in wb]), err)
                 for v in (1, 3, 7):
-                    if v == 7 and M > 512:
+                    if v == 7 and M > 2048:
                         continue
                     report(f"swiglu v{v}", _time([lambda w=w, v=v: LT.gemm_swiglu(x, w, v) for w in wb]), err)
                 wb64 = [LT.interleave_gate_up(w[:I], w[I:], 64) for w in ws]      # layout of the CTA-pair kernel
@@ -124,7 +124,7 @@ def main():
                 plan = LT.plan_splitk(M, N, Kd)
                 for S in sorted({1, 2, 3, 4, 6, plan}):
                     for v in (0, 1, 3, 7, 8, 9):
-                        if v == 7 and M > 512:
+                        if v == 7 and M > 2048:
                             continue
                         parts = LT.gemm_splitk(x, ws[0], S, v)
                         err = (parts.sum(0) - ref).abs().max().item()

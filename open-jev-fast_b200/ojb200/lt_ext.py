@@ -3,7 +3,7 @@
 The reference enumerates cuBLASLt algorithms per shape (lt_setup) and runs one by index (lt_matmul); split-K plans go
 through lt2_*. Here an "algorithm" is one of the library's GEMM variants: index 0 lets the library choose, 1 / 2 force the
 128-row tile kernel with 256 / 128-wide tiles, 3 the 256-row block kernel with automatic w-tile width, 4..6 that kernel
-with w-tile width 256, 192, 128, 7 that kernel with all of x in swapped-operand units (M <= 512), 8 / 9 the CTA-pair
+with w-tile width 256, 192, 128, 7 that kernel with all of x in swapped-operand units (M <= 2048), 8 / 9 the CTA-pair
 kernel (tcgen05.mma.cta_group::2) with automatic width / all of x in swapped-operand units.
 Two entry points have no counterpart in the reference: gemm_swiglu (SwiGLU fused into the epilogue) and gemm_splitk
 (fp32 partial sums from the un-split [N, K] weight).
