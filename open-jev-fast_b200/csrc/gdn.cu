@@ -172,24 +172,31 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
   // 32-63, the cross terms of the two are masked out, so the 64 x 64 algebra is block diagonal and each half is exactly what
   // the chunk alone would give. The short chunks pair up in table order: the even-ranked one takes the next short chunk
   // with it, the odd-ranked CTA has nothing to do. (Any two chunks are independent in this pass.)
-  __shared__ int s_rank, s_next;
+  // `pair` = number of CTA slots of the GPU (0 = never pair): chunks are paired only when one CTA per (non-empty chunk, head)
+  // would not fit a single wave; with room to spare the short chunks finish sooner side by side. Every CTA reads the same
+  // table and reaches the same decision.
+  __shared__ int s_rank, s_next, s_real;
   int partner = -1;
   if (pair && nrows <= 32) {
-    if (tid == 0) { s_rank = 0; s_next = 0x7fffffff; }
+    if (tid == 0) { s_rank = 0; s_next = 0x7fffffff; s_real = 0; }
     __syncthreads();
-    int cnt = 0, nxt = 0x7fffffff;
+    int cnt = 0, nxt = 0x7fffffff, real = 0;
     for (int j = tid; j < static_cast<int>(gridDim.x); j += kIntraThreads) {
       const int nj = chunks[j * 4 + 1];
+      if (nj > 0) ++real;
       if (nj > 0 && nj <= 32) {
         if (j < static_cast<int>(blockIdx.x)) ++cnt;
         else if (j > static_cast<int>(blockIdx.x)) nxt = min(nxt, j);
       }
     }
     if (cnt) atomicAdd(&s_rank, cnt);
+    if (real) atomicAdd(&s_real, real);
     if (nxt != 0x7fffffff) atomicMin(&s_next, nxt);
     __syncthreads();
-    if (s_rank & 1) return;
-    partner = s_next == 0x7fffffff ? -1 : s_next;
+    if (s_real * HV > pair) {
+      if (s_rank & 1) return;
+      partner = s_next == 0x7fffffff ? -1 : s_next;
+    }
   }
   const bool paired = partner >= 0;
   int rowB0 = 0, nB = 0;
@@ -831,14 +838,15 @@ namespace {
 // with room to spare the chunks finish sooner side by side. OJB_GDN_PAIR = 0 / 1 forces the choice (measurements).
 int intra_pairing(int64_t n_chunks, int64_t HV) {
   static const int forced = [] { const char* e = getenv("OJB_GDN_PAIR"); return e ? atoi(e) : -1; }();
-  if (forced >= 0) return forced != 0;
+  if (forced >= 0) return forced != 0 ? 1 : 0;      // 1: pair whenever two short chunks exist; 0: never
   static const int slots = [] {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     return 3 * sms;
   }();
-  return n_chunks * HV > slots;
+  // the table may have empty slots: the kernel counts the chunks that exist and compares with the CTA slots itself
+  return n_chunks * HV > slots ? slots : 0;
 }
 }  // namespace
 }  // namespace ojb
