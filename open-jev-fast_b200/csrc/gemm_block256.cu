@@ -62,7 +62,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* staging = smem + static_cast<size_t>(g.stages) * g.stage_bytes;       // [8 warps][32 rows][128 bytes] when tma_out
-  // staging: 4 KB per epilogue warp when block units store through it, 2 KB when only swapped units do
+  // staging: 4 KB per epilogue warp when block units store through it, 2 KB when only swapped units do (a third tile in
+  // rotation was measured: no gain, the epilogue of a swapped unit is bound by its 2-byte shared-memory stores)
   const uint32_t stg_warp = g.tma_out ? 4096u : (g.tail_tma ? 2048u : 0u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * stg_warp);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 2);
@@ -495,22 +496,28 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           const bool col_ok = col < g.N;
           const float swc = sw_at(col);
           uint8_t* tile0 = staging + (warp - 2) * stg_warp;
-          // two tiles per warp where they fit (bf16: 1 KB each; fp32: 2 KB each, only beside the 4 KB block-unit tiles)
-          const bool two = EPI != kEpiPartialF32 || stg_warp == 4096u;
+          // bf16: two tiles of 1 KB in turn; fp32: tiles of 2 KB, two of them only beside the 4 KB block-unit tiles
+          const bool two = stg_warp == 4096u;
           if (g.tail_tma) {          // the stores of this warp's previous unit have read its tiles
             if (lane == 0) bulk_wait_read();
             __syncwarp();
           }
-#pragma unroll 1
-          for (int c = 0; c < g.tail_box / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(taddr + c * 16, r);
-            tmem_ld_wait();
+          // one chunk of 16 accumulator columns (= 16 rows of x); TMEM loads run one chunk ahead of the chunk being stored
+          auto emit = [&](int c, const uint32_t (&r)[16]) {
             if (g.tail_tma) {
-              uint8_t* t = tile0 + (two ? (c & 1) * (EPI == kEpiPartialF32 ? 2048 : 1024) : 0);
-              if (two ? c >= 2 : c >= 1) {
-                if (lane == 0) { if (two) bulk_wait_read1(); else bulk_wait_read(); }
-                __syncwarp();
+              uint8_t* t;
+              if constexpr (EPI == kEpiPartialF32) {
+                t = tile0 + (two ? (c & 1) * 2048 : 0);
+                if (two ? c >= 2 : c >= 1) {
+                  if (lane == 0) { if (two) bulk_wait_read1(); else bulk_wait_read(); }
+                  __syncwarp();
+                }
+              } else {
+                t = tile0 + (c & 1) * 1024;
+                if (c >= 2) {
+                  if (lane == 0) bulk_wait_read1();
+                  __syncwarp();
+                }
               }
 #pragma unroll
               for (int e = 0; e < 16; ++e) {
@@ -525,7 +532,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 tma_store_3d(&map_tail, smem_u32(t), col0, m0 + c * 16, EPI == kEpiPartialF32 ? u.split : 0);
                 bulk_commit();
               }
-              continue;
+              return;
             }
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
@@ -538,6 +545,21 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                   reinterpret_cast<float*>(g.out)[static_cast<int64_t>(u.split) * g.split_stride + static_cast<int64_t>(m) * g.ldo + col] = v;
                 }
               }
+            }
+          };
+          const int nch = g.tail_box / 16;
+          uint32_t ra[16], rb[16];
+          tmem_ld16(taddr, ra);
+          tmem_ld_wait();
+#pragma unroll 1
+          for (int c = 0; c < nch; c += 2) {
+            if (c + 1 < nch) tmem_ld16(taddr + (c + 1) * 16, rb);
+            emit(c, ra);
+            tmem_ld_wait();
+            if (c + 1 < nch) {
+              if (c + 2 < nch) tmem_ld16(taddr + (c + 2) * 16, ra);
+              emit(c + 1, rb);
+              tmem_ld_wait();
             }
           }
         }
@@ -630,7 +652,7 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   const int out_elt = EPI == kEpiPartialF32 ? 4 : 2;
   g.tma_out = g.n_xblk > 0 && (ldo * out_elt) % 16 == 0 && g.BN % (128 / out_elt) == 0 ? 1 : 0;
   g.tail_tma = (g.tail_rows > 0 && (ldo * out_elt) % 16 == 0 && (EPI != kEpiPartialF32 || (M * N * 4) % 16 == 0)) ? 1 : 0;
-  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16 + (g.tma_out ? kStagingBytes : (g.tail_tma ? kStagingBytes / 2 : 0));
+  const size_t fixed = 1024 + (2 * kMaxStages + 2) * 8 + 16 + (g.tma_out ? kStagingBytes : (g.tail_tma ? kEpiWarps * 2048 : 0));
   g.stages = static_cast<int>((kSmemBudget - fixed) / g.stage_bytes);
   if (g.stages > kMaxStages) g.stages = kMaxStages;
   if (g_max_stages >= 2 && g_max_stages <= 12 && g.stages > g_max_stages) g.stages = g_max_stages;
