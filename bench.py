@@ -1,10 +1,11 @@
 """Benchmark of the prefix-tree scoring forward (64-layer hybrid 27B-scale model, random-init weights, synthetic trees).
 
-    python bench.py --gpus 1 --steps 30 --warmup 5
+    python bench.py --gpus 1 --steps 100 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
     python bench.py --impl reference          # the reference's PyTorch path on the host cores (bounded sample)
+    python bench.py --no-reference-gpu        # skip the leg that times the reference's own CUDA forward on this GPU
 
-A step = one request: the 539-row, 7-candidate tree of BASELINE.json pushed through the forward + scoring head. Data
+A step = one request: the 539-row, 7-candidate tree pushed through the forward + scoring head. Data
 parallel: every rank owns a full copy of the weights and its own requests; nothing is exchanged on the data path, the
 process group only provides the barrier and the max over ranks of the timed region. Prints one JSON line on rank 0.
 """
@@ -17,7 +18,7 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for p in (ROOT, os.path.join(ROOT, "open-jev-fast_b200"), os.path.join(ROOT, "tests")):
+for p in (ROOT, os.path.join(ROOT, "open-jev-fast_b200")):
     if p not in sys.path:
         sys.path.insert(0, p)
 
@@ -105,7 +106,30 @@ def cpu_reference_sample(cfg_kwargs, seqs, threads, reps=0):
     return OH.time_layers(_CPU_CORE["core"], seqs, reps=reps)
 
 
-def run_reference(args, cfg_kwargs, seqs, n_lin, n_full):
+def workload_name(name, seqs, groups):
+    """The same string in both arms: what tree, which graph key (from the host layout builder; no GPU needed)."""
+    from ojb200 import layout as PL
+    d = PL.gtree_host(seqs, groups, 0, 32, 16, vbits=False)[0]
+    return (f"{name} tree: key (N,S,L2)=({d['N']}, {d['S']}, {d['L2']}), real rows {d['Nreal']}, 64-layer hybrid "
+            "(48 GDN + 16 gated GQA), hidden 5120, MLP 17408, HV=32")
+
+
+def reference_on_gpu(args):
+    """The reference's own forward_gtree (its CUDA operators rebuilt for sm_100a + cuBLAS) timed on this GPU in a child
+    process, before this library's model is built: a fault or a missing build there cannot touch the numbers below."""
+    cmd = [sys.executable, "-m", "oracle.ref_forward", "--workload", args.workload, "--steps", "30", "--warmup", "5",
+           "--layers", str(args.layers)]
+    try:
+        r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+        for line in reversed(r.stdout.strip().splitlines()):
+            if line.startswith("{"):
+                return json.loads(line)
+        return {"impl": "reference-gpu", "unavailable": f"no result line (exit code {r.returncode}): {r.stderr[-200:]}"}
+    except Exception as e:
+        return {"impl": "reference-gpu", "unavailable": f"{type(e).__name__}: {e}"}
+
+
+def run_reference(args, cfg_kwargs, seqs, groups, n_lin, n_full):
     """`--impl reference`: K timed samples (after W untimed ones) of the reference's PyTorch path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -123,16 +147,17 @@ def run_reference(args, cfg_kwargs, seqs, n_lin, n_full):
               f"scaled by ({n_lin},{n_full}) layers")
     line = {"metric": METRIC, "value": v, "unit": "requests/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "impl": "reference",
-            "config": {"workload": args.workload, "timed": "host cores; one layer of each type timed, scaled to 64 layers"},
+            "data": "synthetic", "impl": "reference", "extrapolated": True,
+            "config": {"workload": workload_name(args.workload, seqs, groups),
+                       "timed": "host cores; one layer of each type timed, scaled to 64 layers"},
             "cpu_baseline": {"value": v, "unit": "requests/s", "cores": threads, "kind": "reference", "sample": sample},
             "e2e": {"value": v, "unit": "requests/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM from the ncu captures summarised in profiles/
-# (bytes; keyed by M). The algorithmic bytes are weights + x + out = 381.0 MB at M = 544.
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM at M = 544 (profiles/gemm_swiglu_m544_ncu_full.md)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate/up GEMM at M = 544, from one ncu capture of the same
+# kernel and shape (bytes). Not measured by this run: the line says so in `traffic_source`. The algorithmic bytes are
+# weights + x + out = 381.0 MB at M = 544.
 TRAFFIC_NCU = {("gemm_block256", 544): 394.8e6, ("gemm_tile128", 544): 389.1e6}
 
 
@@ -164,18 +189,20 @@ def gemm_roofline(fast, M, pk, pk_kind, dev):
     code = LT.VARIANT_BN[idx] if idx else LT.gemm_plan(M, N2_, Kd_, 1)[0]
     kern = {1: "gemm_tile128_kernel<256,4,swiglu>", 2: "gemm_tile128_kernel<128,6,swiglu>"}.get(code, "gemm_block256_kernel<swiglu>")
     return {"bound": "tensor", "kernel": kern + " (gate/up GEMM + SwiGLU, 64 launches per forward)", "achieved": ach, "peak": peak,
-            "unit": "TFLOP/s", "frac": ach / peak, "traffic": TRAFFIC_NCU.get((kern.split("_kernel")[0], M)), "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
+            "unit": "TFLOP/s", "frac": ach / peak, "traffic": TRAFFIC_NCU.get((kern.split("_kernel")[0], M)),
+            "traffic_source": "one ncu capture of this kernel at this shape (committed summary), not this run", "peak_source": f"{pk_kind} burst bf16", "us_per_launch": best * 1e3,
             "algorithmic_flops_per_launch": flops, "weight_stream_gbs": w_gbs, "hbm_peak_gbs": pk["hbm_gbs"]}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="baseline", choices=["baseline", "example"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's own CUDA forward on this GPU")
     ap.add_argument("--profile", type=int, default=0, help="run this many eager (graph-free) forwards between "
                     "cudaProfilerStart/Stop and exit: for `ncu --profile-from-start off`")
     ap.add_argument("--pack", type=int, default=0, help="also time this many requests packed into one forward (extra key "
@@ -186,7 +213,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
-    import trees
+    from ojb200 import trees
     from ojb200 import modelgen as MG
     cfg_kwargs = dict(MG.FULL)
     cfg_kwargs["num_hidden_layers"] = args.layers
@@ -195,8 +222,8 @@ def main():
     n_full = args.layers - n_lin
     mk = trees.baseline_tree if args.workload == "baseline" else trees.example_tree
     if args.impl == "reference":
-        seqs, _ = mk(0, cfg.vocab_size)
-        return run_reference(args, cfg_kwargs, seqs, n_lin, n_full)
+        seqs, groups = mk(0, cfg.vocab_size)
+        return run_reference(args, cfg_kwargs, seqs, groups, n_lin, n_full)
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -207,6 +234,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     from ojb200 import _lib, fastmodel as FM, server as SV
     pk, pk_kind = peaks()
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_reference_gpu and not args.profile and not args.fp8:
+        ref_gpu = reference_on_gpu(args)
 
     core = MG.build_core(cfg, device=dev, seed=0)
     fast = FM.FastQwen35(core, free_original=True, fp8=args.fp8)
@@ -218,6 +248,8 @@ def main():
     torch.cuda.synchronize()
     _lib.check_status(dev)
     assert bool(torch.isfinite(out).all()), "non-finite scores"
+    # scores of the tree the reference-on-GPU leg runs (seed 0), for the cross-check in the result line
+    ref_scores_ours = scorer.score_tokens(*mk(0, cfg.vocab_size)).float().cpu() if ref_gpu is not None else None
     key = scorer.last["key"]
     ent = scorer.graphs[key]
 
@@ -291,8 +323,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "e4m3 projections with per-row scales, bf16 elsewhere (outside the bf16 parity tolerance)" if args.fp8 else "bf16",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload} tree: key (N,S,L2)={key}, real rows {scorer.last['rows']}, 64-layer hybrid "
-                                   "(48 GDN + 16 gated GQA), hidden 5120, MLP 17408, HV=32",
+            "config": {"workload": workload_name(args.workload, *mk(0, cfg.vocab_size)),
                        "layers": args.layers, "parallelism": f"dp{world}", "l2": "inputs larger than L2 (46 GB of weights per step)",
                        "timing": "CUDA events around K graph replays, max over ranks"},
             "ms_per_request_p50": steps_ms[len(steps_ms) // 2],
@@ -317,6 +348,13 @@ def main():
             line["cpu_baseline"] = None
         if packed is not None:
             line["packed"] = packed
+        if ref_gpu is not None:
+            # the reference's own forward (its CUDA operators + cuBLAS) on this GPU, same weights, same tree, CUDA graph replay
+            line["reference_gpu"] = ref_gpu
+            line["reference_gpu_ms"] = ref_gpu.get("ms_per_request_p50")
+            if ref_gpu.get("scores") is not None:
+                line["reference_gpu"]["max_abs_score_diff_vs_ours"] = float(
+                    (torch.tensor(ref_gpu["scores"]) - ref_scores_ours.flatten()).abs().max())
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -1,6 +1,6 @@
-"""GEMM sweep over the projection shapes of the model (BASELINE.json config 2) for every kernel variant.
+"""GEMM sweep over the projection shapes of the model for every kernel variant.
 
-    python -m ojb200.gemm_sweep [--m 64 288 544 1024 4096] [--quick]
+    python bench_gemm_sweep.py [--m 64 288 544 1024 4096] [--quick]
 
 For each (M, K, N): plain bf16 GEMM per tile variant, the SwiGLU-fused GEMM where N is a gate/up width, and split-K partial
 GEMMs (with their reduce + residual + RMSNorm kernel) where N is the hidden size. Each case is timed with CUDA events over
@@ -10,11 +10,13 @@ operands, and printed as one JSON line: microseconds, TFLOP/s, fraction of the m
 import argparse
 import json
 import os
+import sys
 
 import torch
 
-from . import ext as K
-from . import lt_ext as LT
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
+from ojb200 import ext as K
+from ojb200 import lt_ext as LT
 
 bf16 = torch.bfloat16
 SHAPES = [(5120, 12288), (5120, 12352), (5120, 14336), (5120, 34816), (17408, 5120), (6144, 5120), (4096, 5120)]

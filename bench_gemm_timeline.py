@@ -1,24 +1,27 @@
 """Work-unit timelines of the block GEMM kernels (256-row block kernel and CTA-pair kernel) through ojb_gemm_set_trace.
 
-    python -m ojb200.gemm_trace --m 544 --shape 5120 34816 --kind swiglu --variant 3
-    python -m ojb200.gemm_trace --m 512 --shape 5120 34816 --variant 256 --repeat 0 1 2 3      # copy rate / MMA slope
-    python -m ojb200.gemm_trace --m 512 --shape 5120 34816 --variant 768 --knob 2 3 4 5        # pipeline depth (pair kernel)
+    python bench_gemm_timeline.py --m 544 --shape 5120 34816 --kind swiglu --variant 3
+    python bench_gemm_timeline.py --m 544 --shape 17408 5120 --kind splitk --splits 2 --variant 3 --detail 2
 
 `--variant` is the library's variant code (3 block kernel, 4 all rows swapped, 16..256 forced w-tile width, 5 / 6 CTA-pair
-kernel, 512 + width = pair kernel with forced width). For every (repeat, knob) one JSON line: the span of the launch, and per
-unit type the mean time from the end of the previous epilogue to the completed accumulator ("main") and the mean epilogue
-time, in microseconds, plus how many units each CTA ran. `--repeat r` issues every stage's MMAs r times (0 = none: the pure
-copy rate); `--knob` 2..12 caps the pipeline stages. Results under repeat != 1 are not products, only timings.
+kernel, 512 + width = pair kernel with forced width). One JSON line: the span of the launch, and per unit type the mean time
+from the end of the previous epilogue to the completed accumulator ("main") and the mean epilogue time, in microseconds, plus
+how many units each CTA ran. `--repeat` / `--knob` need a library built with -DOJB_GEMM_PROBES (MMAs of a stage issued r
+times, pipeline depth capped, parts of the epilogue skipped): the shipped library has neither and the options are refused.
 """
 import argparse
 import json
 
+import os
+import sys
+
 import numpy as np
 import torch
 
-from . import _lib
-from . import lt_ext as LT
-from ._lib import call, i32, i64, ptr, stream_ptr
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
+from ojb200 import _lib  # noqa: E402
+from ojb200 import lt_ext as LT  # noqa: E402
+from ojb200._lib import call, i32, i64, ptr, stream_ptr  # noqa: E402
 
 bf16 = torch.bfloat16
 CAP = 8192
@@ -36,6 +39,9 @@ def main():
     ap.add_argument("--detail", type=int, default=0, help="print the timelines of this many latest-finishing CTAs")
     args = ap.parse_args()
     dev = torch.device("cuda")
+    probes = hasattr(_lib.lib(), "ojb_gemm_set_probe")
+    if (args.repeat != [1] or args.knob != [0]) and not probes:
+        raise SystemExit("--repeat / --knob need a library built with -DOJB_GEMM_PROBES")
     M, (K, N) = args.m, args.shape
     g = torch.Generator(device=dev).manual_seed(0)
     x = torch.randn(M, K, generator=g, device=dev).to(bf16)
@@ -62,12 +68,14 @@ def main():
     try:
         for knob in args.knob:
             for rep in args.repeat:
-                call("ojb_gemm_set_trace", None, i32(0), i32(rep), i32(knob))
+                call("ojb_gemm_set_trace", None, i32(0))
+                if probes:
+                    call("ojb_gemm_set_probe", i32(rep), i32(knob))
                 for w in ws:
                     launch(w)                               # warm-up, and the weights of the traced launch leave the L2
                 torch.cuda.synchronize()
                 rec.zero_()
-                call("ojb_gemm_set_trace", ptr(rec), i32(CAP), i32(rep), i32(knob))
+                call("ojb_gemm_set_trace", ptr(rec), i32(CAP))
                 launch(ws[0])
                 torch.cuda.synchronize()
                 t = rec.cpu().numpy()
@@ -95,7 +103,9 @@ def main():
                                 for tl, b, f, e in sorted(zip(tail[m], beg[m], full[m], end[m]), key=lambda z: z[1])]
                 print(json.dumps(line), flush=True)
     finally:
-        call("ojb_gemm_set_trace", None, i32(0), i32(1), i32(0))
+        call("ojb_gemm_set_trace", None, i32(0))
+        if probes:
+            call("ojb_gemm_set_probe", i32(1), i32(0))
     _lib.check_status(dev)
 
 

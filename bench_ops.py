@@ -1,6 +1,6 @@
 """Micro-benchmark of the non-GEMM kernels at the model's dimensions on one tree (for tuning and for ncu captures).
 
-    python -m ojb200.op_bench [--tree baseline|example] [--reps 20] [--only gdn|attn|norm]
+    python bench_ops.py [--tree baseline|example] [--reps 20] [--only gdn|attn|norm]
 
 Prints one JSON line per op: microseconds per call (CUDA events over `reps` back-to-back calls after a warm-up).
 """
@@ -11,8 +11,9 @@ import sys
 
 import torch
 
-from . import ext as K
-from . import layout as PL
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
+from ojb200 import ext as K
+from ojb200 import layout as PL
 
 bf16 = torch.bfloat16
 
@@ -47,8 +48,7 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--hv", type=int, default=32)
     args = ap.parse_args()
-    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "tests"))
-    import trees
+    from ojb200 import trees
     seqs, groups = (trees.baseline_tree if args.tree == "baseline" else trees.example_tree)(0)
     ids, lay = PL.gtree_build(seqs, groups, 0, dev="cuda", dense=False)
     N, HK, HV, HD, H = lay.N, 16, args.hv, 128, 5120

@@ -1,8 +1,8 @@
-"""Length / width sweep of the full model (BASELINE.json config 5) on the GPUs of one node, data parallel.
+"""Length / width sweep of the full model on the GPUs of one node, data parallel.
 
-    python -m ojb200.sweep --requests 64                         # one GPU
+    python bench_sweep.py --requests 64                         # one GPU
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        -m ojb200.sweep --requests 256
+        bench_sweep.py --requests 256
 
 Requests are seeded synthetic trees: shared prefix length log-uniform in [256, 16384], 1-3 questions with stems of 4-40
 tokens, 2-12 candidate leaves of 2-40 tokens. Request i is served by rank i % world (no collective on the data path). Every
@@ -14,6 +14,7 @@ requests per second.
 import argparse
 import json
 import os
+import sys
 import time
 
 import numpy as np
@@ -59,7 +60,8 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    from . import _lib, fastmodel as FM, modelgen as MG, server as SV
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
+from ojb200 import _lib, fastmodel as FM, modelgen as MG, server as SV
     kw = dict(MG.FULL)
     kw["num_hidden_layers"] = args.layers
     cfg = MG.make_config(**kw)

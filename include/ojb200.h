@@ -2,7 +2,10 @@
  *
  * Every entry point takes plain device (or, where stated, host) pointers and sizes, launches on the given CUDA
  * stream (a cudaStream_t passed as void*), never synchronises, never allocates and never reads results back, so each
- * call can be captured into a CUDA graph. Return value: OJB_OK or a negative OJB_ERR_* code. Kernels with device-side
+ * call can be captured into a CUDA graph. Exceptions, stated at their declarations: the two measurement hooks
+ * (ojb_gemm_set_trace, ojb_gdn_set_trace) change process-wide state and the second synchronises; the first call of
+ * ojb_gdn_chunked_static on a device does a one-time look-up. Kernel attributes and the SM count are cached per device, so
+ * one process may drive several GPUs (make each call with its device current). Return value: OJB_OK or a negative OJB_ERR_* code. Kernels with device-side
  * waits additionally take `status`, a device int32 that stays 0 unless a bounded wait ran out.
  *
  * Each declaration names the interface of lyuyiqi/open-jev-fast that it stands in for (path inside that project).
@@ -46,8 +49,9 @@ int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N,
 
 /* Same GEMM with the SwiGLU of src/kernels.cu:1304 silu_mul_lut fused into the epilogue. `w_blk` is the gate/up weight
  * re-laid in blocks of 256 rows: rows [256b, 256b+128) = gate rows [128b, 128b+128), rows [256b+128, 256b+256) = the
- * matching up rows. N = 2*I must be a multiple of 256. out[M, I] = bf16(bf16(silu(bf16(g))) * bf16(u)); the SiLU uses the
- * approximate exponential and reciprocal of the device (about 2 ulp in fp32 before the bf16 rounding). The CTA-pair kernel
+ * matching up rows. N = 2*I must be a multiple of 256. out[M, I] = bf16(silu(g) * u) on the fp32 accumulators g, u (the
+ * reference rounds g, u and silu(g) to bf16 first; those three roundings are dropped here); the SiLU uses the approximate
+ * exponential and reciprocal of the device (about 2 ulp in fp32 before the bf16 rounding). The CTA-pair kernel
  * with block units (variant 5) reads a different interleave: blocks of 64 gate rows followed by their 64 up rows; with all
  * rows swapped (variant 6) it reads the layout above. */
 int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
@@ -82,15 +86,24 @@ int ojb_quantize_rows_e4m3(const void* x, void* q, float* scale, int64_t rows, i
 int ojb_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t kind, int32_t max_splits, int32_t* variant, int32_t* splits,
                   float* microseconds);
 
-/* Measurement hook of the 256-row block GEMM kernel (no counterpart in the reference). `records` = null switches it off;
- * otherwise a device buffer of 1 + 4*capacity uint64 words, word 0 = record counter (zero it before a launch). Every work
- * unit appends {CTA << 32 | tail flag << 31 | unit, ns when its epilogue began to wait, ns when its accumulators were
- * complete, ns when its epilogue ended} (%globaltimer). mma_repeat > 1 issues the MMAs of every shared-memory stage that
- * many times (results are then meaningless): the slope against mma_repeat is the pure tensor-pipe cost of a stage.
- * mma_repeat = 0 issues none (pure copy rate). knob: 0 = nothing, 2..12 = cap on the number of pipeline stages, 100 / 101 =
- * the block epilogue skips its global stores / its TMEM loads, 102 = with mma_repeat > 1 the MMAs of block units are issued
- * with M = 64 instead of 128 (the cost of a half-height MMA). The CTA-pair kernel records the same timelines. */
-int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t knob);
+/* Limit of the device-side waits of the GEMM kernels (every mbarrier wait of producer, MMA issuer and epilogue), in
+ * milliseconds; 0 restores the default of 2000. When a wait runs out the CTA writes OJB_DEV_WAIT_TIMEOUT to `status`, lets
+ * its copies in flight land, frees its tensor memory and returns; the context stays usable and the results of that launch are
+ * invalid. Process-wide, read at launch time. No counterpart in the reference, whose one device-side wait
+ * (src/kernels.cu:4103, gdn_fused7) is unbounded. */
+int ojb_gemm_set_wait_limit_ms(int32_t ms);
+
+/* Failure injection for the tests of that path (host-side switch, off by default): while on, the producer warp of the 128-row
+ * tile kernel (variants 1 / 2) announces the bytes of the second k-block it handles but does not issue the copies, so the
+ * consumer's bounded wait runs out as described above. Nothing faults, traps or spins without a limit. */
+int ojb_gemm_test_drop_copy(int32_t on);
+
+/* Measurement hook of the 256-row block GEMM kernel and the CTA-pair kernel (no counterpart in the reference). `records` =
+ * null switches it off; otherwise a device buffer of 1 + 4*capacity uint64 words, word 0 = record counter (zero it before a
+ * launch). Every work unit appends {CTA << 32 | tail flag << 31 | unit, ns when its epilogue began to wait, ns when its
+ * accumulators were complete, ns when its epilogue ended} (%globaltimer). Results are not affected. Process-wide and not
+ * synchronised: set it while no GEMM of this library is being launched from another thread. */
+int ojb_gemm_set_trace(uint64_t* records, int32_t capacity);
 
 /* ------------------------------------------------------------------------------------------------------------------
  * Row-wise and element-wise kernels.
@@ -107,6 +120,15 @@ int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int
 int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits, const float* w1, const int32_t* rowmask,
                        void* h_out, void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream);
 
+/* src/kernels.cu:41,755 add_rmsnorm and :1444,1488 add_rmsnorm_sk2 with the residual stream held in fp32 (the form the
+ * 64-layer forward of this library uses; the two entry points above keep the reference's bf16 stream bit for bit).
+ * h fp32 [rows, H] is updated in place: h = float(x_init) when x_init (bf16 [rows, H], the embedding rows) is given, else
+ * h += sum_s parts[s] (fp32 [splits, rows, H], splits in [1, 16]) or h += float(delta) (bf16) or h unchanged; exactly one of
+ * x_init / parts / delta may be non-null. The sum is formed and added in fp32 and h is never rounded.
+ * hn = bf16(h * rsqrt(mean(h^2) + eps) * w1), zero where rowmask[n] == 0 (rowmask may be null). H % 8 == 0, H <= 8192. */
+int ojb_resnorm_f32(float* h, const void* x_init, const void* delta, const float* parts, int splits, const float* w1,
+                    const int32_t* rowmask, void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream);
+
 /* src/kernels.cu:1288,1296 act_tables. silu_tab[65536] bf16 and sig_tab[65536] fp32, indexed by the bf16 bit pattern:
  * silu_tab[b] = bf16(x / (1 + expf(-x))), sig_tab[b] = 1 / (1 + expf(-x)). */
 int ojb_act_tables(void* silu_tab, float* sig_tab, ojb_stream_t stream);
@@ -119,6 +141,10 @@ int ojb_silu_mul(const void* gu, const void* silu_tab, void* out, int64_t rows, 
  * att[h*att_stride_h + t*att_stride_t + d]; gate is [T, HQ*D]; y[T, HQ*D] = bf16(att * bf16(sigmoid(gate))). */
 int ojb_gate_mul(const void* att, int64_t att_stride_t, int64_t att_stride_h, const void* gate, void* y, int64_t T,
                  int64_t HQ, int64_t D, ojb_stream_t stream);
+
+/* src/kernels.cu:1381-1392 l2_prefetch: asks the memory system to bring `nbytes` at `data` (16-byte aligned) into L2, one bulk
+ * prefetch per `chunk` bytes (a multiple of 16, at most 1 MiB). Returns at once; nothing waits for the prefetch. */
+int ojb_l2_prefetch(const void* data, int64_t nbytes, int64_t chunk, ojb_stream_t stream);
 
 /* src/kernels.cu:4759,4767 pack_bits. vis uint8/bool [N, N] -> bits int32 [N, N/32], bit b of word w = key 32w+b. */
 int ojb_pack_bits(const uint8_t* vis, int32_t* bits, int64_t N, ojb_stream_t stream);
@@ -160,10 +186,14 @@ int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, const int32_t*
  * rep_pos[rep_ptr[n] .. rep_ptr[n+1]) of every packed row n, pad slots zeroed; q, k, v, g, beta have n_slots rows) and its
  * unreplicated form (rep_ptr == null: one output row per packed row). proj bf16 [N, 2KD+2VD+2HV] = [q|k|v|z|b|a];
  * hist int32 [N+1, 4] = rows t-3..t on the row's own path (-1 = none); convw bf16 [2KD+VD, 4]; A_log, dt_bias bf16 [HV].
- * Head dim is 128: KD = 128*HK, VD = 128*HV. q, k bf16 [*, KD]; v bf16 [*, VD]; g fp32 [*, HV]; beta bf16 [*, HV]. */
+ * Head dim is 128: KD = 128*HK, VD = 128*HV. q, k bf16 [*, KD]; v bf16 [*, VD]; g fp32 [*, HV]; beta bf16 [*, HV].
+ * l2norm = 0 leaves q and k un-normalised (src/kernels.cu:96 linattn_prep and linattn_prep2 with do_l2 = false, whose callers
+ * let the attention kernel normalise); every other prep variant of the reference normalises. The same entry point serves
+ * the reference's older layouts (per-sequence [B, T], single-level tree, src-mapped slots): they differ only in `hist` and in
+ * the slot tables, which the Python layer derives. */
 int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t* rep_ptr, const int32_t* rep_pos, int64_t n_slots,
                  const void* convw, const void* A_log, const void* dt_bias, void* q, void* k, void* v, float* g,
-                 void* beta, int64_t N, int64_t KD, int64_t VD, int64_t HV, int64_t HK, ojb_stream_t stream);
+                 void* beta, int64_t N, int64_t KD, int64_t VD, int64_t HV, int64_t HK, int32_t l2norm, ojb_stream_t stream);
 
 /* Bytes of scratch that ojb_gdn_chunked needs for n_chunks chunk-table entries and HV value heads. */
 int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV);
@@ -201,20 +231,21 @@ int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const fl
  * no allocator for device memory. Limits and rules:
  *   - n_chunks * HV <= ojb_gdn_static_max_items() (1024), else OJB_ERR_LIMIT and nothing is launched;
  *   - the first call on each device looks up the array's device address and raises two kernel attributes; make that first
- *     call with the device current and before any stream capture starts;
+ *     call with the device current and before any stream capture starts. Two host threads that make this first call on the
+ *     same device at the same moment both do the look-up and store the same address: harmless, but not synchronised;
  *   - all calls on one GPU share the array: calls that may overlap on the GPU (different streams, no ordering) race;
  *     the array keeps the previous call's contents, and nothing in it needs clearing between calls. */
 int64_t ojb_gdn_static_max_items(void);
+int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
+                           const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                           int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK, int64_t HV,
+                           float scale, ojb_stream_t stream);
 
 /* Measurement hook of the state pass (no counterpart in the reference): `records` = null switches it off; otherwise a device
  * buffer of 12 uint64 words per walk step. The CTA of head 0 / column slice 0 / walk 0 stores %globaltimer at six points of
  * every step (step begin, operands ready, phase 1 done, v' visible, phase 2 done, step end), words 0-5 from its state-chain
  * warp and 6-11 from its output warp. Synchronises the device (it writes a device variable). */
 int ojb_gdn_set_trace(uint64_t* records);
-int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
-                           const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
-                           int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK, int64_t HV,
-                           float scale, ojb_stream_t stream);
 
 /* src/kernels.cu:1333-1374 gated_rmsnorm_inv2 (inv != null) and :143 gated_rmsnorm (inv == null).
  * out[n, h, :] = bf16(((x[r, h, :] * rstd) * w) * z * sigmoid(z)), r = inv[n] or n, z = proj[n, zoff + h*128 ...],

@@ -57,6 +57,32 @@ __device__ __forceinline__ void report_status(int32_t* status, int32_t code) {
 
 static inline int launch_status(cudaError_t e) { return e == cudaSuccess ? OJB_OK : OJB_ERR_LAUNCH; }
 
+// Launch state that CUDA keeps per device (a kernel's opt-in shared-memory size, the SM count) is cached per device, so one
+// process can drive several GPUs. Two host threads making the first call on one device at once set the same value twice.
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+  int d = -1;
+  return (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < kMaxDevices) ? d : -1;
+}
+// Raises the dynamic shared-memory limit of `kern` on the current device to at least `bytes`; `set` remembers, per device,
+// what has been granted.
+template <typename Kern>
+inline bool raise_smem_limit(Kern kern, int bytes, int (&set)[kMaxDevices]) {
+  const int d = current_device();
+  if (d < 0) return false;
+  if (set[d] >= bytes) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  set[d] = bytes;
+  return true;
+}
+inline int device_sm_count() {
+  static int n[kMaxDevices] = {};
+  const int d = current_device();
+  if (d < 0) return 0;
+  if (n[d] == 0 && cudaDeviceGetAttribute(&n[d], cudaDevAttrMultiProcessorCount, d) != cudaSuccess) n[d] = 0;
+  return n[d];
+}
+
 // ---- Programmatic dependent launch (off unless OJB_PDL=1 is in the environment). Every kernel of the hot loop goes through
 // launch_kernel() and begins with pdl_begin(): with the stream-serialisation attribute set, the next kernel of the stream
 // may be scheduled as soon as all CTAs of this one have started (its CTAs fill SMs that this grid leaves idle, set up their

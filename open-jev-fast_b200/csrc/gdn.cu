@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256)
 gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, const int32_t* __restrict__ rep_ptr,
                 const int32_t* __restrict__ rep_pos, const bf16_t* __restrict__ convw, const bf16_t* __restrict__ A_log,
                 const bf16_t* __restrict__ dt_bias, bf16_t* __restrict__ q, bf16_t* __restrict__ k, bf16_t* __restrict__ v,
-                float* __restrict__ g, bf16_t* __restrict__ beta, int N, int KD, int VD, int HV) {
+                float* __restrict__ g, bf16_t* __restrict__ beta, int N, int KD, int VD, int HV, int l2norm) {
   pdl_begin();
   const int C = 2 * KD + VD, P = C + VD + 2 * HV;
   const int n = blockIdx.y;
@@ -125,7 +125,7 @@ gdn_prep_kernel(const bf16_t* __restrict__ proj, const int4* __restrict__ hist, 
     float o[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = round_bf(silu_f(acc[e]));
-    if (isqk) {  // 16 consecutive threads cover one 128-wide head
+    if (isqk && l2norm) {  // 16 consecutive threads cover one 128-wide head
       float ss = 0.f;
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss += o[e] * o[e];
@@ -581,7 +581,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     bf16_t* Sb = Sb2 + ((s - s_begin) & 1) * (kHD * kLdS);
     if (chain) {
     // ---- choose the incoming state
-    if (st.y == 1) {
+    if (st.y == 1 || (st.y == 4 && init_state == nullptr)) {
 #pragma unroll
       for (int a = 0; a < 2; ++a)
 #pragma unroll
@@ -596,7 +596,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
         for (int b = 0; b < 4; ++b)
 #pragma unroll
           for (int e = 0; e < 4; ++e) S[a][b][e] = sl[((a * 4 + b) * 4 + e) * kChainThreads + tid];
-    } else if (st.y == 4) {
+    } else if (st.y == 4 && init_state != nullptr) {   // (code 4 without an initial state starts from zero, like code 1)
       const float* is = init_state + (static_cast<int64_t>((st.w >> 16) - 1) * HV + h) * (kHD * kHD);
 #pragma unroll
       for (int a = 0; a < 2; ++a)
@@ -801,7 +801,7 @@ using namespace ojb;
 extern "C" int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t* rep_ptr, const int32_t* rep_pos,
                             int64_t n_slots, const void* convw, const void* A_log, const void* dt_bias, void* q, void* k,
                             void* v, float* g, void* beta, int64_t N, int64_t KD, int64_t VD, int64_t HV, int64_t HK,
-                            ojb_stream_t stream) {
+                            int32_t l2norm, ojb_stream_t stream) {
   if (N == 0) return OJB_OK;
   OJB_REQUIRE(proj && hist && convw && A_log && dt_bias && q && k && v && g && beta && N > 0);
   OJB_REQUIRE(HK > 0 && HV > 0 && KD == HK * kHD && VD == HV * kHD && HV <= 256);
@@ -815,14 +815,14 @@ extern "C" int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t
                                                 static_cast<const bf16_t*>(convw), static_cast<const bf16_t*>(A_log),
                                                 static_cast<const bf16_t*>(dt_bias), static_cast<bf16_t*>(q), static_cast<bf16_t*>(k),
                                                 static_cast<bf16_t*>(v), g, static_cast<bf16_t*>(beta), static_cast<int>(N),
-                                                static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV));
+                                                static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV), l2norm ? 1 : 0);
   } else {
     dim3 grid(gx, static_cast<unsigned>(N));
     launch_kernel(gdn_prep_kernel<false>, dim3(grid), dim3(256), 0, st, static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), nullptr, nullptr,
                                                  static_cast<const bf16_t*>(convw), static_cast<const bf16_t*>(A_log),
                                                  static_cast<const bf16_t*>(dt_bias), static_cast<bf16_t*>(q), static_cast<bf16_t*>(k),
                                                  static_cast<bf16_t*>(v), g, static_cast<bf16_t*>(beta), static_cast<int>(N),
-                                                 static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV));
+                                                 static_cast<int>(KD), static_cast<int>(VD), static_cast<int>(HV), l2norm ? 1 : 0);
   }
   return launch_status(cudaGetLastError());
 }
@@ -839,14 +839,17 @@ namespace {
 int intra_pairing(int64_t n_chunks, int64_t HV) {
   static const int forced = [] { const char* e = getenv("OJB_GDN_PAIR"); return e ? atoi(e) : -1; }();
   if (forced >= 0) return forced != 0 ? 1 : 0;      // 1: pair whenever two short chunks exist; 0: never
-  static const int slots = [] {
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return 3 * sms;
-  }();
+  const int sms = device_sm_count();
+  const int slots = 3 * (sms > 0 ? sms : 148);
   // the table may have empty slots: the kernel counts the chunks that exist and compares with the CTA slots itself
   return n_chunks * HV > slots ? slots : 0;
+}
+// Opt-in shared-memory sizes of the two (three with the level form) kernels, once per device.
+bool gdn_raise_limits(bool lean_too) {
+  static int s_intra[kMaxDevices] = {}, s_state[kMaxDevices] = {}, s_lean[kMaxDevices] = {};
+  return raise_smem_limit(gdn_intra_kernel, static_cast<int>(kIntraSmem), s_intra) &&
+         raise_smem_limit(gdn_state_kernel<false>, static_cast<int>(kStateSmem), s_state) &&
+         (!lean_too || raise_smem_limit(gdn_state_kernel<true>, static_cast<int>(kStateSmemLean), s_lean));
 }
 }  // namespace
 }  // namespace ojb
@@ -861,13 +864,7 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
   OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && scratch && out);
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_walks > 0 && n_walks <= 65535 && HV <= 65535);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(gdn_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
-      return OJB_ERR_LAUNCH;
-    attr = true;
-  }
+  if (!gdn_raise_limits(false)) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale,
@@ -899,7 +896,6 @@ namespace ojb {
 namespace {
 constexpr int64_t kStaticItems = 1024;   // (chunk-table entries) x (value heads) that fit: 1024 x 81 936 B = 80 MiB per GPU
 static __device__ __align__(256) unsigned char g_gdn_static_scratch[kStaticItems * kItemElems * 2];
-constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {nullptr};
 }  // namespace
 }  // namespace ojb
@@ -953,14 +949,7 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_levels > 0 && n_levels <= 16 && HV <= 65535);
   for (int64_t l = 0; l < n_levels; ++l) OJB_REQUIRE(levels[l + 1] >= levels[l] && levels[l + 1] - levels[l] <= 65535);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(gdn_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(gdn_state_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmemLean) != cudaSuccess)
-      return OJB_ERR_LAUNCH;
-    attr = true;
-  }
+  if (!gdn_raise_limits(true)) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale,

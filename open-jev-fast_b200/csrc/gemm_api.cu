@@ -107,12 +107,39 @@ extern "C" int ojb_gemm_bf16_splitk(const void* x, const void* w, float* parts, 
   return dispatch(kEpiPartialF32, variant, x, w, parts, M, N, K, splits, N, status, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ojb_gemm_set_trace(uint64_t* records, int32_t capacity, int32_t mma_repeat, int32_t stage_cols) {
-  OJB_REQUIRE(capacity >= 0 && mma_repeat >= 0 && mma_repeat <= 64 && (stage_cols == 0 || (stage_cols >= 2 && stage_cols <= 12) || stage_cols == 100 || stage_cols == 101 || stage_cols == 102));
-  gemm_block256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity, mma_repeat, stage_cols);
-  gemm_pair256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity, mma_repeat, stage_cols);
+namespace ojb {
+namespace { int g_wait_ms = kDefaultWaitMs, g_drop_copy = 0; }
+int gemm_wait_limit_ms() { return g_wait_ms; }
+int gemm_drop_copy() { return g_drop_copy; }
+}  // namespace ojb
+
+extern "C" int ojb_gemm_set_wait_limit_ms(int32_t ms) {
+  OJB_REQUIRE(ms >= 0 && ms <= 60000);
+  ojb::g_wait_ms = ms == 0 ? ojb::kDefaultWaitMs : ms;
   return OJB_OK;
 }
+
+extern "C" int ojb_gemm_test_drop_copy(int32_t on) {
+  ojb::g_drop_copy = on ? 1 : 0;
+  return OJB_OK;
+}
+
+extern "C" int ojb_gemm_set_trace(uint64_t* records, int32_t capacity) {
+  OJB_REQUIRE(capacity >= 0);
+  gemm_block256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity);
+  gemm_pair256_set_trace(reinterpret_cast<unsigned long long*>(records), capacity);
+  return OJB_OK;
+}
+
+#ifdef OJB_GEMM_PROBES
+// Probe builds only (not declared in the public header): MMA repeat count and pipeline / epilogue knobs.
+extern "C" int ojb_gemm_set_probe(int32_t mma_repeat, int32_t knob) {
+  OJB_REQUIRE(mma_repeat >= 0 && mma_repeat <= 64 && (knob == 0 || (knob >= 2 && knob <= 12) || knob == 100 || knob == 101 || knob == 102));
+  gemm_block256_set_probe(mma_repeat, knob);
+  gemm_pair256_set_probe(mma_repeat, knob);
+  return OJB_OK;
+}
+#endif
 
 extern "C" int ojb_gemm_plan(int64_t M, int64_t N, int64_t K, int32_t kind, int32_t max_splits, int32_t* variant, int32_t* splits,
                              float* microseconds) {

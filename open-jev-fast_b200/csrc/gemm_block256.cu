@@ -21,7 +21,7 @@
 // once, more than the L2 holds, and every unit reads its tile from HBM again.) The grid size is kept coprime with the
 // number of units per w tile so that long block units and short tail units are spread evenly over the CTAs.
 //
-// Every wait on an mbarrier is bounded: after kWaitLimitNs the kernel raises the CTA's abort flag, records
+// Every wait on an mbarrier is bounded: after the wait limit (2 s unless ojb_gemm_set_wait_limit_ms changed it) the kernel raises the CTA's abort flag, records
 // OJB_DEV_WAIT_TIMEOUT in the status word, lets copies in flight land, frees its TMEM and returns.
 #include "gemm_units.cuh"
 
@@ -36,13 +36,16 @@ constexpr uint32_t kSubBytes = kBM * kBK * 2;     // 16 KB: one 128-row sub-tile
 constexpr uint32_t kAcc1Col = 256;
 constexpr uint32_t kStagingBytes = kEpiWarps * 4096;                // TMEM column of the second accumulator
 
-// Measurement hooks (process-wide, set by ojb_gemm_set_trace): where the kernel records unit timelines, and how often it
-// repeats the MMAs of a stage.
+// Measurement hook (process-wide, set by ojb_gemm_set_trace): where the kernel records unit timelines.
 unsigned long long* g_trace = nullptr;
 int g_trace_cap = 0;
-int g_mma_repeat = 1;
-int g_max_stages = 0;   // 2..12: cap on the number of pipeline stages (measurement only)
-int g_dbg = 0;
+#ifdef OJB_GEMM_PROBES
+int g_mma_repeat = 1;   // MMAs of every stage issued this many times
+int g_max_stages = 0;   // 2..12: cap on the number of pipeline stages
+int g_dbg = 0;          // 100 / 101: the block epilogue skips its global stores / its TMEM loads; 102: MMAs with M = 64
+#else
+constexpr int g_mma_repeat = 1, g_max_stages = 0, g_dbg = 0;
+#endif
 
 // FP8: the operands are e4m3 bytes (a k-block of 128 bytes is then 128 elements of K and an MMA covers 32 of them); the
 // epilogue multiplies the accumulator by the scale of its row of x and of its row of w. Everything counted in bytes (stages,
@@ -84,7 +87,8 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     }
     mbar_init(accfull, 1);
     mbar_init(accempty, kEpiWarps);
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = g.wait_ms;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -193,7 +197,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           const uint64_t adesc0 = smem_desc_sw128(a_addr);
           const uint64_t adesc1 = smem_desc_sw128(a_addr + kSubBytes);
           const uint64_t bdesc = smem_desc_sw128(a_addr + kABytes);
-          if (g.mma_repeat == 1) {
+          if (OJB_PROBE_REPEAT(g) == 1) {
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k) {
               // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
@@ -201,10 +205,10 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
               mma(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc, accum);
               mma(tmem_base + kAcc1Col, adesc1 + 2 * k, bdesc + 2 * k, idesc, accum);
             }
-          } else {                                   // measurement only (ojb_gemm_set_trace)
+          } else {                                   // probe builds only
             // knob 102: the same MMAs with M = 64 in the instruction descriptor (what does a half-height MMA cost?)
-            const uint32_t idesc_m = g.dbg == 102 ? ((idesc & ~(0x1fu << 24)) | (static_cast<uint32_t>(64 >> 4) << 24)) : idesc;
-            for (int rep = 0; rep < g.mma_repeat; ++rep)
+            const uint32_t idesc_m = OJB_PROBE_DBG(g) == 102 ? ((idesc & ~(0x1fu << 24)) | (static_cast<uint32_t>(64 >> 4) << 24)) : idesc;
+            for (int rep = 0; rep < OJB_PROBE_REPEAT(g); ++rep)
               for (int k = 0; k < kBK / kUmmaK; ++k) {
                 const uint32_t accum = (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u;
                 mma(tmem_base, adesc0 + 2 * k, bdesc + 2 * k, idesc_m, accum);
@@ -285,9 +289,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                       u0 *= rs * sw_at(wr + 128); u1 *= rs * sw_at(wr + 129);
                     }
                     float s0, s1;
-                    silu2_f(round_bf(g0), round_bf(g1), s0, s1);
-                    o[e] = round_bf(s0) * round_bf(u0);
-                    o[e + 1] = round_bf(s1) * round_bf(u1);
+                    silu2_f(g0, g1, s0, s1);
+                    o[e] = s0 * u0;
+                    o[e + 1] = s1 * u1;
                   }
                   put(c * 4 + j, pack8(o));
                 }
@@ -351,9 +355,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 float o[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                  const float gv = round_bf(__uint_as_float(gr[j + e]));
-                  const float uv = round_bf(__uint_as_float(ur[j + e]));
-                  o[e] = round_bf(silu_f(gv)) * uv;
+                  const float gv = __uint_as_float(gr[j + e]);
+                  const float uv = __uint_as_float(ur[j + e]);
+                  o[e] = silu_f(gv) * uv;
                 }
                 *reinterpret_cast<uint4*>(orow + c * 16 + j) = pack8(o);
               }
@@ -385,7 +389,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           const int ncols = min(g.N - u.wt * g.BN, g.BN);      // columns of this tile that exist
           const bool vec_ok = (g.ldo % 8) == 0 && (g.BN % 8) == 0;
           auto emit = [&](int c, const uint32_t (&r)[32]) {
-            if (!row_ok || g.dbg == 100) return;
+            if (!row_ok || OJB_PROBE_DBG(g) == 100) return;
             if constexpr (kF32) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
@@ -418,7 +422,7 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           // chunks of 32 columns; the last one may reach past BN into unused columns of this accumulator's 256
           const int nch = (g.BN + 31) / 32;
           uint32_t ra[32], rb[32];
-          const bool ld = g.dbg != 101;
+          const bool ld = OJB_PROBE_DBG(g) != 101;
           if (ld) tmem_ld32(taddr, ra);
           tmem_ld_wait();
 #pragma unroll 1
@@ -467,9 +471,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                   const float xs = sx_at(m0 + c * 16 + e);
-                  const float gv = round_bf(__uint_as_float(gr[e]) * (FP8 ? xs * swg : 1.f));
-                  const float uv = round_bf(__uint_as_float(ur[e]) * (FP8 ? xs * swu : 1.f));
-                  t[e * 32 + lane] = f2bf(round_bf(silu_f(gv)) * uv);
+                  const float gv = __uint_as_float(gr[e]) * (FP8 ? xs * swg : 1.f);
+                  const float uv = __uint_as_float(ur[e]) * (FP8 ? xs * swu : 1.f);
+                  t[e * 32 + lane] = f2bf(silu_f(gv) * uv);
                 }
                 fence_proxy_async();
                 __syncwarp();
@@ -484,9 +488,9 @@ gemm_block256_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 const int m = m0 + c * 16 + e;
                 if (col_ok && m < g.M) {
                   const float xs = sx_at(m);
-                  const float gv = round_bf(__uint_as_float(gr[e]) * (FP8 ? xs * swg : 1.f));
-                  const float uv = round_bf(__uint_as_float(ur[e]) * (FP8 ? xs * swu : 1.f));
-                  ocol[static_cast<int64_t>(m) * g.ldo] = f2bf(round_bf(silu_f(gv)) * uv);
+                  const float gv = __uint_as_float(gr[e]) * (FP8 ? xs * swg : 1.f);
+                  const float uv = __uint_as_float(ur[e]) * (FP8 ? xs * swu : 1.f);
+                  ocol[static_cast<int64_t>(m) * g.ldo] = f2bf(silu_f(gv) * uv);
                 }
               }
             }
@@ -602,16 +606,13 @@ constexpr size_t kSmemBudget = 227 * 1024;
 template <int EPI, bool FP8 = false>
 int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
                 int32_t* status, cudaStream_t stream, const float* sx = nullptr, const float* sw = nullptr) {
-  static bool attr_set = false;
+  static int smem_set[kMaxDevices] = {};
   auto kern = gemm_block256_kernel<EPI, FP8>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)) != cudaSuccess)
-      return OJB_ERR_LAUNCH;
-    attr_set = true;
-  }
+  if (!raise_smem_limit(kern, static_cast<int>(kSmemBudget), smem_set)) return OJB_ERR_LAUNCH;
   const int sms = sm_count();
   if (sms <= 0) return OJB_ERR_LAUNCH;
   GemmArgs g{};
+  g.wait_ms = gemm_wait_limit_ms();
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
@@ -698,13 +699,17 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
 
 }  // namespace
 
-void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int knob) {
+void gemm_block256_set_trace(unsigned long long* buf, int cap) {
   g_trace = buf;
   g_trace_cap = buf ? cap : 0;
+}
+#ifdef OJB_GEMM_PROBES
+void gemm_block256_set_probe(int repeat, int knob) {
   g_mma_repeat = repeat >= 0 ? repeat : 1;
   g_max_stages = knob >= 100 ? 0 : knob;
   g_dbg = knob >= 100 ? knob : 0;
 }
+#endif
 
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream) {

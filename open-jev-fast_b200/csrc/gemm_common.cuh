@@ -11,7 +11,7 @@ namespace {
 constexpr int kBM = 128;           // UMMA M
 constexpr int kBK = 64;            // bf16 elements per stage along K = one 128-byte swizzle row
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr int kDefaultWaitMs = 2000;   // limit of every device-side wait unless ojb_gemm_set_wait_limit_ms changed it
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -37,7 +37,8 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false when the limit ran out or another role of this CTA already gave up.
+// Bounded wait. Returns false when the limit ran out or another role of this CTA already gave up. abort_flag[0] is the
+// CTA's give-up flag, abort_flag[1] the limit in milliseconds (both in shared memory, set up by thread 0 of the CTA).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
@@ -45,7 +46,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try(bar, parity)) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > static_cast<uint64_t>(abort_flag[1]) * 1000000ull) {
         *abort_flag = 1;
         return false;
       }
@@ -266,15 +267,7 @@ int make_tail_out_map(CUtensorMap* map, void* base, int elt, int64_t rows, int64
   return r == CUDA_SUCCESS ? OJB_OK : OJB_ERR_ARG;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
-  }
-  return n;
-}
+inline int sm_count() { return device_sm_count(); }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -285,12 +278,19 @@ int gemm_tile128_launch(int epi, int bn, const void* x, const void* w, void* out
                         int64_t ldo, int32_t* status, cudaStream_t stream);
 int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
-void gemm_block256_set_trace(unsigned long long* buf, int cap, int repeat, int knob);
+void gemm_block256_set_trace(unsigned long long* buf, int cap);
+// process-wide settings kept in gemm_api.cu: limit of the device-side waits (ms) and the failure-injection switch of the tests
+int gemm_wait_limit_ms();
+int gemm_drop_copy();
 // e4m3 operands with one fp32 scale per row of x (sx) and per row of w (sw): out = (xq . wq^T) * sx[m] * sw[n]
 int gemm_block256_launch_e4m3(int epi, const void* xq, const float* sx, const void* wq, const float* sw, void* out, int64_t M,
                               int64_t N, int64_t K, int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 int gemm_pair256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                         int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
-void gemm_pair256_set_trace(unsigned long long* buf, int cap, int repeat, int max_stages);
+void gemm_pair256_set_trace(unsigned long long* buf, int cap);
+#ifdef OJB_GEMM_PROBES
+void gemm_block256_set_probe(int repeat, int knob);
+void gemm_pair256_set_probe(int repeat, int max_stages);
+#endif
 
 }  // namespace ojb

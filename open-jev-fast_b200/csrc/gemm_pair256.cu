@@ -38,8 +38,12 @@ constexpr uint32_t kAccCols = 256;                   // TMEM columns per accumul
 
 unsigned long long* g_ptrace = nullptr;
 int g_ptrace_cap = 0;
+#ifdef OJB_GEMM_PROBES
 int g_pmma_repeat = 1;
 int g_pmax_stages = 0;
+#else
+constexpr int g_pmma_repeat = 1, g_pmax_stages = 0;
+#endif
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -166,7 +170,8 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
       mbar_init(accfull0 + 8 * b, 1);                       // one tcgen05.commit per unit, delivered to both CTAs
       mbar_init(accempty0 + 8 * b, 2 * kPairEpiWarps);      // the epilogue warps of both CTAs (leader's barrier only)
     }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = g.wait_ms;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_xh) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_wh) : "memory");
@@ -250,7 +255,7 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
           const uint64_t adesc = smem_desc_sw128(a_addr);
           const uint64_t bdesc = smem_desc_sw128(a_addr + kHalfABytes);
           if (u.tail) {
-            for (int rep = 0; rep < g.mma_repeat; ++rep) {      // (repeat > 1 only for measurements)
+            for (int rep = 0; rep < OJB_PROBE_REPEAT(g); ++rep) {      // (repeat > 1 in probe builds only)
               for (int c = 0; c < g.n_chunk; ++c) {
                 const int wc = min(g.chunk_w, g.tail_box - c * g.chunk_w);
                 const uint32_t idesc_c = umma_idesc_m256(wc);
@@ -261,12 +266,12 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
                                  (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u);
               }
             }
-          } else if (g.mma_repeat == 1) {
+          } else if (OJB_PROBE_REPEAT(g) == 1) {
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k)
               umma_bf16_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > u.kb0 || k > 0) ? 1u : 0u);
-          } else {                                   // measurement only (ojb_gemm_set_trace)
-            for (int rep = 0; rep < g.mma_repeat; ++rep)
+          } else {                                   // probe builds only
+            for (int rep = 0; rep < OJB_PROBE_REPEAT(g); ++rep)
               for (int k = 0; k < kBK / kUmmaK; ++k)
                 umma_bf16_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > u.kb0 || k > 0 || rep > 0) ? 1u : 0u);
           }
@@ -357,9 +362,9 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
               float o[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
-                const float gv = round_bf(__uint_as_float(gr[8 * j + e]));
-                const float uv = round_bf(__uint_as_float(ur[8 * j + e]));
-                o[e] = round_bf(silu_f(gv)) * uv;
+                const float gv = __uint_as_float(gr[8 * j + e]);
+                const float uv = __uint_as_float(ur[8 * j + e]);
+                o[e] = silu_f(gv) * uv;
               }
               stage_put(tile, lane, c * 4 + j, pack8(o));
             }
@@ -395,8 +400,8 @@ gemm_pair256_kernel(const __grid_constant__ CUtensorMap map_xh, const __grid_con
               for (int e = 0; e < 16; ++e) {
                 const int m = m0 + c * 16 + e;
                 if (col_ok && m < g.M) {
-                  const float gv = round_bf(__uint_as_float(r[e])), uv = round_bf(xch[e]);
-                  reinterpret_cast<bf16_t*>(g.out)[static_cast<int64_t>(m) * g.ldo + j] = f2bf(round_bf(silu_f(gv)) * uv);
+                  const float gv = __uint_as_float(r[e]), uv = xch[e];
+                  reinterpret_cast<bf16_t*>(g.out)[static_cast<int64_t>(m) * g.ldo + j] = f2bf(silu_f(gv) * uv);
                 }
               }
             }
@@ -461,16 +466,13 @@ constexpr size_t kPairSmemBudget = 227 * 1024;
 template <int EPI>
 int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int bn_req, int64_t ldo,
                 int32_t* status, cudaStream_t stream) {
-  static bool attr_set = false;
+  static int smem_set[kMaxDevices] = {};
   auto kern = gemm_pair256_kernel<EPI>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBudget)) != cudaSuccess)
-      return OJB_ERR_LAUNCH;
-    attr_set = true;
-  }
+  if (!raise_smem_limit(kern, static_cast<int>(kPairSmemBudget), smem_set)) return OJB_ERR_LAUNCH;
   const int pairs = sm_count() / 2;
   if (pairs <= 0) return OJB_ERR_LAUNCH;
   GemmArgs g{};
+  g.wait_ms = gemm_wait_limit_ms();
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
@@ -543,12 +545,16 @@ int launch_pair(const void* x, const void* w, void* out, int64_t M, int64_t N, i
 
 }  // namespace
 
-void gemm_pair256_set_trace(unsigned long long* buf, int cap, int repeat, int max_stages) {
+void gemm_pair256_set_trace(unsigned long long* buf, int cap) {
   g_ptrace = buf;
   g_ptrace_cap = buf ? cap : 0;
+}
+#ifdef OJB_GEMM_PROBES
+void gemm_pair256_set_probe(int repeat, int max_stages) {
   g_pmma_repeat = repeat >= 0 ? repeat : 1;
   g_pmax_stages = max_stages;
 }
+#endif
 
 int gemm_pair256_launch(int epi, int bn_req, const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K,
                         int splits, int64_t ldo, int32_t* status, cudaStream_t stream) {

@@ -11,7 +11,7 @@
 // Work units are (m-block, k-split, n-block) with the m-block varying fastest, so that the CTAs running at the same time
 // share one w-tile column (read once from HBM, then from L2) while x (a few MB) stays L2-resident.
 //
-// Every wait on an mbarrier is bounded: after kWaitLimitNs the kernel raises the CTA's abort flag, records
+// Every wait on an mbarrier is bounded: after the wait limit (2 s unless ojb_gemm_set_wait_limit_ms changed it) the kernel raises the CTA's abort flag, records
 // OJB_DEV_WAIT_TIMEOUT in the status word, lets copies in flight land, frees its TMEM and returns.
 #include "gemm_common.cuh"
 
@@ -27,6 +27,8 @@ struct GemmArgs {
   int64_t ldo;          // leading dimension of out in elements
   int64_t split_stride; // elements between consecutive split planes (fp32 partials)
   int32_t* status;
+  int wait_ms;          // limit of every mbarrier wait, milliseconds
+  int drop_copy;        // failure injection of the tests: the producer leaves out the copies of the second k-block it handles
 };
 
 template <int BN, int STAGES>
@@ -68,7 +70,8 @@ gemm_tile128_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       mbar_init(accfull0 + 8 * a, 1);
       mbar_init(accempty0 + 8 * a, 4);
     }
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = g.wait_ms;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -88,7 +91,7 @@ gemm_tile128_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int stage = 0;
+      int stage = 0, issued = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
@@ -102,8 +105,13 @@ gemm_tile128_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint32_t a_dst = tiles0 + stage * Plan::kStageBytes;
           const uint32_t fb = full0 + 8 * stage;
           mbar_expect_tx(fb, Plan::kStageBytes);
-          tma_load_2d(a_dst, &map_x, fb, kb * kBK, m_blk * kBM);
-          tma_load_2d(a_dst + Plan::kABytes, &map_w, fb, kb * kBK, n_blk * BN);
+          if (g.drop_copy && issued++ == 1) {
+            // tests only (ojb_gemm_test_drop_copy): the bytes announced for this stage never arrive, the consumer's bounded
+            // wait on its barrier runs out, the CTA reports OJB_DEV_WAIT_TIMEOUT and leaves in order
+          } else {
+            tma_load_2d(a_dst, &map_x, fb, kb * kBK, m_blk * kBM);
+            tma_load_2d(a_dst + Plan::kABytes, &map_w, fb, kb * kBK, n_blk * BN);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -176,9 +184,9 @@ gemm_tile128_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 float o[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                  const float gv = round_bf(__uint_as_float(gr[j + e]));
-                  const float uv = round_bf(__uint_as_float(ur[j + e]));
-                  o[e] = round_bf(silu_f(gv)) * uv;
+                  const float gv = __uint_as_float(gr[j + e]);
+                  const float uv = __uint_as_float(ur[j + e]);
+                  o[e] = silu_f(gv) * uv;
                 }
                 *reinterpret_cast<uint4*>(orow + c * 32 + j) = pack8(o);
               }
@@ -263,19 +271,17 @@ template <int BN, int STAGES, int EPI>
 int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int splits, int64_t ldo,
                 int32_t* status, cudaStream_t stream) {
   using Plan = SmemPlan<BN, STAGES>;
-  static bool attr_set = false;
+  static int smem_set[kMaxDevices] = {};
   auto kern = gemm_tile128_kernel<BN, STAGES, EPI>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::kTotal) != cudaSuccess)
-      return OJB_ERR_LAUNCH;
-    attr_set = true;
-  }
+  if (!raise_smem_limit(kern, static_cast<int>(Plan::kTotal), smem_set)) return OJB_ERR_LAUNCH;
   CUtensorMap map_x, map_w;
   int rc = make_map(&map_x, x, M, K, kBM);
   if (rc != OJB_OK) return rc;
   rc = make_map(&map_w, w, N, K, BN);
   if (rc != OJB_OK) return rc;
   GemmArgs g{};
+  g.wait_ms = gemm_wait_limit_ms();
+  g.drop_copy = gemm_drop_copy();
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);

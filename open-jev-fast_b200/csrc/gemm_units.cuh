@@ -2,6 +2,16 @@
 // per unit): block units of 256 rows of x times BN rows of w, swapped-operand tail units of 256 rows of w times up to 256
 // rows of x, optional K ranges, and the order in which the units are dealt out.
 #pragma once
+// Probe builds (-DOJB_GEMM_PROBES, never the shipped library) can repeat the MMAs of a stage, cap the pipeline depth and
+// skip parts of the epilogue to separate tensor-pipe, copy and store costs; in the shipped build these read as constants
+// and the code behind them is compiled out.
+#ifdef OJB_GEMM_PROBES
+#define OJB_PROBE_REPEAT(g) ((g).mma_repeat)
+#define OJB_PROBE_DBG(g) ((g).dbg)
+#else
+#define OJB_PROBE_REPEAT(g) 1
+#define OJB_PROBE_DBG(g) 0
+#endif
 #include "gemm_common.cuh"
 
 namespace ojb {
@@ -25,12 +35,13 @@ struct GemmArgs {
   int64_t ldo;           // leading dimension of out in elements
   int64_t split_stride;  // elements between split planes (fp32 partials)
   int32_t* status;
+  int wait_ms;                 // limit of every mbarrier wait of the kernel, milliseconds
   unsigned long long* trace;   // null, or [0] = record counter followed by records of 4 words (see ojb_gemm_set_trace)
   int trace_cap;
   int tail_sub;                // bytes of a tail sub-stage (128 rows of w + the x rows), 0 = one k-block per stage
   int tma_out;                 // the block epilogue stores through shared-memory tiles and bulk tensor stores
-  int dbg;                     // measurement only: 100 = the block epilogue skips its global stores, 101 = its TMEM loads
-  int mma_repeat;              // 1; > 1 only for measurements: every stage's MMAs are issued this many times
+  int dbg;                     // probe builds only (see below); 0 otherwise
+  int mma_repeat;              // probe builds only; 1 otherwise
   // CTA-pair kernel, swapped-operand units: the tail_box accumulator columns (= rows of x) of a unit are produced by
   // n_chunk MMAs per k-step of chunk_w columns each (the last one narrower), so one pass over 256 rows of w serves up to
   // 512 rows of x; w_split64: the 128 rows of w of a CTA are fetched as rows [64r, 64r+64) and [128+64r, 128+64r+64) of the

@@ -93,6 +93,78 @@ add_rmsnorm_kernel(const bf16_t* __restrict__ x, const bf16_t* __restrict__ delt
   }
 }
 
+// Residual stream kept in fp32. One CTA per row: h = x_init (bf16, first norm of a forward) or h + delta, where delta is the
+// sum of SPLITS fp32 partial rows (SPLITS > 0) or one bf16 row or nothing; the sum is added in fp32 and h is never rounded.
+// hn = bf16(h * rstd * w1): the only rounding is the one the consuming GEMM needs for its operand.
+template <int SPLITS>
+__global__ void __launch_bounds__(kRowThreads)
+resnorm_f32_kernel(float* __restrict__ h, const bf16_t* __restrict__ x_init, const bf16_t* __restrict__ delta,
+                   const float* __restrict__ parts, int64_t part_stride, const float* __restrict__ w1,
+                   const int32_t* __restrict__ rowmask, bf16_t* __restrict__ hn_out, int H, float eps) {
+  pdl_begin();
+  __shared__ float red[kRowThreads / 32];
+  const int64_t row = blockIdx.x;
+  const int nvec = H >> 3;
+  float v[kRowVecs][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kRowVecs; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+      const int64_t off = row * H + static_cast<int64_t>(vi) * 8;
+      if (x_init != nullptr) {
+        unpack8(ldg_stream(x_init + off), v[i]);
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(h + off), b = *reinterpret_cast<const float4*>(h + off + 4);
+        v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+        v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+      }
+      if constexpr (SPLITS > 0) {
+        float d[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d[e] = 0.f;
+#pragma unroll
+        for (int s = 0; s < SPLITS; ++s) {
+          const float* pp = parts + s * part_stride + off;
+          const uint4 a = ldg_stream(pp), b = ldg_stream(pp + 4);
+          d[0] += __uint_as_float(a.x); d[1] += __uint_as_float(a.y); d[2] += __uint_as_float(a.z); d[3] += __uint_as_float(a.w);
+          d[4] += __uint_as_float(b.x); d[5] += __uint_as_float(b.y); d[6] += __uint_as_float(b.z); d[7] += __uint_as_float(b.w);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[e];
+      } else if (delta != nullptr) {
+        float d[8];
+        unpack8(ldg_stream(delta + off), d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[e];
+      }
+      if (x_init != nullptr || SPLITS > 0 || delta != nullptr) {
+        *reinterpret_cast<float4*>(h + off) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+        *reinterpret_cast<float4*>(h + off + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+    }
+  }
+  ss = block_sum_256(ss, red);
+  const float rstd = rsqrtf(ss / static_cast<float>(H) + eps);
+  const bool keep = rowmask ? (rowmask[row] != 0) : true;
+#pragma unroll
+  for (int i = 0; i < kRowVecs; ++i) {
+    const int vi = threadIdx.x + i * kRowThreads;
+    if (vi < nvec) {
+      const int col = vi * 8;
+      const float4 wa = __ldg(reinterpret_cast<const float4*>(w1 + col));
+      const float4 wb = __ldg(reinterpret_cast<const float4*>(w1 + col + 4));
+      const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = keep ? (v[i][e] * rstd) * w[e] : 0.f;
+      *reinterpret_cast<uint4*>(hn_out + row * H + col) = pack8(o);
+    }
+  }
+}
+
 __global__ void act_tables_kernel(bf16_t* __restrict__ silu_tab, float* __restrict__ sig_tab) {
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= 65536u) return;
@@ -285,12 +357,31 @@ quantize_rows_e4m3_kernel(const bf16_t* __restrict__ x, uint8_t* __restrict__ q,
   }
 }
 
+// One thread per slice: a bulk prefetch into L2, nothing is held or waited for.
+__global__ void l2_prefetch_kernel(const uint8_t* __restrict__ base, int64_t nbytes, int chunk) {
+  const int64_t off = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * chunk;
+  if (off >= nbytes) return;
+  const uint32_t sz = static_cast<uint32_t>(nbytes - off < chunk ? nbytes - off : chunk);
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
+}
+
 }  // namespace
 }  // namespace ojb
 
 using namespace ojb;
 
-extern "C" int ojb_abi_version(void) { return 2; }
+extern "C" int ojb_l2_prefetch(const void* data, int64_t nbytes, int64_t chunk, ojb_stream_t stream) {
+  OJB_REQUIRE(data && nbytes >= 0 && chunk >= 16 && chunk % 16 == 0 && chunk <= (1 << 20));
+  OJB_REQUIRE((reinterpret_cast<uintptr_t>(data) & 15u) == 0);
+  nbytes &= ~static_cast<int64_t>(15);
+  if (nbytes == 0) return OJB_OK;
+  const int64_t n = ceil_div(nbytes, chunk);
+  l2_prefetch_kernel<<<static_cast<unsigned>(ceil_div(n, 128)), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(data), nbytes, static_cast<int>(chunk));
+  return launch_status(cudaGetLastError());
+}
+
+extern "C" int ojb_abi_version(void) { return 3; }
 
 extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
                                void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream) {
@@ -322,6 +413,30 @@ extern "C" int ojb_add_rmsnorm_sk(const void* x, const float* parts, int splits,
     OJB_SK(9) OJB_SK(10) OJB_SK(11) OJB_SK(12) OJB_SK(13) OJB_SK(14) OJB_SK(15) OJB_SK(16)
   }
 #undef OJB_SK
+  return launch_status(cudaGetLastError());
+}
+
+extern "C" int ojb_resnorm_f32(float* h, const void* x_init, const void* delta, const float* parts, int splits,
+                               const float* w1, const int32_t* rowmask, void* hn_out, int64_t rows, int64_t H, float eps,
+                               ojb_stream_t stream) {
+  if (rows == 0) return OJB_OK;
+  OJB_REQUIRE(h && w1 && hn_out && rows > 0 && H > 0 && H % 8 == 0 && splits >= 0 && splits <= 16);
+  OJB_REQUIRE((splits == 0) == (parts == nullptr));
+  OJB_REQUIRE(!(parts && delta) && !(x_init && (parts || delta)));
+  if (H > kRowThreads * kRowVecs * 8) return OJB_ERR_LIMIT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t ps = rows * H;
+#define OJB_RN(S)                                                                                                      \
+  case S:                                                                                                              \
+    launch_kernel(resnorm_f32_kernel<S>, dim3(static_cast<unsigned>(rows)), dim3(kRowThreads), 0, st, h,               \
+                  static_cast<const bf16_t*>(x_init), static_cast<const bf16_t*>(delta), parts, ps, w1, rowmask,        \
+                  static_cast<bf16_t*>(hn_out), static_cast<int>(H), eps);                                             \
+    break;
+  switch (splits) {
+    OJB_RN(0) OJB_RN(1) OJB_RN(2) OJB_RN(3) OJB_RN(4) OJB_RN(5) OJB_RN(6) OJB_RN(7) OJB_RN(8)
+    OJB_RN(9) OJB_RN(10) OJB_RN(11) OJB_RN(12) OJB_RN(13) OJB_RN(14) OJB_RN(15) OJB_RN(16)
+  }
+#undef OJB_RN
   return launch_status(cudaGetLastError());
 }
 

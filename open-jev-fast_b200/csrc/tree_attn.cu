@@ -293,12 +293,8 @@ int launch_attn(const void* qt, const void* kt, const void* vt, const void* gate
   const size_t smem = (GQ * kRows * kLd + 2 * kSplit * 2 * kKeys * kLd) * 2 + kRows * NW * 4 + (NW + 1) * 4;
   if (smem > 227 * 1024) return OJB_ERR_LIMIT;
   auto kern = tree_attn_kernel<D, kSplit>;
-  static size_t smem_set = 0;
-  if (smem > smem_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-      return OJB_ERR_LAUNCH;
-    smem_set = smem;
-  }
+  static int smem_set[kMaxDevices] = {};
+  if (!raise_smem_limit(kern, static_cast<int>(smem), smem_set)) return OJB_ERR_LAUNCH;
   const int G = static_cast<int>(HQ / HKV);
   dim3 grid(static_cast<unsigned>(HKV * (G / GQ)), static_cast<unsigned>(N / kRows));
   launch_kernel(kern, dim3(grid), dim3(static_cast<unsigned>(GQ * kSplit * 32)), smem, st, static_cast<const bf16_t*>(qt), static_cast<const bf16_t*>(kt),

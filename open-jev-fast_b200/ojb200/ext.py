@@ -56,6 +56,21 @@ def add_rmsnorm_sk(x, parts, w1, rowmask, eps):
 add_rmsnorm_sk2 = add_rmsnorm_sk
 
 
+def resnorm_f32(h, x_init, delta, parts, w1, rowmask, eps):
+    """Residual add + RMSNorm on an fp32 residual stream (ojb_resnorm_f32): h fp32 [N, H] is updated in place with
+    x_init (bf16 rows that start the stream), the sum of the fp32 partial planes `parts` [S, N, H] or a bf16 `delta`
+    (at most one of the three), and the bf16 norm output hn is returned. Same place in the forward as the reference's
+    add_rmsnorm / add_rmsnorm_sk2 (src/fastmodel.py:196-203), without their bf16 roundings of the stream."""
+    _chk(h, x_init, delta, parts, w1, rowmask)
+    N, H = h.shape
+    if h.dtype != torch.float32 or (parts is not None and (parts.dtype != torch.float32 or tuple(parts.shape[1:]) != (N, H))):
+        raise RuntimeError("resnorm_f32: h must be fp32 [N, H] and parts fp32 [S, N, H]")
+    hn = torch.empty(N, H, dtype=bf16, device=h.device)
+    call("ojb_resnorm_f32", ptr(h), ptr(x_init), ptr(delta), ptr(parts), i32(0 if parts is None else parts.shape[0]), ptr(w1),
+         ptr(rowmask), ptr(hn), i64(N), i64(H), f32(eps), stream_ptr())
+    return hn
+
+
 def act_tables(like):
     """src/ext.py:23 — [silu_tab bf16[65536], sig_tab f32[65536]] on like's device."""
     silu_tab = torch.empty(65536, dtype=bf16, device=like.device)
@@ -151,7 +166,7 @@ fullattn_prep = fullattn_prep2   # src/ext.py:10 — same contract
 
 
 # ------------------------------------------------------------------------------------------------ Gated DeltaNet
-def _prep(proj, hist, rep_ptr, rep_pos, n_out, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+def _prep(proj, hist, rep_ptr, rep_pos, n_out, convw, A_log, dt_bias, KD, VD, HV, HK, HD, l2norm=True):
     _chk(proj, hist, rep_ptr, rep_pos, convw, A_log, dt_bias)
     if HD != 128 or HK * HD != KD or HV * HD != VD or convw.shape[1] != 4:
         raise RuntimeError("linattn_prep: head dim must be 128 and the conv width 4")
@@ -170,7 +185,7 @@ def _prep(proj, hist, rep_ptr, rep_pos, n_out, convw, A_log, dt_bias, KD, VD, HV
     beta = torch.empty(n_out, HV, dtype=bf16, device=dev)
     call("ojb_gdn_prep", ptr(proj), ptr(hist), ptr(rep_ptr), ptr(rep_pos), i64(0 if rep_pos is None else rep_pos.numel()),
          ptr(convw), ptr(A_log), ptr(dt_bias), ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), i64(N), i64(KD), i64(VD),
-         i64(HV), i64(HK), stream_ptr())
+         i64(HV), i64(HK), i32(1 if l2norm else 0), stream_ptr())
     return q, k, v, g, beta
 
 
@@ -193,6 +208,145 @@ def linattn_prep_dedup2(proj, hist, rep_ptr, rep_pos, L2, convw, A_log, dt_bias,
     if rep_qk:
         q, k = _expand(q, HK, HV, HD), _expand(k, HK, HV, HD)
     return [q, k, v, g, beta]
+
+
+# ---- the reference's older prep variants (src/ext.py:8,12,16-21,45): same arithmetic, other row layouts. Each is the one prep
+# kernel above with the history table (and, where the output is replicated, the slot tables) of its layout; the tables are
+# small integer arrays built on the host and cached per layout.
+_hist_cache = {}
+
+
+def _np():
+    import numpy as np
+    return np
+
+
+def _dev_i32(a, device):
+    return torch.as_tensor(_np().ascontiguousarray(a, dtype=_np().int32)).to(device)
+
+
+def _hist_seq(B, T, device):
+    """hist for B sequences of T rows laid back to back: row b*T+t sees rows t-3..t of its own sequence."""
+    key = ("seq", B, T, str(device))
+    if key not in _hist_cache:
+        np = _np()
+        t = np.arange(B * T) % T
+        h = np.arange(B * T)[:, None] - 3 + np.arange(4)[None, :]
+        h = np.where(t[:, None] - 3 + np.arange(4)[None, :] >= 0, h, -1)
+        _hist_cache[key] = _dev_i32(np.concatenate([h, np.full((1, 4), -1)]), device)
+    return _hist_cache[key]
+
+
+def _hist_tree1(Lp, S, Ls, device):
+    """hist for [prefix (Lp) | S suffix blocks of Ls rows]: a suffix row continues the prefix."""
+    key = ("tree1", Lp, S, Ls, str(device))
+    if key not in _hist_cache:
+        np = _np()
+        N = Lp + S * Ls
+        h = np.full((N + 1, 4), -1, np.int64)
+        for n in range(N):
+            if n < Lp:
+                path = list(range(max(0, n - 3), n + 1))
+            else:
+                s, t = divmod(n - Lp, Ls)
+                path = (list(range(max(0, Lp - 3), Lp)) + list(range(Lp + s * Ls, n + 1)))[-4:]
+            h[n, 4 - len(path):] = path
+        _hist_cache[key] = _dev_i32(h, device)
+    return _hist_cache[key]
+
+
+def _slots_from_src(src_np, N):
+    """CSR (rep_ptr [N+2], rep_pos [S*L2]) of the slots that hold each packed row; group N = pad slots; plus hist from src."""
+    np = _np()
+    S, L2 = src_np.shape
+    flat = src_np.reshape(-1)
+    order = np.argsort(np.where(flat >= 0, flat, N), kind="stable")
+    counts = np.bincount(np.where(flat >= 0, flat, N), minlength=N + 1)
+    rep_ptr = np.concatenate([[0], np.cumsum(counts)])
+    hist = np.full((N + 1, 4), -1, np.int64)
+    for s in range(S):
+        row = src_np[s]
+        for t in range(L2):
+            n = row[t]
+            if n >= 0 and hist[n, 3] < 0:
+                path = row[max(0, t - 3): t + 1]
+                hist[n, 4 - len(path):] = path
+    return rep_ptr, order, hist
+
+
+def linattn_prep(proj, convw, A_log, dt_bias, T, KD, VD, HV, HK, HD):
+    """src/ext.py:8 — rows are sequences of T tokens back to back; q and k are NOT normalised (the caller's attention kernel
+    does it) and are expanded to the value heads: [q [N, HV*HD], k [N, HV*HD], v [N, VD], g f32 [N, HV], beta [N, HV]]."""
+    N = proj.shape[0]
+    q, k, v, g, beta = _prep(proj, _hist_seq(N // T, T, proj.device), None, None, N, convw, A_log, dt_bias, KD, VD, HV, HK, HD, False)
+    return [_expand(q, HK, HV, HD), _expand(k, HK, HV, HD), v, g, beta]
+
+
+def linattn_prep2(proj, convw, A_log, dt_bias, B, T, KD, VD, HV, HK, HD, do_l2):
+    """src/ext.py:12 — as linattn_prep for a [B, T] batch, with the L2 norm of q and k optional (what the reference's
+    non-tree forward calls, src/fastmodel.py:223)."""
+    N = proj.shape[0]
+    q, k, v, g, beta = _prep(proj, _hist_seq(B, T, proj.device), None, None, N, convw, A_log, dt_bias, KD, VD, HV, HK, HD, bool(do_l2))
+    return [_expand(q, HK, HV, HD), _expand(k, HK, HV, HD), v, g, beta]
+
+
+def linattn_prep_tree(proj, convw, A_log, dt_bias, Lp, S, Ls, KD, VD, HV, HK, HD):
+    """src/ext.py:45 — single-level tree [prefix | S suffixes], one output row per packed row, q / k on the value heads."""
+    N = proj.shape[0]
+    if N != Lp + S * Ls:
+        raise RuntimeError("linattn_prep_tree: proj must have Lp + S*Ls rows")
+    q, k, v, g, beta = _prep(proj, _hist_tree1(Lp, S, Ls, proj.device), None, None, N, convw, A_log, dt_bias, KD, VD, HV, HK, HD)
+    return [_expand(q, HK, HV, HD), _expand(k, HK, HV, HD), v, g, beta]
+
+
+def linattn_prep_rep(proj, convw, A_log, dt_bias, Lp, S, Ls, KD, VD, HV, HK, HD):
+    """src/ext.py:16 — as linattn_prep_tree, written in replicated form: S sequences of Lp + Ls rows (the prefix in front of
+    every suffix), q / k on the value heads."""
+    N = proj.shape[0]
+    if N != Lp + S * Ls:
+        raise RuntimeError("linattn_prep_rep: proj must have Lp + S*Ls rows")
+    key = ("rep", Lp, S, Ls, str(proj.device))
+    if key not in _hist_cache:
+        np = _np()
+        L2 = Lp + Ls
+        src = np.concatenate([np.tile(np.arange(Lp), (S, 1)), Lp + np.arange(S * Ls).reshape(S, Ls)], 1)
+        rep_ptr, rep_pos, _ = _slots_from_src(src, N)
+        _hist_cache[key] = (_dev_i32(rep_ptr, proj.device), _dev_i32(rep_pos, proj.device))
+    rep_ptr, rep_pos = _hist_cache[key]
+    q, k, v, g, beta = _prep(proj, _hist_tree1(Lp, S, Ls, proj.device), rep_ptr, rep_pos, S * (Lp + Ls), convw, A_log, dt_bias,
+                             KD, VD, HV, HK, HD)
+    return [_expand(q, HK, HV, HD), _expand(k, HK, HV, HD), v, g, beta]
+
+
+def _prep_src(proj, src, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+    if src.dim() != 2 or src.dtype != torch.int32:
+        raise RuntimeError("linattn_prep_map: src must be int32 [S, L2]")
+    N = proj.shape[0]
+    rep_ptr, rep_pos, hist = _slots_from_src(src.detach().cpu().numpy(), N)      # host round trip: not a graph-capturable path
+    dev = proj.device
+    return _prep(proj, _dev_i32(hist, dev), _dev_i32(rep_ptr, dev), _dev_i32(rep_pos, dev), src.numel(), convw, A_log, dt_bias,
+                 KD, VD, HV, HK, HD)
+
+
+def linattn_prep_map(proj, src, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+    """src/ext.py:18 — slot (s, t) holds packed row src[s, t] (-1: pad slot, zeros); q / k on the value heads."""
+    q, k, v, g, beta = _prep_src(proj, src, convw, A_log, dt_bias, KD, VD, HV, HK, HD)
+    return [_expand(q, HK, HV, HD), _expand(k, HK, HV, HD), v, g, beta]
+
+
+def linattn_prep_map2(proj, src, convw, A_log, dt_bias, KD, VD, HV, HK, HD, tch):
+    """src/ext.py:20 — as linattn_prep_map with q / k on the key heads (grouped value attention); tch (tokens per thread in
+    the reference's schedule) has no meaning here."""
+    return list(_prep_src(proj, src, convw, A_log, dt_bias, KD, VD, HV, HK, HD))
+
+
+def linattn_prep_dedup(proj, src, rep_ptr, rep_pos, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
+    """src/ext.py:21 — as linattn_prep_dedup2 with the history taken from src [S, L2] instead of a hist table."""
+    N = proj.shape[0]
+    if rep_ptr.numel() != N + 2 or rep_pos.numel() != src.numel():
+        raise RuntimeError("linattn_prep_dedup: rep_ptr must have N+2 entries and rep_pos S*L2")
+    hist = _slots_from_src(src.detach().cpu().numpy(), N)[2]
+    return list(_prep(proj, _dev_i32(hist, proj.device), rep_ptr, rep_pos, rep_pos.numel(), convw, A_log, dt_bias, KD, VD, HV, HK, HD))
 
 
 def linattn_prep_dedup3(proj, hist, rep_ptr, rep_pos, L2, convw, A_log, dt_bias, KD, VD, HV, HK, HD):
@@ -271,6 +425,34 @@ def gdn_fused6(q, k, v, g, beta, scale):
 gdn_fused = gdn_fused2 = gdn_fused3 = gdn_fused4 = gdn_fused8 = gdn_fused9 = gdn_fused6   # src/ext.py:30-33,41-42
 
 
+def gdn_fused5(q, k, v, g, beta, scale, proj, zoff, normw, sig, canon, rowmask, neps):
+    """src/ext.py:44 — gdn_fused6 followed by the gated RMSNorm, written per packed row: [N, HV*128]; packed row n reads the
+    Gated DeltaNet output at its canonical slot (canon[slot] = n), rows with rowmask 0 are zero. Two launches plus the index
+    arithmetic here; the reference fuses them into one kernel and rejected that form as slower."""
+    B, T, HV, HD = v.shape
+    N = proj.shape[0]
+    if canon.numel() != B * T or rowmask.numel() != N:
+        raise RuntimeError("gdn_fused5: canon must have B*T entries and rowmask N")
+    o = gdn_fused6(q, k, v, g, beta, scale)
+    c = canon.reshape(-1).long()
+    ok = c >= 0
+    inv = torch.zeros(N, dtype=torch.int32, device=proj.device)
+    inv[c[ok]] = torch.arange(B * T, device=proj.device, dtype=torch.int32)[ok]
+    y = _gated_norm(o.view(B * T, HV, HD), inv, proj, normw, HV, HD, zoff, neps)
+    return y * (rowmask != 0).to(y.dtype)[:, None]
+
+
+gdn_fused7 = gdn_fused5   # src/ext.py:35 — same contract (the reference's persistent-CTA schedule of it)
+
+
+def gdn_fused6ts(q, k, v, g, beta, scale):
+    """src/ext.py:36 — the reference's instrumented build of gdn_fused6 returns int64 [B*HV, 16] clock stamps instead of the
+    output. The kernels here are instrumented through ojb_gdn_set_trace instead; this name runs the operator and returns
+    a zero tensor of the reference's shape."""
+    gdn_fused6(q, k, v, g, beta, scale)
+    return torch.zeros(v.shape[0] * v.shape[2], 16, dtype=torch.int64, device=v.device)
+
+
 def gdn_tree(q, k, v, g, beta, scale, lay, final_state=None):
     """Tree-native pass over packed rows: q, k [N, HK*128], v [N, HV*128] from linattn_prep_rows; the chunk / walk tables
     come from the layout (lay.chunks, lay.steps, lay.meta). Shared nodes are computed once. Returns o [N, HV, 128]; rows
@@ -281,6 +463,19 @@ def gdn_tree(q, k, v, g, beta, scale, lay, final_state=None):
     out = torch.zeros(N, HV, 128, dtype=bf16, device=v.device)
     return gdn_chunked(q.view(N, HK, 128), k.view(N, HK, 128), v.view(N, HV, 128), g, beta, scale, lay.chunks, lay.steps,
                        lay.meta[6:8], 1, None, final_state, out)
+
+
+def gated_rmsnorm_map(x, proj, w, HV, HD, zoff, eps, Lp, Ls):
+    """src/ext.py:17 — x is the Gated DeltaNet output in replicated form [S, Lp + Ls, HV, HD] (linattn_prep_rep); packed row n
+    of [prefix | S suffixes] reads slot (0, n) for a prefix row and (s, Lp + t) for row t of suffix s."""
+    N = proj.shape[0]
+    key = ("gmap", N, Lp, Ls, str(proj.device))
+    if key not in _hist_cache:
+        np = _np()
+        n = np.arange(N)
+        s_, t_ = np.divmod(np.maximum(n - Lp, 0), max(Ls, 1))
+        _hist_cache[key] = _dev_i32(np.where(n < Lp, n, s_ * (Lp + Ls) + Lp + t_), proj.device)
+    return _gated_norm(x, _hist_cache[key], proj, w, HV, HD, zoff, eps)
 
 
 def _gated_norm(x, inv, proj, w, HV, HD, zoff, eps):
@@ -345,6 +540,20 @@ def fattn_tree2(proj, qw1, kw1, cosb, sinb, sig, vbits, HQ, HKV, scale, eps):
     qt, kt, vt, gate = fullattn_prep2(proj, qw1, kw1, cosb, sinb, 1, N, HQ, HKV, D, eps)
     G = HQ // HKV
     return _tree_attn(qt, kt, vt, gate, vbits, None, scale, 3 if G % 3 == 0 else 1)
+
+
+def fattn_tree2_ts(proj, qw1, kw1, cosb, sinb, sig, vbits, HQ, HKV, scale, eps):
+    """src/ext.py:38 (instrumented fattn_tree2) — int64 [CTAs, 16] clock stamps in the reference; here the operator runs and a
+    zero tensor of that shape (CTAs of the reference's grid: HKV * (HQ/HKV/3) * N/16) is returned."""
+    fattn_tree2(proj, qw1, kw1, cosb, sinb, sig, vbits, HQ, HKV, scale, eps)
+    return torch.zeros(HKV * max(HQ // HKV // 3, 1) * (proj.shape[0] // 16), 16, dtype=torch.int64, device=proj.device)
+
+
+def l2_prefetch(t, chunk):
+    """src/ext.py:26 — bulk L2 prefetch of a contiguous CUDA tensor in slices of `chunk` bytes (a multiple of 16)."""
+    if not (t.is_cuda and t.is_contiguous()) or chunk % 16:
+        raise RuntimeError("l2_prefetch: contiguous CUDA tensor and chunk % 16 == 0 required")
+    call("ojb_l2_prefetch", ptr(t), i64(t.numel() * t.element_size()), i64(min(int(chunk), 1 << 20)), stream_ptr())
 
 
 # ------------------------------------------------------------------------------------------------ scoring head

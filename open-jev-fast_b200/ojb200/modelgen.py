@@ -31,8 +31,8 @@ SMALL = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=8, num_at
 
 
 def make_config(**over):
-    """Qwen3_5TextConfig with full attention on every 4th layer; `over` overrides FULL (the 27B-scale dimensions of
-    BASELINE.json: hidden 5120, MLP 17408, 64 layers, 24/4 attention heads of 256, GDN 16 key / 32 value heads of 128)."""
+    """Qwen3_5TextConfig with full attention on every 4th layer; `over` overrides FULL (the 27B-scale dimensions the
+    benchmark is quoted on: hidden 5120, MLP 17408, 64 layers, 24/4 attention heads of 256, GDN 16 key / 32 value heads of 128)."""
     from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
     d = dict(FULL)
     d.update(over)

@@ -234,20 +234,26 @@ class Scorer:
             self.graphs.move_to_end(key)
         return ent, captured
 
-    def score_tokens(self, seqs, groups):
-        """Candidate token lists + question index per candidate -> fp32 [S, A] scores on the GPU (not synchronised)."""
+    def score_tokens(self, seqs, groups, with_info=False):
+        """Candidate token lists + question index per candidate -> fp32 [S, A] scores on the GPU (not synchronised; a copy
+        owned by the caller). with_info=True also returns this call's record (key, rows, build time, ...), which under
+        concurrent callers is not necessarily `self.last`."""
         t0 = time.perf_counter()
         # the kernels read key ranges, not the N x N/32 visibility words: those are neither built nor uploaded
         dims, b64, b32, e32 = _layout.gtree_host(seqs, groups, self.pad_id, NB, PB, pin=True, vbits=False)
         t1 = time.perf_counter()
         with self.lock, torch.cuda.device(self.device):
             ent, captured = self.entry_for(dims, (b64, b32, e32))
-            out = ent.run((b64, b32, e32))
-        self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=ent.lay.key, rows=dims["Nreal"],
-                         h2d_bytes=b64.numel() * 8 + dims["n32_used"] * 4 + e32.numel() * 4, launches=ent.launches)
+            # the graph writes into one static buffer per key: take a private copy before the lock is released, or a second
+            # thread with the same key could overwrite it before this caller has read it (src/server.py:129 clones, too)
+            out = ent.run((b64, b32, e32)).clone()
+            info = self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=ent.lay.key, rows=dims["Nreal"],
+                                    h2d_bytes=b64.numel() * 8 + dims["n32_used"] * 4 + e32.numel() * 4, launches=ent.launches)
+        if with_info:
+            return out, info
         return out
 
-    def score_state(self, seqs):
+    def score_state(self, seqs, with_info=False):
         """The reference's route for one question over a long shared context (src/server.py:100-115): the common prefix of
         the candidates is cut off (left-padded to a bucket), the rest of each candidate is one suffix row block. Returns
         fp32 [S, A] (GPU, not synchronised). The general tree route (score_tokens) serves the same requests; this one keeps
@@ -279,9 +285,11 @@ class Scorer:
                     self.graphs.popitem(last=False)
             else:
                 self.graphs.move_to_end(key)
-            out = ent.run(pre, suf, msk, pad)
-        self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=key, rows=Lp + sum(len(q) - Lp for q in seqs),
-                         h2d_bytes=0, launches=ent.launches)
+            out = ent.run(pre, suf, msk, pad).clone()
+            info = self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=key,
+                                    rows=Lp + sum(len(q) - Lp for q in seqs), h2d_bytes=0, launches=ent.launches)
+        if with_info:
+            return out, info
         return out
 
     def score_packed(self, requests):
@@ -302,9 +310,9 @@ class Scorer:
                     self.graphs.popitem(last=False)
             else:
                 self.graphs.move_to_end(key)
-            out = ent.run(host)
-        self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=key, rows=lay.N,
-                         h2d_bytes=sum(v.numel() * v.element_size() for v in host.values()), launches=ent.launches)
+            out = ent.run(host).clone()
+            self.last = dict(build_ms=(t1 - t0) * 1e3, captured=captured, key=key, rows=lay.N,
+                             h2d_bytes=sum(v.numel() * v.element_size() for v in host.values()), launches=ent.launches)
         return list(out.split(lay.counts))
 
     def forward(self, records):
@@ -322,16 +330,19 @@ class Scorer:
             while Lp < mn - 1 and all(q[Lp] == seqs[0][Lp] for q in seqs):
                 Lp += 1
         if STATE_PATH and len(records) == 1 and (len(seqs) - 1) * Lp > REP_MAX:        # src/server.py:102
-            scores = self.score_state(seqs).cpu()
+            scores, info = self.score_state(seqs, with_info=True)
         else:
-            scores = self.score_tokens(seqs, groups).cpu()      # device-to-host read = the synchronisation point
+            scores, info = self.score_tokens(seqs, groups, with_info=True)
+        scores = scores.cpu()                                   # device-to-host read = the synchronisation point
         _lib.check_status(self.device)
         t1 = time.perf_counter()
-        self.nreq += 1
+        with self.lock:
+            self.nreq += 1
+            nreq = self.nreq
         if self.log:
-            rec = dict(ts=time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), req=self.nreq, path="state" if self.last["key"][0] == "state" else "tree2", gpu=self.device.index,
-                       questions=len(records), candidates=len(seqs), tokens=sum(map(len, seqs)), rows=self.last["rows"],
-                       key=self.last["key"], captured=int(self.last["captured"]), build_ms=round(self.last["build_ms"], 3),
+            rec = dict(ts=time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), req=nreq, path="state" if info["key"][0] == "state" else "tree2", gpu=self.device.index,
+                       questions=len(records), candidates=len(seqs), tokens=sum(map(len, seqs)), rows=info["rows"],
+                       key=info["key"], captured=int(info["captured"]), build_ms=round(info["build_ms"], 3),
                        ms=round((t1 - t0) * 1e3, 3))
             self.log.write(json.dumps(rec) + "\n")
         out, off = [], 0

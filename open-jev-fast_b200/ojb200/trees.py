@@ -1,7 +1,7 @@
 """Seeded synthetic request trees used by the parity tests, the golden-vector generator and the benchmark.
 
 Token ids are uniform random integers; only the shape of a request (how many questions and candidates, how long the shared
-root, the question stems and the candidate tails are) follows the workloads named in BASELINE.json. No benchmark text.
+root, the question stems and the candidate tails are) follows the workloads the benchmark is quoted on. No benchmark text.
 """
 import numpy as np
 
@@ -29,7 +29,7 @@ def make_tree(seed, root_len, q_lens, leaf_lens, groups, vocab=4096):
 
 
 def baseline_tree(seed=0, vocab=4096):
-    """BASELINE.json config 3/4: 420-token root, 3 question nodes of about 25 tokens, 7 leaves of 4-12 tokens = 539 rows."""
+    """The benchmark tree: 420-token root, 3 question nodes of about 25 tokens, 7 leaves of 4-12 tokens = 539 rows."""
     rng = np.random.default_rng(1000 + seed)
     q_lens = [24, 25, 26]
     groups = [0, 0, 0, 1, 2, 2, 2]

@@ -6,8 +6,9 @@
 
 Nothing of the reference is copied: its `src/kernels.cu` and the prototype string of its `src/ext.py` are read where they
 lie and handed to torch's inline-extension builder, exactly as `src/ext.py:47-56` does, except for the target architecture
-(`compute_100a` instead of `compute_103`). The only output is `oracle/_ref/ojref/ojref.so` (git-ignored). Tests load that file
-when it exists and skip otherwise; the product never touches it.
+(`compute_100a` instead of `compute_103`). Its Python forward (`src/fastmodel.py`, unmodified) is byte-compiled where it lies.
+The only outputs are `oracle/_ref/ojref/ojref.so` and `oracle/_ref/ojref/fastmodel.pyc` (git-ignored, built artefacts). Tests
+and the benchmark's reference legs load them when they exist and skip otherwise; the product never touches them.
 """
 import importlib.util
 import os
@@ -22,12 +23,29 @@ def default_ref_root():
     return os.environ.get("OJ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
+def build_forward(ref_root=None):
+    """Byte-compiles the reference's src/fastmodel.py (FastQwen35 with gtree_build / forward_gtree) into
+    oracle/_ref/ojref/fastmodel.pyc. Returns the path, or None when the reference tree is not around."""
+    import py_compile
+    ref_root = ref_root or default_ref_root()
+    src = os.path.join(ref_root, "src", "fastmodel.py")
+    if not os.path.exists(src):
+        return None
+    out = os.path.join(OUT, "fastmodel.pyc")
+    if os.path.exists(out) and os.path.getmtime(out) >= os.path.getmtime(src):
+        return out
+    os.makedirs(OUT, exist_ok=True)
+    py_compile.compile(src, cfile=out, dfile="open-jev-fast/src/fastmodel.py", doraise=True)
+    return out
+
+
 def build(ref_root=None, verbose=False):
     ref_root = ref_root or default_ref_root()
     src_dir = os.path.join(ref_root, "src")
     cu = os.path.join(src_dir, "kernels.cu")
     if not os.path.exists(cu):
         return None
+    build_forward(ref_root)
     so = os.path.join(OUT, "ojref.so")
     if os.path.exists(so) and os.path.getmtime(so) >= max(os.path.getmtime(cu), os.path.getmtime(os.path.join(src_dir, "ext.py"))):
         return so
@@ -43,8 +61,8 @@ def build(ref_root=None, verbose=False):
     load_inline(name="ojref", cpp_sources=[protos], cuda_sources=[open(cu).read()], functions=names,
                 extra_cuda_cflags=["-O3", "-gencode=arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr", "-lineinfo"],
                 build_directory=OUT, verbose=verbose, is_python_module=True)
-    for f in os.listdir(OUT):                         # keep the module only: the builder's scratch holds a copy of the sources
-        if f != "ojref.so":
+    for f in os.listdir(OUT):                         # keep the built files only: the builder's scratch holds a copy of the sources
+        if f not in ("ojref.so", "fastmodel.pyc"):
             os.remove(os.path.join(OUT, f))
     return so if os.path.exists(so) else None
 
@@ -58,6 +76,63 @@ def load():
     spec = importlib.util.spec_from_file_location("ojref", so)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
+    return mod
+
+
+def load_fastmodel():
+    """The reference's `fastmodel` module (FastQwen35, gdn_split, ...) from the byte-compiled file, bound to the rebuilt
+    operators: the module does `from ext import load; K = load()` at import (src/fastmodel.py:42-43), which is answered here
+    with the sm_100a build; its cuBLASLt search (`lt_ext`) is not built, so it uses F.linear / torch.bmm, its own fallback
+    (src/fastmodel.py:65-69). Returns None when either built file is missing."""
+    import importlib.machinery
+    import sys
+    import types
+    pyc = os.path.join(OUT, "fastmodel.pyc")
+    K = load()
+    if K is None or not os.path.exists(pyc):
+        return None
+    if "oj_ref_fastmodel" in sys.modules:
+        return sys.modules["oj_ref_fastmodel"]
+    try:                                              # the module imports FLA's Triton entry points although its default path
+        import fla.ops.gated_delta_rule  # noqa: F401   (GDN_FUSED) never calls them; stand-ins keep the import alive without FLA
+        from fla.ops.gated_delta_rule.chunk_fwd import chunk_gated_delta_rule_fwd_kkt_solve_kernel  # noqa: F401
+        from fla.ops.gated_delta_rule.wy_fast import recompute_w_u_fwd  # noqa: F401
+        from fla.ops.common.chunk_delta_h import chunk_gated_delta_rule_fwd_h  # noqa: F401
+        from fla.ops.common.chunk_o import chunk_fwd_o  # noqa: F401
+        from fla.ops.utils import chunk_local_cumsum  # noqa: F401
+        from fla.ops.utils.constant import RCP_LN2  # noqa: F401
+    except Exception:
+        def _absent(*a, **k):
+            raise RuntimeError("flash-linear-attention is not installed: only the reference's fused GDN path is available")
+        names = {"fla": [], "fla.ops": [], "fla.ops.gated_delta_rule": ["chunk_gated_delta_rule"],
+                 "fla.ops.utils": ["chunk_local_cumsum"], "fla.ops.utils.constant": [],
+                 "fla.ops.gated_delta_rule.chunk_fwd": ["chunk_gated_delta_rule_fwd_intra", "chunk_gated_delta_rule_fwd_kkt_solve_kernel"],
+                 "fla.ops.common": [], "fla.ops.common.chunk_delta_h": ["chunk_gated_delta_rule_fwd_h"],
+                 "fla.ops.common.chunk_o": ["chunk_fwd_o"], "fla.ops.gated_delta_rule.wy_fast": ["recompute_w_u_fwd"]}
+        for mname, attrs in names.items():
+            m = types.ModuleType(mname)
+            m.__path__ = []
+            for a in attrs:
+                setattr(m, a, _absent)
+            sys.modules[mname] = m
+        sys.modules["fla.ops.utils.constant"].RCP_LN2 = 1.4426950408889634
+    shim = types.ModuleType("ext")
+    shim.load = lambda verbose=False: K
+    saved = {n: sys.modules.get(n) for n in ("ext", "lt_ext")}
+    sys.modules["ext"] = shim
+    sys.modules.pop("lt_ext", None)
+    try:
+        loader = importlib.machinery.SourcelessFileLoader("oj_ref_fastmodel", pyc)
+        spec = importlib.util.spec_from_loader("oj_ref_fastmodel", loader)
+        mod = importlib.util.module_from_spec(spec)
+        loader.exec_module(mod)
+    finally:
+        for n, m in saved.items():
+            if m is None:
+                sys.modules.pop(n, None)
+            else:
+                sys.modules[n] = m
+    sys.modules["oj_ref_fastmodel"] = mod
     return mod
 
 

@@ -43,7 +43,7 @@ def scores(hidden, head_w, head_b=None):
 
 @torch.no_grad()
 def gdn_layer(layer, x, output_final_state=False):
-    """One Qwen3_5GatedDeltaNet module on x [1, T, H] -> [1, T, H] (BASELINE.json config 1)."""
+    """One Qwen3_5GatedDeltaNet module on x [1, T, H] -> [1, T, H]."""
     return layer(hidden_states=x)
 
 

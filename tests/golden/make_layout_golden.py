@@ -4,7 +4,7 @@ Run in a container that mounts open-jev-fast ($OJ_REFERENCE, else the directory 
     python tests/golden/make_layout_golden.py
 The two functions are lifted out of src/fastmodel.py by AST (the module itself cannot be imported without a GPU because it
 builds its CUDA extension at import) and executed unmodified with dev="cpu". The inputs are the seeded synthetic trees of
-tests/trees.py; only integers are stored.
+open-jev-fast_b200/ojb200/trees.py; only integers are stored.
 """
 import ast
 import os
@@ -15,8 +15,8 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.dirname(HERE))
-import trees  # noqa: E402
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(HERE)), "open-jev-fast_b200"))
+from ojb200 import trees  # noqa: E402
 
 REF = os.environ.get("OJ_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
 

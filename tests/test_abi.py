@@ -58,3 +58,19 @@ def test_gemm_plan_is_host_arithmetic():
     # more rows never make the modelled time shorter
     t = [lt_ext.gemm_plan(M, 34816, 5120, 1)[2] for M in (256, 512, 1024, 2048, 4096)]
     assert all(a <= b for a, b in zip(t, t[1:]))
+
+
+def test_operator_surface_has_every_name_of_the_reference():
+    """The 40 operator names of open-jev-fast's src/ext.py:52 and the 8 of src/lt_ext.py:7 exist in the Python layer (legacy
+    variants alias the production kernels under their own layout contract)."""
+    from ojb200 import ext, lt_ext
+    ops = ["add_rmsnorm", "silu_mul", "linattn_prep", "gated_rmsnorm", "fullattn_prep", "gate_mul", "linattn_prep2", "fullattn_prep2",
+           "gate_mul2", "linattn_prep_tree", "add_rmsnorm_sk", "linattn_prep_rep", "gated_rmsnorm_map", "linattn_prep_map",
+           "gated_rmsnorm_inv", "linattn_prep_map2", "linattn_prep_dedup", "linattn_prep_dedup2", "act_tables", "silu_mul_lut",
+           "gated_rmsnorm_inv2", "l2_prefetch", "linattn_prep_dedup3", "gate_mul3", "add_rmsnorm_sk2", "gdn_fused", "gdn_fused2",
+           "gdn_fused3", "gdn_fused4", "gdn_fused5", "gdn_fused6", "gdn_fused7", "gdn_fused6ts", "fattn_tree", "fattn_tree2",
+           "fattn_tree2_ts", "fattn_tree3", "pack_bits", "gdn_fused8", "gdn_fused9"]
+    assert len(ops) == 40
+    assert not [n for n in ops if not callable(getattr(ext, n, None))]
+    lt = ["lt_setup", "lt_matmul", "lt2_plan", "lt2_search", "lt2_info", "lt2_run", "lt2_raw", "lt2_add_raw"]
+    assert not [n for n in lt if not callable(getattr(lt_ext, n, None))]

@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-import trees
+from ojb200 import trees
 
 
 def _worker(rank, world, port, out):

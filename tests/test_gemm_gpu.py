@@ -1,4 +1,4 @@
-"""tcgen05 GEMM against torch.matmul on fp32-upcast operands (the check BASELINE's GEMM sweep names)."""
+"""tcgen05 GEMM against torch.matmul on fp32-upcast operands."""
 import pytest
 import torch
 
@@ -177,3 +177,62 @@ def test_gemm_e4m3_swiglu(M, I, K):
     assert out.shape == (M, I)
     err = (out.float() - ref).abs().max().item()
     assert err <= ref.abs().max().item() * 2 ** -6 + 1e-3, err
+
+
+# the four projection shapes of the model at the ends of the row-count sweep (64 and 4096 rows), library's own choice of kernel
+@pytest.mark.parametrize("M", [64, 4096])
+@pytest.mark.parametrize("K,N", [(5120, 12288), (5120, 34816), (17408, 5120), (6144, 5120)])
+def test_gemm_projection_shapes_at_64_and_4096_rows(M, K, N):
+    from ojb200 import lt_ext, _lib
+    x, w = _mk(M, N, K, 7)
+    out = lt_ext.lt_matmul(x, w, 0)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _close(out, _ref(x, w))
+    if N == 34816:                                  # the fused SwiGLU form of the gate/up shape
+        I = N // 2
+        wb = lt_ext.interleave_gate_up(w[:I].contiguous(), w[I:].contiguous())
+        got = lt_ext.gemm_swiglu(x, wb, 0)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        r = _ref(x, w)
+        ref = torch.nn.functional.silu(r[:, :I]) * r[:, I:]
+        assert (got.float() - ref).abs().max().item() <= ref.abs().max().item() * 2 ** -7 + 1e-3
+    if N == 5120:                                   # the split-K form of the two output projections
+        S = lt_ext.plan_splitk(M, N, K)
+        parts = lt_ext.gemm_splitk(x, w, S, 0)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        r = _ref(x, w)
+        assert (parts.sum(0) - r).abs().max().item() <= r.abs().max().item() * 2 ** -12 + 1e-4
+
+
+def test_bounded_wait_runs_out_and_reports_through_the_status_word():
+    """Every device-side wait of the GEMM kernels has a limit. With the limit set to 50 ms and the host-side failure switch
+    on, the producer of a one-CTA GEMM leaves out the copies of its second k-block: the consumer's wait runs out, the kernel
+    writes OJB_DEV_WAIT_TIMEOUT, frees its tensor memory and returns; the host sees the status, and the next launch on the
+    same context is correct. Nothing faults or spins without a limit."""
+    import ctypes
+    from ojb200 import lt_ext, _lib
+    lib = _lib.lib()
+    x, w = _mk(128, 256, 128, 11)                   # one 128 x 256 tile, two k-blocks
+    good = lt_ext.lt_matmul(x, w, 1)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    try:
+        assert lib.ojb_gemm_set_wait_limit_ms(ctypes.c_int32(50)) == 0
+        assert lib.ojb_gemm_test_drop_copy(ctypes.c_int32(1)) == 0
+        t0 = __import__("time").perf_counter()
+        lt_ext.lt_matmul(x, w, 1)
+        torch.cuda.synchronize()
+        dt = __import__("time").perf_counter() - t0
+    finally:
+        lib.ojb_gemm_test_drop_copy(ctypes.c_int32(0))
+        lib.ojb_gemm_set_wait_limit_ms(ctypes.c_int32(0))
+    assert dt < 1.5, dt                             # gave up after the 50 ms limit, not after the default 2 s
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        _lib.check_status()
+    again = lt_ext.lt_matmul(x, w, 1)               # the context is intact
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(again, good)

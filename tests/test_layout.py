@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-import trees
+from ojb200 import trees
 from oracle import layout as OL
 
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "layout_golden.npz"))

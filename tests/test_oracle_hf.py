@@ -3,7 +3,7 @@
 import pytest
 import torch
 
-import trees
+from ojb200 import trees
 from oracle import gdn as OG
 from oracle import hf_path as OH
 from oracle import layout as OL
@@ -68,3 +68,24 @@ def test_packed_tree_forward_is_exact_in_fp32():
     got = hn[torch.as_tensor(lay["lastidx"])].float()
     ref = OH.candidate_hidden(core, seqs)
     assert ((got - ref).norm() / ref.norm()).item() < 1e-4
+
+
+@pytest.mark.parametrize("mode,upcast", [("fp32", True), ("bf16", False)])
+def test_streamed_oracle_equals_whole_model_forward(mode, upcast):
+    """oracle/hf_stream.py applies the Hugging Face decoder layers one at a time (the 64-layer model of the benchmark cannot be
+    held a second time in fp32); on a model that fits, it must reproduce the whole-model forward of oracle/hf_path.py."""
+    from ojb200 import modelgen as MG
+    from oracle import hf_stream as OS
+    cfg = MG.make_config(**MG.SMALL)
+    core = MG.build_core(cfg, device="cpu", seed=3, std=0.05, draw_on="cpu")
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()["doc"]
+    ref = OH.candidate_hidden(OH.prepare(core, upcast=upcast), seqs)
+    got = OS.candidate_hidden(core, seqs, mode=mode)
+    assert ((got - ref).norm() / ref.norm()).item() < (1e-6 if upcast else 1e-9)
+    # the operand-rounding floor sits between the fp32 run and the bf16 run
+    if upcast:
+        low = OS.candidate_hidden(core, seqs, mode="operands")
+        b16 = OH.candidate_hidden(OH.prepare(core, upcast=False), seqs)
+        e_low = ((low - ref).norm() / ref.norm()).item()
+        e_b16 = ((b16 - ref).norm() / ref.norm()).item()
+        assert 0 < e_low < e_b16, (e_low, e_b16)

@@ -8,7 +8,7 @@ import os
 import pytest
 import torch
 
-import trees
+from ojb200 import trees
 
 pytestmark = pytest.mark.gpu
 bf16 = torch.bfloat16

@@ -3,7 +3,7 @@ convention, LRU eviction, and the scoring head against the oracle."""
 import pytest
 import torch
 
-import trees
+from ojb200 import trees
 from oracle import hf_path as OH
 
 pytestmark = pytest.mark.gpu
@@ -36,6 +36,33 @@ def test_graph_replay_equals_eager_and_is_shared_by_key():
     assert len(sc.graphs) == 1                              # three different trees, one key, one graph
     assert not torch.equal(outs[0], outs[1])
     assert sc.last["launches"] > 0
+
+
+def test_concurrent_callers_with_one_key_get_their_own_scores():
+    """Two threads push different trees of the same key through one Scorer: the graph's output buffer is shared, so each
+    caller must leave with a private copy taken under the lock (src/server.py:97,129 serialises and clones the same way)."""
+    import threading
+    cfg, fast, sc, W, b = _scorer()
+    reqs = [_tree(seed, cfg.vocab_size) for seed in (1, 2, 3, 4)]
+    want = [sc.score_tokens(*r).clone() for r in reqs]
+    torch.cuda.synchronize()
+    assert len(sc.graphs) == 1
+    got = [[None] * 40 for _ in reqs]
+    start = threading.Barrier(len(reqs))
+
+    def client(i):
+        start.wait()
+        for j in range(40):
+            got[i][j] = sc.forward([{"kind": "choice", "candidates": reqs[i][0][:2]},
+                                    {"kind": "choice", "candidates": reqs[i][0][2:]}])
+    ths = [threading.Thread(target=client, args=(i,)) for i in range(len(reqs))]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    for i in range(len(reqs)):
+        for j in range(40):
+            assert torch.equal(torch.cat(got[i][j]), want[i].cpu()), (i, j)
 
 
 def test_forward_records_noul_and_lru():

@@ -30,7 +30,8 @@ def test_static_scratch_entry_point_matches_allocating_one():
     lib.ojb_gdn_static_max_items.restype = ctypes.c_int64
     assert lib.ojb_gdn_static_max_items() == 1024
     HK, HV, scale = 2, 4, 128 ** -0.5
-    for call_no, (B, T) in enumerate([(3, 150), (2, 96)]):          # two calls in a row, different shapes and data
+    # two calls in a row with different shapes and data, then one that fills the array exactly (256 chunks x 4 heads = 1024)
+    for call_no, (B, T) in enumerate([(3, 150), (2, 96), (1, 256 * 64)]):
         chunks, steps, walks = K._seq_tables(B, T, torch.device("cuda"))
         q, k, v, g, beta = _inputs(B * T, HK, HV, 40 + call_no)
         want = K.gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walks, B)
