@@ -1,20 +1,22 @@
-"""Length / width sweep of the full model on the GPUs of one node, data parallel.
+"""Length / width sweep of the full model: one stream of mixed-shape requests through the router onto 1 .. 8 GPUs of a node.
 
-    python bench_sweep.py --requests 64                         # one GPU
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        bench_sweep.py --requests 256
+    python bench_sweep.py --gpus 1 --requests 256
+    python bench_sweep.py --gpus 8 --requests 256
 
 Requests are seeded synthetic trees: shared prefix length log-uniform in [256, 16384], 1-3 questions with stems of 4-40
-tokens, 2-12 candidate leaves of 2-40 tokens. Request i is served by rank i % world (no collective on the data path). Every
-request goes through Scorer.score_tokens (host layout build, pinned H2D, graph replay, D2H of the scores); graphs are
-captured per (N, S, L2) bucket on first use and that cost is reported separately from the per-request latency, which is
-taken on a second pass over the same requests. Prints one JSON line on rank 0: p50 / p95 ms per request and aggregate
-requests per second.
+tokens, 2-12 candidate leaves of 2-40 tokens. One host process: ojb200.router.Router in front of one ojb200.server.Scorer per
+GPU (full weights, own graph cache, own stream), shortest queue by outstanding tokens; nothing is exchanged between GPUs.
+Every request goes through Scorer.score_tokens (host layout build, pinned H2D, graph lookup or capture, replay, D2H of the
+scores). The stream is served twice: the first pass captures one graph per (N, S, L2) key where a GPU meets the key for the
+first time (reported as capture cost), the second pass is the steady state. One JSON line: service time per request (p50 /
+p95 / mean, host clock around the worker's call), sojourn time with queueing, aggregate requests per second, host layout
+time, graphs captured and requests served per GPU.
 """
 import argparse
 import json
 import os
 import sys
+import threading
 import time
 
 import numpy as np
@@ -49,67 +51,78 @@ def make_requests(n, seed, vocab, max_prefix):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--max-prefix", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=64, help="debugging only")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--tune", action="store_true", help="time the GEMM candidates per new row count (FastQwen35.tune) instead of "
+                    "using the library's cost model: better kernels below 1024 rows, a much longer capture pass")
     args = ap.parse_args()
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
-from ojb200 import _lib, fastmodel as FM, modelgen as MG, server as SV
+    from ojb200 import _lib, fastmodel as FM, modelgen as MG, router as RT, server as SV
+    if not args.tune:
+        FM.FastQwen35.TUNE_MAX_ROWS = 0
     kw = dict(MG.FULL)
     kw["num_hidden_layers"] = args.layers
     cfg = MG.make_config(**kw)
-    fast = FM.FastQwen35(MG.build_core(cfg, device=dev, seed=0), free_original=True)
-    W, b = MG.make_head(cfg.hidden_size, A=1, seed=1, device=dev)
-    scorer = SV.Scorer(fast, W, b, pad_id=0, device=dev, max_graphs=4096)
-    reqs = make_requests(args.requests, args.seed, cfg.vocab_size, args.max_prefix)
-    mine = SV.shard_requests(len(reqs), rank, world)
+    n_gpu = min(args.gpus, torch.cuda.device_count())
+    scorers = [None] * n_gpu
+
+    def build(i):
+        dev = torch.device("cuda", i)
+        with torch.cuda.device(dev):
+            fast = FM.FastQwen35(MG.build_core(cfg, device=dev, seed=0), free_original=True)
+            W, b = MG.make_head(cfg.hidden_size, A=1, seed=1, device=dev)
+            scorers[i] = SV.Scorer(fast, W, b, pad_id=0, device=dev, max_graphs=4096)
 
     t0 = time.perf_counter()
-    for i in mine:                                   # first pass: captures one graph per bucket
-        scorer.score_tokens(*reqs[i]).cpu()
-    capture_s = time.perf_counter() - t0
-    _lib.check_status(dev)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    lat, rows = [], []
-    t0 = time.perf_counter()
-    for i in mine:                                   # second pass: steady state
-        t = time.perf_counter()
-        scorer.score_tokens(*reqs[i]).cpu()
-        lat.append((time.perf_counter() - t) * 1e3)
-        rows.append(scorer.last["rows"])
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    _lib.check_status(dev)
-    stats = torch.tensor([wall, capture_s, float(len(mine))], dtype=torch.float64, device=dev)
-    all_lat = torch.tensor(lat, dtype=torch.float64, device=dev)
-    if world > 1:
-        gathered = [torch.zeros(2 * (len(reqs) // world + 1), dtype=torch.float64, device=dev) for _ in range(world)]
-        pad = torch.full((2 * (len(reqs) // world + 1),), -1.0, dtype=torch.float64, device=dev)
-        pad[:len(lat)] = all_lat
-        dist.all_gather(gathered, pad)
-        all_lat = torch.cat([g[g >= 0] for g in gathered])
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        wall, capture_s = float(mx[0]), float(mx[1])
-    if rank == 0:
-        l = np.sort(all_lat.cpu().numpy())
-        print(json.dumps({"sweep": "prefix 256..%d log-uniform, 1-3 questions, 2-12 leaves of 2-40 tokens" % args.max_prefix,
-                          "requests": len(reqs), "n_gpus": world, "layers": args.layers,
-                          "p50_ms": float(l[len(l) // 2]), "p95_ms": float(l[int(len(l) * 0.95)]), "mean_ms": float(l.mean()),
-                          "requests_per_s": len(reqs) / wall, "rows_min_max": [int(min(rows)), int(max(rows))],
-                          "graphs_captured_rank0": len(scorer.graphs), "capture_pass_s": capture_s}), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    ths = [threading.Thread(target=build, args=(i,)) for i in range(n_gpu)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    build_s = time.perf_counter() - t0
+    assert all(s is not None for s in scorers), "a model failed to build"
+
+    def serve(i):
+        sc = scorers[i]
+
+        def fn(req):
+            t = time.perf_counter()
+            out, info = sc.score_tokens(req[0], req[1], with_info=True)
+            out = out.cpu()                                  # the synchronisation point of this request
+            _lib.check_status(sc.device)
+            return dict(scores=out, ms=(time.perf_counter() - t) * 1e3, gpu=i, rows=info["rows"], build_ms=info["build_ms"],
+                        captured=info["captured"])
+        return fn
+
+    reqs = make_requests(args.requests, args.seed, cfg.vocab_size, args.max_prefix)
+    router = RT.Router([serve(i) for i in range(n_gpu)])
+    try:
+        t0 = time.perf_counter()
+        first = router.map(reqs)                             # pass 1: graphs captured where a GPU meets a key for the first time
+        capture_s = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        futs = [router.submit(r) for r in reqs]
+        second = [f.result() for f in futs]
+        wall = time.perf_counter() - t0
+    finally:
+        router.close()
+    lat = np.sort(np.array([r["ms"] for r in second]))
+    rows = np.array([r["rows"] for r in second])
+    same = all(torch.equal(a["scores"], b["scores"]) for a, b in zip(first, second) if a["gpu"] == b["gpu"])
+    st = router.stats()
+    print(json.dumps({"sweep": "prefix 256..%d log-uniform, 1-3 questions, 2-12 leaves of 2-40 tokens" % args.max_prefix,
+                      "requests": len(reqs), "n_gpus": n_gpu, "layers": args.layers, "tuned": bool(args.tune),
+                      "p50_ms": float(lat[len(lat) // 2]), "p95_ms": float(lat[int(len(lat) * 0.95)]), "mean_ms": float(lat.mean()),
+                      "requests_per_s": len(reqs) / wall, "steady_pass_s": wall, "capture_pass_s": capture_s,
+                      "model_build_s": build_s, "graphs_captured": int(sum(r["captured"] for r in first)),
+                      "recaptured_in_steady_pass": int(sum(r["captured"] for r in second)),
+                      "host_layout_ms_mean": float(np.mean([r["build_ms"] for r in second])),
+                      "host_layout_ms_max": float(np.max([r["build_ms"] for r in second])),
+                      "rows_min": int(rows.min()), "rows_median": int(np.median(rows)), "rows_max": int(rows.max()),
+                      "served_per_gpu": st["served"], "replay_equals_first_pass": bool(same)}), flush=True)
 
 
 if __name__ == "__main__":

@@ -42,7 +42,8 @@ int ojb_abi_version(void);
  * kernel with all rows of x in swapped-operand units (M <= 2048); a multiple of 16 in [16, 256] = that kernel with this
  * w-tile width; 5 = CTA-pair kernel (tcgen05.mma.cta_group::2) with automatic width; 6 = CTA-pair kernel with all rows of
  * x in swapped-operand units (any M: one pass over w per 512 rows of x, up to 512 accumulator columns per unit);
- * 512 + a multiple of 16 in [16, 256] = the pair kernel with that width.
+ * 512 + a multiple of 16 in [16, 256] = the pair kernel with that width; 7 = the block kernel with all but the last full
+ * 256-row block of x in block units and the remaining 257..511 rows in two swapped-operand chunks that fit them exactly.
  * ------------------------------------------------------------------------------------------------------------------ */
 int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, int variant,
                   int32_t* status, ojb_stream_t stream);
@@ -56,7 +57,7 @@ int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M, int64_t N,
  * rows swapped (variant 6) it reads the layout above. */
 int ojb_gemm_bf16_swiglu(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K,
                          int32_t* status, ojb_stream_t stream);
-/* The same with the kernel variant forced (0, 1, 3, 4, 5 or 6 as for ojb_gemm_bf16); for tuning. */
+/* The same with the kernel variant forced (0, 1, 3, 4, 5, 6 or 7 as for ojb_gemm_bf16); for tuning. */
 int ojb_gemm_bf16_swiglu_v(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K, int variant,
                            int32_t* status, ojb_stream_t stream);
 

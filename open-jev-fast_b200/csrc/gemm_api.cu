@@ -19,9 +19,10 @@ namespace {
 // block256 with that w-tile width; 3 = block256 with automatic width; 4 = block256 with every row of x in swapped-operand
 // units (M <= 2048).
 // 5 = pair256 (CTA pairs, cta_group::2) with automatic width; 6 = pair256 with every row of x in swapped-operand units
-// (any M); 512 + a multiple of 16 in [16, 256] = pair256 with that w-tile width.
+// (any M); 512 + a multiple of 16 in [16, 256] = pair256 with that w-tile width; 7 = block256 with the last 257..511 rows of x in
+// two swapped-operand chunks and the rows before them in block units.
 bool variant_ok(int v) {
-  return (v >= 0 && v <= 6) || (v >= 16 && v <= 256 && v % 16 == 0) || (v >= 528 && v <= 768 && v % 16 == 0);
+  return (v >= 0 && v <= 7) || (v >= 16 && v <= 256 && v % 16 == 0) || (v >= 528 && v <= 768 && v % 16 == 0);
 }
 
 // Modelled SM clocks of the 128-row tile kernel: per k-block a CTA fills (128 + BN) rows and its MMAs read them once,
@@ -76,7 +77,7 @@ int dispatch(int epi, int variant, const void* x, const void* w, void* out, int6
     return gemm_pair256_launch(epi, variant == 5 ? 0 : (variant == 6 ? -1 : variant - 512), x, w, out, M, N, K, splits, ldo, status, st);
   if (variant == 1 || variant == 2)
     return gemm_tile128_launch(epi, variant == 1 ? 256 : 128, x, w, out, M, N, K, splits, ldo, status, st);
-  return gemm_block256_launch(epi, variant == 3 ? 0 : (variant == 4 ? -1 : variant), x, w, out, M, N, K, splits, ldo, status, st);
+  return gemm_block256_launch(epi, variant == 3 ? 0 : (variant == 4 ? -1 : (variant == 7 ? -2 : variant)), x, w, out, M, N, K, splits, ldo, status, st);
 }
 
 }  // namespace
@@ -91,7 +92,7 @@ extern "C" int ojb_gemm_bf16(const void* x, const void* w, void* out, int64_t M,
 extern "C" int ojb_gemm_bf16_swiglu_v(const void* x, const void* w_blk, void* out, int64_t M, int64_t N, int64_t K, int variant,
                                       int32_t* status, ojb_stream_t stream) {
   OJB_REQUIRE(x && w_blk && out && M > 0 && N > 0 && K > 0 && K % 8 == 0 && N % 256 == 0);
-  OJB_REQUIRE(aligned16(x) && aligned16(w_blk) && aligned16(out) && (variant == 0 || variant == 1 || variant == 3 || variant == 4 || variant == 5 || variant == 6));
+  OJB_REQUIRE(aligned16(x) && aligned16(w_blk) && aligned16(out) && (variant == 0 || variant == 1 || variant == 3 || variant == 4 || variant == 5 || variant == 6 || variant == 7));
   return dispatch(kEpiSwiglu, variant, x, w_blk, out, M, N, K, 1, N / 2, status, static_cast<cudaStream_t>(stream));
 }
 

@@ -616,9 +616,13 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.M = static_cast<int>(M);
   g.N = static_cast<int>(N);
   g.K = static_cast<int>(K);
-  // bn_req < 0: every row of x goes through swapped-operand units (M <= 2048: chunks of <= 256 rows); otherwise full
-  // 256-row blocks plus a swapped tail of <= 128 rows (a longer remainder is cheaper as one more zero-padded block)
-  const bool all_swapped = bn_req < 0 || M <= kBM;
+  // bn_req == -1: every row of x goes through swapped-operand units (M <= 2048: chunks of <= 256 rows); bn_req == -2: all
+  // but the last full 256-row block go through block units and the remaining 257..511 rows through two swapped-operand
+  // chunks that fit them exactly (544 rows = one block + 2 x 144: no MMA runs at the 64-clock floor of a short tail);
+  // otherwise full 256-row blocks plus a swapped tail of <= 128 rows (a longer remainder is cheaper as one more zero-padded
+  // block)
+  const bool hybrid = bn_req == -2 && M > kBlockM;
+  const bool all_swapped = (bn_req < 0 && !hybrid) || M <= kBM;
   if (bn_req < 0) bn_req = 0;
   if (all_swapped) {
     if (M > 2048) return OJB_ERR_LIMIT;
@@ -626,6 +630,11 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
     g.tail_rows = static_cast<int>(M);
     g.n_xchunk = static_cast<int>(ceil_div(M, 256));
     g.tail_box = static_cast<int>(ceil_div(ceil_div(M, g.n_xchunk), 16) * 16);
+  } else if (hybrid) {
+    g.n_xblk = static_cast<int>(M / kBlockM) - 1;
+    g.tail_rows = static_cast<int>(M - static_cast<int64_t>(g.n_xblk) * kBlockM);      // 256 .. 511 rows
+    g.n_xchunk = static_cast<int>(ceil_div(g.tail_rows, 256));
+    g.tail_box = static_cast<int>(ceil_div(ceil_div(g.tail_rows, g.n_xchunk), 16) * 16);
   } else {
     g.n_xblk = static_cast<int>(M / kBlockM);
     int r = static_cast<int>(M % kBlockM);

@@ -67,6 +67,13 @@ class FastQwen35(torch.nn.Module):
         self.v2, self.fuse_l2 = v2, fuse_l2
         self._bufs = {}
         self._plan, self._tuned = {}, set()     # (op, M, N, K) -> kernel choice, filled by tune()
+        # OJ_GEMM_FORCE="gu=8,mm=8,res=8:2" pins the lt_matmul algorithm index (and K ranges) of a projection kind for every
+        # shape, like the reference's OJ_SK_* switches (src/fastmodel.py:45-64): for measurements
+        self._force = {}
+        for item in os.environ.get("OJ_GEMM_FORCE", "").split(","):
+            if "=" in item:
+                k, v = item.split("=")
+                self._force[k.strip()] = tuple(int(t) for t in v.split(":")) if ":" in v else int(v)
         w1 = lambda norm: (1.0 + norm.weight.float()).contiguous()
         self.in_w1 = [w1(L.input_layernorm) for L in core.layers]
         self.post_w1 = [w1(L.post_attention_layernorm) for L in core.layers]
@@ -121,7 +128,7 @@ class FastQwen35(torch.nn.Module):
         if q8 is not None:
             xq, sx = LT.quantize_rows_e4m3(x)
             return LT.gemm_e4m3(xq, sx, q8[0], q8[1], 0)
-        return LT.lt_matmul(x, w, self._plan.get(("mm", x.shape[0], w.shape[0], w.shape[1]), 0))
+        return LT.lt_matmul(x, w, self._force.get("mm", self._plan.get(("mm", x.shape[0], w.shape[0], w.shape[1]), 0)))
 
     @staticmethod
     def _split(W, S):
@@ -143,7 +150,7 @@ class FastQwen35(torch.nn.Module):
             S8 = S if S > 0 else LT.plan_splitk(M, w.shape[0], Kd // 2)      # a 128-byte k-block holds twice the elements
             return [h, K.resnorm_f32(h, None, None, LT.gemm_e4m3(yq, sy, q8[0], q8[1], 2, S8), w1, mask, self.eps)]
         if S == 0:
-            idx, S = self._plan.get(("res", M, w.shape[0], Kd), (0, 0))
+            idx, S = self._force.get("res", self._plan.get(("res", M, w.shape[0], Kd), (0, 0)))
             if S == 0:
                 S = LT.plan_splitk(M, w.shape[0], Kd)
         return [h, K.resnorm_f32(h, None, None, LT.gemm_splitk(y, w, S, idx), w1, mask, self.eps)]
@@ -154,10 +161,13 @@ class FastQwen35(torch.nn.Module):
             xq, sx = LT.quantize_rows_e4m3(hn)
             return LT.gemm_e4m3(xq, sx, q8[0], q8[1], 1)
         if d.fused_mlp:
-            return LT.gemm_swiglu(hn, d.w_gu_blk, self._plan.get(("gu", hn.shape[0]) + tuple(d.w_gu_blk.shape), 0))
+            return LT.gemm_swiglu(hn, d.w_gu_blk, self._force.get("gu", self._plan.get(("gu", hn.shape[0]) + tuple(d.w_gu_blk.shape), 0)))
         return K.silu_mul(self._mm(hn, d.w_gu_cat))
 
     TUNE_MAX_ROWS = int(os.environ.get("OJ_TUNE_MAX_ROWS", "1024"))
+    # OJ_TUNE_EXTRA="8,9": more lt_matmul algorithm indices for tune() to race (the CTA-pair kernels are not raced by default:
+    # in isolation they tie with the one-CTA kernels)
+    TUNE_EXTRA = [int(v) for v in os.environ.get("OJ_TUNE_EXTRA", "").split(",") if v.strip()]
 
     def tune(self, M, force=False, report=None):
         """Choose kernel variant (and K split) of every projection for M packed rows by timing (src/fastmodel.py:114-156
@@ -207,7 +217,7 @@ class FastQwen35(torch.nn.Module):
                     out.setdefault(tuple(w.shape), []).append(d)
             return out
 
-        kernels = [1, 3] + ([7] if M <= 2048 else [])
+        kernels = [1, 3] + ([7] if M <= 2048 else []) + ([10] if M > 256 and M % 256 else []) + self.TUNE_EXTRA
         for (N, Kd), layers in groups("w_in").items():
             x = rnd(M, Kd)
             res = race({i: (lambda d, i=i: LT.lt_matmul(x, d.w_in, i)) for i in kernels + [2]}, layers)

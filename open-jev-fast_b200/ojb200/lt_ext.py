@@ -4,7 +4,8 @@ The reference enumerates cuBLASLt algorithms per shape (lt_setup) and runs one b
 through lt2_*. Here an "algorithm" is one of the library's GEMM variants: index 0 lets the library choose, 1 / 2 force the
 128-row tile kernel with 256 / 128-wide tiles, 3 the 256-row block kernel with automatic w-tile width, 4..6 that kernel
 with w-tile width 256, 192, 128, 7 that kernel with all of x in swapped-operand units (M <= 2048), 8 / 9 the CTA-pair
-kernel (tcgen05.mma.cta_group::2) with automatic width / all of x in swapped-operand units.
+kernel (tcgen05.mma.cta_group::2) with automatic width / all of x in swapped-operand units, 10 the block kernel with
+block units for all but the last full block of x and two swapped-operand chunks for the remaining 257..511 rows.
 Two entry points have no counterpart in the reference: gemm_swiglu (SwiGLU fused into the epilogue) and gemm_splitk
 (fp32 partial sums from the un-split [N, K] weight).
 """
@@ -17,7 +18,7 @@ from . import _lib
 from ._lib import call, i32, i64, ptr, stream_ptr
 
 bf16 = torch.bfloat16
-VARIANT_BN = [0, 1, 2, 3, 256, 192, 128, 4, 5, 6]
+VARIANT_BN = [0, 1, 2, 3, 256, 192, 128, 4, 5, 6, 7]
 N_VARIANTS = len(VARIANT_BN)
 SM_COUNT = 148
 _plans = []          # lt2 plans: dicts

@@ -67,7 +67,9 @@ def token_records(records, tok, candidate_prompts):
 
 class Entry:
     """Static buffers + CUDA graph of `score_gtree` for one key (N, S, L2). The tree structure lives in the index tables,
-    so every request with the same key replays the same graph after three host-to-device copies."""
+    so every request with the same key replays the same graph after three host-to-device copies. Capture runs in
+    thread-local error mode: other threads of the process (the workers of other GPUs behind the router) may allocate and
+    launch on their own devices while this one captures."""
 
     def __init__(self, scorer, dims, host_bufs):
         fast = scorer.fast
@@ -91,7 +93,7 @@ class Entry:
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
             n0 = _lib.launch_count()
-            with torch.cuda.graph(self.g, pool=scorer.pool):
+            with torch.cuda.graph(self.g, pool=scorer.pool, capture_error_mode="thread_local"):
                 self.out = body()
             self.launches = _lib.launch_count() - n0
             torch.cuda.synchronize(dev)
@@ -145,7 +147,7 @@ class EntryState:
         n0 = _lib.launch_count()
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.g, pool=scorer.pool):
+            with torch.cuda.graph(self.g, pool=scorer.pool, capture_error_mode="thread_local"):
                 self.out = body()
             torch.cuda.synchronize(dev)
         else:
@@ -189,7 +191,7 @@ class PackedEntry:
         n0 = _lib.launch_count()
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.g, pool=scorer.pool):
+            with torch.cuda.graph(self.g, pool=scorer.pool, capture_error_mode="thread_local"):
                 self.out = body()
             torch.cuda.synchronize(dev)
         else:

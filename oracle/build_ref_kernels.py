@@ -7,7 +7,7 @@
 Nothing of the reference is copied: its `src/kernels.cu` and the prototype string of its `src/ext.py` are read where they
 lie and handed to torch's inline-extension builder, exactly as `src/ext.py:47-56` does, except for the target architecture
 (`compute_100a` instead of `compute_103`). Its Python forward (`src/fastmodel.py`, unmodified) is byte-compiled where it lies.
-The only outputs are `oracle/_ref/ojref/ojref.so` and `oracle/_ref/ojref/fastmodel.pyc` (git-ignored, built artefacts). Tests
+The only outputs are `oracle/_ref/ojref/ojref.so` and `oracle/_ref/ojref/fastmodel_bytecode.bin` (git-ignored, built artefacts). Tests
 and the benchmark's reference legs load them when they exist and skip otherwise; the product never touches them.
 """
 import importlib.util
@@ -25,13 +25,13 @@ def default_ref_root():
 
 def build_forward(ref_root=None):
     """Byte-compiles the reference's src/fastmodel.py (FastQwen35 with gtree_build / forward_gtree) into
-    oracle/_ref/ojref/fastmodel.pyc. Returns the path, or None when the reference tree is not around."""
+    oracle/_ref/ojref/fastmodel_bytecode.bin. Returns the path, or None when the reference tree is not around."""
     import py_compile
     ref_root = ref_root or default_ref_root()
     src = os.path.join(ref_root, "src", "fastmodel.py")
     if not os.path.exists(src):
         return None
-    out = os.path.join(OUT, "fastmodel.pyc")
+    out = os.path.join(OUT, "fastmodel_bytecode.bin")
     if os.path.exists(out) and os.path.getmtime(out) >= os.path.getmtime(src):
         return out
     os.makedirs(OUT, exist_ok=True)
@@ -62,7 +62,7 @@ def build(ref_root=None, verbose=False):
                 extra_cuda_cflags=["-O3", "-gencode=arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr", "-lineinfo"],
                 build_directory=OUT, verbose=verbose, is_python_module=True)
     for f in os.listdir(OUT):                         # keep the built files only: the builder's scratch holds a copy of the sources
-        if f not in ("ojref.so", "fastmodel.pyc"):
+        if f not in ("ojref.so", "fastmodel_bytecode.bin"):
             os.remove(os.path.join(OUT, f))
     return so if os.path.exists(so) else None
 
@@ -87,7 +87,7 @@ def load_fastmodel():
     import importlib.machinery
     import sys
     import types
-    pyc = os.path.join(OUT, "fastmodel.pyc")
+    pyc = os.path.join(OUT, "fastmodel_bytecode.bin")
     K = load()
     if K is None or not os.path.exists(pyc):
         return None

@@ -25,8 +25,8 @@ def _close(out, ref):
 
 
 # lt_matmul indices: 0 planner, 1 / 2 tile128, 3 block256, 4-6 block256 with forced width, 7 block256 all swapped,
-# 8 / 9 CTA-pair kernel (automatic width / all swapped)
-@pytest.mark.parametrize("variant", [0, 1, 3, 4, 5, 7, 8, 9])
+# 8 / 9 CTA-pair kernel (automatic width / all swapped), 10 block256 with blocks + two exact swapped chunks
+@pytest.mark.parametrize("variant", [0, 1, 3, 4, 5, 7, 8, 9, 10])
 @pytest.mark.parametrize("M,N,K", [(64, 512, 256), (16, 48, 64), (257, 300, 136), (400, 1000, 512), (1000, 520, 192), (128, 256, 64), (288, 1280, 5120), (539, 12352, 5120), (100, 200, 72),
                                    (1024, 5120, 6144), (544, 5120, 4096)])
 def test_gemm_plain(M, N, K, variant):
@@ -40,7 +40,7 @@ def test_gemm_plain(M, N, K, variant):
     _close(out, _ref(x, w))
 
 
-@pytest.mark.parametrize("variant", [0, 1, 3, 7, 8, 9])
+@pytest.mark.parametrize("variant", [0, 1, 3, 7, 8, 9, 10])
 @pytest.mark.parametrize("M,I,K", [(64, 128, 128), (288, 1024, 5120), (544, 17408, 5120), (256, 256, 320), (700, 384, 512), (539, 2048, 1024)])
 def test_gemm_swiglu(M, I, K, variant):
     from ojb200 import lt_ext, _lib
@@ -63,7 +63,7 @@ def test_gemm_swiglu(M, I, K, variant):
     assert err <= tol, (err, tol)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 3, 7, 8])
+@pytest.mark.parametrize("variant", [0, 1, 3, 7, 8, 10])
 @pytest.mark.parametrize("M,N,K,S", [(64, 256, 256, 2), (288, 5120, 6144, 2), (544, 5120, 17408, 4), (539, 5120, 4096, 2),
                                      (544, 5120, 17408, 7), (64, 5120, 4096, 16), (300, 520, 1000, 3)])
 def test_gemm_splitk(M, N, K, S, variant):
