@@ -187,7 +187,8 @@ int ojb_gtree_fill(const int64_t* tokens, const int64_t* seq_off, const int32_t*
  * rep_pos[rep_ptr[n] .. rep_ptr[n+1]) of every packed row n, pad slots zeroed; q, k, v, g, beta have n_slots rows) and its
  * unreplicated form (rep_ptr == null: one output row per packed row). proj bf16 [N, 2KD+2VD+2HV] = [q|k|v|z|b|a];
  * hist int32 [N+1, 4] = rows t-3..t on the row's own path (-1 = none); convw bf16 [2KD+VD, 4]; A_log, dt_bias bf16 [HV].
- * Head dim is 128: KD = 128*HK, VD = 128*HV. q, k bf16 [*, KD]; v bf16 [*, VD]; g fp32 [*, HV]; beta bf16 [*, HV].
+ * Head dim is 128: KD = 128*HK, VD = 128*HV; HV % 4 == 0 (rows of proj are read 16 bytes at a time, so the row length must be
+ * a multiple of 8 elements; OJB_ERR_ARG otherwise). q, k bf16 [*, KD]; v bf16 [*, VD]; g fp32 [*, HV]; beta bf16 [*, HV].
  * l2norm = 0 leaves q and k un-normalised (src/kernels.cu:96 linattn_prep and linattn_prep2 with do_l2 = false, whose callers
  * let the attention kernel normalise); every other prep variant of the reference normalises. The same entry point serves
  * the reference's older layouts (per-sequence [B, T], single-level tree, src-mapped slots): they differ only in `hist` and in
@@ -214,6 +215,18 @@ int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g,
                     int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr, int64_t n_walks,
                     const float* init_state, float* final_state, void* scratch, void* out, int64_t HK, int64_t HV,
                     float scale, ojb_stream_t stream);
+
+/* ojb_gdn_chunked with ojb_gdn_prep fused into its first launch (src/kernels.cu:1173 linattn_prep_dedup2 + :4225 gdn_fused6 in
+ * two launches instead of three): the state-independent pass reads the in-projection output itself — proj bf16
+ * [N, 2KD+2VD+2HV] = [q|k|v|z|b|a], hist int32 [N+1, 4], convw bf16 [2KD+VD, 4], A_log / dt_bias bf16 [HV] as for ojb_gdn_prep —
+ * and applies conv, SiLU, the L2 norm of q and k and the beta / log-decay formulas per (chunk, head) in shared memory, with
+ * the arithmetic of ojb_gdn_prep operation for operation (same bits). Every chunk must be a run of consecutive packed rows of
+ * one tree node (what ojb_gtree_fill produces): the rows before a chunk's first row are taken from hist[first row]. Tables,
+ * states, scratch and out as for ojb_gdn_chunked. KD = 128*HK, VD = 128*HV, HV % 4 == 0. */
+int ojb_gdn_chunked_proj(const void* proj, const int32_t* hist, const void* convw, const void* A_log, const void* dt_bias,
+                         const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
+                         int64_t n_walks, const float* init_state, float* final_state, void* scratch, void* out, int64_t KD,
+                         int64_t VD, int64_t HK, int64_t HV, float scale, ojb_stream_t stream);
 
 /* ojb_gdn_chunked with the state pass run level by level (1 + n_levels launches): `levels` is a HOST array of n_levels + 1
  * walk indices; the walks [levels[l], levels[l+1]) of level l run side by side and start from the end states that walks of
@@ -243,9 +256,10 @@ int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const fl
                            float scale, ojb_stream_t stream);
 
 /* Measurement hook of the state pass (no counterpart in the reference): `records` = null switches it off; otherwise a device
- * buffer of 12 uint64 words per walk step. The CTA of head 0 / column slice 0 / walk 0 stores %globaltimer at six points of
- * every step (step begin, operands ready, phase 1 done, v' visible, phase 2 done, step end), words 0-5 from its state-chain
- * warp and 6-11 from its output warp. Synchronises the device (it writes a device variable). */
+ * buffer of 4 + 12 uint64 words per walk step. The CTA of head 0 / column slice 0 / walk 0 stores %globaltimer at kernel entry,
+ * when its tables are staged and its first operands requested, and at its exit (words 0-2), then at six points of every step
+ * (step begin, operands ready, phase 1 done, v' visible, phase 2 done, step end), words 0-5 of the step's record from its
+ * state-chain warp and 6-11 from its output warp. Synchronises the device (it writes a device variable). */
 int ojb_gdn_set_trace(uint64_t* records);
 
 /* src/kernels.cu:1333-1374 gated_rmsnorm_inv2 (inv != null) and :143 gated_rmsnorm (inv == null).

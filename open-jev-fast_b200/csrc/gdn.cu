@@ -159,10 +159,25 @@ constexpr int kIntraSmem = 3 * kChunk * kLd * 2 + kChunk * kChunk * 4 + 3 * 256 
 static_assert(kChunk * kChunk * 4 <= kChunk * kLd * 2, "the fp32 inverse must fit over the Q tile");
 static_assert(2 * kChunk * kLdT * 2 <= kChunk * kChunk * 4 + 3 * 256 * 4, "the bf16 pair of T must fit over A and P");
 
+// Source of q, k, v, g, beta when the preparation (gdn_prep) is fused into this kernel: the in-projection output itself.
+struct PrepSrc {
+  const bf16_t* proj;      // [N, P] = [q(KD) | k(KD) | v(VD) | z(VD) | b(HV) | a(HV)]
+  const int4* hist;        // [N+1]: rows t-3, t-2, t-1, t on the row's own tree path (-1 = none)
+  const bf16_t* convw;     // [2KD+VD, 4]
+  const bf16_t* A_log;     // [HV]
+  const bf16_t* dt_bias;   // [HV]
+  int P;
+};
+
+// FUSED: q / k / v / g / beta are not read; the CTA loads the raw in-projection rows of its chunk (plus the three rows that
+// precede the chunk on its tree path), applies the causal conv, SiLU and the L2 norm of q and k in shared memory, and derives
+// beta and the log-decay from the b / a columns. The arithmetic is that of gdn_prep_kernel, operation for operation, so both
+// forms give the same bits; what is saved is a launch and the round trip of q, k, v through global memory.
+template <bool FUSED>
 __global__ void __launch_bounds__(kIntraThreads, 3)
 gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, const bf16_t* __restrict__ v,
                  const float* __restrict__ g, const bf16_t* __restrict__ beta, const int32_t* __restrict__ chunks,
-                 bf16_t* __restrict__ scratch, int HK, int HV, float scale, int pair) {
+                 bf16_t* __restrict__ scratch, int HK, int HV, float scale, int pair, PrepSrc ps) {
   pdl_begin();
   const int4 ch = reinterpret_cast<const int4*>(chunks)[blockIdx.x];
   const int row0 = ch.x, nrows = ch.y;
@@ -246,6 +261,7 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     }
   }
 
+  if constexpr (!FUSED) {
   // ---- load K, Q, V rows (zero rows past the end of the chunk)
   for (int i = tid; i < 3 * kChunk * (kHD / 8); i += kIntraThreads) {
     const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
@@ -259,16 +275,111 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     bf16_t* dst = which == 0 ? Ks : which == 1 ? Qs : Vs;
     *reinterpret_cast<uint4*>(dst + r * kLd + cv) = val;
   }
+  } else {
+  // ---- raw in-projection rows of the chunk into the K / Q / V tiles, and the three rows before each (sub-)chunk on its
+  //      tree path into Hs (over A, which is not written before the K K^T phase): [sub-chunk][3 rows][k | q | v][128]
+  bf16_t* Hs = reinterpret_cast<bf16_t*>(As);
+  const int coff[3] = {KD + hk * kHD, hk * kHD, 2 * KD + h * kHD};   // column of this head's k, q, v inside a proj row
+  for (int i = tid; i < 3 * kChunk * (kHD / 8); i += kIntraThreads) {
+    const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
+    const int r = rem >> 4, cv = (rem & 15) * 8;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    const int64_t row = grow(r);
+    if (row >= 0) val = *reinterpret_cast<const uint4*>(ps.proj + row * ps.P + coff[which] + cv);
+    bf16_t* dst = which == 0 ? Ks : which == 1 ? Qs : Vs;
+    *reinterpret_cast<uint4*>(dst + r * kLd + cv) = val;
+  }
+  for (int i = tid; i < 2 * 3 * 3 * (kHD / 8); i += kIntraThreads) {
+    const int cv = (i & 15) * 8, which = (i >> 4) % 3, j = (i / 48) % 3, sub = i / 144;
+    const int64_t first = sub == 0 ? static_cast<int64_t>(row0) : (paired ? static_cast<int64_t>(rowB0) : -1);
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (first >= 0) {
+      const int4 hr = ps.hist[first];
+      const int prow = j == 0 ? hr.x : (j == 1 ? hr.y : hr.z);
+      if (prow >= 0) val = *reinterpret_cast<const uint4*>(ps.proj + static_cast<int64_t>(prow) * ps.P + coff[which] + cv);
+    }
+    *reinterpret_cast<uint4*>(Hs + ((sub * 3 + j) * 3 + which) * kHD + cv) = val;
+  }
+  __syncthreads();
+  // ---- conv (4 taps, oldest first) + SiLU (+ L2 norm of q and k over the 128 dims of the head) in place. One thread = one
+  //      8-column vector of one tile over 16 consecutive rows, the last three rows it has seen kept in registers; every
+  //      thread fetches the three rows in front of its segment before any row is overwritten.
+  const bool worker = tid < 3 * 4 * 16;
+  const int c_which = tid / 64, c_seg = (tid >> 4) & 3, c_cv = (tid & 15) * 8;
+  bf16_t* tile = c_which == 0 ? Ks : c_which == 1 ? Qs : Vs;
+  uint4 win[3], wv[4];
+  if (worker) {
+    const bool from_hist = c_seg == 0 || (paired && c_seg == 2);      // the segment starts a (sub-)chunk
+    const int sub = (paired && c_seg == 2) ? 1 : 0;
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+      win[j] = from_hist ? *reinterpret_cast<const uint4*>(Hs + ((sub * 3 + j) * 3 + c_which) * kHD + c_cv)
+                         : *reinterpret_cast<const uint4*>(tile + (16 * c_seg - 3 + j) * kLd + c_cv);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      wv[u] = __ldg(reinterpret_cast<const uint4*>(ps.convw + static_cast<int64_t>(coff[c_which] + c_cv) * 4 + u * 8));
+  }
+  __syncthreads();
+  if (worker) {
+    const bf16_t* wb = reinterpret_cast<const bf16_t*>(wv);  // wb[e * 4 + tap]
+    for (int r = 16 * c_seg; r < 16 * c_seg + 16; ++r) {
+      const uint4 cur = *reinterpret_cast<const uint4*>(tile + r * kLd + c_cv);
+      float x0[8], x1[8], x2[8], x3[8], o[8];
+      unpack8(win[0], x0); unpack8(win[1], x1); unpack8(win[2], x2); unpack8(cur, x3);
+      const bool real = grow(r) >= 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float acc = 0.f;
+        acc += bf2f(wb[e * 4 + 0]) * x0[e];
+        acc += bf2f(wb[e * 4 + 1]) * x1[e];
+        acc += bf2f(wb[e * 4 + 2]) * x2[e];
+        acc += bf2f(wb[e * 4 + 3]) * x3[e];
+        o[e] = real ? round_bf(silu_f(acc)) : 0.f;
+      }
+      if (c_which < 2) {      // 16 consecutive lanes hold one row of one head
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += o[e] * o[e];
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float rn = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= rn;
+      }
+      *reinterpret_cast<uint4*>(tile + r * kLd + c_cv) = pack8(o);
+      win[0] = win[1]; win[1] = win[2]; win[2] = cur;
+    }
+  }
+  }
   // ---- cumulative log-decay (warp 0): two elements per lane
   if (warp == 0) {
     const int r0 = lane * 2, r1 = r0 + 1;
     // log-decays below -1e4 are clamped: e^-1e4 is zero in fp32 either way, and -inf would turn the differences of the
     // cumulative sums into NaN
     const int64_t gr0 = grow(r0), gr1 = grow(r1);
-    float g0 = gr0 >= 0 ? fmaxf(g[gr0 * HV + h], -1e4f) : 0.f;
-    float g1 = gr1 >= 0 ? fmaxf(g[gr1 * HV + h], -1e4f) : 0.f;
-    Bs[r0] = gr0 >= 0 ? bf2f(beta[gr0 * HV + h]) : 0.f;
-    Bs[r1] = gr1 >= 0 ? bf2f(beta[gr1 * HV + h]) : 0.f;
+    float g0 = 0.f, g1 = 0.f, be0 = 0.f, be1 = 0.f;
+    if constexpr (FUSED) {
+      // beta = bf16(sigmoid(b)), g = -exp(A_log) * softplus(a + dt_bias) from the b / a columns of the row (as gdn_prep)
+      const int ba = 2 * KD + 2 * VD;
+      const float na = -expf(bf2f(ps.A_log[h])), db = bf2f(ps.dt_bias[h]);
+      if (gr0 >= 0) {
+        const bf16_t* pr = ps.proj + gr0 * ps.P + ba;
+        be0 = round_bf(sigmoid_f(bf2f(pr[h])));
+        const float xs = bf2f(pr[HV + h]) + db;
+        g0 = fmaxf(na * (xs > 20.f ? xs : log1pf(expf(xs))), -1e4f);
+      }
+      if (gr1 >= 0) {
+        const bf16_t* pr = ps.proj + gr1 * ps.P + ba;
+        be1 = round_bf(sigmoid_f(bf2f(pr[h])));
+        const float xs = bf2f(pr[HV + h]) + db;
+        g1 = fmaxf(na * (xs > 20.f ? xs : log1pf(expf(xs))), -1e4f);
+      }
+    } else {
+      if (gr0 >= 0) { g0 = fmaxf(g[gr0 * HV + h], -1e4f); be0 = bf2f(beta[gr0 * HV + h]); }
+      if (gr1 >= 0) { g1 = fmaxf(g[gr1 * HV + h], -1e4f); be1 = bf2f(beta[gr1 * HV + h]); }
+    }
+    Bs[r0] = be0;
+    Bs[r1] = be1;
     float s = g0 + g1;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -515,6 +626,7 @@ __global__ void __launch_bounds__(kStateThreads)
 gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__ chunks, const int32_t* __restrict__ steps,
                  const int32_t* __restrict__ walk_ptr, const float* __restrict__ init_state, float* __restrict__ final_state,
                  bf16_t* __restrict__ out, int HV) {
+  const unsigned long long t_entry = global_timer_ns();
   pdl_begin();
   const int h = blockIdx.x, dv0 = blockIdx.y * kDv;
   const int s_begin = walk_ptr[blockIdx.z], s_end = walk_ptr[blockIdx.z + 1];
@@ -563,8 +675,9 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
 
   unsigned long long* trace = g_state_trace;
   const bool tracer = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == kChainThreads);
+  if (tracer && tid == 0) { trace[0] = t_entry; trace[1] = global_timer_ns(); }
   for (int s = s_begin; s < s_end; ++s) {
-    unsigned long long* rec = tracer ? trace + (static_cast<size_t>(s - s_begin) * 12 + (tid ? 6 : 0)) : nullptr;
+    unsigned long long* rec = tracer ? trace + 4 + (static_cast<size_t>(s - s_begin) * 12 + (tid ? 6 : 0)) : nullptr;
     if (rec) rec[0] = global_timer_ns();
     const bool staged = s - s_begin < kWin;
     const int4 st = staged ? sm_step[s - s_begin] : reinterpret_cast<const int4*>(steps)[s];
@@ -757,6 +870,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     if (rec) rec[5] = global_timer_ns();
   }
   cp_async_wait<0>();
+  if (tracer && tid == 0) trace[2] = global_timer_ns();
 }
 
 // ------------------------------------------------------------------------------------------------------ gated RMSNorm
@@ -804,7 +918,8 @@ extern "C" int ojb_gdn_prep(const void* proj, const int32_t* hist, const int32_t
                             int32_t l2norm, ojb_stream_t stream) {
   if (N == 0) return OJB_OK;
   OJB_REQUIRE(proj && hist && convw && A_log && dt_bias && q && k && v && g && beta && N > 0);
-  OJB_REQUIRE(HK > 0 && HV > 0 && KD == HK * kHD && VD == HV * kHD && HV <= 256);
+  // every row of proj must start on a 16-byte boundary (the kernel reads 16 bytes at a time): (2KD + 2VD + 2HV) % 8 == 0
+  OJB_REQUIRE(HK > 0 && HV > 0 && KD == HK * kHD && VD == HV * kHD && HV <= 256 && HV % 4 == 0);
   const int C = static_cast<int>(2 * KD + VD);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned gx = static_cast<unsigned>(ceil_div(C / 8, 256));
@@ -846,8 +961,9 @@ int intra_pairing(int64_t n_chunks, int64_t HV) {
 }
 // Opt-in shared-memory sizes of the two (three with the level form) kernels, once per device.
 bool gdn_raise_limits(bool lean_too) {
-  static int s_intra[kMaxDevices] = {}, s_state[kMaxDevices] = {}, s_lean[kMaxDevices] = {};
-  return raise_smem_limit(gdn_intra_kernel, static_cast<int>(kIntraSmem), s_intra) &&
+  static int s_intra[kMaxDevices] = {}, s_intra_f[kMaxDevices] = {}, s_state[kMaxDevices] = {}, s_lean[kMaxDevices] = {};
+  return raise_smem_limit(gdn_intra_kernel<false>, static_cast<int>(kIntraSmem), s_intra) &&
+         raise_smem_limit(gdn_intra_kernel<true>, static_cast<int>(kIntraSmem), s_intra_f) &&
          raise_smem_limit(gdn_state_kernel<false>, static_cast<int>(kStateSmem), s_state) &&
          (!lean_too || raise_smem_limit(gdn_state_kernel<true>, static_cast<int>(kStateSmemLean), s_lean));
 }
@@ -865,14 +981,38 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_walks > 0 && n_walks <= 65535 && HV <= 65535);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!gdn_raise_limits(false)) return OJB_ERR_LAUNCH;
-  launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
+  launch_kernel(gdn_intra_kernel<false>, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale,
-      intra_pairing(n_chunks, HV));
+      intra_pairing(n_chunks, HV), PrepSrc{});
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out),
       static_cast<int>(HV));
+  return launch_status(cudaGetLastError());
+}
+
+extern "C" int ojb_gdn_chunked_proj(const void* proj, const int32_t* hist, const void* convw, const void* A_log,
+                                    const void* dt_bias, const int32_t* chunks, int64_t n_chunks, const int32_t* steps,
+                                    const int32_t* walk_ptr, int64_t n_walks, const float* init_state, float* final_state,
+                                    void* scratch, void* out, int64_t KD, int64_t VD, int64_t HK, int64_t HV, float scale,
+                                    ojb_stream_t stream) {
+  if (n_chunks == 0 || n_walks == 0) return OJB_OK;
+  OJB_REQUIRE(proj && hist && convw && A_log && dt_bias && chunks && steps && walk_ptr && scratch && out);
+  OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && KD == HK * kHD && VD == HV * kHD && n_chunks > 0 && n_walks > 0 &&
+              n_walks <= 65535 && HV <= 65535 && HV % 4 == 0);      // HV % 4: 16-byte aligned rows of proj
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!gdn_raise_limits(false)) return OJB_ERR_LAUNCH;
+  PrepSrc ps{static_cast<const bf16_t*>(proj), reinterpret_cast<const int4*>(hist), static_cast<const bf16_t*>(convw),
+             static_cast<const bf16_t*>(A_log), static_cast<const bf16_t*>(dt_bias), static_cast<int>(2 * KD + 2 * VD + 2 * HV)};
+  launch_kernel(gdn_intra_kernel<true>, dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV)), dim3(kIntraThreads),
+                kIntraSmem, st, static_cast<const bf16_t*>(nullptr), static_cast<const bf16_t*>(nullptr),
+                static_cast<const bf16_t*>(nullptr), static_cast<const float*>(nullptr), static_cast<const bf16_t*>(nullptr), chunks,
+                static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale, intra_pairing(n_chunks, HV), ps);
+  if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
+  launch_kernel(gdn_state_kernel<false>, dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)),
+                dim3(kStateThreads), kStateSmem, st, static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state,
+                final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
   return launch_status(cudaGetLastError());
 }
 
@@ -917,7 +1057,7 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
     // device address. Also raises the shared-memory limits of the two kernels for this device.
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_gdn_static_scratch) != cudaSuccess || p == nullptr) return OJB_ERR_LAUNCH;
-    if (cudaFuncSetAttribute(gdn_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
+    if (cudaFuncSetAttribute(gdn_intra_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraSmem) != cudaSuccess ||
         cudaFuncSetAttribute(gdn_state_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStateSmem) != cudaSuccess)
       return OJB_ERR_LAUNCH;
     g_static_scratch_addr[dev] = p;
@@ -926,10 +1066,10 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // Nothing in the array has to start at zero: the first kernel overwrites every byte of every item that the second one
   // reads (items of unused chunk-table entries are neither written nor read).
-  launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
+  launch_kernel(gdn_intra_kernel<false>, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, scratch, static_cast<int>(HK), static_cast<int>(HV), scale,
-      intra_pairing(n_chunks, HV));
+      intra_pairing(n_chunks, HV), PrepSrc{});
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
@@ -950,10 +1090,10 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
   for (int64_t l = 0; l < n_levels; ++l) OJB_REQUIRE(levels[l + 1] >= levels[l] && levels[l + 1] - levels[l] <= 65535);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!gdn_raise_limits(true)) return OJB_ERR_LAUNCH;
-  launch_kernel(gdn_intra_kernel, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
+  launch_kernel(gdn_intra_kernel<false>, dim3(dim3(static_cast<unsigned>(n_chunks), static_cast<unsigned>(HV))), dim3(kIntraThreads), kIntraSmem, st, 
       static_cast<const bf16_t*>(q), static_cast<const bf16_t*>(k), static_cast<const bf16_t*>(v), g,
       static_cast<const bf16_t*>(beta), chunks, static_cast<bf16_t*>(scratch), static_cast<int>(HK), static_cast<int>(HV), scale,
-      intra_pairing(n_chunks, HV));
+      intra_pairing(n_chunks, HV), PrepSrc{});
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   for (int64_t l = 0; l < n_levels; ++l) {
     const int nw = levels[l + 1] - levels[l];

@@ -75,7 +75,7 @@ def check_status(device=None):
             raise RuntimeError(f"ojb200: device-side wait ran out (status {v}); results of the last calls are invalid")
 
 
-_KERNELS_PER_CALL = {"ojb_gdn_chunked": 2, "ojb_gdn_chunked_static": 2, "ojb_gdn_chunked_levels": 4, "ojb_gemm_plan": 0,
+_KERNELS_PER_CALL = {"ojb_gdn_chunked": 2, "ojb_gdn_chunked_proj": 2, "ojb_gdn_chunked_static": 2, "ojb_gdn_chunked_levels": 4, "ojb_gemm_plan": 0,
                      "ojb_gemm_set_trace": 0}
 _launches = 0
 

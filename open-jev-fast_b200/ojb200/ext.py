@@ -395,6 +395,29 @@ def gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walk_ptr, n_walks, init_
     return out
 
 
+def gdn_chunked_proj(proj, hist, convw, A_log, dt_bias, KD, VD, HV, HK, scale, chunks, steps, walk_ptr, n_walks, init_state=None,
+                     final_state=None, out=None):
+    """gdn_chunked with the preparation fused into its first launch (ojb_gdn_chunked_proj): reads the in-projection output
+    `proj` [N, 2KD+2VD+2HV] and the history table directly — linattn_prep_rows + gdn_chunked in two launches instead of three,
+    same bits. Chunks must be runs of consecutive packed rows of one tree node (the layout builder's tables).
+    Returns out bf16 [N, HV, 128] (rows outside every chunk are left as they are)."""
+    _chk(proj, hist, convw, A_log, dt_bias, chunks, steps, walk_ptr, init_state, final_state)
+    N = proj.shape[0]
+    if any(t.dtype != bf16 for t in (proj, convw, A_log, dt_bias)) or proj.shape[1] != 2 * KD + 2 * VD + 2 * HV \
+            or hist.shape != (N + 1, 4) or hist.dtype != torch.int32 or convw.shape != (2 * KD + VD, 4):
+        raise RuntimeError("gdn_chunked_proj: proj [N, 2KD+2VD+2HV], convw [2KD+VD, 4], A_log / dt_bias bf16 and hist int32 [N+1, 4]")
+    nch = chunks.shape[0]
+    nbytes = _lib.lib().ojb_gdn_scratch_bytes
+    nbytes.restype = _lib.ctypes.c_int64
+    scratch = torch.empty(nbytes(i64(nch), i64(HV)), dtype=torch.uint8, device=proj.device)
+    if out is None:
+        out = torch.zeros(N, HV, 128, dtype=bf16, device=proj.device)
+    call("ojb_gdn_chunked_proj", ptr(proj), ptr(hist), ptr(convw), ptr(A_log), ptr(dt_bias), ptr(chunks), i64(nch), ptr(steps),
+         ptr(walk_ptr), i64(n_walks), ptr(init_state), ptr(final_state), ptr(scratch), ptr(out), i64(KD), i64(VD), i64(HK), i64(HV),
+         f32(scale), stream_ptr())
+    return out
+
+
 def gdn_tree_levels(q, k, v, g, beta, scale, lay, out, states=None):
     """Tree-native pass with the state recurrence run level by level (root, question stems, leaves as three launches whose
     walks run side by side). q, k [N, HK, 128], v [N, HV, 128]; `out` [N, HV, 128] is written for real rows only; `states`

@@ -6,8 +6,7 @@ Interface of open-jev-fast's src/fastmodel.py: `FastQwen35(core)` reads a Huggin
 Everything below that interface is different: per layer the launches are
 
     in-proj GEMM (tcgen05)                                        -> proj
-    GDN layers : prep (conv+SiLU+L2norm+gates, one row per packed row) -> intra-chunk pass -> tree-walking state pass
-                 -> gated RMSNorm
+    GDN layers : intra-chunk pass (conv+SiLU+L2norm+gates of its rows fused in) -> tree-walking state pass -> gated RMSNorm
     attention  : q/k norm + rotary -> tree attention from three key ranges per row, output gate fused
     out-proj GEMM, split-K fp32 partials -> reduce + residual (fp32 stream) + RMSNorm
     gate/up GEMM with SwiGLU in the epilogue
@@ -36,6 +35,10 @@ FATTN = int(os.environ.get("OJ_FATTN", "0"))               # query heads per CTA
 FATTN_MAX = int(os.environ.get("OJ_FATTN_MAX", "1000000000"))   # kept for compatibility: the kernel serves every N
 GDN_FUSED, GDN_VER, PREP, GVA, LUT, SK2 = True, 6, "dedup", True, True, True
 TREE_NATIVE = os.environ.get("OJ_TREE_NATIVE", "1") == "1"      # 0: replicated per-candidate GDN layout of the reference
+# 1: conv + SiLU + L2 norm + gates inside the first Gated DeltaNet launch (same bits, one launch fewer per layer). Measured:
+# 32.00 against 31.91 ms on the 539-row tree, 20.86 against 20.19 ms on the 277-row tree — the work lands on the latency chain
+# of a kernel that is latency-bound already, so it is off.
+FUSE_PREP = os.environ.get("OJ_FUSE_PREP", "0") == "1"
 TREE_LEVELS = os.environ.get("OJ_TREE_LEVELS", "0") == "1"      # 1: state pass per tree level (3 launches), 0: one depth-first walk
 # (measured on the 539-row tree: depth-first 84 us per layer for intra + state, level-parallel 88 us: the two extra launches
 # and the six waves of short single-step CTAs cost more than the shorter dependency chain saves)
@@ -274,8 +277,12 @@ class FastQwen35(torch.nn.Module):
     def _linear_tree(self, d, proj, lay):
         N = proj.shape[0]
         if TREE_NATIVE and hasattr(lay, "chunks"):
-            q, k, v, g, beta = K.linattn_prep_rows(proj, lay.hist, d.convw, d.A_log, d.dt_bias, d.KD, d.VD, d.HV, d.HK, d.HD)
             o = self._zero_buf("gdn_o", (N, d.HV, d.HD), proj.device)
+            if FUSE_PREP and not (hasattr(lay, "lsteps") and TREE_LEVELS):
+                K.gdn_chunked_proj(proj, lay.hist, d.convw, d.A_log, d.dt_bias, d.KD, d.VD, d.HV, d.HK, d.HD ** -0.5, lay.chunks,
+                                   lay.steps, lay.walk_ptr, lay.n_walks, None, None, o)
+                return K.gated_rmsnorm(o, proj, d.normw, d.HV, d.HD, 2 * d.KD + d.VD, d.norm_eps)
+            q, k, v, g, beta = K.linattn_prep_rows(proj, lay.hist, d.convw, d.A_log, d.dt_bias, d.KD, d.VD, d.HV, d.HK, d.HD)
             if hasattr(lay, "lsteps") and TREE_LEVELS:
                 st = self._bufs.get(("gdn_states", lay.S, d.HV))
                 if st is None:

@@ -152,3 +152,54 @@ def test_gated_rmsnorm():
     a, b = y.float().cpu(), ref.float()
     assert bool(((a - b).abs() <= b.abs() * 2 ** -7 + 1e-6).all())
     assert (a == b).float().mean().item() > 0.98
+
+
+@pytest.mark.parametrize("name,HK,HV", [(n, hk, hv) for n in ("doc", "baseline", "example", "nostem", "wide", "single", "ragged",
+                                                               "prefix_of", "long") for hk, hv in ((2, 4), (4, 4))] +
+                         [("baseline", 16, 32), ("wide", 16, 32)])     # model width: short chunks run two to a CTA there
+def test_prep_fused_into_the_intra_pass_gives_the_same_bits(name, HK, HV):
+    """ojb_gdn_chunked_proj (conv + SiLU + L2 norm + gates inside the first Gated DeltaNet launch) against ojb_gdn_prep followed
+    by ojb_gdn_chunked on the same in-projection output: same arithmetic, so the same bits — outputs and exported final state,
+    on every tree shape of the layout cases (single-row nodes, empty stems, nodes longer than a chunk, paired short chunks)."""
+    from ojb200 import ext as K
+    from ojb200 import layout as PL
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()[name]
+    ids, lay = PL.gtree_build(seqs, groups, pad_id, NB, PB, dev="cuda", dense=False)
+    N, HD = lay.N, 128
+    KD, VD = HK * HD, HV * HD
+    gen = torch.Generator().manual_seed(17)
+    proj = torch.randn(N, 2 * KD + 2 * VD + 2 * HV, generator=gen).to(bf16).cuda()
+    convw = (torch.randn(2 * KD + VD, 4, generator=gen) * 0.3).to(bf16).cuda()
+    A_log = torch.log(torch.rand(HV, generator=gen) * 16 + 1e-3).to(bf16).cuda()
+    dt_bias = torch.ones(HV).to(bf16).cuda()
+    scale = HD ** -0.5
+    q, k, v, g, beta = K.linattn_prep_rows(proj, lay.hist, convw, A_log, dt_bias, KD, VD, HV, HK, HD)
+    fin_a = torch.zeros(1, HV, HD, HD, device="cuda")
+    fin_b = torch.zeros(1, HV, HD, HD, device="cuda")
+    steps = lay.steps.clone()
+    w0, w1 = int(lay.walk_ptr[0]), int(lay.walk_ptr[1])
+    steps[w1 - 1, 3] = steps[w1 - 1, 3] | 1                       # export the state after the last step of the walk
+    want = torch.zeros(N, HV, HD, dtype=bf16, device="cuda")
+    K.gdn_chunked(q.view(N, HK, HD), k.view(N, HK, HD), v.view(N, HV, HD), g, beta, scale, lay.chunks, steps, lay.walk_ptr, 1,
+                  None, fin_a, want)
+    got = torch.zeros(N, HV, HD, dtype=bf16, device="cuda")
+    K.gdn_chunked_proj(proj, lay.hist, convw, A_log, dt_bias, KD, VD, HV, HK, scale, lay.chunks, steps, lay.walk_ptr, 1, None,
+                       fin_b, got)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert torch.equal(fin_a, fin_b)
+    assert float(want.float().abs().max()) > 0
+
+
+def test_prep_refuses_projection_rows_that_are_not_16_byte_aligned():
+    """The prep kernels read rows of proj 16 bytes at a time: a row length that is not a multiple of 8 elements (HV % 4 != 0)
+    is refused by the entry points instead of being launched."""
+    from ojb200 import ext as K
+    HK = HV = 1
+    N = 32
+    proj = torch.zeros(N, 2 * 128 + 2 * 128 + 2, dtype=bf16, device="cuda")
+    hist = torch.full((N + 1, 4), -1, dtype=torch.int32, device="cuda")
+    convw = torch.zeros(3 * 128, 4, dtype=bf16, device="cuda")
+    one = torch.ones(HV, dtype=bf16, device="cuda")
+    with pytest.raises(RuntimeError):
+        K.linattn_prep_rows(proj, hist, convw, one, one, 128, 128, HV, HK, 128)
