@@ -49,7 +49,10 @@ def main():
     ap.add_argument("--hv", type=int, default=32)
     args = ap.parse_args()
     from ojb200 import trees
-    seqs, groups = (trees.baseline_tree if args.tree == "baseline" else trees.example_tree)(0)
+    if args.tree.startswith("root"):       # e.g. --tree root8192: one long shared root, two questions, four candidates
+        seqs, groups = trees.make_tree(7, int(args.tree[4:]), [20, 22], [6, 9, 4, 12], [0, 0, 1, 1])
+    else:
+        seqs, groups = (trees.baseline_tree if args.tree == "baseline" else trees.example_tree)(0)
     ids, lay = PL.gtree_build(seqs, groups, 0, dev="cuda", dense=False)
     N, HK, HV, HD, H = lay.N, 16, args.hv, 128, 5120
     KD, VD = HK * HD, HV * HD
@@ -80,9 +83,13 @@ def main():
         cosb, sinb = torch.cat([ang.cos()] * 2, -1).to(bf16), torch.cat([ang.sin()] * 2, -1).to(bf16)
         qt, kt, vt, gate = K.fullattn_prep2(proj, w1, w1, cosb, sinb, 1, N, HQ, HKV, D, 1e-6)
         out("fullattn_prep", _time(lambda: K.fullattn_prep2(proj, w1, w1, cosb, sinb, 1, N, HQ, HKV, D, 1e-6), args.reps))
-        for gq in (3, 6):
+        for gq in ((6,) if N > 2048 else (3, 6)):
             out(f"tree_attn ranges gq={gq}", _time(lambda: K.fattn_tree_ranges(qt, kt, vt, gate, lay.krange, D ** -0.5, gq), args.reps))
-        out("tree_attn bits gq=6", _time(lambda: K.fattn_tree(qt, kt, vt, gate, None, lay.vbits, D ** -0.5, 6), args.reps))
+        if N <= 2048:
+            out("tree_attn bits gq=6", _time(lambda: K.fattn_tree(qt, kt, vt, gate, None, lay.vbits, D ** -0.5, 6), args.reps))
+        vt_t = K.fullattn_prep2(proj, w1, w1, cosb, sinb, 1, N, HQ, HKV, D, 1e-6, with_vt_t=True)[4]
+        out("fullattn_prep + transposed V", _time(lambda: K.fullattn_prep2(proj, w1, w1, cosb, sinb, 1, N, HQ, HKV, D, 1e-6, with_vt_t=True), args.reps))
+        out("tree_attn tcgen05", _time(lambda: K.fattn_tree_tc(qt, kt, vt_t, gate, lay.krange, D ** -0.5), args.reps))
     if want("norm"):
         x, d = rnd(N, H).to(bf16), rnd(N, H).to(bf16)
         w1 = torch.ones(H, device="cuda")

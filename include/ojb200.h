@@ -153,9 +153,10 @@ int ojb_pack_bits(const uint8_t* vis, int32_t* bits, int64_t N, ojb_stream_t str
 /* src/kernels.cu:302,843 fullattn_prep2. proj [N, HQ*2D + 2*HKV*D] = per q head [q(D) | gate(D)], then k heads, then
  * v heads. Writes qt [HQ, N, D], kt / vt [HKV, N, D] (head-major), gate [N, HQ*D]. q, k: RMSNorm over D with (1+w)
  * weights qw1 / kw1 (fp32) rounded to bf16, then rotary on the first RD dims (cos / sin bf16 [N, RD], rotate-half
- * pairing d <-> d + RD/2) with a bf16 rounding after each product and the sum. D % 64 == 0, D <= 256. */
+ * pairing d <-> d + RD/2) with a bf16 rounding after each product and the sum. D % 64 == 0, D <= 256. vt_t (may be null)
+ * additionally receives V with rows and columns exchanged, [HKV, D, N]: the operand layout of ojb_tree_attn_tc. */
 int ojb_fullattn_prep(const void* proj, const float* qw1, const float* kw1, const void* cosb, const void* sinb,
-                      void* qt, void* kt, void* vt, void* gate, int64_t N, int64_t HQ, int64_t HKV, int64_t D,
+                      void* qt, void* kt, void* vt, void* vt_t, void* gate, int64_t N, int64_t HQ, int64_t HKV, int64_t D,
                       int64_t RD, float eps, ojb_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------------------------
@@ -281,6 +282,23 @@ int ojb_gated_rmsnorm(const void* x, const int32_t* inv, const void* proj, const
 int ojb_tree_attn(const void* qt, const void* kt, const void* vt, const void* gate, const int32_t* vbits,
                   const int32_t* krange, void* y, int64_t N, int64_t HQ, int64_t HKV, int64_t D, int64_t gq, float scale,
                   ojb_stream_t stream);
+
+/* The same attention on the tcgen05 tensor cores (head dim 256, key-range mask only): one CTA per (kv head, 16 query rows)
+ * stacks the rows of all HQ/HKV <= 8 query heads of the kv head into one 128-row operand tile; Q, K and V blocks arrive by
+ * TMA, Q K^T and P V are tcgen05.mma with S, P's source and O in tensor memory; two-pass softmax (row maxima first, then
+ * P = exp2((s - max) scale log2 e) and O += P V) in the exp2 domain. vt_t bf16 [HKV, 256, N] is V with keys contiguous
+ * (second V output of ojb_fullattn_prep). Same result as ojb_tree_attn up to the rounding of P and the summation order.
+ * `status` receives OJB_DEV_WAIT_TIMEOUT if a bounded device-side wait ran out. Replaces the same reference code as
+ * ojb_tree_attn (src/kernels.cu:4287-4458; above 384 rows src/fastmodel.py:470-473). */
+int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t, const void* gate, const int32_t* krange, void* y,
+                     int64_t N, int64_t HQ, int64_t HKV, int64_t D, float scale, int32_t* status, ojb_stream_t stream);
+
+/* Measurement hook of ojb_tree_attn_tc (no counterpart in the reference): `records` = null switches it off; otherwise a device
+ * buffer of 16 uint64 words. The CTA of kv head 0 and the last-but-one block of 16 query rows stores %globaltimer at kernel
+ * entry [0], after its set-up [1], at the first scores of pass 1 [2] and of pass 2 [3], when the last P tile is handed over
+ * [4], when O is complete [5], after its epilogue [6] and at exit [7]; its MMA thread when Q has landed [8] and when every MMA
+ * is issued [9]; word 15 = number of key blocks it visits. Synchronises the device (it writes a device variable). */
+int ojb_tree_attn_set_trace(uint64_t* records);
 
 /* Scoring head — replaces src/server.py:37 `mdl.head(forward_gtree(...).float())` together with the gather
  * src/fastmodel.py:482 `hn[lay.lastidx]`: out[s, a] = bias[a] + sum_h float(hn[rows[s], h]) * W[a, h], all fp32.

@@ -236,8 +236,8 @@ template <int PER>
 __global__ void __launch_bounds__(256)
 fullattn_prep_kernel(const bf16_t* __restrict__ proj, const float* __restrict__ qw1, const float* __restrict__ kw1,
                      const bf16_t* __restrict__ cosb, const bf16_t* __restrict__ sinb, bf16_t* __restrict__ qt,
-                     bf16_t* __restrict__ kt, bf16_t* __restrict__ vt, bf16_t* __restrict__ gate, int64_t N, int HQ, int HKV,
-                     int D, int RD, float eps) {
+                     bf16_t* __restrict__ kt, bf16_t* __restrict__ vt, bf16_t* __restrict__ vt_t, bf16_t* __restrict__ gate,
+                     int64_t N, int HQ, int HKV, int D, int RD, float eps) {
   pdl_begin();
   const int ntask = HQ + 2 * HKV;
   const int64_t wid = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -275,6 +275,10 @@ fullattn_prep_kernel(const bf16_t* __restrict__ proj, const float* __restrict__ 
     const int kh = task - HQ - HKV;
     load(prow + HQ * 2 * D + HKV * D + kh * D + d0, xv);
     store(vt + (static_cast<int64_t>(kh) * N + n) * D + d0, xv);
+    if (vt_t != nullptr) {      // the same values with rows and columns exchanged: [HKV, D, N] (the tcgen05 attention kernel reads V
+#pragma unroll                  // blocks as K-major operand tiles, keys contiguous)
+      for (int e = 0; e < PER; ++e) vt_t[(static_cast<int64_t>(kh) * D + d0 + e) * N + n] = f2bf(xv[e]);
+    }
     return;
   }
   const bool isq = task < HQ;
@@ -381,7 +385,7 @@ extern "C" int ojb_l2_prefetch(const void* data, int64_t nbytes, int64_t chunk, 
   return launch_status(cudaGetLastError());
 }
 
-extern "C" int ojb_abi_version(void) { return 3; }
+extern "C" int ojb_abi_version(void) { return 4; }
 
 extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
                                void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream) {
@@ -475,8 +479,8 @@ extern "C" int ojb_pack_bits(const uint8_t* vis, int32_t* bits, int64_t N, ojb_s
 }
 
 extern "C" int ojb_fullattn_prep(const void* proj, const float* qw1, const float* kw1, const void* cosb, const void* sinb,
-                                 void* qt, void* kt, void* vt, void* gate, int64_t N, int64_t HQ, int64_t HKV, int64_t D,
-                                 int64_t RD, float eps, ojb_stream_t stream) {
+                                 void* qt, void* kt, void* vt, void* vt_t, void* gate, int64_t N, int64_t HQ, int64_t HKV,
+                                 int64_t D, int64_t RD, float eps, ojb_stream_t stream) {
   OJB_REQUIRE(proj && qw1 && kw1 && cosb && sinb && qt && kt && vt && gate && N >= 0 && HQ > 0 && HKV > 0);
   OJB_REQUIRE(D == 256 || D == 128 || D == 64);
   const int per = static_cast<int>(D / 32);
@@ -489,7 +493,8 @@ extern "C" int ojb_fullattn_prep(const void* proj, const float* qw1, const float
   launch_kernel(fullattn_prep_kernel<P>, dim3(grid), dim3(256), 0, st, static_cast<const bf16_t*>(proj), qw1, kw1,                             \
                                                 static_cast<const bf16_t*>(cosb), static_cast<const bf16_t*>(sinb),     \
                                                 static_cast<bf16_t*>(qt), static_cast<bf16_t*>(kt),                     \
-                                                static_cast<bf16_t*>(vt), static_cast<bf16_t*>(gate), N,                \
+                                                static_cast<bf16_t*>(vt), static_cast<bf16_t*>(vt_t),                   \
+                                                static_cast<bf16_t*>(gate), N,                                          \
                                                 static_cast<int>(HQ), static_cast<int>(HKV), static_cast<int>(D),       \
                                                 static_cast<int>(RD), eps)
   if (per == 8) OJB_PREP(8); else if (per == 4) OJB_PREP(4); else OJB_PREP(2);

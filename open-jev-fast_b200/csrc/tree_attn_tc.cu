@@ -1,0 +1,408 @@
+// Prefix-tree GQA attention on the tcgen05 tensor cores (head dim 256), with the sigmoid output gate fused in.
+//
+// One CTA = one kv head x 16 query rows x ALL query heads of that kv head: the G <= 8 heads share K and V, so their rows are
+// stacked into one 128-row operand tile (row 16 w + r = head w, query row r) and every K / V tile that reaches the SM is
+// used by all of them. Keys are visited in blocks of 64; a block is skipped when none of the 16 rows sees any of its keys
+// (the mask is three half-open key ranges per row: root, own question stem, own leaf up to the row itself).
+//
+//   S = Q K^T   tcgen05.mma, M = 128, N = 64, K = 256: Q [128 x 256] and the K block [64 x 256] are K-major 128-byte-swizzled
+//               tiles written by TMA; S lives in tensor memory (two 64-column buffers, so the product of the next block runs
+//               while the softmax warps work on this one)
+//   softmax     four warps, one thread per (head, row) = one lane of tensor memory: tcgen05.ld of its 64 scores, mask, exp2
+//   O += P V    P is written as a bf16 K-major swizzled tile [128 x 64] by the softmax threads; V arrives transposed
+//               ([256 x N], written by the prep kernel), so the V block [256 d x 64 keys] is K-major too; O [128 x 256] fp32
+//               stays in tensor memory for the whole CTA
+//
+// The softmax is two-pass: pass 1 runs Q K^T over the visible blocks and keeps only the row maxima, pass 2 forms
+// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. With at most four visible key blocks all
+// scores stay in tensor memory between the passes; with more, pass 2 recomputes the (cheap) Q K^T products. Roles: warps 0-3 softmax / epilogue, warp 4 TMA producer, warp 5 MMA issuer; mbarriers between them,
+// every wait bounded (the CTA then reports OJB_DEV_WAIT_TIMEOUT through `status`, frees its tensor memory and returns).
+#include "gemm_common.cuh"
+
+namespace ojb {
+namespace {
+
+constexpr int kD = 256;
+constexpr int kQRows = 16;            // query rows per CTA and head
+constexpr int kKB = 64;               // keys per block
+constexpr int kTcThreads = 192;
+constexpr uint32_t kQBytes = 128 * kD * 2;     // 4 k-blocks of [128 rows][64]
+constexpr uint32_t kKBytes = kKB * kD * 2;     // 4 k-blocks of [64 keys][64]
+constexpr uint32_t kVBytes = kD * kKB * 2;     // [256 d][64 keys]
+constexpr uint32_t kPBytes = 128 * kKB * 2;    // [128 rows][64 keys]
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColO = 0, kColS = 256;     // O: 256 columns; S: two buffers of 64 columns
+constexpr int kStagePitch = kD * 2 + 16;       // bytes per row of the output staging tile
+constexpr int kMaxBlocks = 1024;               // key blocks a CTA can list (65 536 keys)
+
+// Measurement hook (ojb_tree_attn_set_trace): when non-null, the CTA of kv head 0 and the last-but-one block of query rows
+// stores %globaltimer at a few points of its life (see the stamps below).
+__device__ unsigned long long* g_attn_trace = nullptr;
+
+struct AttnArgs {
+  const bf16_t* gate;
+  const int32_t* krange;
+  bf16_t* y;
+  int32_t* status;
+  int N, HQ, HKV, G;
+  float scale_log2e;
+  int wait_ms;
+};
+
+// bits of keys [32 * w, 32 * w + 32) that fall in [lo, hi)
+__device__ __forceinline__ uint32_t range_bits(int lo, int hi, int w) {
+  const int a = max(lo - w * 32, 0), b = min(hi - w * 32, 32);
+  if (a >= b) return 0u;
+  const uint32_t upto_b = b == 32 ? 0xffffffffu : ((1u << b) - 1u);
+  return upto_b & ~((1u << a) - 1u);
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_vt, AttnArgs g) {
+  const unsigned long long t_entry = global_timer_ns();
+  pdl_launch_dependents();
+  unsigned long long* trace = (blockIdx.x == 0 && blockIdx.y + 2 == gridDim.y) ? g_attn_trace : nullptr;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* Qs = smem;
+  uint8_t* Ks = Qs + kQBytes;                  // two stages
+  uint8_t* Vs = Ks + 2 * kKBytes;              // two stages
+  uint8_t* Ps = Vs + 2 * kVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + kPBytes);
+  // barriers: 0 q_full | 1-2 k_full | 3-4 k_free | 5-6 v_full | 7-8 v_free | 9-10 s_full | 11-12 s_free | 13 p_full | 14 p_free
+  //           | 15 o_full | 16-19 s_full of the four S buffers of the one-pass form
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);      // [0] give-up flag, [1] wait limit in ms
+  int* kr = reinterpret_cast<int*>(tmem_slot + 4);                                 // [16 rows][8]
+  int* vis_list = kr + kQRows * 8;                                                 // visible key blocks; count at [kMaxBlocks]
+
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int kvh = blockIdx.x, r0 = blockIdx.y * kQRows;
+  const int G = g.G, N = g.N;
+  const int nw = (G * kQRows + 31) / 32;       // softmax warps that own real rows
+  const int hq0 = kvh * G;
+
+  if (tid == 0) {
+    mbar_init(bar(0), 1);
+    for (int i = 1; i <= 10; ++i) mbar_init(bar(i), 1);
+    mbar_init(bar(11), nw); mbar_init(bar(12), nw);
+    mbar_init(bar(13), nw);
+    mbar_init(bar(14), 1); mbar_init(bar(15), 1);
+    for (int i = 16; i < 20; ++i) mbar_init(bar(i), 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = g.wait_ms;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vt) : "memory");
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  pdl_wait();      // from here on the previous kernel of the stream has completed
+  // key ranges of the 16 rows
+  if (tid < kQRows * 8) kr[tid] = g.krange[static_cast<int64_t>(r0) * 8 + tid];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (warp == 4 && lane == 0) {      // the Q rows do not depend on the list of key blocks: requested while warp 0 builds it
+    mbar_expect_tx(bar(0), static_cast<uint32_t>(G) * 4u * (kQRows * 128u));
+    for (int w = 0; w < G; ++w)
+      for (int kb4 = 0; kb4 < 4; ++kb4)
+        tma_load_2d(smem_u32(Qs) + kb4 * (128 * 128) + w * (kQRows * 128), &map_q, bar(0), kb4 * 64, (hq0 + w) * N + r0);
+  }
+  // ordered list of the 64-key blocks that at least one of the 16 rows sees
+  const int NB = (N + kKB - 1) / kKB;
+  if (warp == 0) {
+    int count = 0;
+    for (int base = 0; base < NB; base += 32) {
+      const int kb = base + lane;
+      bool any = false;
+      if (kb < NB) {
+        const int k0 = kb * kKB, k1 = k0 + kKB;
+        for (int r = 0; r < kQRows && !any; ++r) {
+          const int* q = kr + r * 8;      // (e0, a1, e1, a2, e2, a0)
+          any = (q[5] < q[0] && q[5] < k1 && q[0] > k0) || (q[1] < q[2] && q[1] < k1 && q[2] > k0) ||
+                (q[3] < q[4] && q[3] < k1 && q[4] > k0);
+        }
+      }
+      const uint32_t bal = __ballot_sync(0xffffffffu, any);
+      if (any && count + __popc(bal & ((1u << lane) - 1u)) < kMaxBlocks) vis_list[count + __popc(bal & ((1u << lane) - 1u))] = kb;
+      count += __popc(bal);
+    }
+    if (lane == 0) vis_list[kMaxBlocks] = count < kMaxBlocks ? count : kMaxBlocks;
+  }
+  __syncthreads();
+  const int nvis = vis_list[kMaxBlocks];
+  const int T = 2 * nvis;                       // pass 1 (maxima) then pass 2 (P V) over the same blocks
+  // Up to four key blocks: the scores of all of them fit in tensor memory beside O (4 x 64 columns), so Q K^T runs once and
+  // pass 2 reads the scores again from there. More blocks: two S buffers in rotation, Q K^T recomputed in pass 2.
+  const bool one_pass = nvis <= 4;
+  // Gate values of the 16 output pieces this thread multiplies at the very end (consecutive threads take consecutive 16-byte
+  // pieces of the [G * 16 rows][256] output tile). Each warp requests them as soon as it has nothing else to wait for, so their
+  // latency runs under the last P V products and the staging of O.
+  const int pieces = G * kQRows * (kD / 8);
+  constexpr int kBatch = 16;
+  uint4 gq[kBatch];
+  auto prefetch_gates = [&](int base) {
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int i = base + u * kTcThreads;
+      gq[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < pieces) {
+        const int row = i >> 5, piece = i & 31;             // tile row = 16 * head + query row
+        gq[u] = *reinterpret_cast<const uint4*>(g.gate + (static_cast<int64_t>(r0 + (row & 15)) * g.HQ + (hq0 + (row >> 4))) * kD + piece * 8);
+      }
+    }
+  };
+  if (trace && tid == 0) { trace[0] = t_entry; trace[1] = global_timer_ns(); trace[15] = static_cast<unsigned long long>(nvis); }
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      auto load_k = [&](int it, int kb) {
+        const int st = it & 1, u = it >> 1;
+        if (!mbar_wait(bar(3 + st), (u & 1) ^ 1, abort_flag)) return false;
+        mbar_expect_tx(bar(1 + st), kKBytes);
+        for (int kb4 = 0; kb4 < 4; ++kb4)
+          tma_load_2d(smem_u32(Ks) + st * kKBytes + kb4 * (kKB * 128), &map_k, bar(1 + st), kb4 * 64, kvh * N + kb * kKB);
+        return true;
+      };
+      auto load_v = [&](int j, int kb) {
+        const int vs = j & 1, uv = j >> 1;
+        if (!mbar_wait(bar(7 + vs), (uv & 1) ^ 1, abort_flag)) return false;
+        mbar_expect_tx(bar(5 + vs), kVBytes);
+        tma_load_2d(smem_u32(Vs) + vs * kVBytes, &map_vt, bar(5 + vs), kb * kKB, kvh * kD);
+        return true;
+      };
+      if (one_pass) {
+        // K 0, K 1, V 0, V 1 need no stage to become free; the later K blocks wait for Q K^T of two blocks earlier, the later V
+        // blocks for P V of two blocks earlier, which only starts after every Q K^T: all K loads come before those V loads
+        for (int it = 0; it < nvis && it < 2 && ok; ++it) ok = load_k(it, vis_list[it]);
+        for (int j = 0; j < nvis && j < 2 && ok; ++j) ok = load_v(j, vis_list[j]);
+        for (int it = 2; it < nvis && ok; ++it) ok = load_k(it, vis_list[it]);
+        for (int j = 2; j < nvis && ok; ++j) ok = load_v(j, vis_list[j]);
+      } else {
+        for (int it = 0; it < T && ok; ++it) {
+          const int kb = vis_list[it < nvis ? it : it - nvis];
+          ok = load_k(it, kb);
+          if (ok && it >= nvis) ok = load_v(it - nvis, kb);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc(kKB), idesc_o = umma_idesc(kD);
+      bool ok = mbar_wait(bar(0), 0, abort_flag);
+      if (trace) trace[8] = global_timer_ns();          // Q has landed
+      auto pv = [&](int j) {        // O += P V of pass-2 block j
+        const int vs = j & 1, uv = j >> 1;
+        if (!mbar_wait(bar(13), j & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(5 + vs), uv & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t pdesc = smem_desc_sw128(smem_u32(Ps));
+        const uint64_t vdesc = smem_desc_sw128(smem_u32(Vs) + vs * kVBytes);
+#pragma unroll
+        for (int k = 0; k < kKB / kUmmaK; ++k)
+          umma_bf16(tmem_base + kColO, pdesc + 2 * k, vdesc + 2 * k, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar(7 + vs));
+        umma_commit(bar(14));
+        return true;
+      };
+      const int t_qk = one_pass ? nvis : T;
+      for (int it = 0; it < t_qk && ok; ++it) {
+        const int st = it & 1, u = it >> 1;
+        const int sb = one_pass ? it : st;               // S buffer
+        if (!mbar_wait(bar(1 + st), u & 1, abort_flag)) { ok = false; break; }
+        if (!one_pass && !mbar_wait(bar(11 + sb), (u & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_s = tmem_base + kColS + static_cast<uint32_t>(sb) * kKB;
+#pragma unroll
+        for (int kb4 = 0; kb4 < 4; ++kb4) {
+          const uint64_t qdesc = smem_desc_sw128(smem_u32(Qs) + kb4 * (128 * 128));
+          const uint64_t kdesc = smem_desc_sw128(smem_u32(Ks) + st * kKBytes + kb4 * (kKB * 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, (kb4 > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(3 + st));
+        umma_commit(bar(16 + sb));
+        if (!one_pass && it - 1 >= nvis) ok = pv(it - 1 - nvis);
+      }
+      if (one_pass) {
+        for (int j = 0; j < nvis && ok; ++j) ok = pv(j);
+      } else if (ok && nvis > 0) {
+        ok = pv(nvis - 1);
+      }
+      if (ok) umma_commit(bar(15));
+      if (trace) trace[9] = global_timer_ns();          // every MMA issued
+    }
+  } else if (warp < nw) {
+    // ------------------------------------------------------------------ softmax + epilogue: one thread per (head, row)
+    const int my = warp * 32 + lane;             // tile row = 16 * head + query row
+    const int head = my >> 4, qr = my & 15;
+    const bool real = head < G;
+    const int* q = kr + qr * 8;
+    const int a0 = q[5], e0 = q[0], a1 = q[1], e1 = q[2], a2 = q[3], e2 = q[4];
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int it = 0; it < T && ok; ++it) {
+      const int blk = it < nvis ? it : it - nvis;
+      const int kb = vis_list[blk];
+      const int sb = one_pass ? blk : (it & 1);          // S buffer
+      // (pass 2 of the one-pass form reads scores that pass 1 has already waited for)
+      if (!(one_pass && it >= nvis) && !mbar_wait(bar(16 + sb), one_pass ? 0 : ((it >> 1) & 1), abort_flag)) { ok = false; break; }
+      if (trace && my == 0 && (it == 0 || it == nvis)) trace[it == 0 ? 2 : 3] = global_timer_ns();   // first S of pass 1 / pass 2
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
+      const uint32_t taddr = tmem_base + lane_base + kColS + static_cast<uint32_t>(sb) * kKB;
+      tmem_ld32(taddr, s0);
+      tmem_ld32(taddr + 32, s1);
+      tmem_ld_wait();
+      if (!one_pass) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(11 + sb));        // this warp has consumed the S buffer
+      }
+      const uint32_t w0 = range_bits(a0, e0, 2 * kb) | range_bits(a1, e1, 2 * kb) | range_bits(a2, e2, 2 * kb);
+      const uint32_t w1 = range_bits(a0, e0, 2 * kb + 1) | range_bits(a1, e1, 2 * kb + 1) | range_bits(a2, e2, 2 * kb + 1);
+      if (it < nvis) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if ((w0 >> c) & 1u) m = fmaxf(m, __uint_as_float(s0[c]));
+          if ((w1 >> c) & 1u) m = fmaxf(m, __uint_as_float(s1[c]));
+        }
+      } else {
+        const int j = it - nvis;
+        const float mc = m * g.scale_log2e;
+        uint32_t pk[32];                                  // 64 probabilities as bf16 pairs
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = ((w0 >> c) & 1u) ? exp2f_fast(__uint_as_float(s0[c]) * g.scale_log2e - mc) : 0.f;
+          const float p1 = ((w0 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s0[c + 1]) * g.scale_log2e - mc) : 0.f;
+          const float p2 = ((w1 >> c) & 1u) ? exp2f_fast(__uint_as_float(s1[c]) * g.scale_log2e - mc) : 0.f;
+          const float p3 = ((w1 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s1[c + 1]) * g.scale_log2e - mc) : 0.f;
+          l += (p0 + p1) + (p2 + p3);
+          pk[c >> 1] = pack2(p0, p1);
+          pk[16 + (c >> 1)] = pack2(p2, p3);
+        }
+        if (!mbar_wait(bar(14), (j & 1) ^ 1, abort_flag)) { ok = false; break; }      // P V of the previous block has read P
+        // row `my` of the K-major swizzled tile: 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7)
+        uint8_t* prow = Ps + my * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (my & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(13));
+      }
+    }
+    // ---- att = bf16(O / l) of this thread's (head, row) into the staging tile [128][kStagePitch] (over Q and K, which no MMA
+    //      reads any more once O is complete); rows are 16 bytes longer than 512 so that the 32 rows of a warp spread over banks
+    if (trace && my == 0) trace[4] = global_timer_ns();      // last P handed over
+    prefetch_gates(tid);
+    if (ok) ok = mbar_wait(bar(15), 0, abort_flag);
+    if (trace && my == 0) trace[5] = global_timer_ns();      // O complete
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      uint8_t* srow = smem + my * kStagePitch;
+#pragma unroll
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_base + lane_base + kColO + c * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v8 = 0; v8 < 4; ++v8) {
+          float a[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(o[v8 * 8 + e]) * inv_l;
+          *reinterpret_cast<uint4*>(srow + c * 64 + v8 * 16) = pack8(a);
+        }
+      }
+    }
+  }
+  // ---- y = bf16(att * bf16(sigmoid(gate))): all six warps, consecutive threads on consecutive 16-byte pieces of a row, so
+  //      the gate is read and y is written in whole 512-byte rows
+  if (trace && tid == 0) trace[6] = global_timer_ns();       // staging written (warp 0)
+  if (warp >= nw) prefetch_gates(tid);
+  tc_fence_before();
+  __syncthreads();
+  if (!abort_flag[0]) {
+    // sigmoid(x) = 0.5 tanh(0.5 x) + 0.5: one special-function instruction per value (the exp / reciprocal form needs two, and
+    // this loop is bound by them). The gate factor is applied in fp32 and the product rounded once.
+    for (int base = tid; base < pieces; base += kBatch * kTcThreads) {
+      if (base != tid) prefetch_gates(base);      // (more than 16 pieces per thread only with seven or eight heads per kv head)
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int i = base + u * kTcThreads;
+        if (i < pieces) {
+          const int row = i >> 5, piece = i & 31;
+          float gv[8], a[8], out[8];
+          unpack8(gq[u], gv);
+          unpack8(*reinterpret_cast<const uint4*>(smem + row * kStagePitch + piece * 16), a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float t;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * gv[e]));
+            out[e] = a[e] * fmaf(0.5f, t, 0.5f);
+          }
+          *reinterpret_cast<uint4*>(g.y + (static_cast<int64_t>(r0 + (row & 15)) * g.HQ + (hq0 + (row >> 4))) * kD + piece * 8) = pack8(out);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (trace && tid == 0) trace[7] = global_timer_ns();
+  if (abort_flag[0]) {
+    if (tid == 0) report_status(g.status, OJB_DEV_WAIT_TIMEOUT);
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);       // copies that were already issued land before the CTA leaves
+    __syncthreads();
+  }
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+}  // namespace ojb
+
+using namespace ojb;
+
+extern "C" int ojb_tree_attn_set_trace(uint64_t* records) {
+  unsigned long long* p = reinterpret_cast<unsigned long long*>(records);
+  return launch_status(cudaMemcpyToSymbol(ojb::g_attn_trace, &p, sizeof(p)));
+}
+
+extern "C" int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t, const void* gate, const int32_t* krange, void* y,
+                                int64_t N, int64_t HQ, int64_t HKV, int64_t D, float scale, int32_t* status,
+                                ojb_stream_t stream) {
+  if (N == 0) return OJB_OK;
+  OJB_REQUIRE(qt && kt && vt_t && gate && krange && y && N > 0 && N % 32 == 0 && D == kD);
+  OJB_REQUIRE(HQ > 0 && HKV > 0 && HQ % HKV == 0 && (HQ / HKV) * kQRows <= 128);
+  OJB_REQUIRE(aligned16(qt) && aligned16(kt) && aligned16(vt_t) && aligned16(gate) && aligned16(y));
+  if ((N + kKB - 1) / kKB > kMaxBlocks) return OJB_ERR_LIMIT;
+  CUtensorMap map_q, map_k, map_vt;
+  int rc = make_map(&map_q, qt, HQ * N, kD, kQRows);
+  if (rc == OJB_OK) rc = make_map(&map_k, kt, HKV * N, kD, kKB);
+  if (rc == OJB_OK) rc = make_map(&map_vt, vt_t, HKV * kD, N, kD);
+  if (rc != OJB_OK) return rc;
+  const size_t smem = 1024 + kQBytes + 2 * kKBytes + 2 * kVBytes + kPBytes + 20 * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4;
+  static int smem_set[kMaxDevices] = {};
+  if (!raise_smem_limit(tree_attn_tc_kernel, static_cast<int>(smem), smem_set)) return OJB_ERR_LAUNCH;
+  AttnArgs a{static_cast<const bf16_t*>(gate), krange, static_cast<bf16_t*>(y), status, static_cast<int>(N), static_cast<int>(HQ),
+             static_cast<int>(HKV), static_cast<int>(HQ / HKV), scale * 1.4426950408889634f, gemm_wait_limit_ms()};
+  launch_kernel(tree_attn_tc_kernel, dim3(static_cast<unsigned>(HKV), static_cast<unsigned>(N / kQRows)), dim3(kTcThreads), smem,
+                static_cast<cudaStream_t>(stream), map_q, map_k, map_vt, a);
+  return launch_status(cudaGetLastError());
+}

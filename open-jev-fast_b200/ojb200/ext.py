@@ -141,8 +141,9 @@ def pack_bits(vis):
 
 
 # ------------------------------------------------------------------------------------------------ full attention
-def fullattn_prep2(proj, qw1, kw1, cosb, sinb, B, T, HQ, HKV, D, eps):
-    """src/ext.py:13 — returns [qt [B,HQ,T,D], kt [B,HKV,T,D], vt [B,HKV,T,D], gate [B*T, HQ*D]]."""
+def fullattn_prep2(proj, qw1, kw1, cosb, sinb, B, T, HQ, HKV, D, eps, with_vt_t=False):
+    """src/ext.py:13 — returns [qt [B,HQ,T,D], kt [B,HKV,T,D], vt [B,HKV,T,D], gate [B*T, HQ*D]]; with_vt_t=True appends V with
+    keys contiguous, [B, HKV, D, T] (operand layout of fattn_tree_tc)."""
     _chk(proj, qw1, kw1, cosb, sinb)
     N = B * T
     RD = cosb.shape[-1]
@@ -153,13 +154,15 @@ def fullattn_prep2(proj, qw1, kw1, cosb, sinb, B, T, HQ, HKV, D, eps):
     kt = torch.empty(B, HKV, T, D, dtype=bf16, device=dev)
     vt = torch.empty(B, HKV, T, D, dtype=bf16, device=dev)
     gate = torch.empty(N, HQ * D, dtype=bf16, device=dev)
+    vt_t = torch.empty(B, HKV, D, T, dtype=bf16, device=dev) if with_vt_t else None
     cosb = cosb.reshape(N, RD)
     sinb = sinb.reshape(N, RD)
     for b in range(B):
         sl = slice(b * T, (b + 1) * T)
         call("ojb_fullattn_prep", ptr(proj[sl]), ptr(qw1), ptr(kw1), ptr(cosb[sl]), ptr(sinb[sl]), ptr(qt[b]), ptr(kt[b]),
-             ptr(vt[b]), ptr(gate[sl]), i64(T), i64(HQ), i64(HKV), i64(D), i64(RD), f32(eps), stream_ptr())
-    return [qt, kt, vt, gate]
+             ptr(vt[b]), ptr(None if vt_t is None else vt_t[b]), ptr(gate[sl]), i64(T), i64(HQ), i64(HKV), i64(D), i64(RD),
+             f32(eps), stream_ptr())
+    return [qt, kt, vt, gate] + ([vt_t] if with_vt_t else [])
 
 
 fullattn_prep = fullattn_prep2   # src/ext.py:10 — same contract
@@ -554,6 +557,21 @@ def fattn_tree3(qt, kt, vt, gate, sig, vbits, scale):
 def fattn_tree_ranges(qt, kt, vt, gate, krange, scale, gq):
     """Same attention with the mask given as three key ranges per row (lay.krange): no N x N structure anywhere."""
     return _tree_attn(qt, kt, vt, gate, None, krange, scale, gq)
+
+
+def fattn_tree_tc(qt, kt, vt_t, gate, krange, scale):
+    """Tree attention + gate on the tcgen05 tensor cores (ojb_tree_attn_tc): head dim 256, at most 8 query heads per kv head,
+    mask from the three key ranges per row. qt [1, HQ, N, 256], kt [1, HKV, N, 256], vt_t [1, HKV, 256, N] (fullattn_prep2 with
+    with_vt_t=True), gate [N, HQ*256] -> y [N, HQ*256]."""
+    _chk(qt, kt, vt_t, gate, krange)
+    _, HQ, N, D = qt.shape
+    HKV = kt.shape[1]
+    if D != 256 or N % 32 or HQ % HKV or HQ // HKV > 8 or tuple(vt_t.shape) != (1, HKV, D, N):
+        raise RuntimeError("fattn_tree_tc: head dim 256, N % 32 == 0, HQ/HKV <= 8 and vt_t [1, HKV, 256, N] required")
+    y = torch.empty(N, HQ * D, dtype=bf16, device=qt.device)
+    call("ojb_tree_attn_tc", ptr(qt), ptr(kt), ptr(vt_t), ptr(gate), ptr(krange), ptr(y), i64(N), i64(HQ), i64(HKV), i64(D),
+         f32(scale), ptr(_lib.status_word(qt.device)), stream_ptr())
+    return y
 
 
 def fattn_tree2(proj, qw1, kw1, cosb, sinb, sig, vbits, HQ, HKV, scale, eps):

@@ -33,6 +33,7 @@ SK_FULL_OUT = int(os.environ.get("OJ_SK_FULL_OUT", "0"))   # split-K of the atte
 SK_DOWN = int(os.environ.get("OJ_SK_DOWN", "0"))           # split-K of the MLP down-projection
 FATTN = int(os.environ.get("OJ_FATTN", "0"))               # query heads per CTA of the tree attention (3 or 6); 0 = by row count
 FATTN_MAX = int(os.environ.get("OJ_FATTN_MAX", "1000000000"))   # kept for compatibility: the kernel serves every N
+FATTN_TC = os.environ.get("OJ_FATTN_TC", "1") == "1"            # tcgen05 / TMA attention kernel (head dim 256, key-range mask)
 GDN_FUSED, GDN_VER, PREP, GVA, LUT, SK2 = True, 6, "dedup", True, True, True
 TREE_NATIVE = os.environ.get("OJ_TREE_NATIVE", "1") == "1"      # 0: replicated per-candidate GDN layout of the reference
 # 1: conv + SiLU + L2 norm + gates inside the first Gated DeltaNet launch (same bits, one launch fewer per layer). Measured:
@@ -304,8 +305,11 @@ class FastQwen35(torch.nn.Module):
 
     def _attn_tree(self, d, proj, lay, cos, sin):
         N = proj.shape[0]
-        qt, kt, vt, gate = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps)
         G = d.HQ // d.HKV
+        if FATTN_TC and hasattr(lay, "krange") and d.D == 256 and G <= 8 and N % 32 == 0:
+            qt, kt, vt, gate, vt_t = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps, with_vt_t=True)
+            return K.fattn_tree_tc(qt, kt, vt_t, gate, lay.krange, d.scale)
+        qt, kt, vt, gate = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps)
         # measured: 3 heads per CTA (twice the CTAs) is faster up to a few hundred rows (17.7 vs 21.5 us at 288), 6 heads per
         # CTA (each K / V tile loaded once per kv head) above (44 vs 54 us at 544)
         want = FATTN if FATTN else (3 if N <= 384 else 6)

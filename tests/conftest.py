@@ -21,3 +21,15 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _device_wait_limit():
+    """OJB_TEST_WAIT_MS=<ms> shortens the limit of the kernels' bounded device-side waits for the whole run (a protocol mistake
+    in a kernel under development then ends its launch after that time with a status word instead of after the default 2 s)."""
+    ms = os.environ.get("OJB_TEST_WAIT_MS")
+    if ms:
+        import ctypes
+        from ojb200 import _lib
+        _lib.lib().ojb_gemm_set_wait_limit_ms(ctypes.c_int32(int(ms)))
+    yield

@@ -44,6 +44,44 @@ def test_tree_attention(N_case, HQ, HKV, D, gq, mask_form):
     assert (got - ref).abs().max().item() < 3e-2
 
 
+@pytest.mark.parametrize("N_case,HQ,HKV", [("baseline", 24, 4), ("example", 24, 4), ("ragged", 4, 2), ("doc", 8, 1), ("wide", 6, 2),
+                                           ("long", 12, 2), ("nostem", 5, 1)])
+def test_tree_attention_tcgen05(N_case, HQ, HKV):
+    """The tcgen05 / TMA attention kernel (head dim 256, key-range mask, all query heads of a kv head in one 128-row tile)
+    against the masked-softmax oracle, and against the mma.sync kernel on the same inputs."""
+    from ojb200 import ext as K, _lib
+    from ojb200 import layout as PL
+    D = 256
+    seqs, groups, pad_id, NB, PB = trees.layout_cases()[N_case]
+    ids, lay = PL.gtree_build(seqs, groups, pad_id, NB, PB, dev="cuda", dense=False)
+    N, RD = lay.N, D // 4
+    g = torch.Generator().manual_seed(23)
+    proj = torch.randn(N, 2 * HQ * D + 2 * HKV * D, generator=g).to(bf16)
+    qw1 = 1.0 + torch.randn(D, generator=g) * 0.02
+    kw1 = 1.0 + torch.randn(D, generator=g) * 0.02
+    inv_freq = 1.0 / (10000 ** (torch.arange(0, RD, 2).float() / RD))
+    ang = lay.pos.cpu().float()[:, None] * inv_freq[None]
+    cosb, sinb = torch.cat([ang.cos()] * 2, -1).to(bf16), torch.cat([ang.sin()] * 2, -1).to(bf16)
+    scale = D ** -0.5
+    qt, kt, vt, gate, vt_t = K.fullattn_prep2(proj.cuda(), qw1.cuda(), kw1.cuda(), cosb.cuda(), sinb.cuda(), 1, N, HQ, HKV, D, 1e-6,
+                                              with_vt_t=True)
+    assert torch.equal(vt_t[0].transpose(1, 2).contiguous(), vt[0])
+    y = K.fattn_tree_tc(qt, kt, vt_t, gate, lay.krange, scale)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    vis = torch.as_tensor(OL.gtree_layout(seqs, groups, pad_id, NB, PB)["vis"])
+    ref = O.tree_attention(qt[0].cpu(), kt[0].cpu(), vt[0].cpu(), gate.cpu(), vis, scale).float()
+    got = y.float().cpu()
+    real = lay.rowmask.cpu().bool()
+    rel = ((got[real] - ref[real]).norm() / ref[real].norm()).item()
+    assert rel < 4e-3, rel
+    assert (got[real] - ref[real]).abs().max().item() < 3e-2
+    G = HQ // HKV
+    gq = 3 if G % 3 == 0 else (2 if G % 2 == 0 else 1)
+    old = K.fattn_tree_ranges(qt, kt, vt, gate, lay.krange, scale, gq).float().cpu()
+    assert ((got[real] - old[real]).norm() / old[real].norm()).item() < 4e-3
+
+
 def _small_model(seed=0):
     from ojb200 import modelgen as MG
     cfg = MG.make_config(**MG.SMALL)
