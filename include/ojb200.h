@@ -284,12 +284,13 @@ int ojb_tree_attn(const void* qt, const void* kt, const void* vt, const void* ga
                   ojb_stream_t stream);
 
 /* The same attention on the tcgen05 tensor cores (head dim 256, key-range mask only): one CTA per (kv head, 16 query rows)
- * stacks the rows of all HQ/HKV <= 8 query heads of the kv head into one 128-row operand tile; Q, K and V blocks arrive by
+ * stacks the rows of all HQ/HKV <= 6 query heads of the kv head into one operand tile; Q, K and V blocks of 128 keys arrive by
  * TMA, Q K^T and P V are tcgen05.mma with S, P's source and O in tensor memory; two-pass softmax (row maxima first, then
- * P = exp2((s - max) scale log2 e) and O += P V) in the exp2 domain. vt_t bf16 [HKV, 256, N] is V with keys contiguous
- * (second V output of ojb_fullattn_prep). Same result as ojb_tree_attn up to the rounding of P and the summation order.
- * `status` receives OJB_DEV_WAIT_TIMEOUT if a bounded device-side wait ran out. Replaces the same reference code as
- * ojb_tree_attn (src/kernels.cu:4287-4458; above 384 rows src/fastmodel.py:470-473). */
+ * P = exp2((s - max) scale log2 e) and O += P V) in the exp2 domain; the gate factor sigmoid(gate) is applied in fp32.
+ * vt_t bf16 [HKV, 256, N] is V with keys contiguous (second V output of ojb_fullattn_prep). Same result as ojb_tree_attn up to
+ * the rounding of P, of the gate factor and the summation order. `status` receives OJB_DEV_WAIT_TIMEOUT if a bounded
+ * device-side wait ran out. Replaces the same reference code as ojb_tree_attn (src/kernels.cu:4287-4458; above 384 rows
+ * src/fastmodel.py:470-473). */
 int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t, const void* gate, const int32_t* krange, void* y,
                      int64_t N, int64_t HQ, int64_t HKV, int64_t D, float scale, int32_t* status, ojb_stream_t stream);
 

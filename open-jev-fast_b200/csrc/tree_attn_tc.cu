@@ -1,22 +1,27 @@
 // Prefix-tree GQA attention on the tcgen05 tensor cores (head dim 256), with the sigmoid output gate fused in.
 //
-// One CTA = one kv head x 16 query rows x ALL query heads of that kv head: the G <= 8 heads share K and V, so their rows are
-// stacked into one 128-row operand tile (row 16 w + r = head w, query row r) and every K / V tile that reaches the SM is
-// used by all of them. Keys are visited in blocks of 64; a block is skipped when none of the 16 rows sees any of its keys
-// (the mask is three half-open key ranges per row: root, own question stem, own leaf up to the row itself).
+// One CTA = one kv head x 16 query rows x ALL query heads of that kv head: the G <= 6 heads share K and V, so their rows are
+// stacked into one operand tile (row 16 w + r = head w, query row r; M = 128 in the instruction, the rows past 16 G are never
+// looked at) and every K / V tile that reaches the SM is used by all of them. Keys are visited in blocks of 128; a block is
+// skipped when none of the 16 rows sees any of its keys (the mask is three half-open key ranges per row: root, own question
+// stem, own leaf up to the row itself).
 //
-//   S = Q K^T   tcgen05.mma, M = 128, N = 64, K = 256: Q [128 x 256] and the K block [64 x 256] are K-major 128-byte-swizzled
-//               tiles written by TMA; S lives in tensor memory (two 64-column buffers, so the product of the next block runs
-//               while the softmax warps work on this one)
-//   softmax     four warps, one thread per (head, row) = one lane of tensor memory: tcgen05.ld of its 64 scores, mask, exp2
-//   O += P V    P is written as a bf16 K-major swizzled tile [128 x 64] by the softmax threads; V arrives transposed
-//               ([256 x N], written by the prep kernel), so the V block [256 d x 64 keys] is K-major too; O [128 x 256] fp32
+//   S = Q K^T   tcgen05.mma, M = 128, N = 128, K = 256: Q and the K block [128 x 256] are K-major 128-byte-swizzled tiles
+//               written by TMA; S lives in tensor memory (two 128-column buffers, so the product of the next block runs while
+//               the softmax warps work on this one)
+//   softmax     one thread per (head, row) = one lane of tensor memory: tcgen05.ld of its 128 scores, mask, exp2
+//   O += P V    P is written as a bf16 K-major swizzled tile [128 x 128] by the softmax threads; V arrives transposed
+//               ([256 x N], written by the prep kernel), so the V block [256 d x 128 keys] is K-major too; O [128 x 256] fp32
 //               stays in tensor memory for the whole CTA
 //
 // The softmax is two-pass: pass 1 runs Q K^T over the visible blocks and keeps only the row maxima, pass 2 forms
-// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. With at most four visible key blocks all
-// scores stay in tensor memory between the passes; with more, pass 2 recomputes the (cheap) Q K^T products. Roles: warps 0-3 softmax / epilogue, warp 4 TMA producer, warp 5 MMA issuer; mbarriers between them,
-// every wait bounded (the CTA then reports OJB_DEV_WAIT_TIMEOUT through `status`, frees its tensor memory and returns).
+// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. With at most two visible key blocks all
+// scores stay in tensor memory between the passes; with more, pass 2 recomputes the (cheap) Q K^T products.
+// Shared memory holds Q (48 KB), two 64 KB regions for K / V blocks and P (32 KB): in pass 1 the regions alternate as K
+// stages; in pass 2 region 0 takes the K block and region 1 the V block of a key block (the natural stagger of Q K^T ->
+// softmax -> P V hides their loads).
+// Roles: warps 0-3 softmax / epilogue, warp 4 TMA producer, warp 5 MMA issuer; mbarriers between them, every wait bounded (the
+// CTA then reports OJB_DEV_WAIT_TIMEOUT through `status`, frees its tensor memory and returns).
 #include "gemm_common.cuh"
 
 namespace ojb {
@@ -24,16 +29,17 @@ namespace {
 
 constexpr int kD = 256;
 constexpr int kQRows = 16;            // query rows per CTA and head
-constexpr int kKB = 64;               // keys per block
+constexpr int kMaxG = 6;              // query heads per kv head that fit the shared-memory plan
+constexpr int kKB = 128;              // keys per block
 constexpr int kTcThreads = 192;
-constexpr uint32_t kQBytes = 128 * kD * 2;     // 4 k-blocks of [128 rows][64]
-constexpr uint32_t kKBytes = kKB * kD * 2;     // 4 k-blocks of [64 keys][64]
-constexpr uint32_t kVBytes = kD * kKB * 2;     // [256 d][64 keys]
-constexpr uint32_t kPBytes = 128 * kKB * 2;    // [128 rows][64 keys]
+constexpr uint32_t kQBytes = kMaxG * kQRows * kD * 2;    // 4 k-blocks of [16 G rows][64]
+constexpr uint32_t kRegion = kKB * kD * 2;               // 64 KB: a K block (4 k-blocks of [128 keys][64]) or a V block (2 of [256 d][64])
+constexpr uint32_t kPBytes = 128 * kKB * 2;              // 2 k-blocks of [128 rows][64 keys]
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS = 256;     // O: 256 columns; S: two buffers of 64 columns
-constexpr int kStagePitch = kD * 2 + 16;       // bytes per row of the output staging tile
-constexpr int kMaxBlocks = 1024;               // key blocks a CTA can list (65 536 keys)
+constexpr uint32_t kColO = 0, kColS = 256;               // O: 256 columns; S: two buffers of 128 columns
+constexpr int kStagePitch = kD * 2 + 16;                 // bytes per row of the output staging tile
+constexpr int kMaxBlocks = 1024;                         // key blocks a CTA can list (131 072 keys)
+enum { kBarQ = 0, kBarFull = 1, kBarFree = 3, kBarSFull = 5, kBarSFree = 7, kBarPFull = 9, kBarPFree = 10, kBarO = 11, kNumBars = 12 };
 
 // Measurement hook (ojb_tree_attn_set_trace): when non-null, the CTA of kv head 0 and the last-but-one block of query rows
 // stores %globaltimer at a few points of its life (see the stamps below).
@@ -66,13 +72,10 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* Qs = smem;
-  uint8_t* Ks = Qs + kQBytes;                  // two stages
-  uint8_t* Vs = Ks + 2 * kKBytes;              // two stages
-  uint8_t* Ps = Vs + 2 * kVBytes;
+  uint8_t* Rg = Qs + kQBytes;                  // two regions
+  uint8_t* Ps = Rg + 2 * kRegion;
   uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + kPBytes);
-  // barriers: 0 q_full | 1-2 k_full | 3-4 k_free | 5-6 v_full | 7-8 v_free | 9-10 s_full | 11-12 s_free | 13 p_full | 14 p_free
-  //           | 15 o_full | 16-19 s_full of the four S buffers of the one-pass form
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);      // [0] give-up flag, [1] wait limit in ms
   int* kr = reinterpret_cast<int*>(tmem_slot + 4);                                 // [16 rows][8]
   int* vis_list = kr + kQRows * 8;                                                 // visible key blocks; count at [kMaxBlocks]
@@ -84,14 +87,12 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int G = g.G, N = g.N;
   const int nw = (G * kQRows + 31) / 32;       // softmax warps that own real rows
   const int hq0 = kvh * G;
+  const uint32_t qstride = static_cast<uint32_t>(G) * (kQRows * 128);      // bytes of one k-block of the Q tile: [16 G rows][128 B]
 
   if (tid == 0) {
-    mbar_init(bar(0), 1);
-    for (int i = 1; i <= 10; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(11), nw); mbar_init(bar(12), nw);
-    mbar_init(bar(13), nw);
-    mbar_init(bar(14), 1); mbar_init(bar(15), 1);
-    for (int i = 16; i < 20; ++i) mbar_init(bar(i), 1);
+    for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), 1);
+    mbar_init(bar(kBarSFree), nw); mbar_init(bar(kBarSFree + 1), nw);
+    mbar_init(bar(kBarPFull), nw);
     abort_flag[0] = 0;
     abort_flag[1] = g.wait_ms;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -111,12 +112,12 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (warp == 4 && lane == 0) {      // the Q rows do not depend on the list of key blocks: requested while warp 0 builds it
-    mbar_expect_tx(bar(0), static_cast<uint32_t>(G) * 4u * (kQRows * 128u));
+    mbar_expect_tx(bar(kBarQ), static_cast<uint32_t>(G) * 4u * (kQRows * 128u));
     for (int w = 0; w < G; ++w)
       for (int kb4 = 0; kb4 < 4; ++kb4)
-        tma_load_2d(smem_u32(Qs) + kb4 * (128 * 128) + w * (kQRows * 128), &map_q, bar(0), kb4 * 64, (hq0 + w) * N + r0);
+        tma_load_2d(smem_u32(Qs) + kb4 * qstride + w * (kQRows * 128), &map_q, bar(kBarQ), kb4 * 64, (hq0 + w) * N + r0);
   }
-  // ordered list of the 64-key blocks that at least one of the 16 rows sees
+  // ordered list of the 128-key blocks that at least one of the 16 rows sees
   const int NB = (N + kKB - 1) / kKB;
   if (warp == 0) {
     int count = 0;
@@ -140,9 +141,9 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   const int nvis = vis_list[kMaxBlocks];
   const int T = 2 * nvis;                       // pass 1 (maxima) then pass 2 (P V) over the same blocks
-  // Up to four key blocks: the scores of all of them fit in tensor memory beside O (4 x 64 columns), so Q K^T runs once and
-  // pass 2 reads the scores again from there. More blocks: two S buffers in rotation, Q K^T recomputed in pass 2.
-  const bool one_pass = nvis <= 4;
+  // Up to two key blocks: the scores of both fit in tensor memory beside O, so Q K^T runs once and pass 2 reads the scores
+  // again from there. More blocks: the two S buffers rotate and pass 2 recomputes Q K^T.
+  const bool one_pass = nvis <= 2;
   // Gate values of the 16 output pieces this thread multiplies at the very end (consecutive threads take consecutive 16-byte
   // pieces of the [G * 16 rows][256] output tile). Each warp requests them as soon as it has nothing else to wait for, so their
   // latency runs under the last P V products and the staging of O.
@@ -165,34 +166,31 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      int use[2] = {0, 0};
       bool ok = true;
-      auto load_k = [&](int it, int kb) {
-        const int st = it & 1, u = it >> 1;
-        if (!mbar_wait(bar(3 + st), (u & 1) ^ 1, abort_flag)) return false;
-        mbar_expect_tx(bar(1 + st), kKBytes);
-        for (int kb4 = 0; kb4 < 4; ++kb4)
-          tma_load_2d(smem_u32(Ks) + st * kKBytes + kb4 * (kKB * 128), &map_k, bar(1 + st), kb4 * 64, kvh * N + kb * kKB);
-        return true;
-      };
-      auto load_v = [&](int j, int kb) {
-        const int vs = j & 1, uv = j >> 1;
-        if (!mbar_wait(bar(7 + vs), (uv & 1) ^ 1, abort_flag)) return false;
-        mbar_expect_tx(bar(5 + vs), kVBytes);
-        tma_load_2d(smem_u32(Vs) + vs * kVBytes, &map_vt, bar(5 + vs), kb * kKB, kvh * kD);
+      auto load = [&](int R, bool is_v, int kb) {     // the K block or the V block of key block kb into region R
+        if (!mbar_wait(bar(kBarFree + R), (use[R] & 1) ^ 1, abort_flag)) return false;
+        ++use[R];
+        mbar_expect_tx(bar(kBarFull + R), kRegion);
+        const uint32_t dst = smem_u32(Rg) + R * kRegion;
+        if (!is_v) {
+          for (int kb4 = 0; kb4 < 4; ++kb4) tma_load_2d(dst + kb4 * (kKB * 128), &map_k, bar(kBarFull + R), kb4 * 64, kvh * N + kb * kKB);
+        } else {
+          for (int kb2 = 0; kb2 < 2; ++kb2) tma_load_2d(dst + kb2 * (kD * 128), &map_vt, bar(kBarFull + R), kb * kKB + kb2 * 64, kvh * kD);
+        }
         return true;
       };
       if (one_pass) {
-        // K 0, K 1, V 0, V 1 need no stage to become free; the later K blocks wait for Q K^T of two blocks earlier, the later V
-        // blocks for P V of two blocks earlier, which only starts after every Q K^T: all K loads come before those V loads
-        for (int it = 0; it < nvis && it < 2 && ok; ++it) ok = load_k(it, vis_list[it]);
-        for (int j = 0; j < nvis && j < 2 && ok; ++j) ok = load_v(j, vis_list[j]);
-        for (int it = 2; it < nvis && ok; ++it) ok = load_k(it, vis_list[it]);
-        for (int j = 2; j < nvis && ok; ++j) ok = load_v(j, vis_list[j]);
+        for (int it = 0; it < nvis && ok; ++it) ok = load(it, false, vis_list[it]);
+        for (int j = 0; j < nvis && ok; ++j) ok = load(j, true, vis_list[j]);       // region j is free once Q K^T of block j is done
       } else {
-        for (int it = 0; it < T && ok; ++it) {
-          const int kb = vis_list[it < nvis ? it : it - nvis];
-          ok = load_k(it, kb);
-          if (ok && it >= nvis) ok = load_v(it - nvis, kb);
+        for (int it = 0; it < nvis && ok; ++it) ok = load(it & 1, false, vis_list[it]);
+        // pass 2: region 0 is free again when Q K^T of the block before is done, region 1 when P V of the block before is done;
+        // Q K^T (j) is issued before P V (j - 1), so the K block of j + 1 is asked for before the V block of j
+        if (ok) ok = load(0, false, vis_list[0]);
+        for (int j = 0; j < nvis && ok; ++j) {
+          if (j + 1 < nvis) ok = load(0, false, vis_list[j + 1]);
+          if (ok) ok = load(1, true, vis_list[j]);
         }
       }
     }
@@ -200,115 +198,137 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(kKB), idesc_o = umma_idesc(kD);
-      bool ok = mbar_wait(bar(0), 0, abort_flag);
+      int use[2] = {0, 0}, use_s[2] = {0, 0};
+      bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
       if (trace) trace[8] = global_timer_ns();          // Q has landed
-      auto pv = [&](int j) {        // O += P V of pass-2 block j
-        const int vs = j & 1, uv = j >> 1;
-        if (!mbar_wait(bar(13), j & 1, abort_flag)) return false;
-        if (!mbar_wait(bar(5 + vs), uv & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint64_t pdesc = smem_desc_sw128(smem_u32(Ps));
-        const uint64_t vdesc = smem_desc_sw128(smem_u32(Vs) + vs * kVBytes);
-#pragma unroll
-        for (int k = 0; k < kKB / kUmmaK; ++k)
-          umma_bf16(tmem_base + kColO, pdesc + 2 * k, vdesc + 2 * k, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(bar(7 + vs));
-        umma_commit(bar(14));
-        return true;
-      };
-      const int t_qk = one_pass ? nvis : T;
-      for (int it = 0; it < t_qk && ok; ++it) {
-        const int st = it & 1, u = it >> 1;
-        const int sb = one_pass ? it : st;               // S buffer
-        if (!mbar_wait(bar(1 + st), u & 1, abort_flag)) { ok = false; break; }
-        if (!one_pass && !mbar_wait(bar(11 + sb), (u & 1) ^ 1, abort_flag)) { ok = false; break; }
+      auto qk = [&](int R, int sb) {                    // S[sb] = Q K^T with the K block in region R
+        if (!mbar_wait(bar(kBarFull + R), use[R] & 1, abort_flag)) return false;
+        ++use[R];
+        if (!one_pass && !mbar_wait(bar(kBarSFree + sb), (use_s[sb] & 1) ^ 1, abort_flag)) return false;
+        ++use_s[sb];
         tc_fence_after();
         const uint32_t tmem_s = tmem_base + kColS + static_cast<uint32_t>(sb) * kKB;
 #pragma unroll
         for (int kb4 = 0; kb4 < 4; ++kb4) {
-          const uint64_t qdesc = smem_desc_sw128(smem_u32(Qs) + kb4 * (128 * 128));
-          const uint64_t kdesc = smem_desc_sw128(smem_u32(Ks) + st * kKBytes + kb4 * (kKB * 128));
+          const uint64_t qdesc = smem_desc_sw128(smem_u32(Qs) + kb4 * qstride);
+          const uint64_t kdesc = smem_desc_sw128(smem_u32(Rg) + R * kRegion + kb4 * (kKB * 128));
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, (kb4 > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(bar(3 + st));
-        umma_commit(bar(16 + sb));
-        if (!one_pass && it - 1 >= nvis) ok = pv(it - 1 - nvis);
-      }
+        umma_commit(bar(kBarFree + R));
+        umma_commit(bar(kBarSFull + sb));
+        return true;
+      };
+      auto pv = [&](int j, int R) {                     // O += P V of pass-2 block j, V block in region R
+        if (!mbar_wait(bar(kBarPFull), j & 1, abort_flag)) return false;
+        if (!mbar_wait(bar(kBarFull + R), use[R] & 1, abort_flag)) return false;
+        ++use[R];
+        tc_fence_after();
+#pragma unroll
+        for (int kb2 = 0; kb2 < 2; ++kb2) {
+          const uint64_t pdesc = smem_desc_sw128(smem_u32(Ps) + kb2 * (128 * 128));
+          const uint64_t vdesc = smem_desc_sw128(smem_u32(Rg) + R * kRegion + kb2 * (kD * 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + kColO, pdesc + 2 * k, vdesc + 2 * k, idesc_o, (j > 0 || kb2 > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(kBarFree + R));
+        umma_commit(bar(kBarPFree));
+        return true;
+      };
       if (one_pass) {
-        for (int j = 0; j < nvis && ok; ++j) ok = pv(j);
-      } else if (ok && nvis > 0) {
-        ok = pv(nvis - 1);
+        for (int it = 0; it < nvis && ok; ++it) ok = qk(it, it);
+        for (int j = 0; j < nvis && ok; ++j) ok = pv(j, j);
+      } else {
+        for (int it = 0; it < nvis && ok; ++it) ok = qk(it & 1, it & 1);
+        for (int j = 0; j < nvis && ok; ++j) {
+          ok = qk(0, (nvis + j) & 1);
+          if (ok && j > 0) ok = pv(j - 1, 1);
+        }
+        if (ok && nvis > 0) ok = pv(nvis - 1, 1);
       }
-      if (ok) umma_commit(bar(15));
+      if (ok) umma_commit(bar(kBarO));
       if (trace) trace[9] = global_timer_ns();          // every MMA issued
     }
   } else if (warp < nw) {
     // ------------------------------------------------------------------ softmax + epilogue: one thread per (head, row)
     const int my = warp * 32 + lane;             // tile row = 16 * head + query row
-    const int head = my >> 4, qr = my & 15;
-    const bool real = head < G;
+    const int qr = my & 15;
     const int* q = kr + qr * 8;
     const int a0 = q[5], e0 = q[0], a1 = q[1], e1 = q[2], a2 = q[3], e2 = q[4];
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     float m = -INFINITY, l = 0.f;
+    int use_s[2] = {0, 0};
     bool ok = true;
     for (int it = 0; it < T && ok; ++it) {
-      const int blk = it < nvis ? it : it - nvis;
+      const bool pass2 = it >= nvis;
+      const int blk = pass2 ? it - nvis : it;
       const int kb = vis_list[blk];
       const int sb = one_pass ? blk : (it & 1);          // S buffer
       // (pass 2 of the one-pass form reads scores that pass 1 has already waited for)
-      if (!(one_pass && it >= nvis) && !mbar_wait(bar(16 + sb), one_pass ? 0 : ((it >> 1) & 1), abort_flag)) { ok = false; break; }
+      if (!(one_pass && pass2)) {
+        if (!mbar_wait(bar(kBarSFull + sb), use_s[sb] & 1, abort_flag)) { ok = false; break; }
+        ++use_s[sb];
+      }
       if (trace && my == 0 && (it == 0 || it == nvis)) trace[it == 0 ? 2 : 3] = global_timer_ns();   // first S of pass 1 / pass 2
       tc_fence_after();
-      uint32_t s0[32], s1[32];
-      const uint32_t taddr = tmem_base + lane_base + kColS + static_cast<uint32_t>(sb) * kKB;
-      tmem_ld32(taddr, s0);
-      tmem_ld32(taddr + 32, s1);
-      tmem_ld_wait();
-      if (!one_pass) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(11 + sb));        // this warp has consumed the S buffer
+      const float mc = m * g.scale_log2e;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {             // 64 scores at a time
+        uint32_t s0[32], s1[32];
+        const uint32_t taddr = tmem_base + lane_base + kColS + static_cast<uint32_t>(sb) * kKB + half * 64;
+        tmem_ld32(taddr, s0);
+        tmem_ld32(taddr + 32, s1);
+        tmem_ld_wait();
+        if (half == 1 && !one_pass) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarSFree + sb));        // this warp has consumed the S buffer
+        }
+        const int w = 4 * kb + 2 * half;
+        const uint32_t w0 = range_bits(a0, e0, w) | range_bits(a1, e1, w) | range_bits(a2, e2, w);
+        const uint32_t w1 = range_bits(a0, e0, w + 1) | range_bits(a1, e1, w + 1) | range_bits(a2, e2, w + 1);
+        if (!pass2) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if ((w0 >> c) & 1u) m = fmaxf(m, __uint_as_float(s0[c]));
+            if ((w1 >> c) & 1u) m = fmaxf(m, __uint_as_float(s1[c]));
+          }
+        } else {
+          uint32_t pk[32];                                // 64 probabilities as bf16 pairs
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float p0 = ((w0 >> c) & 1u) ? exp2f_fast(__uint_as_float(s0[c]) * g.scale_log2e - mc) : 0.f;
+            const float p1 = ((w0 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s0[c + 1]) * g.scale_log2e - mc) : 0.f;
+            const float p2 = ((w1 >> c) & 1u) ? exp2f_fast(__uint_as_float(s1[c]) * g.scale_log2e - mc) : 0.f;
+            const float p3 = ((w1 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s1[c + 1]) * g.scale_log2e - mc) : 0.f;
+            l += (p0 + p1) + (p2 + p3);
+            pk[c >> 1] = pack2(p0, p1);
+            pk[16 + (c >> 1)] = pack2(p2, p3);
+          }
+          // P V of the previous block must have read P before the first piece of this block's P is written
+          if (half == 0 && !mbar_wait(bar(kBarPFree), ((it - nvis) & 1) ^ 1, abort_flag)) ok = false;
+          if (ok) {
+            // row `my` of k-block `half` of the K-major swizzled tile: 128 bytes = 8 chunks of 16, chunk c stored at c ^ (row & 7)
+            uint8_t* prow = Ps + half * (128 * 128) + my * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(prow + ((c ^ (my & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          }
+        }
       }
-      const uint32_t w0 = range_bits(a0, e0, 2 * kb) | range_bits(a1, e1, 2 * kb) | range_bits(a2, e2, 2 * kb);
-      const uint32_t w1 = range_bits(a0, e0, 2 * kb + 1) | range_bits(a1, e1, 2 * kb + 1) | range_bits(a2, e2, 2 * kb + 1);
-      if (it < nvis) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if ((w0 >> c) & 1u) m = fmaxf(m, __uint_as_float(s0[c]));
-          if ((w1 >> c) & 1u) m = fmaxf(m, __uint_as_float(s1[c]));
-        }
-      } else {
-        const int j = it - nvis;
-        const float mc = m * g.scale_log2e;
-        uint32_t pk[32];                                  // 64 probabilities as bf16 pairs
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float p0 = ((w0 >> c) & 1u) ? exp2f_fast(__uint_as_float(s0[c]) * g.scale_log2e - mc) : 0.f;
-          const float p1 = ((w0 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s0[c + 1]) * g.scale_log2e - mc) : 0.f;
-          const float p2 = ((w1 >> c) & 1u) ? exp2f_fast(__uint_as_float(s1[c]) * g.scale_log2e - mc) : 0.f;
-          const float p3 = ((w1 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s1[c + 1]) * g.scale_log2e - mc) : 0.f;
-          l += (p0 + p1) + (p2 + p3);
-          pk[c >> 1] = pack2(p0, p1);
-          pk[16 + (c >> 1)] = pack2(p2, p3);
-        }
-        if (!mbar_wait(bar(14), (j & 1) ^ 1, abort_flag)) { ok = false; break; }      // P V of the previous block has read P
-        // row `my` of the K-major swizzled tile: 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (row & 7)
-        uint8_t* prow = Ps + my * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(prow + ((c ^ (my & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      if (pass2 && ok) {
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(13));
+        if (lane == 0) mbar_arrive(bar(kBarPFull));
       }
     }
-    // ---- att = bf16(O / l) of this thread's (head, row) into the staging tile [128][kStagePitch] (over Q and K, which no MMA
-    //      reads any more once O is complete); rows are 16 bytes longer than 512 so that the 32 rows of a warp spread over banks
+    // ---- att = bf16(O / l) of this thread's (head, row) into the staging tile [128][kStagePitch] (over Q and region 0, which
+    //      no MMA reads any more once O is complete); rows are 16 bytes longer than 512 so that the 32 rows of a warp spread
+    //      over the banks
     if (trace && my == 0) trace[4] = global_timer_ns();      // last P handed over
     prefetch_gates(tid);
-    if (ok) ok = mbar_wait(bar(15), 0, abort_flag);
+    if (ok) ok = mbar_wait(bar(kBarO), 0, abort_flag);
     if (trace && my == 0) trace[5] = global_timer_ns();      // O complete
     if (ok) {
       tc_fence_after();
@@ -329,8 +349,8 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   }
-  // ---- y = bf16(att * bf16(sigmoid(gate))): all six warps, consecutive threads on consecutive 16-byte pieces of a row, so
-  //      the gate is read and y is written in whole 512-byte rows
+  // ---- y = bf16(att * sigmoid(gate)): all six warps, consecutive threads on consecutive 16-byte pieces of a row, so the
+  //      gate is read and y is written in whole 512-byte rows
   if (trace && tid == 0) trace[6] = global_timer_ns();       // staging written (warp 0)
   if (warp >= nw) prefetch_gates(tid);
   tc_fence_before();
@@ -339,7 +359,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // sigmoid(x) = 0.5 tanh(0.5 x) + 0.5: one special-function instruction per value (the exp / reciprocal form needs two, and
     // this loop is bound by them). The gate factor is applied in fp32 and the product rounded once.
     for (int base = tid; base < pieces; base += kBatch * kTcThreads) {
-      if (base != tid) prefetch_gates(base);      // (more than 16 pieces per thread only with seven or eight heads per kv head)
+      if (base != tid) prefetch_gates(base);
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {
         const int i = base + u * kTcThreads;
@@ -389,7 +409,7 @@ extern "C" int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t
                                 ojb_stream_t stream) {
   if (N == 0) return OJB_OK;
   OJB_REQUIRE(qt && kt && vt_t && gate && krange && y && N > 0 && N % 32 == 0 && D == kD);
-  OJB_REQUIRE(HQ > 0 && HKV > 0 && HQ % HKV == 0 && (HQ / HKV) * kQRows <= 128);
+  OJB_REQUIRE(HQ > 0 && HKV > 0 && HQ % HKV == 0 && HQ / HKV <= kMaxG);
   OJB_REQUIRE(aligned16(qt) && aligned16(kt) && aligned16(vt_t) && aligned16(gate) && aligned16(y));
   if ((N + kKB - 1) / kKB > kMaxBlocks) return OJB_ERR_LIMIT;
   CUtensorMap map_q, map_k, map_vt;
@@ -397,7 +417,7 @@ extern "C" int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t
   if (rc == OJB_OK) rc = make_map(&map_k, kt, HKV * N, kD, kKB);
   if (rc == OJB_OK) rc = make_map(&map_vt, vt_t, HKV * kD, N, kD);
   if (rc != OJB_OK) return rc;
-  const size_t smem = 1024 + kQBytes + 2 * kKBytes + 2 * kVBytes + kPBytes + 20 * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4;
+  const size_t smem = 1024 + kQBytes + 2 * kRegion + kPBytes + kNumBars * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4;
   static int smem_set[kMaxDevices] = {};
   if (!raise_smem_limit(tree_attn_tc_kernel, static_cast<int>(smem), smem_set)) return OJB_ERR_LAUNCH;
   AttnArgs a{static_cast<const bf16_t*>(gate), krange, static_cast<bf16_t*>(y), status, static_cast<int>(N), static_cast<int>(HQ),

@@ -560,14 +560,14 @@ def fattn_tree_ranges(qt, kt, vt, gate, krange, scale, gq):
 
 
 def fattn_tree_tc(qt, kt, vt_t, gate, krange, scale):
-    """Tree attention + gate on the tcgen05 tensor cores (ojb_tree_attn_tc): head dim 256, at most 8 query heads per kv head,
+    """Tree attention + gate on the tcgen05 tensor cores (ojb_tree_attn_tc): head dim 256, at most 6 query heads per kv head,
     mask from the three key ranges per row. qt [1, HQ, N, 256], kt [1, HKV, N, 256], vt_t [1, HKV, 256, N] (fullattn_prep2 with
     with_vt_t=True), gate [N, HQ*256] -> y [N, HQ*256]."""
     _chk(qt, kt, vt_t, gate, krange)
     _, HQ, N, D = qt.shape
     HKV = kt.shape[1]
-    if D != 256 or N % 32 or HQ % HKV or HQ // HKV > 8 or tuple(vt_t.shape) != (1, HKV, D, N):
-        raise RuntimeError("fattn_tree_tc: head dim 256, N % 32 == 0, HQ/HKV <= 8 and vt_t [1, HKV, 256, N] required")
+    if D != 256 or N % 32 or HQ % HKV or HQ // HKV > 6 or tuple(vt_t.shape) != (1, HKV, D, N):
+        raise RuntimeError("fattn_tree_tc: head dim 256, N % 32 == 0, HQ/HKV <= 6 and vt_t [1, HKV, 256, N] required")
     y = torch.empty(N, HQ * D, dtype=bf16, device=qt.device)
     call("ojb_tree_attn_tc", ptr(qt), ptr(kt), ptr(vt_t), ptr(gate), ptr(krange), ptr(y), i64(N), i64(HQ), i64(HKV), i64(D),
          f32(scale), ptr(_lib.status_word(qt.device)), stream_ptr())

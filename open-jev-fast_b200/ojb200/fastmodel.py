@@ -306,7 +306,7 @@ class FastQwen35(torch.nn.Module):
     def _attn_tree(self, d, proj, lay, cos, sin):
         N = proj.shape[0]
         G = d.HQ // d.HKV
-        if FATTN_TC and hasattr(lay, "krange") and d.D == 256 and G <= 8 and N % 32 == 0:
+        if FATTN_TC and hasattr(lay, "krange") and d.D == 256 and G <= 6 and N % 32 == 0:
             qt, kt, vt, gate, vt_t = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps, with_vt_t=True)
             return K.fattn_tree_tc(qt, kt, vt_t, gate, lay.krange, d.scale)
         qt, kt, vt, gate = K.fullattn_prep2(proj, d.qw1, d.kw1, cos, sin, 1, N, d.HQ, d.HKV, d.D, self.eps)

@@ -44,7 +44,7 @@ def test_tree_attention(N_case, HQ, HKV, D, gq, mask_form):
     assert (got - ref).abs().max().item() < 3e-2
 
 
-@pytest.mark.parametrize("N_case,HQ,HKV", [("baseline", 24, 4), ("example", 24, 4), ("ragged", 4, 2), ("doc", 8, 1), ("wide", 6, 2),
+@pytest.mark.parametrize("N_case,HQ,HKV", [("baseline", 24, 4), ("example", 24, 4), ("ragged", 4, 2), ("doc", 6, 1), ("wide", 6, 2),
                                            ("long", 12, 2), ("nostem", 5, 1)])
 def test_tree_attention_tcgen05(N_case, HQ, HKV):
     """The tcgen05 / TMA attention kernel (head dim 256, key-range mask, all query heads of a kv head in one 128-row tile)
