@@ -56,6 +56,7 @@ def main():
     ap.add_argument("--max-prefix", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=64, help="debugging only")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--verbose", action="store_true", help="per-request first pass / replay comparison on stderr")
     ap.add_argument("--tune", action="store_true", help="time the GEMM candidates per new row count (FastQwen35.tune) instead of "
                     "using the library's cost model: better kernels below 1024 rows, a much longer capture pass")
     args = ap.parse_args()
@@ -112,6 +113,10 @@ def main():
     lat = np.sort(np.array([r["ms"] for r in second]))
     rows = np.array([r["rows"] for r in second])
     same = all(torch.equal(a["scores"], b["scores"]) for a, b in zip(first, second) if a["gpu"] == b["gpu"])
+    if args.verbose:
+        for i, (a, b) in enumerate(zip(first, second)):
+            print("request", i, "rows", a["rows"], "gpu", a["gpu"], b["gpu"], "captured", a["captured"], "max diff",
+                  float((a["scores"] - b["scores"]).abs().max()), file=sys.stderr)
     st = router.stats()
     print(json.dumps({"sweep": "prefix 256..%d log-uniform, 1-3 questions, 2-12 leaves of 2-40 tokens" % args.max_prefix,
                       "requests": len(reqs), "n_gpus": n_gpu, "layers": args.layers, "tuned": bool(args.tune),
@@ -122,7 +127,8 @@ def main():
                       "host_layout_ms_mean": float(np.mean([r["build_ms"] for r in second])),
                       "host_layout_ms_max": float(np.max([r["build_ms"] for r in second])),
                       "rows_min": int(rows.min()), "rows_median": int(np.median(rows)), "rows_max": int(rows.max()),
-                      "served_per_gpu": st["served"], "replay_equals_first_pass": bool(same)}), flush=True)
+                      "served_per_gpu": st["served"], "workers_alive": st["alive"], "requeued": st["requeued"],
+                      "worker_errors": st["errors"], "replay_equals_first_pass": bool(same)}), flush=True)
 
 
 if __name__ == "__main__":

@@ -2,25 +2,27 @@
 //
 // One CTA = one kv head x 16 query rows x ALL query heads of that kv head: the G <= 6 heads share K and V, so their rows are
 // stacked into one operand tile (row 16 w + r = head w, query row r; M = 128 in the instruction, the rows past 16 G are never
-// looked at) and every K / V tile that reaches the SM is used by all of them. Keys are visited in blocks of 128; a block is
-// skipped when none of the 16 rows sees any of its keys (the mask is three half-open key ranges per row: root, own question
-// stem, own leaf up to the row itself).
+// looked at) and every K / V tile that reaches the SM is used by all of them. Keys are visited in blocks of KB = 128 (64 for
+// trees of at most 384 rows); a block is skipped when none of the 16 rows sees any of its keys (the mask is three half-open
+// key ranges per row: root, own question stem, own leaf up to the row itself).
 //
-//   S = Q K^T   tcgen05.mma, M = 128, N = 128, K = 256: Q and the K block [128 x 256] are K-major 128-byte-swizzled tiles
-//               written by TMA; S lives in tensor memory (two 128-column buffers, so the product of the next block runs while
-//               the softmax warps work on this one)
-//   softmax     one thread per (head, row) = one lane of tensor memory: tcgen05.ld of its 128 scores, mask, exp2
-//   O += P V    P is written as a bf16 K-major swizzled tile [128 x 128] by the softmax threads; V arrives transposed
-//               ([256 x N], written by the prep kernel), so the V block [256 d x 128 keys] is K-major too; O [128 x 256] fp32
+//   S = Q K^T   tcgen05.mma, M = 128, N = KB, K = 256: Q and the K block [KB x 256] are K-major 128-byte-swizzled tiles
+//               written by TMA; S lives in tensor memory (KB-column buffers beside O, so the product of the next block runs
+//               while the softmax warps work on this one)
+//   softmax     two threads per (head, row) = one lane of tensor memory, each taking half of the block's columns:
+//               tcgen05.ld of its scores, mask, exp2
+//   O += P V    P is written as a bf16 K-major swizzled tile [128 x KB] by the softmax threads; V arrives transposed
+//               ([256 x N], written by the prep kernel), so the V block [256 d x KB keys] is K-major too; O [128 x 256] fp32
 //               stays in tensor memory for the whole CTA
 //
 // The softmax is two-pass: pass 1 runs Q K^T over the visible blocks and keeps only the row maxima, pass 2 forms
-// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. With at most two visible key blocks all
-// scores stay in tensor memory between the passes; with more, pass 2 recomputes the (cheap) Q K^T products.
-// Shared memory holds Q (48 KB), two 64 KB regions for K / V blocks and P (32 KB): in pass 1 the regions alternate as K
-// stages; in pass 2 region 0 takes the K block and region 1 the V block of a key block (the natural stagger of Q K^T ->
-// softmax -> P V hides their loads).
-// Roles: warps 0-3 softmax / epilogue, warp 4 TMA producer, warp 5 MMA issuer; mbarriers between them, every wait bounded (the
+// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. When the scores of all visible blocks fit
+// in tensor memory beside O (256 columns: two blocks of 128 keys, four of 64) they stay there between the passes; with more
+// blocks, pass 2 recomputes the (cheap) Q K^T products.
+// Shared memory holds Q (48 KB), two regions of one K or V block each and P: in pass 1 the regions alternate as K stages; in
+// pass 2 region 0 takes the K block and region 1 the V block of a key block (the natural stagger of Q K^T -> softmax -> P V
+// hides their loads).
+// Roles: warps 0-7 softmax / epilogue, warp 8 TMA producer, warp 9 MMA issuer; mbarriers between them, every wait bounded (the
 // CTA then reports OJB_DEV_WAIT_TIMEOUT through `status`, frees its tensor memory and returns).
 #include "gemm_common.cuh"
 
@@ -30,16 +32,23 @@ namespace {
 constexpr int kD = 256;
 constexpr int kQRows = 16;            // query rows per CTA and head
 constexpr int kMaxG = 6;              // query heads per kv head that fit the shared-memory plan
-constexpr int kKB = 128;              // keys per block
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;       // 8 softmax warps, producer warp, MMA warp
+constexpr int kSoftWarps = 8;
 constexpr uint32_t kQBytes = kMaxG * kQRows * kD * 2;    // 4 k-blocks of [16 G rows][64]
-constexpr uint32_t kRegion = kKB * kD * 2;               // 64 KB: a K block (4 k-blocks of [128 keys][64]) or a V block (2 of [256 d][64])
-constexpr uint32_t kPBytes = 128 * kKB * 2;              // 2 k-blocks of [128 rows][64 keys]
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS = 256;               // O: 256 columns; S: two buffers of 128 columns
+constexpr uint32_t kColO = 0, kColS = 256;               // O: 256 columns; S: 256 / KB buffers of KB columns
 constexpr int kStagePitch = kD * 2 + 16;                 // bytes per row of the output staging tile
-constexpr int kMaxBlocks = 1024;                         // key blocks a CTA can list (131 072 keys)
-enum { kBarQ = 0, kBarFull = 1, kBarFree = 3, kBarSFull = 5, kBarSFree = 7, kBarPFull = 9, kBarPFree = 10, kBarO = 11, kNumBars = 12 };
+constexpr int kMaxBlocks = 1024;                         // key blocks a CTA can list
+enum { kBarQ = 0, kBarFull = 1, kBarFree = 3, kBarSFull = 5, kBarSFree = 9, kBarPFull = 11, kBarPFree = 12, kBarO = 13, kBarX = 14,
+       kNumBars = 15 };
+// per key-block size: a region holds one K block (4 k-blocks of [KB keys][64]) or one V block (KB / 64 k-blocks of [256 d][64])
+template <int KB> struct Blk {
+  static constexpr uint32_t kRegion = KB * kD * 2;
+  static constexpr uint32_t kPBytes = 128 * KB * 2;      // KB / 64 k-blocks of [128 rows][64 keys]
+  static constexpr int kNS = 256 / KB;                   // S buffers that fit beside O
+  static constexpr size_t kSmem = 1024 + kQBytes + 2 * kRegion + kPBytes + kNumBars * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4 +
+                                  4 * 128 * 4;
+};
 
 // Measurement hook (ojb_tree_attn_set_trace): when non-null, the CTA of kv head 0 and the last-but-one block of query rows
 // stores %globaltimer at a few points of its life (see the stamps below).
@@ -63,6 +72,7 @@ __device__ __forceinline__ uint32_t range_bits(int lo, int hi, int w) {
   return upto_b & ~((1u << a) - 1u);
 }
 
+template <int KB>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_vt, AttnArgs g) {
@@ -72,6 +82,9 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* Qs = smem;
+  constexpr uint32_t kRegion = Blk<KB>::kRegion, kPBytes = Blk<KB>::kPBytes;
+  constexpr int kKB = KB, kNS = Blk<KB>::kNS;
+  constexpr int kCols = KB / 2;                // score columns per softmax thread
   uint8_t* Rg = Qs + kQBytes;                  // two regions
   uint8_t* Ps = Rg + 2 * kRegion;
   uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + kPBytes);
@@ -79,6 +92,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);      // [0] give-up flag, [1] wait limit in ms
   int* kr = reinterpret_cast<int*>(tmem_slot + 4);                                 // [16 rows][8]
   int* vis_list = kr + kQRows * 8;                                                 // visible key blocks; count at [kMaxBlocks]
+  float* xch = reinterpret_cast<float*>(vis_list + kMaxBlocks + 1);                // [maxima, sums][2 column halves][128 rows]
 
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
@@ -91,8 +105,9 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (tid == 0) {
     for (int i = 0; i < kNumBars; ++i) mbar_init(bar(i), 1);
-    mbar_init(bar(kBarSFree), nw); mbar_init(bar(kBarSFree + 1), nw);
-    mbar_init(bar(kBarPFull), nw);
+    mbar_init(bar(kBarSFree), 2 * nw); mbar_init(bar(kBarSFree + 1), 2 * nw);
+    mbar_init(bar(kBarPFull), 2 * nw);
+    mbar_init(bar(kBarX), 2 * nw);
     abort_flag[0] = 0;
     abort_flag[1] = g.wait_ms;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -100,7 +115,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vt) : "memory");
   }
-  if (warp == 4) {
+  if (warp == kSoftWarps) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
@@ -111,13 +126,13 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (warp == 4 && lane == 0) {      // the Q rows do not depend on the list of key blocks: requested while warp 0 builds it
+  if (warp == kSoftWarps && lane == 0) {      // the Q rows do not depend on the list of key blocks: requested while warp 0 builds it
     mbar_expect_tx(bar(kBarQ), static_cast<uint32_t>(G) * 4u * (kQRows * 128u));
     for (int w = 0; w < G; ++w)
       for (int kb4 = 0; kb4 < 4; ++kb4)
         tma_load_2d(smem_u32(Qs) + kb4 * qstride + w * (kQRows * 128), &map_q, bar(kBarQ), kb4 * 64, (hq0 + w) * N + r0);
   }
-  // ordered list of the 128-key blocks that at least one of the 16 rows sees
+  // ordered list of the key blocks that at least one of the 16 rows sees
   const int NB = (N + kKB - 1) / kKB;
   if (warp == 0) {
     int count = 0;
@@ -141,14 +156,14 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   const int nvis = vis_list[kMaxBlocks];
   const int T = 2 * nvis;                       // pass 1 (maxima) then pass 2 (P V) over the same blocks
-  // Up to two key blocks: the scores of both fit in tensor memory beside O, so Q K^T runs once and pass 2 reads the scores
-  // again from there. More blocks: the two S buffers rotate and pass 2 recomputes Q K^T.
-  const bool one_pass = nvis <= 2;
+  // Up to kNS key blocks: their scores fit in tensor memory beside O, so Q K^T runs once and pass 2 reads the scores again
+  // from there. More blocks: two S buffers rotate and pass 2 recomputes Q K^T.
+  const bool one_pass = nvis <= kNS;
   // Gate values of the 16 output pieces this thread multiplies at the very end (consecutive threads take consecutive 16-byte
   // pieces of the [G * 16 rows][256] output tile). Each warp requests them as soon as it has nothing else to wait for, so their
   // latency runs under the last P V products and the staging of O.
   const int pieces = G * kQRows * (kD / 8);
-  constexpr int kBatch = 16;
+  constexpr int kBatch = (kMaxG * kQRows * (kD / 8) + kTcThreads - 1) / kTcThreads;      // 10
   uint4 gq[kBatch];
   auto prefetch_gates = [&](int base) {
 #pragma unroll
@@ -163,7 +178,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   };
   if (trace && tid == 0) { trace[0] = t_entry; trace[1] = global_timer_ns(); trace[15] = static_cast<unsigned long long>(nvis); }
 
-  if (warp == 4) {
+  if (warp == kSoftWarps) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int use[2] = {0, 0};
@@ -176,13 +191,14 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (!is_v) {
           for (int kb4 = 0; kb4 < 4; ++kb4) tma_load_2d(dst + kb4 * (kKB * 128), &map_k, bar(kBarFull + R), kb4 * 64, kvh * N + kb * kKB);
         } else {
-          for (int kb2 = 0; kb2 < 2; ++kb2) tma_load_2d(dst + kb2 * (kD * 128), &map_vt, bar(kBarFull + R), kb * kKB + kb2 * 64, kvh * kD);
+          for (int kb2 = 0; kb2 < KB / 64; ++kb2) tma_load_2d(dst + kb2 * (kD * 128), &map_vt, bar(kBarFull + R), kb * kKB + kb2 * 64, kvh * kD);
         }
         return true;
       };
       if (one_pass) {
-        for (int it = 0; it < nvis && ok; ++it) ok = load(it, false, vis_list[it]);
-        for (int j = 0; j < nvis && ok; ++j) ok = load(j, true, vis_list[j]);       // region j is free once Q K^T of block j is done
+        // (a region is free for the next block once the product that read it is done; all Q K^T come before the first P V)
+        for (int it = 0; it < nvis && ok; ++it) ok = load(it & 1, false, vis_list[it]);
+        for (int j = 0; j < nvis && ok; ++j) ok = load(j & 1, true, vis_list[j]);
       } else {
         for (int it = 0; it < nvis && ok; ++it) ok = load(it & 1, false, vis_list[it]);
         // pass 2: region 0 is free again when Q K^T of the block before is done, region 1 when P V of the block before is done;
@@ -194,11 +210,11 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kSoftWarps + 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(kKB), idesc_o = umma_idesc(kD);
-      int use[2] = {0, 0}, use_s[2] = {0, 0};
+      int use[2] = {0, 0}, use_s[4] = {0, 0, 0, 0};
       bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
       if (trace) trace[8] = global_timer_ns();          // Q has landed
       auto qk = [&](int R, int sb) {                    // S[sb] = Q K^T with the K block in region R
@@ -225,7 +241,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++use[R];
         tc_fence_after();
 #pragma unroll
-        for (int kb2 = 0; kb2 < 2; ++kb2) {
+        for (int kb2 = 0; kb2 < KB / 64; ++kb2) {
           const uint64_t pdesc = smem_desc_sw128(smem_u32(Ps) + kb2 * (128 * 128));
           const uint64_t vdesc = smem_desc_sw128(smem_u32(Rg) + R * kRegion + kb2 * (kD * 128));
 #pragma unroll
@@ -237,8 +253,8 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         return true;
       };
       if (one_pass) {
-        for (int it = 0; it < nvis && ok; ++it) ok = qk(it, it);
-        for (int j = 0; j < nvis && ok; ++j) ok = pv(j, j);
+        for (int it = 0; it < nvis && ok; ++it) ok = qk(it & 1, it);
+        for (int j = 0; j < nvis && ok; ++j) ok = pv(j, j & 1);
       } else {
         for (int it = 0; it < nvis && ok; ++it) ok = qk(it & 1, it & 1);
         for (int j = 0; j < nvis && ok; ++j) {
@@ -250,92 +266,109 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (ok) umma_commit(bar(kBarO));
       if (trace) trace[9] = global_timer_ns();          // every MMA issued
     }
-  } else if (warp < nw) {
-    // ------------------------------------------------------------------ softmax + epilogue: one thread per (head, row)
-    const int my = warp * 32 + lane;             // tile row = 16 * head + query row
+  } else if (warp < kSoftWarps && (warp & 3) < nw) {
+    // ------------------------------------------------------------------ softmax + epilogue: two threads per (head, row).
+    // Thread (half, my) takes columns [half * KB / 2, +KB / 2) of every key block and columns [half * 128, +128) of O; the two
+    // halves exchange their row maxima before pass 2 and their row sums after it through shared memory.
+    const int half = warp >> 2;
+    const int my = (warp & 3) * 32 + lane;       // tile row = 16 * head + query row = lane of tensor memory
     const int qr = my & 15;
     const int* q = kr + qr * 8;
     const int a0 = q[5], e0 = q[0], a1 = q[1], e1 = q[2], a2 = q[3], e2 = q[4];
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const bool stamp = trace && my == 0 && half == 0;
+    constexpr int kLd = kCols / 32;              // 32-column loads per block: 1 or 2
     float m = -INFINITY, l = 0.f;
-    int use_s[2] = {0, 0};
+    int use_s[4] = {0, 0, 0, 0}, xphase = 0;
     bool ok = true;
+    auto exchange = [&](float v, int slot) {     // hands v to the thread of the other half, returns that thread's value
+      xch[(2 * slot + half) * 128 + my] = v;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarX));
+      if (!mbar_wait(bar(kBarX), xphase & 1, abort_flag)) { ok = false; return v; }
+      ++xphase;
+      return xch[(2 * slot + (half ^ 1)) * 128 + my];
+    };
     for (int it = 0; it < T && ok; ++it) {
       const bool pass2 = it >= nvis;
       const int blk = pass2 ? it - nvis : it;
       const int kb = vis_list[blk];
       const int sb = one_pass ? blk : (it & 1);          // S buffer
+      if (it == nvis) {
+        m = fmaxf(m, exchange(m, 0));
+        if (!ok) break;
+      }
       // (pass 2 of the one-pass form reads scores that pass 1 has already waited for)
       if (!(one_pass && pass2)) {
         if (!mbar_wait(bar(kBarSFull + sb), use_s[sb] & 1, abort_flag)) { ok = false; break; }
         ++use_s[sb];
       }
-      if (trace && my == 0 && (it == 0 || it == nvis)) trace[it == 0 ? 2 : 3] = global_timer_ns();   // first S of pass 1 / pass 2
+      if (stamp && (it == 0 || it == nvis)) trace[it == 0 ? 2 : 3] = global_timer_ns();   // first S of pass 1 / pass 2
       tc_fence_after();
       const float mc = m * g.scale_log2e;
+      uint32_t s[kLd][32];
+      const uint32_t taddr = tmem_base + lane_base + kColS + static_cast<uint32_t>(sb * kKB + half * kCols);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {             // 64 scores at a time
-        uint32_t s0[32], s1[32];
-        const uint32_t taddr = tmem_base + lane_base + kColS + static_cast<uint32_t>(sb) * kKB + half * 64;
-        tmem_ld32(taddr, s0);
-        tmem_ld32(taddr + 32, s1);
-        tmem_ld_wait();
-        if (half == 1 && !one_pass) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(kBarSFree + sb));        // this warp has consumed the S buffer
-        }
-        const int w = 4 * kb + 2 * half;
-        const uint32_t w0 = range_bits(a0, e0, w) | range_bits(a1, e1, w) | range_bits(a2, e2, w);
-        const uint32_t w1 = range_bits(a0, e0, w + 1) | range_bits(a1, e1, w + 1) | range_bits(a2, e2, w + 1);
-        if (!pass2) {
+      for (int i = 0; i < kLd; ++i) tmem_ld32(taddr + 32 * i, s[i]);
+      tmem_ld_wait();
+      if (!one_pass) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarSFree + sb));          // this warp has consumed its part of the S buffer
+      }
+      uint32_t bits[kLd];
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if ((w0 >> c) & 1u) m = fmaxf(m, __uint_as_float(s0[c]));
-            if ((w1 >> c) & 1u) m = fmaxf(m, __uint_as_float(s1[c]));
-          }
-        } else {
-          uint32_t pk[32];                                // 64 probabilities as bf16 pairs
+      for (int i = 0; i < kLd; ++i) {
+        const int w = (kb * kKB + half * kCols) / 32 + i;
+        bits[i] = range_bits(a0, e0, w) | range_bits(a1, e1, w) | range_bits(a2, e2, w);
+      }
+      if (!pass2) {
+#pragma unroll
+        for (int i = 0; i < kLd; ++i)
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if ((bits[i] >> c) & 1u) m = fmaxf(m, __uint_as_float(s[i][c]));
+      } else {
+        uint32_t pk[kLd * 16];                            // the probabilities as bf16 pairs
+#pragma unroll
+        for (int i = 0; i < kLd; ++i)
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
-            const float p0 = ((w0 >> c) & 1u) ? exp2f_fast(__uint_as_float(s0[c]) * g.scale_log2e - mc) : 0.f;
-            const float p1 = ((w0 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s0[c + 1]) * g.scale_log2e - mc) : 0.f;
-            const float p2 = ((w1 >> c) & 1u) ? exp2f_fast(__uint_as_float(s1[c]) * g.scale_log2e - mc) : 0.f;
-            const float p3 = ((w1 >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s1[c + 1]) * g.scale_log2e - mc) : 0.f;
-            l += (p0 + p1) + (p2 + p3);
-            pk[c >> 1] = pack2(p0, p1);
-            pk[16 + (c >> 1)] = pack2(p2, p3);
+            const float p0 = ((bits[i] >> c) & 1u) ? exp2f_fast(__uint_as_float(s[i][c]) * g.scale_log2e - mc) : 0.f;
+            const float p1 = ((bits[i] >> (c + 1)) & 1u) ? exp2f_fast(__uint_as_float(s[i][c + 1]) * g.scale_log2e - mc) : 0.f;
+            l += p0 + p1;
+            pk[i * 16 + (c >> 1)] = pack2(p0, p1);
           }
-          // P V of the previous block must have read P before the first piece of this block's P is written
-          if (half == 0 && !mbar_wait(bar(kBarPFree), ((it - nvis) & 1) ^ 1, abort_flag)) ok = false;
-          if (ok) {
-            // row `my` of k-block `half` of the K-major swizzled tile: 128 bytes = 8 chunks of 16, chunk c stored at c ^ (row & 7)
-            uint8_t* prow = Ps + half * (128 * 128) + my * 128;
+        // P V of the previous block must have read P before this block's P is written
+        if (!mbar_wait(bar(kBarPFree), (blk & 1) ^ 1, abort_flag)) { ok = false; break; }
+        // row `my` of the K-major swizzled tile: each 64-key k-block is 128 bytes = 8 chunks of 16, chunk c stored at
+        // c ^ (row & 7); this thread's columns start at chunk (half * kCols % 64) / 8 of k-block half * kCols / 64
+        uint8_t* prow = Ps + ((half * kCols) / 64) * (128 * 128) + my * 128;
+        constexpr int kChunks = kCols / 8;
+        const int chunk0 = ((half * kCols) % 64) / 8;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-              *reinterpret_cast<uint4*>(prow + ((c ^ (my & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-          }
-        }
-      }
-      if (pass2 && ok) {
+        for (int c = 0; c < kChunks; ++c)
+          *reinterpret_cast<uint4*>(prow + (((chunk0 + c) ^ (my & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarPFull));
       }
     }
-    // ---- att = bf16(O / l) of this thread's (head, row) into the staging tile [128][kStagePitch] (over Q and region 0, which
-    //      no MMA reads any more once O is complete); rows are 16 bytes longer than 512 so that the 32 rows of a warp spread
-    //      over the banks
-    if (trace && my == 0) trace[4] = global_timer_ns();      // last P handed over
+    if (stamp) trace[4] = global_timer_ns();                  // last P handed over
+    if (ok) l += exchange(l, 1);
+    // ---- att = bf16(O / l) of this thread's half of its (head, row) into the staging tile [128][kStagePitch] (over Q and
+    //      region 0, which no MMA reads any more once O is complete); rows are 16 bytes longer than 512 so that the 32 rows of
+    //      a warp spread over the banks
     prefetch_gates(tid);
     if (ok) ok = mbar_wait(bar(kBarO), 0, abort_flag);
-    if (trace && my == 0) trace[5] = global_timer_ns();      // O complete
+    if (stamp) trace[5] = global_timer_ns();                  // O complete
     if (ok) {
       tc_fence_after();
       const float inv_l = l > 0.f ? 1.0f / l : 0.f;
       uint8_t* srow = smem + my * kStagePitch;
 #pragma unroll
-      for (int c = 0; c < kD / 32; ++c) {
+      for (int cc = 0; cc < kD / 64; ++cc) {
+        const int c = half * (kD / 64) + cc;
         uint32_t o[32];
         tmem_ld32(tmem_base + lane_base + kColO + c * 32, o);
         tmem_ld_wait();
@@ -349,10 +382,10 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   }
-  // ---- y = bf16(att * sigmoid(gate)): all six warps, consecutive threads on consecutive 16-byte pieces of a row, so the
+  // ---- y = bf16(att * sigmoid(gate)): all ten warps, consecutive threads on consecutive 16-byte pieces of a row, so the
   //      gate is read and y is written in whole 512-byte rows
   if (trace && tid == 0) trace[6] = global_timer_ns();       // staging written (warp 0)
-  if (warp >= nw) prefetch_gates(tid);
+  if (warp >= kSoftWarps || (warp & 3) >= nw) prefetch_gates(tid);
   tc_fence_before();
   __syncthreads();
   if (!abort_flag[0]) {
@@ -388,7 +421,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int i = 0; i < 200; ++i) __nanosleep(1000);       // copies that were already issued land before the CTA leaves
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == kSoftWarps) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -411,18 +444,28 @@ extern "C" int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t
   OJB_REQUIRE(qt && kt && vt_t && gate && krange && y && N > 0 && N % 32 == 0 && D == kD);
   OJB_REQUIRE(HQ > 0 && HKV > 0 && HQ % HKV == 0 && HQ / HKV <= kMaxG);
   OJB_REQUIRE(aligned16(qt) && aligned16(kt) && aligned16(vt_t) && aligned16(gate) && aligned16(y));
-  if ((N + kKB - 1) / kKB > kMaxBlocks) return OJB_ERR_LIMIT;
+  // 64-key blocks for short trees: a leaf row then visits fewer masked-out keys and up to four blocks of scores stay in tensor
+  // memory between the passes; 128-key blocks halve the per-block hand-overs of long roots.
+  const bool small = N <= 384;
+  const int KB = small ? 64 : 128;
+  if ((N + KB - 1) / KB > kMaxBlocks) return OJB_ERR_LIMIT;
   CUtensorMap map_q, map_k, map_vt;
   int rc = make_map(&map_q, qt, HQ * N, kD, kQRows);
-  if (rc == OJB_OK) rc = make_map(&map_k, kt, HKV * N, kD, kKB);
+  if (rc == OJB_OK) rc = make_map(&map_k, kt, HKV * N, kD, KB);
   if (rc == OJB_OK) rc = make_map(&map_vt, vt_t, HKV * kD, N, kD);
   if (rc != OJB_OK) return rc;
-  const size_t smem = 1024 + kQBytes + 2 * kRegion + kPBytes + kNumBars * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4;
-  static int smem_set[kMaxDevices] = {};
-  if (!raise_smem_limit(tree_attn_tc_kernel, static_cast<int>(smem), smem_set)) return OJB_ERR_LAUNCH;
   AttnArgs a{static_cast<const bf16_t*>(gate), krange, static_cast<bf16_t*>(y), status, static_cast<int>(N), static_cast<int>(HQ),
              static_cast<int>(HKV), static_cast<int>(HQ / HKV), scale * 1.4426950408889634f, gemm_wait_limit_ms()};
-  launch_kernel(tree_attn_tc_kernel, dim3(static_cast<unsigned>(HKV), static_cast<unsigned>(N / kQRows)), dim3(kTcThreads), smem,
-                static_cast<cudaStream_t>(stream), map_q, map_k, map_vt, a);
+  const dim3 grid(static_cast<unsigned>(HKV), static_cast<unsigned>(N / kQRows));
+  static int set64[kMaxDevices] = {}, set128[kMaxDevices] = {};
+  if (small) {
+    if (!raise_smem_limit(tree_attn_tc_kernel<64>, static_cast<int>(Blk<64>::kSmem), set64)) return OJB_ERR_LAUNCH;
+    launch_kernel(tree_attn_tc_kernel<64>, grid, dim3(kTcThreads), Blk<64>::kSmem, static_cast<cudaStream_t>(stream), map_q, map_k,
+                  map_vt, a);
+  } else {
+    if (!raise_smem_limit(tree_attn_tc_kernel<128>, static_cast<int>(Blk<128>::kSmem), set128)) return OJB_ERR_LAUNCH;
+    launch_kernel(tree_attn_tc_kernel<128>, grid, dim3(kTcThreads), Blk<128>::kSmem, static_cast<cudaStream_t>(stream), map_q, map_k,
+                  map_vt, a);
+  }
   return launch_status(cudaGetLastError());
 }

@@ -49,6 +49,7 @@ class Router:
         self.alive = [True] * len(self.fns)
         self.served = [0] * len(self.fns)
         self.requeued = 0
+        self.errors = []                             # (worker, repr of the error that retired it)
         self.lock = threading.Lock()
         self.stop = False
         self._rid = 0
@@ -126,6 +127,7 @@ class Router:
             return
         self.alive[w] = False
         self.load[w] = 0
+        self.errors.append((w, repr(err)))
         pending = []
         while True:
             try:
@@ -167,4 +169,4 @@ class Router:
 
     def stats(self):
         with self.lock:
-            return dict(alive=list(self.alive), served=list(self.served), requeued=self.requeued)
+            return dict(alive=list(self.alive), served=list(self.served), requeued=self.requeued, errors=list(self.errors))
