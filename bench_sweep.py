@@ -4,8 +4,9 @@
     python bench_sweep.py --gpus 8 --requests 256
 
 Requests are seeded synthetic trees: shared prefix length log-uniform in [256, 16384], 1-3 questions with stems of 4-40
-tokens, 2-12 candidate leaves of 2-40 tokens. One host process: ojb200.router.Router in front of one ojb200.server.Scorer per
-GPU (full weights, own graph cache, own stream), shortest queue by outstanding tokens; nothing is exchanged between GPUs.
+tokens, 2-12 candidate leaves of 2-40 tokens. ojb200.router.Router in front of one ojb200.server.Scorer per GPU (full
+weights, own graph cache, own stream; by default each in a child process of its own, fed over a pipe), shortest queue by
+outstanding tokens; nothing is exchanged between GPUs.
 Every request goes through Scorer.score_tokens (host layout build, pinned H2D, graph lookup or capture, replay, D2H of the
 scores). The stream is served twice: the first pass captures one graph per (N, S, L2) key where a GPU meets the key for the
 first time (reported as capture cost), the second pass is the steady state. One JSON line: service time per request (p50 /
@@ -49,6 +50,33 @@ def make_requests(n, seed, vocab, max_prefix):
     return reqs
 
 
+def scorer_worker(i, layers, tune):
+    """Builds the model and its Scorer on GPU i and returns the serve function of one worker: request -> record with the
+    scores (numpy), the service time and what the scorer reports. Runs in the router's process (thread workers) or in a child
+    process of its own (process workers)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
+    from ojb200 import _lib, fastmodel as FM, modelgen as MG, server as SV
+    if not tune:
+        FM.FastQwen35.TUNE_MAX_ROWS = 0
+    kw = dict(MG.FULL)
+    kw["num_hidden_layers"] = layers
+    cfg = MG.make_config(**kw)
+    dev = torch.device("cuda", i)
+    with torch.cuda.device(dev):
+        fast = FM.FastQwen35(MG.build_core(cfg, device=dev, seed=0), free_original=True)
+        W, b = MG.make_head(cfg.hidden_size, A=1, seed=1, device=dev)
+        sc = SV.Scorer(fast, W, b, pad_id=0, device=dev, max_graphs=4096)
+
+    def fn(req):
+        t = time.perf_counter()
+        out, info = sc.score_tokens(req[0], req[1], with_info=True)
+        out = out.cpu().numpy()                              # the synchronisation point of this request
+        _lib.check_status(sc.device)
+        return dict(scores=out, ms=(time.perf_counter() - t) * 1e3, gpu=i, rows=info["rows"], build_ms=info["build_ms"],
+                    captured=info["captured"])
+    return fn
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -56,50 +84,37 @@ def main():
     ap.add_argument("--max-prefix", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=64, help="debugging only")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--workers", choices=("process", "thread"), default="process",
+                    help="one child process per GPU behind the router (own interpreter: layout builds and graph launches of "
+                    "different GPUs never wait for each other), or all scorers in the router's process")
     ap.add_argument("--verbose", action="store_true", help="per-request first pass / replay comparison on stderr")
     ap.add_argument("--tune", action="store_true", help="time the GEMM candidates per new row count (FastQwen35.tune) instead of "
                     "using the library's cost model: better kernels below 1024 rows, a much longer capture pass")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "open-jev-fast_b200"))
-    from ojb200 import _lib, fastmodel as FM, modelgen as MG, router as RT, server as SV
-    if not args.tune:
-        FM.FastQwen35.TUNE_MAX_ROWS = 0
-    kw = dict(MG.FULL)
-    kw["num_hidden_layers"] = args.layers
-    cfg = MG.make_config(**kw)
+    from ojb200 import modelgen as MG, router as RT
     n_gpu = min(args.gpus, torch.cuda.device_count())
-    scorers = [None] * n_gpu
-
-    def build(i):
-        dev = torch.device("cuda", i)
-        with torch.cuda.device(dev):
-            fast = FM.FastQwen35(MG.build_core(cfg, device=dev, seed=0), free_original=True)
-            W, b = MG.make_head(cfg.hidden_size, A=1, seed=1, device=dev)
-            scorers[i] = SV.Scorer(fast, W, b, pad_id=0, device=dev, max_graphs=4096)
-
+    vocab = MG.make_config(**MG.FULL).vocab_size
     t0 = time.perf_counter()
-    ths = [threading.Thread(target=build, args=(i,)) for i in range(n_gpu)]
-    for t in ths:
-        t.start()
-    for t in ths:
-        t.join()
+    if args.workers == "process":
+        workers = [RT.ProcessWorker(scorer_worker, (i, args.layers, args.tune)) for i in range(n_gpu)]
+        for w in workers:
+            w.wait_ready(1800)
+    else:
+        workers = [None] * n_gpu
+
+        def build(i):
+            workers[i] = scorer_worker(i, args.layers, args.tune)
+        ths = [threading.Thread(target=build, args=(i,)) for i in range(n_gpu)]
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join()
+        assert all(w is not None for w in workers), "a model failed to build"
     build_s = time.perf_counter() - t0
-    assert all(s is not None for s in scorers), "a model failed to build"
 
-    def serve(i):
-        sc = scorers[i]
-
-        def fn(req):
-            t = time.perf_counter()
-            out, info = sc.score_tokens(req[0], req[1], with_info=True)
-            out = out.cpu()                                  # the synchronisation point of this request
-            _lib.check_status(sc.device)
-            return dict(scores=out, ms=(time.perf_counter() - t) * 1e3, gpu=i, rows=info["rows"], build_ms=info["build_ms"],
-                        captured=info["captured"])
-        return fn
-
-    reqs = make_requests(args.requests, args.seed, cfg.vocab_size, args.max_prefix)
-    router = RT.Router([serve(i) for i in range(n_gpu)])
+    reqs = make_requests(args.requests, args.seed, vocab, args.max_prefix)
+    router = RT.Router(workers)
     try:
         t0 = time.perf_counter()
         first = router.map(reqs)                             # pass 1: graphs captured where a GPU meets a key for the first time
@@ -112,14 +127,14 @@ def main():
         router.close()
     lat = np.sort(np.array([r["ms"] for r in second]))
     rows = np.array([r["rows"] for r in second])
-    same = all(torch.equal(a["scores"], b["scores"]) for a, b in zip(first, second) if a["gpu"] == b["gpu"])
+    same = all(np.array_equal(a["scores"], b["scores"]) for a, b in zip(first, second) if a["gpu"] == b["gpu"])
     if args.verbose:
         for i, (a, b) in enumerate(zip(first, second)):
             print("request", i, "rows", a["rows"], "gpu", a["gpu"], b["gpu"], "captured", a["captured"], "max diff",
-                  float((a["scores"] - b["scores"]).abs().max()), file=sys.stderr)
+                  float(np.abs(a["scores"] - b["scores"]).max()), file=sys.stderr)
     st = router.stats()
     print(json.dumps({"sweep": "prefix 256..%d log-uniform, 1-3 questions, 2-12 leaves of 2-40 tokens" % args.max_prefix,
-                      "requests": len(reqs), "n_gpus": n_gpu, "layers": args.layers, "tuned": bool(args.tune),
+                      "requests": len(reqs), "n_gpus": n_gpu, "workers": args.workers, "layers": args.layers, "tuned": bool(args.tune),
                       "p50_ms": float(lat[len(lat) // 2]), "p95_ms": float(lat[int(len(lat) * 0.95)]), "mean_ms": float(lat.mean()),
                       "requests_per_s": len(reqs) / wall, "steady_pass_s": wall, "capture_pass_s": capture_s,
                       "model_build_s": build_s, "graphs_captured": int(sum(r["captured"] for r in first)),

@@ -5,13 +5,20 @@ the request's key and returns the scores, one request at a time (src/server.py:9
 means more of exactly that loop: every worker owns a `server.Scorer` (full weights, its own graph cache and stream) on its
 device, and the router only decides which worker gets a request. Nothing crosses between GPUs; there is no collective.
 
-Assignment is shortest queue by outstanding work, where the work of a request is its token count (a forward costs roughly
-in proportion to its packed rows, which the token count bounds). A worker that raises on a request, or does not answer
+Assignment is shortest queue by outstanding work, where the work of a request is an estimate of its packed rows (what the
+prefix tree keeps of the candidates' tokens) plus the fixed cost of a forward: that is what a forward's time follows. A worker that raises on a request, or does not answer
 within `timeout_s`, is taken out of rotation and everything it still held is queued again for the others; a request is
 retried at most `max_retries` times and then fails with the last error. Failure handling lives on the host only: nothing here
 waits on a GPU event of another worker.
+
+A worker is any callable request -> result. Two forms are provided for GPU workers: a `Scorer` called from the router's
+worker thread of the same process (all workers then share one Python interpreter, i.e. one interpreter lock for the layout
+builds and graph launches of all GPUs), or `ProcessWorker`: the scorer lives in a child process of its own and the router's
+thread only ships the request over a pipe and waits for the answer. A child that exits or stops answering looks to the
+router like any other failed worker.
 """
 import concurrent.futures
+import multiprocessing
 import queue
 import threading
 import time
@@ -29,11 +36,105 @@ class _Job:
         self.error = None
 
 
+def _common_prefix(a, b):
+    """Length of the common prefix of two token lists (slices compare at C speed: 1024 tokens at a time, then bisection)."""
+    n, i = min(len(a), len(b)), 0
+    while i < n and a[i:i + 1024] == b[i:i + 1024]:
+        i += 1024
+    if i >= n:
+        return n
+    lo, hi = i, min(i + 1024, n)                 # a[:lo] == b[:lo]; they differ somewhere before hi
+    while lo < hi:
+        mid = (lo + hi + 1) // 2
+        if a[lo:mid] == b[lo:mid]:
+            lo = mid
+        else:
+            hi = mid - 1
+    return lo
+
+
+FIXED_COST_ROWS = 400        # a forward costs about 15 ms + 0.038 ms per packed row on a B200: the fixed part, in rows
+
+
 def request_cost(request):
-    """Tokens of a request = sum of its candidates' lengths (records of `Scorer.forward`, or a (seqs, groups) pair)."""
-    if isinstance(request, tuple):
-        return sum(len(s) for s in request[0])
-    return sum(len(c) for r in request for c in r["candidates"])
+    """Estimated cost of a request in packed rows: the first candidate in full plus, for every further candidate, what it
+    does not share with the one before it (candidates of one question are adjacent, so this is the size of the prefix tree
+    unless a request interleaves its questions), plus the fixed cost of a forward. Takes the records of `Scorer.forward` or
+    a (seqs, groups) pair."""
+    seqs = request[0] if isinstance(request, tuple) else [c for r in request for c in r["candidates"]]
+    rows, prev = FIXED_COST_ROWS, None
+    for s_ in seqs:
+        rows += len(s_) - (_common_prefix(prev, s_) if prev is not None else 0)
+        prev = s_
+    return rows
+
+
+def _child_main(conn, factory, args):
+    """Body of a ProcessWorker's child: build the serve function, say so, then answer requests until told to stop."""
+    try:
+        fn = factory(*args)
+    except BaseException as e:                               # the parent must learn why there is no worker
+        conn.send(("failed", repr(e)))
+        return
+    conn.send(("ready", None))
+    while True:
+        try:
+            kind, payload = conn.recv()
+        except EOFError:
+            return
+        if kind == "stop":
+            return
+        try:
+            conn.send(("ok", fn(payload)))
+        except Exception as e:
+            conn.send(("err", repr(e)))
+
+
+class ProcessWorker:
+    """A worker in a process of its own. `factory(*args)` runs in the child (started with the `spawn` method, so it must be
+    importable there) and returns the serve function; requests and results cross a pipe, so both must pickle (token lists,
+    numpy arrays, numbers). Calling the object serves one request; it raises if the child reported an error, has exited, or
+    the pipe broke, which is what makes the router retire it."""
+
+    def __init__(self, factory, args=()):
+        ctx = multiprocessing.get_context("spawn")
+        self.conn, child = ctx.Pipe()
+        self.proc = ctx.Process(target=_child_main, args=(child, factory, tuple(args)), daemon=True)
+        self.proc.start()
+        child.close()
+        self.ready = False
+
+    def wait_ready(self, timeout_s=None):
+        """Blocks until the child has built its serve function; raises if it could not."""
+        if self.ready:
+            return
+        if not self.conn.poll(timeout_s):
+            raise TimeoutError("router: worker process did not come up in time")
+        kind, payload = self.conn.recv()
+        if kind != "ready":
+            raise RuntimeError(f"router: worker process failed to start: {payload}")
+        self.ready = True
+
+    def __call__(self, request):
+        self.wait_ready()
+        self.conn.send(("req", request))
+        kind, payload = self.conn.recv()                     # EOFError when the child has died
+        if kind != "ok":
+            raise RuntimeError(f"router: worker process: {payload}")
+        return payload
+
+    def abandon(self):
+        """Called by the router when it retires this worker: the child is not asked, it is ended."""
+        if self.proc.is_alive():
+            self.proc.terminate()
+
+    def close(self):
+        try:
+            self.conn.send(("stop", None))
+        except (OSError, ValueError):
+            pass
+        self.proc.join(timeout=5.0)
+        self.abandon()
 
 
 class Router:
@@ -128,6 +229,9 @@ class Router:
         self.alive[w] = False
         self.load[w] = 0
         self.errors.append((w, repr(err)))
+        abandon = getattr(self.fns[w], "abandon", None)
+        if abandon is not None:
+            abandon()
         pending = []
         while True:
             try:
@@ -166,6 +270,9 @@ class Router:
         self.stop = True
         for t in self.threads:
             t.join(timeout=1.0)
+        for fn in self.fns:
+            if isinstance(fn, ProcessWorker):
+                fn.close()
 
     def stats(self):
         with self.lock:

@@ -93,7 +93,7 @@ class Entry:
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
             n0 = _lib.launch_count()
-            with torch.cuda.graph(self.g, pool=scorer.pool, capture_error_mode="thread_local"):
+            with torch.cuda.graph(self.g, pool=scorer.pool, stream=scorer.capture_stream, capture_error_mode="thread_local"):
                 self.out = body()
             self.launches = _lib.launch_count() - n0
             torch.cuda.synchronize(dev)
@@ -147,7 +147,7 @@ class EntryState:
         n0 = _lib.launch_count()
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.g, pool=scorer.pool, capture_error_mode="thread_local"):
+            with torch.cuda.graph(self.g, pool=scorer.pool, stream=scorer.capture_stream, capture_error_mode="thread_local"):
                 self.out = body()
             torch.cuda.synchronize(dev)
         else:
@@ -191,7 +191,7 @@ class PackedEntry:
         n0 = _lib.launch_count()
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.g, pool=scorer.pool, capture_error_mode="thread_local"):
+            with torch.cuda.graph(self.g, pool=scorer.pool, stream=scorer.capture_stream, capture_error_mode="thread_local"):
                 self.out = body()
             torch.cuda.synchronize(dev)
         else:
@@ -219,6 +219,9 @@ class Scorer:
         self.use_graph, self.max_graphs = use_graph, max_graphs
         self.graphs = collections.OrderedDict()
         self.pool = torch.cuda.graph_pool_handle() if use_graph else None
+        # torch keeps ONE default capture stream per process, on the device that captured first: a scorer on another GPU
+        # must bring its own, or its capture would run on the first GPU's stream
+        self.capture_stream = torch.cuda.Stream(device=self.device) if use_graph else None
         self.lock = threading.Lock()
         self.nreq = 0
         self.log = open(access_log, "a", buffering=1 << 16) if access_log else None

@@ -25,8 +25,9 @@ def test_requests_go_to_the_least_loaded_worker_and_all_complete():
 
     rt = R.Router([mk(0), mk(1)])
     try:
-        # costs 100, 10, 10, 10: the heavy one goes to worker 0, the three light ones pile up on worker 1 (10, 20, 30 < 100)
-        futs = [rt.submit(_req(100, 0))] + [rt.submit(_req(10, i)) for i in (1, 2, 3)]
+        # costs 2400, 410, 410, 410 (rows + the fixed cost of a forward): the heavy one goes to worker 0, the three light
+        # ones pile up on worker 1 (410, 820, 1230 < 2400)
+        futs = [rt.submit(_req(2000, 0))] + [rt.submit(_req(10, i)) for i in (1, 2, 3)]
         gate.set()
         res = [f.result(timeout=5) for f in futs]
     finally:
@@ -92,3 +93,52 @@ def test_a_request_fails_with_the_workers_error_when_every_retry_fails():
             f.result(timeout=5)
     finally:
         rt.close()
+
+
+def test_cost_of_a_request_is_the_size_of_its_prefix_tree():
+    root = list(range(3000))
+    seqs = [root + [7, 8, 9, i] for i in range(5)]               # 3000 shared + 3 shared stem tokens + one own token each
+    assert R.request_cost((seqs, [0] * 5)) == R.FIXED_COST_ROWS + 3004 + 4
+    recs = [{"kind": "score", "candidates": seqs[:2]}, {"kind": "score", "candidates": seqs[2:]}]
+    assert R.request_cost(recs) == R.request_cost((seqs, [0] * 5))
+    assert R._common_prefix([], [1]) == 0 and R._common_prefix([1, 2], [1, 2]) == 2 and R._common_prefix(root, root[:2047] + [0]) == 2047
+
+
+# ---- workers in processes of their own (the factories below run in the spawned children, which import this module)
+def _echo_factory(tag, die_after):
+    import os
+    served = {"n": 0}
+
+    def serve(records):
+        served["n"] += 1
+        if die_after and served["n"] > die_after:
+            os._exit(3)                                     # the process is gone in the middle of a request
+        return (tag, records[0]["candidates"][0][0])
+    return serve
+
+
+def _broken_factory():
+    raise RuntimeError("no device")
+
+
+def test_a_worker_process_that_dies_is_retired_and_its_requests_are_served_by_the_others():
+    workers = [R.ProcessWorker(_echo_factory, ("a", 2)), R.ProcessWorker(_echo_factory, ("b", 0))]
+    for w in workers:
+        w.wait_ready(60)
+    rt = R.Router(workers)
+    try:
+        res = rt.map([_req(8, i) for i in range(10)])
+        st = rt.stats()
+    finally:
+        rt.close()
+    assert [r[1] for r in res] == list(range(10))       # every request answered once, in order
+    assert st["alive"] == [False, True] and st["requeued"] >= 1 and st["served"][0] == 2 and sum(st["served"]) == 10
+    assert "EOFError" in st["errors"][0][1] or "Connection" in st["errors"][0][1]
+    assert not workers[0].proc.is_alive()
+
+
+def test_a_worker_process_that_cannot_start_reports_why():
+    w = R.ProcessWorker(_broken_factory)
+    with pytest.raises(RuntimeError, match="no device"):
+        w.wait_ready(60)
+    w.close()
