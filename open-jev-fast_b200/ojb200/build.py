@@ -2,6 +2,7 @@
 
     python -m ojb200.build            # rebuild what is out of date
     python -m ojb200.build --force
+    python -m ojb200.build --force --probes      # with the GEMM measurement knobs (-DOJB_GEMM_PROBES); never shipped
 
 The library lands next to this file so that it travels with the source tree; nothing is installed anywhere else.
 """
@@ -19,6 +20,7 @@ LIB_PATH = os.path.join(HERE, "libojb200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-I", INCLUDE]
+EXTRA_FLAGS = []
 
 
 def _nvcc():
@@ -49,7 +51,7 @@ def _compile(src, force, log):
     obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
     if not force and not _stale(obj, [src] + _deps()):
         return obj
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-x", "cu", "-c", src, "-o", obj]
+    cmd = [_nvcc()] + NVCC_FLAGS + EXTRA_FLAGS + ["-x", "cu", "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     with open(os.path.join(OBJ_DIR, os.path.basename(src) + ".log"), "w") as f:
         f.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
@@ -77,4 +79,6 @@ def build(force=False, log=True):
 
 
 if __name__ == "__main__":
+    if "--probes" in sys.argv:
+        EXTRA_FLAGS.append("-DOJB_GEMM_PROBES")
     build(force="--force" in sys.argv)
