@@ -2,26 +2,26 @@
 //
 // One CTA = one kv head x 16 query rows x ALL query heads of that kv head: the G <= 6 heads share K and V, so their rows are
 // stacked into one operand tile (row 16 w + r = head w, query row r; M = 128 in the instruction, the rows past 16 G are never
-// looked at) and every K / V tile that reaches the SM is used by all of them. Keys are visited in blocks of KB = 128 (64 for
-// trees of at most 384 rows); a block is skipped when none of the 16 rows sees any of its keys (the mask is three half-open
-// key ranges per row: root, own question stem, own leaf up to the row itself).
+// looked at) and every K / V tile that reaches the SM is used by all of them. Visibility is decided per 64 keys: a 64-key
+// block is skipped when none of the 16 rows sees any of its keys (the mask is three half-open key ranges per row: root, own
+// question stem, own leaf up to the row itself). The visible blocks are taken two at a time — any two, they need not be
+// neighbours — so every tensor-core product covers 128 keys (an M = 128 instruction costs the same for 64 columns as for 128).
 //
-//   S = Q K^T   tcgen05.mma, M = 128, N = KB, K = 256: Q and the K block [KB x 256] are K-major 128-byte-swizzled tiles
-//               written by TMA; S lives in tensor memory (KB-column buffers beside O, so the product of the next block runs
-//               while the softmax warps work on this one)
-//   softmax     two threads per (head, row) = one lane of tensor memory, each taking half of the block's columns:
-//               tcgen05.ld of its scores, mask, exp2
-//   O += P V    P is written as a bf16 K-major swizzled tile [128 x KB] by the softmax threads; V arrives transposed
-//               ([256 x N], written by the prep kernel), so the V block [256 d x KB keys] is K-major too; O [128 x 256] fp32
+//   S = Q K^T   tcgen05.mma, M = 128, N = 128, K = 256: Q and the two K blocks [64 x 256] are K-major 128-byte-swizzled tiles
+//               written by TMA (the two blocks land as the two halves of one [128 x 256] operand); S lives in tensor memory
+//               (two 128-column buffers, so the product of the next pair runs while the softmax warps work on this one)
+//   softmax     two threads per (head, row) = one lane of tensor memory, one per block of the pair: tcgen05.ld of its 64
+//               scores, mask, exp2
+//   O += P V    P is written as a bf16 K-major swizzled tile [128 x 128] by the softmax threads; V arrives transposed
+//               ([256 x N], written by the prep kernel), so a V block [256 d x 64 keys] is K-major too; O [128 x 256] fp32
 //               stays in tensor memory for the whole CTA
 //
 // The softmax is two-pass: pass 1 runs Q K^T over the visible blocks and keeps only the row maxima, pass 2 forms
-// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. When the scores of all visible blocks fit
-// in tensor memory beside O (256 columns: two blocks of 128 keys, four of 64) they stay there between the passes; with more
-// blocks, pass 2 recomputes the (cheap) Q K^T products.
-// Shared memory holds Q (48 KB), two regions of one K or V block each and P: in pass 1 the regions alternate as K stages; in
-// pass 2 region 0 takes the K block and region 1 the V block of a key block (the natural stagger of Q K^T -> softmax -> P V
-// hides their loads).
+// P = exp2((s - max) * scale * log2 e) and accumulates O — no rescaling of O ever. With at most two pairs (four visible
+// blocks) all scores stay in tensor memory between the passes; with more, pass 2 recomputes the (cheap) Q K^T products.
+// Shared memory holds Q (48 KB), two 64 KB regions for K / V pairs and P (32 KB): in pass 1 the regions alternate as K
+// stages; in pass 2 region 0 takes the K pair and region 1 the V pair (the natural stagger of Q K^T -> softmax -> P V hides
+// their loads). An odd number of visible blocks repeats the last one as the second half of the last pair, masked out.
 // Roles: warps 0-7 softmax / epilogue, warp 8 TMA producer, warp 9 MMA issuer; mbarriers between them, every wait bounded (the
 // CTA then reports OJB_DEV_WAIT_TIMEOUT through `status`, frees its tensor memory and returns).
 #include "gemm_common.cuh"
@@ -36,19 +36,18 @@ constexpr int kTcThreads = 320;       // 8 softmax warps, producer warp, MMA war
 constexpr int kSoftWarps = 8;
 constexpr uint32_t kQBytes = kMaxG * kQRows * kD * 2;    // 4 k-blocks of [16 G rows][64]
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS = 256;               // O: 256 columns; S: 256 / KB buffers of KB columns
+constexpr uint32_t kColO = 0, kColS = 256;               // O: 256 columns; S: two buffers of 128 columns
 constexpr int kStagePitch = kD * 2 + 16;                 // bytes per row of the output staging tile
-constexpr int kMaxBlocks = 1024;                         // key blocks a CTA can list
-enum { kBarQ = 0, kBarFull = 1, kBarFree = 3, kBarSFull = 5, kBarSFree = 9, kBarPFull = 11, kBarPFree = 12, kBarO = 13, kBarX = 14,
-       kNumBars = 15 };
-// per key-block size: a region holds one K block (4 k-blocks of [KB keys][64]) or one V block (KB / 64 k-blocks of [256 d][64])
-template <int KB> struct Blk {
-  static constexpr uint32_t kRegion = KB * kD * 2;
-  static constexpr uint32_t kPBytes = 128 * KB * 2;      // KB / 64 k-blocks of [128 rows][64 keys]
-  static constexpr int kNS = 256 / KB;                   // S buffers that fit beside O
-  static constexpr size_t kSmem = 1024 + kQBytes + 2 * kRegion + kPBytes + kNumBars * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4 +
-                                  4 * 128 * 4;
-};
+constexpr int kMaxBlocks = 2048;                         // 64-key blocks a CTA can list (131 072 keys)
+constexpr int kSub = 64;               // keys per visibility block
+constexpr int kKB = 128;               // keys per product (two blocks)
+constexpr uint32_t kRegion = kKB * kD * 2;               // 64 KB: a K pair (4 k-blocks of [128 keys][64]) or a V pair (2 of [256 d][64])
+constexpr uint32_t kPBytes = 128 * kKB * 2;              // 2 k-blocks of [128 rows][64 keys]
+constexpr int kNS = 2;                                   // S buffers beside O
+enum { kBarQ = 0, kBarFull = 1, kBarFree = 3, kBarSFull = 5, kBarSFree = 7, kBarPFull = 9, kBarPFree = 10, kBarO = 11, kBarX = 12,
+       kNumBars = 13 };
+constexpr size_t kSmemBytes = 1024 + kQBytes + 2 * kRegion + kPBytes + kNumBars * 8 + 16 + kQRows * 8 * 4 + (kMaxBlocks + 1) * 4 +
+                              4 * 128 * 4;
 
 // Measurement hook (ojb_tree_attn_set_trace): when non-null, the CTA of kv head 0 and the last-but-one block of query rows
 // stores %globaltimer at a few points of its life (see the stamps below).
@@ -72,7 +71,6 @@ __device__ __forceinline__ uint32_t range_bits(int lo, int hi, int w) {
   return upto_b & ~((1u << a) - 1u);
 }
 
-template <int KB>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_vt, AttnArgs g) {
@@ -82,11 +80,10 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* Qs = smem;
-  constexpr uint32_t kRegion = Blk<KB>::kRegion, kPBytes = Blk<KB>::kPBytes;
-  constexpr int kKB = KB, kNS = Blk<KB>::kNS;
-  constexpr int kCols = KB / 2;                // score columns per softmax thread
+  constexpr int kStages = 2, kHalf = 1;
+  constexpr int kCols = kSub;                  // score columns per softmax thread: one block of the pair
   uint8_t* Rg = Qs + kQBytes;                  // two regions
-  uint8_t* Ps = Rg + 2 * kRegion;
+  uint8_t* Ps = Rg + kStages * kRegion;
   uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + kPBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);      // [0] give-up flag, [1] wait limit in ms
@@ -133,14 +130,14 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tma_load_2d(smem_u32(Qs) + kb4 * qstride + w * (kQRows * 128), &map_q, bar(kBarQ), kb4 * 64, (hq0 + w) * N + r0);
   }
   // ordered list of the key blocks that at least one of the 16 rows sees
-  const int NB = (N + kKB - 1) / kKB;
+  const int NB = (N + kSub - 1) / kSub;
   if (warp == 0) {
     int count = 0;
     for (int base = 0; base < NB; base += 32) {
       const int kb = base + lane;
       bool any = false;
       if (kb < NB) {
-        const int k0 = kb * kKB, k1 = k0 + kKB;
+        const int k0 = kb * kSub, k1 = k0 + kSub;
         for (int r = 0; r < kQRows && !any; ++r) {
           const int* q = kr + r * 8;      // (e0, a1, e1, a2, e2, a0)
           any = (q[5] < q[0] && q[5] < k1 && q[0] > k0) || (q[1] < q[2] && q[1] < k1 && q[2] > k0) ||
@@ -154,10 +151,11 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (lane == 0) vis_list[kMaxBlocks] = count < kMaxBlocks ? count : kMaxBlocks;
   }
   __syncthreads();
-  const int nvis = vis_list[kMaxBlocks];
+  const int nblk = vis_list[kMaxBlocks];        // visible 64-key blocks
+  const int nvis = (nblk + 1) >> 1;             // pairs of them
   const int T = 2 * nvis;                       // pass 1 (maxima) then pass 2 (P V) over the same blocks
-  // Up to kNS key blocks: their scores fit in tensor memory beside O, so Q K^T runs once and pass 2 reads the scores again
-  // from there. More blocks: two S buffers rotate and pass 2 recomputes Q K^T.
+  // Up to kNS pairs: their scores fit in tensor memory beside O, so Q K^T runs once and pass 2 reads the scores again from
+  // there. More pairs: the two S buffers rotate and pass 2 recomputes Q K^T.
   const bool one_pass = nvis <= kNS;
   // Gate values of the 16 output pieces this thread multiplies at the very end (consecutive threads take consecutive 16-byte
   // pieces of the [G * 16 rows][256] output tile). Each warp requests them as soon as it has nothing else to wait for, so their
@@ -176,37 +174,43 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   };
-  if (trace && tid == 0) { trace[0] = t_entry; trace[1] = global_timer_ns(); trace[15] = static_cast<unsigned long long>(nvis); }
+  if (trace && tid == 0) { trace[0] = t_entry; trace[1] = global_timer_ns(); trace[15] = static_cast<unsigned long long>(nblk); }
 
   if (warp == kSoftWarps) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int use[2] = {0, 0};
       bool ok = true;
-      auto load = [&](int R, bool is_v, int kb) {     // the K block or the V block of key block kb into region R
+      auto load = [&](int R, bool is_v, int p) {      // the K blocks or the V blocks of pair p into region R
         if (!mbar_wait(bar(kBarFree + R), (use[R] & 1) ^ 1, abort_flag)) return false;
         ++use[R];
         mbar_expect_tx(bar(kBarFull + R), kRegion);
         const uint32_t dst = smem_u32(Rg) + R * kRegion;
-        if (!is_v) {
-          for (int kb4 = 0; kb4 < 4; ++kb4) tma_load_2d(dst + kb4 * (kKB * 128), &map_k, bar(kBarFull + R), kb4 * 64, kvh * N + kb * kKB);
-        } else {
-          for (int kb2 = 0; kb2 < KB / 64; ++kb2) tma_load_2d(dst + kb2 * (kD * 128), &map_vt, bar(kBarFull + R), kb * kKB + kb2 * 64, kvh * kD);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int kb = vis_list[min(2 * p + h, nblk - 1)];      // an odd count repeats the last block (masked out later)
+          if (!is_v) {
+            for (int kb4 = 0; kb4 < 4; ++kb4)
+              tma_load_2d(dst + kb4 * (kKB * 128) + h * (kSub * 128), &map_k, bar(kBarFull + R), kb4 * 64, kvh * N + kb * kSub);
+          } else {
+            tma_load_2d(dst + h * (kD * 128), &map_vt, bar(kBarFull + R), kb * kSub, kvh * kD);
+          }
         }
         return true;
       };
       if (one_pass) {
         // (a region is free for the next block once the product that read it is done; all Q K^T come before the first P V)
-        for (int it = 0; it < nvis && ok; ++it) ok = load(it & 1, false, vis_list[it]);
-        for (int j = 0; j < nvis && ok; ++j) ok = load(j & 1, true, vis_list[j]);
+        for (int it = 0; it < nvis && ok; ++it) ok = load(it % kStages, false, it);
+        for (int j = 0; j < nvis && ok; ++j) ok = load(j % kStages, true, j);
       } else {
-        for (int it = 0; it < nvis && ok; ++it) ok = load(it & 1, false, vis_list[it]);
-        // pass 2: region 0 is free again when Q K^T of the block before is done, region 1 when P V of the block before is done;
-        // Q K^T (j) is issued before P V (j - 1), so the K block of j + 1 is asked for before the V block of j
-        if (ok) ok = load(0, false, vis_list[0]);
+        for (int it = 0; it < nvis && ok; ++it) ok = load(it % kStages, false, it);
+        // pass 2: region 0 takes the K pairs (free again when the Q K^T that read it is done), region 1 the V pairs (free when
+        // their P V is done); Q K^T (j + 1) is issued before P V (j), so the K pair of j + 1 is asked for before the V pair
+        // of j — the order of the requests is the order in which the MMA warp consumes them
+        if (ok) ok = load(0, false, 0);
         for (int j = 0; j < nvis && ok; ++j) {
-          if (j + 1 < nvis) ok = load(0, false, vis_list[j + 1]);
-          if (ok) ok = load(1, true, vis_list[j]);
+          if (j + 1 < nvis) ok = load((j + 1) % kHalf, false, j + 1);
+          if (ok) ok = load(kHalf + j % kHalf, true, j);
         }
       }
     }
@@ -214,7 +218,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(kKB), idesc_o = umma_idesc(kD);
-      int use[2] = {0, 0}, use_s[4] = {0, 0, 0, 0};
+      int use[2] = {0, 0}, use_s[2] = {0, 0};
       bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
       if (trace) trace[8] = global_timer_ns();          // Q has landed
       auto qk = [&](int R, int sb) {                    // S[sb] = Q K^T with the K block in region R
@@ -241,7 +245,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ++use[R];
         tc_fence_after();
 #pragma unroll
-        for (int kb2 = 0; kb2 < KB / 64; ++kb2) {
+        for (int kb2 = 0; kb2 < kKB / 64; ++kb2) {
           const uint64_t pdesc = smem_desc_sw128(smem_u32(Ps) + kb2 * (128 * 128));
           const uint64_t vdesc = smem_desc_sw128(smem_u32(Rg) + R * kRegion + kb2 * (kD * 128));
 #pragma unroll
@@ -253,22 +257,22 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         return true;
       };
       if (one_pass) {
-        for (int it = 0; it < nvis && ok; ++it) ok = qk(it & 1, it);
-        for (int j = 0; j < nvis && ok; ++j) ok = pv(j, j & 1);
+        for (int it = 0; it < nvis && ok; ++it) ok = qk(it % kStages, it);
+        for (int j = 0; j < nvis && ok; ++j) ok = pv(j, j % kStages);
       } else {
-        for (int it = 0; it < nvis && ok; ++it) ok = qk(it & 1, it & 1);
+        for (int it = 0; it < nvis && ok; ++it) ok = qk(it % kStages, it & 1);
         for (int j = 0; j < nvis && ok; ++j) {
-          ok = qk(0, (nvis + j) & 1);
-          if (ok && j > 0) ok = pv(j - 1, 1);
+          ok = qk(j % kHalf, (nvis + j) & 1);
+          if (ok && j > 0) ok = pv(j - 1, kHalf + (j - 1) % kHalf);
         }
-        if (ok && nvis > 0) ok = pv(nvis - 1, 1);
+        if (ok && nvis > 0) ok = pv(nvis - 1, kHalf + (nvis - 1) % kHalf);
       }
       if (ok) umma_commit(bar(kBarO));
       if (trace) trace[9] = global_timer_ns();          // every MMA issued
     }
   } else if (warp < kSoftWarps && (warp & 3) < nw) {
     // ------------------------------------------------------------------ softmax + epilogue: two threads per (head, row).
-    // Thread (half, my) takes columns [half * KB / 2, +KB / 2) of every key block and columns [half * 128, +128) of O; the two
+    // Thread (half, my) takes block `half` of every pair (columns [64 half, +64) of S) and columns [128 half, +128) of O; the two
     // halves exchange their row maxima before pass 2 and their row sums after it through shared memory.
     const int half = warp >> 2;
     const int my = (warp & 3) * 32 + lane;       // tile row = 16 * head + query row = lane of tensor memory
@@ -279,7 +283,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const bool stamp = trace && my == 0 && half == 0;
     constexpr int kLd = kCols / 32;              // 32-column loads per block: 1 or 2
     float m = -INFINITY, l = 0.f;
-    int use_s[4] = {0, 0, 0, 0}, xphase = 0;
+    int use_s[2] = {0, 0}, xphase = 0;
     bool ok = true;
     auto exchange = [&](float v, int slot) {     // hands v to the thread of the other half, returns that thread's value
       xch[(2 * slot + half) * 128 + my] = v;
@@ -292,7 +296,8 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int it = 0; it < T && ok; ++it) {
       const bool pass2 = it >= nvis;
       const int blk = pass2 ? it - nvis : it;
-      const int kb = vis_list[blk];
+      const int sub = 2 * blk + half;                    // this thread's block of the pair; past the end: the masked-out repeat
+      const int kb = vis_list[min(sub, nblk - 1)];
       const int sb = one_pass ? blk : (it & 1);          // S buffer
       if (it == nvis) {
         m = fmaxf(m, exchange(m, 0));
@@ -319,8 +324,8 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       uint32_t bits[kLd];
 #pragma unroll
       for (int i = 0; i < kLd; ++i) {
-        const int w = (kb * kKB + half * kCols) / 32 + i;
-        bits[i] = range_bits(a0, e0, w) | range_bits(a1, e1, w) | range_bits(a2, e2, w);
+        const int w = kb * (kSub / 32) + i;
+        bits[i] = sub < nblk ? (range_bits(a0, e0, w) | range_bits(a1, e1, w) | range_bits(a2, e2, w)) : 0u;
       }
       if (!pass2) {
 #pragma unroll
@@ -444,28 +449,17 @@ extern "C" int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t
   OJB_REQUIRE(qt && kt && vt_t && gate && krange && y && N > 0 && N % 32 == 0 && D == kD);
   OJB_REQUIRE(HQ > 0 && HKV > 0 && HQ % HKV == 0 && HQ / HKV <= kMaxG);
   OJB_REQUIRE(aligned16(qt) && aligned16(kt) && aligned16(vt_t) && aligned16(gate) && aligned16(y));
-  // 64-key blocks for short trees: a leaf row then visits fewer masked-out keys and up to four blocks of scores stay in tensor
-  // memory between the passes; 128-key blocks halve the per-block hand-overs of long roots.
-  const bool small = N <= 384;
-  const int KB = small ? 64 : 128;
-  if ((N + KB - 1) / KB > kMaxBlocks) return OJB_ERR_LIMIT;
+  if ((N + kSub - 1) / kSub > kMaxBlocks) return OJB_ERR_LIMIT;
   CUtensorMap map_q, map_k, map_vt;
   int rc = make_map(&map_q, qt, HQ * N, kD, kQRows);
-  if (rc == OJB_OK) rc = make_map(&map_k, kt, HKV * N, kD, KB);
+  if (rc == OJB_OK) rc = make_map(&map_k, kt, HKV * N, kD, kSub);
   if (rc == OJB_OK) rc = make_map(&map_vt, vt_t, HKV * kD, N, kD);
   if (rc != OJB_OK) return rc;
+  static int smem_set[kMaxDevices] = {};
+  if (!raise_smem_limit(tree_attn_tc_kernel, static_cast<int>(kSmemBytes), smem_set)) return OJB_ERR_LAUNCH;
   AttnArgs a{static_cast<const bf16_t*>(gate), krange, static_cast<bf16_t*>(y), status, static_cast<int>(N), static_cast<int>(HQ),
              static_cast<int>(HKV), static_cast<int>(HQ / HKV), scale * 1.4426950408889634f, gemm_wait_limit_ms()};
-  const dim3 grid(static_cast<unsigned>(HKV), static_cast<unsigned>(N / kQRows));
-  static int set64[kMaxDevices] = {}, set128[kMaxDevices] = {};
-  if (small) {
-    if (!raise_smem_limit(tree_attn_tc_kernel<64>, static_cast<int>(Blk<64>::kSmem), set64)) return OJB_ERR_LAUNCH;
-    launch_kernel(tree_attn_tc_kernel<64>, grid, dim3(kTcThreads), Blk<64>::kSmem, static_cast<cudaStream_t>(stream), map_q, map_k,
-                  map_vt, a);
-  } else {
-    if (!raise_smem_limit(tree_attn_tc_kernel<128>, static_cast<int>(Blk<128>::kSmem), set128)) return OJB_ERR_LAUNCH;
-    launch_kernel(tree_attn_tc_kernel<128>, grid, dim3(kTcThreads), Blk<128>::kSmem, static_cast<cudaStream_t>(stream), map_q, map_k,
-                  map_vt, a);
-  }
+  launch_kernel(tree_attn_tc_kernel, dim3(static_cast<unsigned>(HKV), static_cast<unsigned>(N / kQRows)), dim3(kTcThreads),
+                kSmemBytes, static_cast<cudaStream_t>(stream), map_q, map_k, map_vt, a);
   return launch_status(cudaGetLastError());
 }
