@@ -143,6 +143,14 @@ int ojb_silu_mul(const void* gu, const void* silu_tab, void* out, int64_t rows, 
 int ojb_gate_mul(const void* att, int64_t att_stride_t, int64_t att_stride_h, const void* gate, void* y, int64_t T,
                  int64_t HQ, int64_t D, ojb_stream_t stream);
 
+/* The two inputs of the first layer in one launch (src/fastmodel.py:404-405 does both with torch: `self.embed(ids)` and the
+ * rotary module of the backbone): x[n, :] = table[ids[n], :] (bf16 [vocab, H]; an id outside the table gives a zero row) and,
+ * for the R2 rotary frequencies, cos / sin of pos[n] * inv_freq[j] * 1 written to columns j and j + R2 of cosb / sinb
+ * (bf16 [N, 2 * R2]): angle, cos and sin in fp32, times `scaling`, one rounding to bf16 — the default rope type with text
+ * positions (the three position rows of the multimodal form are equal). ids, pos int64 [N]; inv_freq fp32 [R2]. */
+int ojb_embed_rope(const int64_t* ids, const void* table, int64_t vocab, const int64_t* pos, const float* inv_freq,
+                   float scaling, void* x, void* cosb, void* sinb, int64_t N, int64_t H, int64_t R2, ojb_stream_t stream);
+
 /* src/kernels.cu:1381-1392 l2_prefetch: asks the memory system to bring `nbytes` at `data` (16-byte aligned) into L2, one bulk
  * prefetch per `chunk` bytes (a multiple of 16, at most 1 MiB). Returns at once; nothing waits for the prefetch. */
 int ojb_l2_prefetch(const void* data, int64_t nbytes, int64_t chunk, ojb_stream_t stream);
@@ -284,12 +292,12 @@ int ojb_tree_attn(const void* qt, const void* kt, const void* vt, const void* ga
                   ojb_stream_t stream);
 
 /* The same attention on the tcgen05 tensor cores (head dim 256, key-range mask only): one CTA per (kv head, 16 query rows)
- * stacks the rows of all HQ/HKV <= 6 query heads of the kv head into one operand tile; Q, K and V blocks of 128 keys arrive by
- * TMA, Q K^T and P V are tcgen05.mma with S, P's source and O in tensor memory; two-pass softmax (row maxima first, then
+ * stacks the rows of all HQ/HKV <= 6 query heads of the kv head into one operand tile; Q and the visible 64-key blocks of K and
+ * V (two per 128-key product, any two visible ones) arrive by TMA, Q K^T and P V are tcgen05.mma with S, P's source and O in tensor memory; two-pass softmax (row maxima first, then
  * P = exp2((s - max) scale log2 e) and O += P V) in the exp2 domain; the gate factor sigmoid(gate) is applied in fp32.
  * vt_t bf16 [HKV, 256, N] is V with keys contiguous (second V output of ojb_fullattn_prep). Same result as ojb_tree_attn up to
  * the rounding of P, of the gate factor and the summation order. `status` receives OJB_DEV_WAIT_TIMEOUT if a bounded
- * device-side wait ran out. Replaces the same reference code as ojb_tree_attn (src/kernels.cu:4287-4458; above 384 rows
+ * device-side wait ran out. N <= 131 072 (OJB_ERR_LIMIT beyond). Replaces the same reference code as ojb_tree_attn (src/kernels.cu:4287-4458; above 384 rows
  * src/fastmodel.py:470-473). */
 int ojb_tree_attn_tc(const void* qt, const void* kt, const void* vt_t, const void* gate, const int32_t* krange, void* y,
                      int64_t N, int64_t HQ, int64_t HKV, int64_t D, float scale, int32_t* status, ojb_stream_t stream);

@@ -385,7 +385,7 @@ extern "C" int ojb_l2_prefetch(const void* data, int64_t nbytes, int64_t chunk, 
   return launch_status(cudaGetLastError());
 }
 
-extern "C" int ojb_abi_version(void) { return 4; }
+extern "C" int ojb_abi_version(void) { return 5; }
 
 extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
                                void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream) {
@@ -441,6 +441,42 @@ extern "C" int ojb_resnorm_f32(float* h, const void* x_init, const void* delta, 
     OJB_RN(9) OJB_RN(10) OJB_RN(11) OJB_RN(12) OJB_RN(13) OJB_RN(14) OJB_RN(15) OJB_RN(16)
   }
 #undef OJB_RN
+  return launch_status(cudaGetLastError());
+}
+
+// ---- embedding rows + rotary tables of a packed tree: the two things the forward needs before its first layer.
+// Block n copies row ids[n] of the embedding table to x[n] (an id outside the table gives a zero row) and writes
+// cos / sin of pos[n] * inv_freq[j] for the R2 rotary frequencies, each value twice (columns j and j + R2), as the
+// reference's rotary module does for text positions: angle and cos / sin in fp32, one rounding to bf16.
+__global__ void __launch_bounds__(256)
+embed_rope_kernel(const int64_t* __restrict__ ids, const bf16_t* __restrict__ table, int64_t vocab,
+                  const int64_t* __restrict__ pos, const float* __restrict__ inv_freq, float scaling,
+                  bf16_t* __restrict__ x, bf16_t* __restrict__ cosb, bf16_t* __restrict__ sinb, int H, int R2) {
+  pdl_begin();
+  const int64_t n = blockIdx.x;
+  const int64_t id = ids[n];
+  const bool ok = id >= 0 && id < vocab;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (ok ? id : 0) * H);
+  uint4* dst = reinterpret_cast<uint4*>(x + n * H);
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = ok ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+  const float p = static_cast<float>(pos[n]);
+  for (int j = threadIdx.x; j < R2; j += blockDim.x) {
+    const float a = inv_freq[j] * p;
+    const bf16_t c = f2bf(cosf(a) * scaling), sn = f2bf(sinf(a) * scaling);
+    cosb[n * 2 * R2 + j] = c; cosb[n * 2 * R2 + R2 + j] = c;
+    sinb[n * 2 * R2 + j] = sn; sinb[n * 2 * R2 + R2 + j] = sn;
+  }
+}
+
+extern "C" int ojb_embed_rope(const int64_t* ids, const void* table, int64_t vocab, const int64_t* pos, const float* inv_freq,
+                              float scaling, void* x, void* cosb, void* sinb, int64_t N, int64_t H, int64_t R2,
+                              ojb_stream_t stream) {
+  if (N == 0) return OJB_OK;
+  OJB_REQUIRE(ids && table && pos && inv_freq && x && cosb && sinb && N > 0 && vocab > 0 && H > 0 && H % 8 == 0 && R2 > 0);
+  OJB_REQUIRE((reinterpret_cast<uintptr_t>(table) & 15u) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+  launch_kernel(embed_rope_kernel, dim3(static_cast<unsigned>(N)), dim3(256), 0, static_cast<cudaStream_t>(stream), ids,
+                static_cast<const bf16_t*>(table), vocab, pos, inv_freq, scaling, static_cast<bf16_t*>(x),
+                static_cast<bf16_t*>(cosb), static_cast<bf16_t*>(sinb), static_cast<int>(H), static_cast<int>(R2));
   return launch_status(cudaGetLastError());
 }
 

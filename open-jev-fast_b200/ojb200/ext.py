@@ -597,6 +597,22 @@ def l2_prefetch(t, chunk):
     call("ojb_l2_prefetch", ptr(t), i64(t.numel() * t.element_size()), i64(min(int(chunk), 1 << 20)), stream_ptr())
 
 
+def embed_rope(ids, table, pos, inv_freq, scaling=1.0):
+    """ids, pos int64 [N]; table bf16 [vocab, H]; inv_freq f32 [R2] -> (x bf16 [N, H], cos bf16 [N, 2*R2], sin): the
+    embedding rows and the rotary tables of a packed tree in one launch (the reference calls torch's embedding and the
+    backbone's rotary module, src/fastmodel.py:404-405)."""
+    _chk(ids, table, pos, inv_freq)
+    if ids.dtype != torch.int64 or pos.dtype != torch.int64 or table.dtype != bf16 or inv_freq.dtype != torch.float32:
+        raise RuntimeError("embed_rope: int64 ids / pos, bf16 table and fp32 inv_freq required")
+    N, (V, H), R2 = ids.numel(), table.shape, inv_freq.numel()
+    x = torch.empty(N, H, dtype=bf16, device=table.device)
+    cos = torch.empty(N, 2 * R2, dtype=bf16, device=table.device)
+    sin = torch.empty_like(cos)
+    call("ojb_embed_rope", ptr(ids), ptr(table), i64(V), ptr(pos), ptr(inv_freq), f32(scaling), ptr(x), ptr(cos), ptr(sin),
+         i64(N), i64(H), i64(R2), stream_ptr())
+    return x, cos, sin
+
+
 # ------------------------------------------------------------------------------------------------ scoring head
 def score_head(hn, rows, W, bias):
     """hn bf16 [N, H], rows int64 [S], W f32 [A, H], bias f32 [A] or None -> f32 [S, A] (gather + fp32 linear in one

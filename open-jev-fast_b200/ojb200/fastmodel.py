@@ -68,6 +68,11 @@ class FastQwen35(torch.nn.Module):
         self.H, self.eps = cfg.hidden_size, cfg.rms_norm_eps
         self.layer_types = list(cfg.layer_types)
         self.embed, self.rotary = core.embed_tokens, core.rotary_emb
+        # default rope type on text positions: cos / sin come from ojb_embed_rope together with the embedding rows
+        self._own_rope = (getattr(self.rotary, "rope_type", None) == "default" and self.embed.weight.dtype == torch.bfloat16
+                          and self.embed.weight.is_contiguous())
+        self._inv_freq = self.rotary.inv_freq.detach().float().contiguous()
+        self._rope_scale = float(getattr(self.rotary, "attention_scaling", 1.0))
         self.v2, self.fuse_l2 = v2, fuse_l2
         self._bufs = {}
         self._plan, self._tuned = {}, set()     # (op, M, N, K) -> kernel choice, filled by tune()
@@ -322,8 +327,11 @@ class FastQwen35(torch.nn.Module):
     def forward_gtree(self, ids, lay, return_all=False):
         """src/fastmodel.py:400-482: ids int64 [N] packed rows, lay from gtree_build -> bf16 [S, H] (final norm applied) of
         every candidate's last row; return_all=True gives all N rows (the scoring head gathers by itself)."""
-        x = self.embed(ids).contiguous()
-        cos, sin = self._rope(x, lay.pos)
+        if self._own_rope and ids.dtype == torch.int64 and lay.pos.dtype == torch.int64:
+            x, cos, sin = K.embed_rope(ids, self.embed.weight, lay.pos, self._inv_freq, self._rope_scale)
+        else:                                   # other rope types: the backbone's own module (torch)
+            x = self.embed(ids).contiguous()
+            cos, sin = self._rope(x, lay.pos)
         lin = [t == "linear_attention" for t in self.layer_types]
         rowmask = lay.rowmask
         h = torch.empty(x.shape, dtype=torch.float32, device=x.device)        # the residual stream, fp32 throughout

@@ -25,6 +25,7 @@ REP_MAX = int(os.environ.get("REP_MAX", "4096"))
 STATE_PATH = os.environ.get("OJ_STATE_PATH", "0") == "1"
 MAX_GRAPHS = int(os.environ.get("MAX_GRAPHS", "512"))
 USE_GRAPH = os.environ.get("USE_GRAPH", "1") == "1"
+CAPTURE_AFTER = int(os.environ.get("CAPTURE_AFTER", "1"))
 
 
 _TEMPLATE_PARTS = {}
@@ -71,17 +72,27 @@ class Entry:
     thread-local error mode: other threads of the process (the workers of other GPUs behind the router) may allocate and
     launch on their own devices while this one captures."""
 
-    def __init__(self, scorer, dims, host_bufs):
+    def __init__(self, scorer, dims, host_bufs, capture=True):
         fast = scorer.fast
         dev = scorer.device
+        self.scorer = scorer
         self.dims = dict(dims)
         self.g64, self.g32, self.ge = (b.to(dev) for b in host_bufs)
         f = _layout.field_views(dims, self.g64, self.g32, self.ge)
         self.ids = f.pop("ids")
         self.lay = _layout.SimpleNamespace(N=dims["N"], S=dims["S"], L2=dims["L2"], key=(dims["N"], dims["S"], dims["L2"]), **f)
         self.lay.walk_ptr, self.lay.n_walks = self.lay.meta[6:8], 1
-        fast.tune(dims["N"])            # per-shape choice of GEMM kernel and K split, timed on the model's own weights
-        body = lambda: fast.score_gtree(self.ids, self.lay, scorer.head_w, scorer.head_b)
+        self._body = lambda: fast.score_gtree(self.ids, self.lay, scorer.head_w, scorer.head_b)
+        self.g, self.out, self.launches, self.seen = None, None, 0, 0
+        if capture:
+            self.capture()
+
+    def capture(self):
+        """Tune the GEMM choices for this row count, warm up, and (unless the scorer runs without graphs) capture the graph.
+        A scorer with capture_after > 1 calls this only when a key comes back; until then the entry runs eagerly with the
+        cost model's kernel choices."""
+        scorer, dev, body = self.scorer, self.scorer.device, self._body
+        scorer.fast.tune(self.dims["N"])    # per-shape choice of GEMM kernel and K split, timed on the model's own weights
         st = torch.cuda.Stream(device=dev)
         st.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(st):
@@ -89,19 +100,15 @@ class Entry:
                 body()
         torch.cuda.current_stream(dev).wait_stream(st)
         torch.cuda.synchronize(dev)
-        self.g = None
+        n0 = _lib.launch_count()
         if scorer.use_graph:
             self.g = torch.cuda.CUDAGraph()
-            n0 = _lib.launch_count()
             with torch.cuda.graph(self.g, pool=scorer.pool, stream=scorer.capture_stream, capture_error_mode="thread_local"):
                 self.out = body()
-            self.launches = _lib.launch_count() - n0
             torch.cuda.synchronize(dev)
         else:
-            n0 = _lib.launch_count()
             self.out = body()
-            self.launches = _lib.launch_count() - n0
-        self._body = body
+        self.launches = _lib.launch_count() - n0
 
     def run(self, host_bufs):
         """Upload one request's tables (pinned host buffers) and replay. Returns the static fp32 [S, A] output."""
@@ -112,10 +119,13 @@ class Entry:
         return self.replay()
 
     def replay(self):
+        self.seen += 1
         if self.g is not None:
             self.g.replay()
         else:
+            n0 = _lib.launch_count()
             self.out = self._body()
+            self.launches = _lib.launch_count() - n0
         return self.out
 
 
@@ -213,8 +223,13 @@ class Scorer:
     """One GPU's worth of the service: model + head + graph cache + lock (one request at a time per GPU, src/server.py:97)."""
 
     def __init__(self, fast, head_w, head_b=None, pad_id=0, device=None, use_graph=USE_GRAPH, max_graphs=MAX_GRAPHS,
-                 access_log=None):
+                 access_log=None, capture_after=CAPTURE_AFTER):
+        """capture_after = 1 (the reference's behaviour, src/server.py:118-124): a key's graph is captured the first time the
+        key is seen. capture_after = n > 1: the first n - 1 requests of a key run eagerly (no tuning, no warm-up, no capture:
+        about the time of one forward instead of three forwards plus the instantiation of a 610-node graph) and the graph is
+        captured when the key comes back for the n-th time — for request streams in which most shapes never repeat."""
         self.fast, self.head_w, self.head_b, self.pad_id = fast, head_w, head_b, pad_id
+        self.capture_after = max(1, int(capture_after))
         self.device = torch.device(device if device is not None else head_w.device)
         self.use_graph, self.max_graphs = use_graph, max_graphs
         self.graphs = collections.OrderedDict()
@@ -230,13 +245,17 @@ class Scorer:
     def entry_for(self, dims, host_bufs):
         key = (dims["N"], dims["S"], dims["L2"])
         ent = self.graphs.get(key)
-        captured = ent is None
-        if captured:
-            ent = self.graphs[key] = Entry(self, dims, host_bufs)
+        captured = False
+        if ent is None:
+            captured = self.capture_after <= 1
+            ent = self.graphs[key] = Entry(self, dims, host_bufs, capture=captured)
             while len(self.graphs) > self.max_graphs:
                 self.graphs.popitem(last=False)
         else:
             self.graphs.move_to_end(key)
+            if ent.g is None and self.use_graph and ent.seen + 1 >= self.capture_after:
+                ent.capture()
+                captured = True
         return ent, captured
 
     def score_tokens(self, seqs, groups, with_info=False):

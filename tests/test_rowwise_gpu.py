@@ -107,3 +107,26 @@ def test_fullattn_prep(N, HQ, HKV, D, RD):
     assert torch.equal(vt[0].cpu(), rv) and torch.equal(gate.cpu(), rg)
     _same(qt[0], rq, frac=0.98)
     _same(kt[0], rk, frac=0.98)
+
+
+def test_embed_rope_matches_torch_embedding_and_the_backbone_rotary_module():
+    """ojb_embed_rope against what the reference's forward calls (src/fastmodel.py:404-405): torch's embedding lookup and the
+    Hugging Face rotary module on text positions — bit for bit, including positions in the tens of thousands."""
+    from ojb200 import ext as K, modelgen as MG
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5TextRotaryEmbedding
+    cfg = MG.make_config(**dict(MG.SMALL, head_dim=256))
+    rot = Qwen3_5TextRotaryEmbedding(cfg).cuda()
+    g = torch.Generator().manual_seed(3)
+    N, V, H = 96, 512, 256
+    table = torch.randn(V, H, generator=g).to(torch.bfloat16).cuda()
+    ids = torch.randint(0, V, (N,), generator=g).cuda()
+    pos = torch.cat([torch.arange(40), torch.randint(0, 40000, (N - 40,), generator=g)]).cuda()
+    x, cos, sin = K.embed_rope(ids, table, pos, rot.inv_freq.float().contiguous(), float(rot.attention_scaling))
+    want_x = torch.nn.functional.embedding(ids, table)
+    want_cos, want_sin = rot(want_x.view(1, N, H), pos.view(1, 1, N).expand(3, 1, N))
+    assert torch.equal(x, want_x)
+    assert torch.equal(cos, want_cos.reshape(N, -1)) and torch.equal(sin, want_sin.reshape(N, -1))
+    bad = ids.clone()
+    bad[5] = V + 7                                   # an id outside the table: a zero row, not a fault
+    x2, _, _ = K.embed_rope(bad, table, pos, rot.inv_freq.float().contiguous(), 1.0)
+    assert x2[5].abs().max().item() == 0 and torch.equal(x2[6:], want_x[6:])

@@ -65,6 +65,27 @@ def test_concurrent_callers_with_one_key_get_their_own_scores():
             assert torch.equal(torch.cat(got[i][j]), want[i].cpu()), (i, j)
 
 
+def test_capture_at_second_sight_runs_the_first_request_eagerly():
+    """capture_after=2: a key's first request runs without tuning, warm-up or capture; the graph is taken when the key comes
+    back, and from then on requests replay it."""
+    from ojb200 import fastmodel as FM, modelgen as MG, server as SV
+    cfg = MG.make_config(**MG.SMALL)
+    fast = FM.FastQwen35(MG.build_core(cfg, device="cpu", seed=3, std=0.05, draw_on="cpu").to("cuda"))
+    W, b = MG.make_head(cfg.hidden_size, A=2, seed=2, device="cuda")
+    sc = SV.Scorer(fast, W, b, pad_id=0, capture_after=2)
+    seqs, groups = _tree(1, cfg.vocab_size)
+    outs, infos = [], []
+    for _ in range(3):
+        o, info = sc.score_tokens(seqs, groups, with_info=True)
+        outs.append(o.clone())
+        infos.append(info)
+    ent = sc.graphs[infos[0]["key"]]
+    assert [i["captured"] for i in infos] == [False, True, False] and ent.g is not None and ent.seen == 3
+    assert torch.equal(outs[1], outs[2])                                  # capture pass and replay: same graph
+    assert (outs[0] - outs[1]).abs().max().item() < 6e-2                  # eager run: cost-model kernels, not the tuned ones
+    assert all(i["launches"] > 0 for i in infos)
+
+
 def test_forward_records_noul_and_lru():
     cfg, fast, sc, W, b = _scorer(max_graphs=2, A=1)
     s1, g1 = _tree(5, cfg.vocab_size)
