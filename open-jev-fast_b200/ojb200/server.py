@@ -96,7 +96,7 @@ class Entry:
         st = torch.cuda.Stream(device=dev)
         st.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(st):
-            for _ in range(2):          # warm-up
+            for _ in range(1):          # warm-up (allocations of every shape happen here, outside the capture)
                 body()
         torch.cuda.current_stream(dev).wait_stream(st)
         torch.cuda.synchronize(dev)
