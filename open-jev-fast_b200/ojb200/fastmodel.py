@@ -40,6 +40,7 @@ TREE_NATIVE = os.environ.get("OJ_TREE_NATIVE", "1") == "1"      # 0: replicated 
 # 32.00 against 31.91 ms on the 539-row tree, 20.86 against 20.19 ms on the 277-row tree — the work lands on the latency chain
 # of a kernel that is latency-bound already, so it is off.
 FUSE_PREP = os.environ.get("OJ_FUSE_PREP", "0") == "1"
+
 TREE_LEVELS = os.environ.get("OJ_TREE_LEVELS", "0") == "1"      # 1: state pass per tree level (3 launches), 0: one depth-first walk
 # (measured on the 539-row tree: depth-first 84 us per layer for intra + state, level-parallel 88 us: the two extra launches
 # and the six waves of short single-step CTAs cost more than the shorter dependency chain saves)
