@@ -381,7 +381,7 @@ tree_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int v8 = 0; v8 < 4; ++v8) {
           float a[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) a[e] = __uint_as_float(o[v8 * 8 + e]) * inv_l;
+          for (int e = 0; e < 8; ++e) a[e] = l > 0.f ? __uint_as_float(o[v8 * 8 + e]) * inv_l : 0.f;   // a row that sees no key: zeros, whatever tensor memory holds
           *reinterpret_cast<uint4*>(srow + c * 64 + v8 * 16) = pack8(a);
         }
       }

@@ -72,6 +72,7 @@ def test_tree_attention_tcgen05(N_case, HQ, HKV):
     vis = torch.as_tensor(OL.gtree_layout(seqs, groups, pad_id, NB, PB)["vis"])
     ref = O.tree_attention(qt[0].cpu(), kt[0].cpu(), vt[0].cpu(), gate.cpu(), vis, scale).float()
     got = y.float().cpu()
+    assert torch.isfinite(got).all()                 # padding rows included
     real = lay.rowmask.cpu().bool()
     rel = ((got[real] - ref[real]).norm() / ref[real].norm()).item()
     assert rel < 4e-3, rel
