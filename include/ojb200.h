@@ -219,11 +219,14 @@ int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV);
  *   walk_ptr int32 [n_walks+1] = step ranges that are independent of each other (one CTA column each)
  * q, k bf16 [rows, HK, 128]; v bf16 [rows, HV, 128]; g fp32 (natural-log decay) and beta bf16 [rows, HV];
  * init_state / final_state fp32 [*, HV, 128(dk), 128(dv)] or null; out bf16 [rows, HV, 128], rows not covered by a chunk
- * are left untouched. o = scale * (...). scratch: ojb_gdn_scratch_bytes(n_chunks, HV) bytes, 16-byte aligned. */
+ * are left untouched. o = scale * (...). scratch: ojb_gdn_scratch_bytes(n_chunks, HV) bytes, 16-byte aligned.
+ * The state pass fetches the operands of each step with bulk copies that complete on an mbarrier; its wait for them is
+ * bounded (ojb_gemm_set_wait_limit_ms). `status` (int32 device word, may be null) receives OJB_DEV_WAIT_TIMEOUT if a wait ran
+ * out; the walks of that CTA column are then incomplete. The same holds for the three forms below. */
 int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const void* beta, const int32_t* chunks,
                     int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr, int64_t n_walks,
                     const float* init_state, float* final_state, void* scratch, void* out, int64_t HK, int64_t HV,
-                    float scale, ojb_stream_t stream);
+                    float scale, int32_t* status, ojb_stream_t stream);
 
 /* ojb_gdn_chunked with ojb_gdn_prep fused into its first launch (src/kernels.cu:1173 linattn_prep_dedup2 + :4225 gdn_fused6 in
  * two launches instead of three): the state-independent pass reads the in-projection output itself — proj bf16
@@ -235,7 +238,7 @@ int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g,
 int ojb_gdn_chunked_proj(const void* proj, const int32_t* hist, const void* convw, const void* A_log, const void* dt_bias,
                          const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                          int64_t n_walks, const float* init_state, float* final_state, void* scratch, void* out, int64_t KD,
-                         int64_t VD, int64_t HK, int64_t HV, float scale, ojb_stream_t stream);
+                         int64_t VD, int64_t HK, int64_t HV, float scale, int32_t* status, ojb_stream_t stream);
 
 /* ojb_gdn_chunked with the state pass run level by level (1 + n_levels launches): `levels` is a HOST array of n_levels + 1
  * walk indices; the walks [levels[l], levels[l+1]) of level l run side by side and start from the end states that walks of
@@ -245,9 +248,10 @@ int ojb_gdn_chunked_proj(const void* proj, const int32_t* hist, const void* conv
 int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const float* g, const void* beta,
                            const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                            const int32_t* levels, int64_t n_levels, float* states, void* scratch, void* out, int64_t HK,
-                           int64_t HV, float scale, ojb_stream_t stream);
+                           int64_t HV, float scale, int32_t* status, ojb_stream_t stream);
 
-/* Scratch-free form of ojb_gdn_chunked. It has no counterpart in open-jev-fast. Same arguments without `scratch`: the
+/* Scratch-free form of ojb_gdn_chunked. It has no counterpart in open-jev-fast. Same arguments without `scratch` (`status`
+ * included): the
  * per-(chunk, head) work items live in a fixed 80 MiB array inside the library's device image (every GPU that loads the
  * library holds it until the process exits), so the call needs no device allocation at all. It is meant for callers that
  * cannot allocate around the call — an inference process whose memory plan is frozen after start-up, or host code that has
@@ -262,7 +266,7 @@ int64_t ojb_gdn_static_max_items(void);
 int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
                            const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                            int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK, int64_t HV,
-                           float scale, ojb_stream_t stream);
+                           float scale, int32_t* status, ojb_stream_t stream);
 
 /* Measurement hook of the state pass (no counterpart in the reference): `records` = null switches it off; otherwise a device
  * buffer of 4 + 12 uint64 words per walk step. The CTA of head 0 / column slice 0 / walk 0 stores %globaltimer at kernel entry,

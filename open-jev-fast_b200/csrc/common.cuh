@@ -55,6 +55,55 @@ __device__ __forceinline__ void report_status(int32_t* status, int32_t code) {
   if (status) atomicCAS(status, 0, code);
 }
 
+// ---- mbarrier primitives shared by every kernel that waits for asynchronous copies or tensor-core work
+constexpr int kDefaultWaitMs = 2000;   // limit of every device-side wait unless ojb_gemm_set_wait_limit_ms changed it
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the limit ran out or another role of this CTA already gave up. abort_flag[0] is the
+// CTA's give-up flag, abort_flag[1] the limit in milliseconds (both in shared memory, set up by thread 0 of the CTA).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > static_cast<uint64_t>(abort_flag[1]) * 1000000ull) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// Host-settable limit of those waits and the failure switch of the tests (gemm_api.cu: ojb_gemm_set_wait_limit_ms,
+// ojb_gemm_test_drop_copy); read by every launcher whose kernel waits on an mbarrier.
+int gemm_wait_limit_ms();
+int gemm_drop_copy();
+
 static inline int launch_status(cudaError_t e) { return e == cudaSuccess ? OJB_OK : OJB_ERR_LAUNCH; }
 
 // Launch state that CUDA keeps per device (a kernel's opt-in shared-memory size, the SM count) is cached per device, so one

@@ -36,7 +36,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -590,28 +589,24 @@ constexpr int kStateSmem = 2 * kBufElems * 2 + 2 * kHD * kLdS * 2 + kChunk * kLd
 constexpr int kStateSmemLean = kBufElems * 2 + 2 * kHD * kLdS * 2 + kChunk * kLdS * 2 + 16;
 
 // The operands of one step are three flat byte ranges of the item: w | qg | kg (52 224 B), this CTA's u slice (5 120 B) and
-// Aqk (9 216 B), already in the padded shapes the MMA fragments are read from.
-__device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, int dv0, int tid) {
-  constexpr int kC1 = 3 * kChunk * kLd / 8, kC2 = kChunk * kLdS / 8, kC3 = kChunk * kLdA / 8;   // 16-byte chunks
+// Aqk (9 216 B), already in the padded shapes the MMA fragments are read from. One thread asks the copy engine for them
+// (cp.async.bulk, no tensor map needed for a flat range); the bytes are counted on an mbarrier. As 16-byte cp.async requests
+// of all 256 threads the same fetch took longer than a step on part of the SMs (the walk of those CTAs ran at 2.6 us per
+// step instead of 1.8), which set the duration of the whole kernel.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void state_prefetch(bf16_t* buf, const bf16_t* item, int dv0, uint32_t bar, bool drop) {
+  constexpr uint32_t kB1 = 3 * kChunk * kLd * 2, kB2 = kChunk * kLdS * 2, kB3 = kChunk * kLdA * 2;
+  static_assert(kB1 % 16 == 0 && kB2 % 16 == 0 && kB3 % 16 == 0 && (kOffU * 2) % 16 == 0 && (kOffA * 2) % 16 == 0 &&
+                (kItemElems * 2) % 16 == 0, "bulk copies need 16-byte aligned ranges");
   const uint32_t dst = smem_u32(buf);
-  const uint4* src = reinterpret_cast<const uint4*>(item);
-#pragma unroll
-  for (int j = 0; j < (kC1 + kStateThreads - 1) / kStateThreads; ++j) {
-    const int c = tid + j * kStateThreads;
-    if (c < kC1) cp_async16(dst + c * 16, src + c);
-  }
-  const uint4* usrc = reinterpret_cast<const uint4*>(item + kOffU + (dv0 / kDv) * (kChunk * kLdS));
-#pragma unroll
-  for (int j = 0; j < (kC2 + kStateThreads - 1) / kStateThreads; ++j) {
-    const int c = tid + j * kStateThreads;
-    if (c < kC2) cp_async16(dst + (kC1 + c) * 16, usrc + c);
-  }
-  const uint4* asrc = reinterpret_cast<const uint4*>(item + kOffA);
-#pragma unroll
-  for (int j = 0; j < (kC3 + kStateThreads - 1) / kStateThreads; ++j) {
-    const int c = tid + j * kStateThreads;
-    if (c < kC3) cp_async16(dst + (kC1 + kC2 + c) * 16, asrc + c);
-  }
+  mbar_expect_tx(bar, kB1 + kB2 + kB3);
+  if (drop) return;      // tests only: the announced bytes never arrive, the bounded wait of this step runs out
+  bulk_g2s(dst, item, kB1, bar);
+  bulk_g2s(dst + kB1, item + kOffU + (dv0 / kDv) * (kChunk * kLdS), kB2, bar);
+  bulk_g2s(dst + kB1 + kB2, item + kOffA, kB3, bar);
 }
 
 // Measurement hook (ojb_gdn_set_trace): when non-null, the CTA of head 0 / column slice 0 / walk 0 records six %globaltimer
@@ -625,7 +620,7 @@ template <bool LEAN>
 __global__ void __launch_bounds__(kStateThreads)
 gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__ chunks, const int32_t* __restrict__ steps,
                  const int32_t* __restrict__ walk_ptr, const float* __restrict__ init_state, float* __restrict__ final_state,
-                 bf16_t* __restrict__ out, int HV) {
+                 bf16_t* __restrict__ out, int HV, int32_t* status, int wait_ms, int drop_copy) {
   const unsigned long long t_entry = global_timer_ns();
   pdl_begin();
   const int h = blockIdx.x, dv0 = blockIdx.y * kDv;
@@ -657,6 +652,15 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
   __shared__ int4 sm_step[kWin];
   __shared__ int4 sm_chunk[kWin];
   __shared__ float sm_gl[kWin];
+  __shared__ __align__(8) uint64_t sm_bar[2];      // operand buffers full (bytes of the bulk copies)
+  __shared__ int sm_abort[2];                      // [0] a bounded wait ran out, [1] the limit in milliseconds
+  if (tid == 0) {
+    mbar_init(smem_u32(&sm_bar[0]), 1);
+    mbar_init(smem_u32(&sm_bar[1]), 1);
+    sm_abort[0] = 0;
+    sm_abort[1] = wait_ms;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   for (int i = tid; i < min(kWin, s_end - s_begin); i += kStateThreads) {
     const int4 st = reinterpret_cast<const int4*>(steps)[s_begin + i];
     sm_step[i] = st;
@@ -669,8 +673,7 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     return scratch + (static_cast<int64_t>(c) * HV + h) * kItemElems;
   };
   if constexpr (!LEAN) {
-    state_prefetch(bufs, item_of(s_begin), dv0, tid);
-    cp_async_commit();
+    if (tid == 0) state_prefetch(bufs, item_of(s_begin), dv0, smem_u32(&sm_bar[0]), false);
   }
 
   unsigned long long* trace = g_state_trace;
@@ -684,12 +687,15 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     const int4 ch = staged ? sm_chunk[s - s_begin] : reinterpret_cast<const int4*>(chunks)[st.x];
     bf16_t* buf = LEAN ? bufs : bufs + ((s - s_begin) & 1) * kBufElems;
     const bf16_t* item = item_of(s);
-    if constexpr (LEAN) {
-      state_prefetch(buf, item, dv0, tid);
-    } else {
-      if (s + 1 < s_end) state_prefetch(bufs + ((s + 1 - s_begin) & 1) * kBufElems, item_of(s + 1), dv0, tid);
+    // (the buffer asked for here was last read in the step before this one, which ended with a CTA-wide barrier)
+    if (tid == 0) {
+      if constexpr (LEAN) {
+        state_prefetch(buf, item, dv0, smem_u32(&sm_bar[0]), drop_copy && s == s_begin + 1);
+      } else if (s + 1 < s_end) {
+        state_prefetch(bufs + ((s + 1 - s_begin) & 1) * kBufElems, item_of(s + 1), dv0, smem_u32(&sm_bar[(s + 1 - s_begin) & 1]),
+                       drop_copy && s == s_begin);
+      }
     }
-    cp_async_commit();
 
     bf16_t* Sb = Sb2 + ((s - s_begin) & 1) * (kHD * kLdS);
     if (chain) {
@@ -732,8 +738,12 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
           *reinterpret_cast<uint32_t*>(Sb + dk * kLdS + b * 8 + tc) = pack2(S[a][b][half * 2], S[a][b][half * 2 + 1]);
         }
     }
-    if constexpr (LEAN) cp_async_wait<0>(); else cp_async_wait<1>();   // this step's operands have landed (a prefetch of the next step may still be in flight)
+    // this step's operands have landed (the copies of the next step may still be in flight); the wait is bounded, and a CTA
+    // whose wait ran out leaves the walk as a whole
+    if constexpr (LEAN) mbar_wait(smem_u32(&sm_bar[0]), static_cast<uint32_t>((s - s_begin) & 1), sm_abort);
+    else mbar_wait(smem_u32(&sm_bar[(s - s_begin) & 1]), static_cast<uint32_t>(((s - s_begin) >> 1) & 1), sm_abort);
     __syncthreads();
+    if (sm_abort[0]) break;
     if (rec) rec[1] = global_timer_ns();
 
     const bf16_t* Ws = buf;
@@ -869,7 +879,11 @@ gdn_state_kernel(const bf16_t* __restrict__ scratch, const int32_t* __restrict__
     __syncthreads();   // everyone is done with Vn and this operand buffer before they are overwritten
     if (rec) rec[5] = global_timer_ns();
   }
-  cp_async_wait<0>();
+  if (sm_abort[0]) {
+    if (tid == 0) report_status(status, OJB_DEV_WAIT_TIMEOUT);
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);      // copies that were already issued land before the CTA leaves
+    __syncthreads();
+  }
   if (tracer && tid == 0) trace[2] = global_timer_ns();
 }
 
@@ -975,7 +989,7 @@ extern "C" int64_t ojb_gdn_scratch_bytes(int64_t n_chunks, int64_t HV) { return 
 extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, const float* g, const void* beta,
                                const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                                int64_t n_walks, const float* init_state, float* final_state, void* scratch, void* out,
-                               int64_t HK, int64_t HV, float scale, ojb_stream_t stream) {
+                               int64_t HK, int64_t HV, float scale, int32_t* status, ojb_stream_t stream) {
   if (n_chunks == 0 || n_walks == 0) return OJB_OK;
   OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && scratch && out);
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_walks > 0 && n_walks <= 65535 && HV <= 65535);
@@ -988,7 +1002,7 @@ extern "C" int ojb_gdn_chunked(const void* q, const void* k, const void* v, cons
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
       static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out),
-      static_cast<int>(HV));
+      static_cast<int>(HV), status, gemm_wait_limit_ms(), gemm_drop_copy());
   return launch_status(cudaGetLastError());
 }
 
@@ -996,7 +1010,7 @@ extern "C" int ojb_gdn_chunked_proj(const void* proj, const int32_t* hist, const
                                     const void* dt_bias, const int32_t* chunks, int64_t n_chunks, const int32_t* steps,
                                     const int32_t* walk_ptr, int64_t n_walks, const float* init_state, float* final_state,
                                     void* scratch, void* out, int64_t KD, int64_t VD, int64_t HK, int64_t HV, float scale,
-                                    ojb_stream_t stream) {
+                                    int32_t* status, ojb_stream_t stream) {
   if (n_chunks == 0 || n_walks == 0) return OJB_OK;
   OJB_REQUIRE(proj && hist && convw && A_log && dt_bias && chunks && steps && walk_ptr && scratch && out);
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && KD == HK * kHD && VD == HV * kHD && n_chunks > 0 && n_walks > 0 &&
@@ -1012,7 +1026,7 @@ extern "C" int ojb_gdn_chunked_proj(const void* proj, const int32_t* hist, const
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks)),
                 dim3(kStateThreads), kStateSmem, st, static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr, init_state,
-                final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
+                final_state, static_cast<bf16_t*>(out), static_cast<int>(HV), status, gemm_wait_limit_ms(), gemm_drop_copy());
   return launch_status(cudaGetLastError());
 }
 
@@ -1045,7 +1059,7 @@ extern "C" int64_t ojb_gdn_static_max_items(void) { return ojb::kStaticItems; }
 extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* v, const float* g, const void* beta,
                                       const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                                       int64_t n_walks, const float* init_state, float* final_state, void* out, int64_t HK,
-                                      int64_t HV, float scale, ojb_stream_t stream) {
+                                      int64_t HV, float scale, int32_t* status, ojb_stream_t stream) {
   if (n_chunks == 0 || n_walks == 0) return OJB_OK;
   OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && out);
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_walks > 0 && n_walks <= 65535 && HV <= 65535);
@@ -1072,7 +1086,7 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
       intra_pairing(n_chunks, HV), PrepSrc{});
   if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(n_walks))), dim3(kStateThreads), kStateSmem, st, 
-      scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV));
+      scratch, chunks, steps, walk_ptr, init_state, final_state, static_cast<bf16_t*>(out), static_cast<int>(HV), status, gemm_wait_limit_ms(), gemm_drop_copy());
   return launch_status(cudaGetLastError());
 }
 
@@ -1083,7 +1097,7 @@ extern "C" int ojb_gdn_chunked_static(const void* q, const void* k, const void* 
 extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* v, const float* g, const void* beta,
                                       const int32_t* chunks, int64_t n_chunks, const int32_t* steps, const int32_t* walk_ptr,
                                       const int32_t* levels, int64_t n_levels, float* states, void* scratch, void* out,
-                                      int64_t HK, int64_t HV, float scale, ojb_stream_t stream) {
+                                      int64_t HK, int64_t HV, float scale, int32_t* status, ojb_stream_t stream) {
   if (n_chunks == 0 || n_levels == 0) return OJB_OK;
   OJB_REQUIRE(q && k && v && g && beta && chunks && steps && walk_ptr && levels && states && scratch && out);
   OJB_REQUIRE(HK > 0 && HV > 0 && HV % HK == 0 && n_chunks > 0 && n_levels > 0 && n_levels <= 16 && HV <= 65535);
@@ -1101,11 +1115,11 @@ extern "C" int ojb_gdn_chunked_levels(const void* q, const void* k, const void* 
     if (nw > 1) {   // many short walks: the lean form fits two CTAs per SM
       launch_kernel(gdn_state_kernel<true>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, static_cast<unsigned>(nw))), dim3(kStateThreads), kStateSmemLean, st, 
           static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
-          static_cast<int>(HV));
+          static_cast<int>(HV), status, gemm_wait_limit_ms(), gemm_drop_copy());
     } else {
       launch_kernel(gdn_state_kernel<false>, dim3(dim3(static_cast<unsigned>(HV), kHD / kDv, 1)), dim3(kStateThreads), kStateSmem, st, 
           static_cast<const bf16_t*>(scratch), chunks, steps, walk_ptr + levels[l], states, states, static_cast<bf16_t*>(out),
-          static_cast<int>(HV));
+          static_cast<int>(HV), status, gemm_wait_limit_ms(), gemm_drop_copy());
     }
     if (cudaGetLastError() != cudaSuccess) return OJB_ERR_LAUNCH;
   }

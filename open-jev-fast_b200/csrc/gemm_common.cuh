@@ -11,49 +11,6 @@ namespace {
 constexpr int kBM = 128;           // UMMA M
 constexpr int kBK = 64;            // bf16 elements per stage along K = one 128-byte swizzle row
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma.kind::f16
-constexpr int kDefaultWaitMs = 2000;   // limit of every device-side wait unless ojb_gemm_set_wait_limit_ms changed it
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      " .reg .pred p;\n"
-      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      " selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false when the limit ran out or another role of this CTA already gave up. abort_flag[0] is the
-// CTA's give-up flag, abort_flag[1] the limit in milliseconds (both in shared memory, set up by thread 0 of the CTA).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > static_cast<uint64_t>(abort_flag[1]) * 1000000ull) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -279,8 +236,6 @@ int gemm_block256_launch(int epi, int bn_req, const void* x, const void* w, void
                          int splits, int64_t ldo, int32_t* status, cudaStream_t stream);
 void gemm_block256_set_trace(unsigned long long* buf, int cap);
 // process-wide settings kept in gemm_api.cu: limit of the device-side waits (ms) and the failure-injection switch of the tests
-int gemm_wait_limit_ms();
-int gemm_drop_copy();
 // e4m3 operands with one fp32 scale per row of x (sx) and per row of w (sw): out = (xq . wq^T) * sx[m] * sw[n]
 int gemm_block256_launch_e4m3(int epi, const void* xq, const float* sx, const void* wq, const float* sw, void* out, int64_t M,
                               int64_t N, int64_t K, int splits, int64_t ldo, int32_t* status, cudaStream_t stream);

@@ -385,7 +385,7 @@ extern "C" int ojb_l2_prefetch(const void* data, int64_t nbytes, int64_t chunk, 
   return launch_status(cudaGetLastError());
 }
 
-extern "C" int ojb_abi_version(void) { return 5; }
+extern "C" int ojb_abi_version(void) { return 6; }
 
 extern "C" int ojb_add_rmsnorm(const void* x, const void* delta, const float* w1, const int32_t* rowmask, void* h_out,
                                void* hn_out, int64_t rows, int64_t H, float eps, ojb_stream_t stream) {

@@ -9,7 +9,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libojb200.so")
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 _ERR = {-1: "invalid argument (shape / alignment / null pointer)", -2: "CUDA launch or API failure",
         -3: "CUDA driver tensor-map encoder unavailable", -4: "size beyond the documented maximum"}

@@ -394,7 +394,8 @@ def gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walk_ptr, n_walks, init_
     if out is None:
         out = torch.empty(v.shape, dtype=bf16, device=v.device)
     call("ojb_gdn_chunked", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(chunks), i64(nch), ptr(steps), ptr(walk_ptr),
-         i64(n_walks), ptr(init_state), ptr(final_state), ptr(scratch), ptr(out), i64(HK), i64(HV), f32(scale), stream_ptr())
+         i64(n_walks), ptr(init_state), ptr(final_state), ptr(scratch), ptr(out), i64(HK), i64(HV), f32(scale),
+         ptr(_lib.status_word(v.device)), stream_ptr())
     return out
 
 
@@ -417,7 +418,7 @@ def gdn_chunked_proj(proj, hist, convw, A_log, dt_bias, KD, VD, HV, HK, scale, c
         out = torch.zeros(N, HV, 128, dtype=bf16, device=proj.device)
     call("ojb_gdn_chunked_proj", ptr(proj), ptr(hist), ptr(convw), ptr(A_log), ptr(dt_bias), ptr(chunks), i64(nch), ptr(steps),
          ptr(walk_ptr), i64(n_walks), ptr(init_state), ptr(final_state), ptr(scratch), ptr(out), i64(KD), i64(VD), i64(HK), i64(HV),
-         f32(scale), stream_ptr())
+         f32(scale), ptr(_lib.status_word(proj.device)), stream_ptr())
     return out
 
 
@@ -436,7 +437,8 @@ def gdn_tree_levels(q, k, v, g, beta, scale, lay, out, states=None):
     scratch = torch.empty(nbytes(i64(nch), i64(HV)), dtype=torch.uint8, device=v.device)
     levels = (_lib.ctypes.c_int32 * 4)(0, 1, 1 + S, 1 + 2 * S)
     call("ojb_gdn_chunked_levels", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(lay.chunks), i64(nch), ptr(lay.lsteps),
-         ptr(lay.lwalks), levels, i64(3), ptr(states), ptr(scratch), ptr(out), i64(HK), i64(HV), f32(scale), stream_ptr())
+         ptr(lay.lwalks), levels, i64(3), ptr(states), ptr(scratch), ptr(out), i64(HK), i64(HV), f32(scale),
+         ptr(_lib.status_word(v.device)), stream_ptr())
     return out, states
 
 

@@ -137,6 +137,44 @@ def test_prep_rows_and_scatter(name):
         assert torch.equal(got.cpu(), O.scatter_slots(rows.cpu(), src))
 
 
+def test_state_pass_bounded_wait_runs_out_and_reports_through_the_status_word():
+    """The state pass waits for the bulk copies of each step's operands on an mbarrier, with the library's wait limit. With the
+    limit at 50 ms and the host-side failure switch on, the copies of the second step are announced but never issued: the wait
+    runs out, every CTA leaves its walk, the status word says so, and the next call on the same context is correct."""
+    import ctypes
+    import time
+    from ojb200 import ext as K, _lib
+    lib = _lib.lib()
+    B, T, HK, HV = 2, 150, 2, 4
+    g_ = torch.Generator().manual_seed(12)
+    q = torch.nn.functional.normalize(torch.randn(B * T, HK, 128, generator=g_), dim=-1).to(bf16).cuda()
+    k = torch.nn.functional.normalize(torch.randn(B * T, HK, 128, generator=g_), dim=-1).to(bf16).cuda()
+    v = torch.randn(B * T, HV, 128, generator=g_).to(bf16).cuda()
+    g = torch.nn.functional.logsigmoid(torch.randn(B * T, HV, generator=g_)).cuda()
+    beta = torch.sigmoid(torch.randn(B * T, HV, generator=g_)).to(bf16).cuda()
+    chunks, steps, walks = K._seq_tables(B, T, torch.device("cuda"))
+    good = K.gdn_chunked(q, k, v, g, beta, 128 ** -0.5, chunks, steps, walks, B)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    try:
+        assert lib.ojb_gemm_set_wait_limit_ms(ctypes.c_int32(50)) == 0
+        assert lib.ojb_gemm_test_drop_copy(ctypes.c_int32(1)) == 0
+        t0 = time.perf_counter()
+        K.gdn_chunked(q, k, v, g, beta, 128 ** -0.5, chunks, steps, walks, B)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    finally:
+        lib.ojb_gemm_test_drop_copy(ctypes.c_int32(0))
+        lib.ojb_gemm_set_wait_limit_ms(ctypes.c_int32(0))
+    assert dt < 1.5, dt                             # gave up after the 50 ms limit, not after the default 2 s
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        _lib.check_status()
+    again = K.gdn_chunked(q, k, v, g, beta, 128 ** -0.5, chunks, steps, walks, B)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(again, good)
+
+
 def test_gated_rmsnorm():
     from ojb200 import ext as K
     N, HV, HD = 37, 4, 128

@@ -37,8 +37,10 @@ def test_static_scratch_entry_point_matches_allocating_one():
         want = K.gdn_chunked(q, k, v, g, beta, scale, chunks, steps, walks, B)
         got = torch.empty_like(want)                                 # outputs are the caller's; the call allocates nothing
         call("ojb_gdn_chunked_static", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(chunks), i64(chunks.shape[0]),
-             ptr(steps), ptr(walks), i64(B), ptr(None), ptr(None), ptr(got), i64(HK), i64(HV), f32(scale), stream_ptr())
+             ptr(steps), ptr(walks), i64(B), ptr(None), ptr(None), ptr(got), i64(HK), i64(HV), f32(scale),
+             ptr(_lib.status_word(got.device)), stream_ptr())
         torch.cuda.synchronize()
+        _lib.check_status()
         rel = ((got.float() - want.float()).norm() / want.float().norm()).item()
         assert rel < 4e-3, (call_no, rel)           # the tolerance of the other Gated DeltaNet tests; in practice 0
         assert torch.equal(got, want)               # same kernels, same inputs
@@ -51,5 +53,5 @@ def test_static_scratch_rejects_oversize():
     lib.ojb_gdn_chunked_static.restype = ctypes.c_int
     t = torch.zeros(16, dtype=torch.int32, device="cuda")
     rc = lib.ojb_gdn_chunked_static(ptr(t), ptr(t), ptr(t), ptr(t), ptr(t), ptr(t), i64(300), ptr(t), ptr(t), i64(1), ptr(None),
-                                    ptr(None), ptr(t), i64(2), i64(4), f32(1.0), stream_ptr())
+                                    ptr(None), ptr(t), i64(2), i64(4), f32(1.0), ptr(None), stream_ptr())
     assert rc == -4                                 # 300 * 4 items > 1024: refused, nothing launched
