@@ -260,20 +260,32 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
     }
   }
 
+  // log-decay and beta of the two rows that each lane of warp 0 sums below: requested before the tiles, so that their
+  // latency runs under the tile loads
+  float pg0 = 0.f, pg1 = 0.f, pb0 = 0.f, pb1 = 0.f;
   if constexpr (!FUSED) {
-  // ---- load K, Q, V rows (zero rows past the end of the chunk)
+    if (warp == 0) {
+      const int64_t a0 = grow(lane * 2), a1 = grow(lane * 2 + 1);
+      if (a0 >= 0) { pg0 = g[a0 * HV + h]; pb0 = bf2f(beta[a0 * HV + h]); }
+      if (a1 >= 0) { pg1 = g[a1 * HV + h]; pb1 = bf2f(beta[a1 * HV + h]); }
+    }
+  }
+  if constexpr (!FUSED) {
+  // ---- load K, Q, V rows (zero rows past the end of the chunk): asynchronous 16-byte copies, all twelve of a thread in
+  //      flight at once (as plain loads in this loop they went one after the other: 4 to 10 us for 48 KB per CTA)
   for (int i = tid; i < 3 * kChunk * (kHD / 8); i += kIntraThreads) {
     const int which = i / (kChunk * 16), rem = i - which * (kChunk * 16);
     const int r = rem >> 4, cv = (rem & 15) * 8;
-    uint4 val = make_uint4(0u, 0u, 0u, 0u);
     const int64_t row = grow(r);
+    bf16_t* dst = which == 0 ? Ks : which == 1 ? Qs : Vs;
     if (row >= 0) {
       const bf16_t* src = which == 0 ? k + row * KD + hk * kHD : which == 1 ? q + row * KD + hk * kHD : v + row * VD + h * kHD;
-      val = *reinterpret_cast<const uint4*>(src + cv);
+      cp_async16(smem_u32(dst + r * kLd + cv), src + cv);
+    } else {
+      *reinterpret_cast<uint4*>(dst + r * kLd + cv) = make_uint4(0u, 0u, 0u, 0u);
     }
-    bf16_t* dst = which == 0 ? Ks : which == 1 ? Qs : Vs;
-    *reinterpret_cast<uint4*>(dst + r * kLd + cv) = val;
   }
+  cp_async_commit();
   } else {
   // ---- raw in-projection rows of the chunk into the K / Q / V tiles, and the three rows before each (sub-)chunk on its
   //      tree path into Hs (over A, which is not written before the K K^T phase): [sub-chunk][3 rows][k | q | v][128]
@@ -374,8 +386,8 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
         g1 = fmaxf(na * (xs > 20.f ? xs : log1pf(expf(xs))), -1e4f);
       }
     } else {
-      if (gr0 >= 0) { g0 = fmaxf(g[gr0 * HV + h], -1e4f); be0 = bf2f(beta[gr0 * HV + h]); }
-      if (gr1 >= 0) { g1 = fmaxf(g[gr1 * HV + h], -1e4f); be1 = bf2f(beta[gr1 * HV + h]); }
+      if (gr0 >= 0) { g0 = fmaxf(pg0, -1e4f); be0 = pb0; }
+      if (gr1 >= 0) { g1 = fmaxf(pg1, -1e4f); be1 = pb1; }
     }
     Bs[r0] = be0;
     Bs[r1] = be1;
@@ -397,6 +409,7 @@ gdn_intra_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ k, con
       if (paired) *reinterpret_cast<float*>(itemB + kOffGl) = exp2f(total_hi * kLog2e);
     }
   }
+  if constexpr (!FUSED) cp_async_wait<0>();
   __syncthreads();
 
   // ---- K K^T (warps 0-3) and Q K^T (warps 4-7): 16 rows x 64 columns per warp
