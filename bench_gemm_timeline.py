@@ -6,7 +6,7 @@
 `--variant` is the library's variant code (3 block kernel, 4 all rows swapped, 16..256 forced w-tile width, 5 / 6 CTA-pair
 kernel, 512 + width = pair kernel with forced width). One JSON line: the span of the launch, and per unit type the mean time
 from the end of the previous epilogue to the completed accumulator ("main") and the mean epilogue time, in microseconds, plus
-how many units each CTA ran. `--repeat` / `--knob` need a library built with -DOJB_GEMM_PROBES (MMAs of a stage issued r
+how many units each CTA ran, the spread of the main-loop time over the units of a type and of the finishing time over the CTAs. `--repeat` / `--knob` need a library built with -DOJB_GEMM_PROBES (MMAs of a stage issued r
 times, pipeline depth capped, parts of the epilogue skipped): the shipped library has neither and the options are refused.
 """
 import argparse
@@ -90,8 +90,12 @@ def main():
                     line["span_us"] = round(float(end.max()), 1)
                     for lab, m in (("block", ~tail), ("swapped", tail)):
                         if m.any():
-                            line[lab] = dict(n=int(m.sum()), main_us=round(float((full - beg)[m].mean()), 2),
+                            d = (full - beg)[m]
+                            line[lab] = dict(n=int(m.sum()), main_us=round(float(d.mean()), 2),
+                                             main_min_med_max_us=[round(float(np.percentile(d, q)), 1) for q in (0, 50, 100)],
                                              epilogue_us=round(float((end - full)[m].mean()), 2))
+                    ends_cta = np.array([end[cta == c].max() for c in np.unique(cta)])
+                    line["cta_finish_min_med_max_us"] = [round(float(np.percentile(ends_cta, q)), 1) for q in (0, 50, 100)]
                     cnt = np.bincount(cta)
                     line["units_per_cta"] = {int(k): int(v) for k, v in zip(*np.unique(cnt[cnt > 0], return_counts=True))}
                     if args.detail:
