@@ -6,6 +6,8 @@ For each (M, K, N): plain bf16 GEMM per tile variant, the SwiGLU-fused GEMM wher
 GEMMs (with their reduce + residual + RMSNorm kernel) where N is the hidden size. Each case is timed with CUDA events over
 launches that cycle through enough distinct weight copies to exceed the L2, checked against torch.matmul on fp32-upcast
 operands, and printed as one JSON line: microseconds, TFLOP/s, fraction of the measured bf16 peak, weight-stream GB/s.
+With --sustained SECS every case runs back to back for SECS seconds and the line also carries the board power, the SM clock
+and the energy per call (NVML).
 """
 import argparse
 import json
@@ -30,8 +32,54 @@ def _peak():
         return 1590.0
 
 
+SUSTAINED = 0.0      # --sustained: seconds of back-to-back launches per case, with board power and SM clock sampled
+_LAST = {}           # power / clock / energy of the case timed last (sustained mode)
+
+
+def _time_sustained(fns, secs):
+    """Back-to-back launches for `secs` seconds (the GPU settles against its power cap, as inside a forward), NVML samples of
+    board power and SM clock every 20 ms; the first third of the samples is dropped. Returns microseconds per call."""
+    import threading
+    import time
+    import pynvml
+    pynvml.nvmlInit()
+    hd = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    for f in fns[:2]:
+        f()
+    torch.cuda.synchronize()
+    stop, samples = threading.Event(), []
+
+    def sample():
+        while not stop.is_set():
+            samples.append((pynvml.nvmlDeviceGetPowerUsage(hd) / 1e3, pynvml.nvmlDeviceGetClockInfo(hd, pynvml.NVML_CLOCK_SM)))
+            time.sleep(0.02)
+    th = threading.Thread(target=sample)
+    th.start()
+    a, b = torch.cuda.Event(True), torch.cuda.Event(True)
+    n, t0 = 0, time.perf_counter()
+    a.record()
+    while time.perf_counter() - t0 < secs:
+        for _ in range(8):
+            for f in fns:
+                f()
+        n += 8 * len(fns)
+        torch.cuda.synchronize()
+    b.record()
+    torch.cuda.synchronize()
+    stop.set()
+    th.join()
+    us = a.elapsed_time(b) * 1e3 / n
+    samples = samples[len(samples) // 3:] or [(0.0, 0)]
+    watts = sum(x[0] for x in samples) / len(samples)
+    _LAST.clear()
+    _LAST.update(watts=round(watts), sm_mhz=round(sum(x[1] for x in samples) / len(samples)), mj_per_call=round(watts * us / 1e3, 1))
+    return us
+
+
 def _time(fns, reps=3):
     """fns: list of closures over distinct weight copies; returns microseconds per call (best of reps passes)."""
+    if SUSTAINED > 0:
+        return _time_sustained(fns, SUSTAINED)
     for f in fns[:2]:
         f()
     best = float("inf")
@@ -57,8 +105,13 @@ def main():
     ap.add_argument("--e4m3", action="store_true",
                     help="also time the 8-bit form (ojb_gemm_e4m3: bf16 out, SwiGLU where N is a gate/up width, fp32 partials where N is "
                          "the hidden size) and the row quantisation kernel")
+    ap.add_argument("--sustained", type=float, default=0.0, metavar="SECS",
+                    help="time every case over SECS seconds of back-to-back launches and report board power, SM clock and "
+                    "energy per call (the GPU runs against its power cap, as it does inside a forward)")
     ap.add_argument("--copies", type=int, default=0, help="distinct weight copies to cycle through (default: enough to exceed L2)")
     args = ap.parse_args()
+    global SUSTAINED
+    SUSTAINED = args.sustained
     dev = torch.device("cuda")
     peak = _peak()
     g = torch.Generator(device=dev).manual_seed(0)
@@ -74,7 +127,7 @@ def main():
             def report(name, us, err):
                 print(json.dumps({"M": M, "K": Kd, "N": N, "kernel": name, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                                   "frac_of_peak": round(flops / us / 1e6 / peak, 3), "weight_gbs": round(N * Kd * 2 / us / 1e3, 1),
-                                  "max_err": err}), flush=True)
+                                  "max_err": err, **_LAST}), flush=True)
             for v in ((0, 1, 2, 3, 7, 8, 9) if want("plain") else ()):
                 if v == 7 and M > 2048:
                     continue
