@@ -31,7 +31,7 @@ double tile128_clocks(int64_t M, int64_t N, int kb_total, int splits, int bn, in
   const int64_t units = ceil_div(M, 128) * ceil_div(N, bn) * splits;
   const int64_t grid = units < sms ? units : sms;
   const int per = static_cast<int>(ceil_div(kb_total, splits));
-  const double kb = bn == 256 ? 768.0 : 512.0;
+  const double kb = bn == 256 ? 900.0 : 600.0;   // fitted to back-to-back runs against the power cap (133 us at 288 rows, 206 us at 544 for gate/up)
   return static_cast<double>(ceil_div(units, grid)) * (per * kb + 1500.0) + 9000.0;
 }
 
