@@ -651,6 +651,16 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   if (FP8 && g.BN % 64 != 0) g.BN = (g.BN + 63) / 64 * 64;      // whole 128-byte store tiles (the scaled epilogue needs them)
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
+  {
+    // x beyond what the L2 keeps beside the streaming weight (64 MB): bands of about 40 MB of x, equal in size
+    const int64_t xblk_bytes = static_cast<int64_t>(kBlockM) * K * (FP8 ? 1 : 2);
+    g.band_xblk = 0;
+    if (static_cast<int64_t>(g.n_xblk) * xblk_bytes > (64ll << 20)) {
+      const int64_t per_band = (40ll << 20) / xblk_bytes > 2 ? (40ll << 20) / xblk_bytes : 2;
+      const int64_t n_bands = ceil_div(g.n_xblk, per_band);
+      g.band_xblk = static_cast<int>(ceil_div(g.n_xblk, n_bands));
+    }
+  }
   const int b_rows = g.n_xblk > 0 ? (g.BN > g.tail_box ? g.BN : g.tail_box) : g.tail_box;
   g.stage_bytes = kABytes + static_cast<uint32_t>(b_rows) * (kBK * 2);
   {

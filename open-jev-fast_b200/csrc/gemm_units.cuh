@@ -51,6 +51,7 @@ struct GemmArgs {
   const float* sx;
   const float* sw;
   int tail_tma;                // block kernel: swapped-operand units store through [16][32] shared-memory tiles and bulk tensor stores
+  int band_xblk;               // 0, or the x blocks of a band: all units of a band come before those of the next (see decode_unit)
 };
 
 struct Unit {
@@ -63,28 +64,43 @@ struct Unit {
 // by the tail units that start inside it, so a tail unit finds its w rows in L2 instead of streaming them from HBM again.
 // group_begin(j) = position of the first unit of tile j; tails_before(j) = tail tiles (256 w rows each) that start before
 // row j * BN.
-__device__ __forceinline__ int tails_before(const GemmArgs& g, int j) {
-  if (g.tail_rows == 0) return 0;
+// When x is larger than the L2 keeps (tens of thousands of rows), that order would stream all of x from HBM once per w tile:
+// the x blocks are then cut into bands of band_xblk blocks, each band small enough to stay in L2, and the whole order above
+// runs band after band (w is streamed once per band instead); the tail units belong to the last band.
+__device__ __forceinline__ int tails_before(const GemmArgs& g, int j, bool tails) {
+  if (!tails) return 0;
   const int t = (j * g.BN + 255) / 256;
   return t < g.n_wtile256 ? t : g.n_wtile256;
 }
-__device__ __forceinline__ int group_begin(const GemmArgs& g, int j) {
-  return (j * g.n_xblk + tails_before(g, j) * g.n_xchunk) * g.splits;
+__device__ __forceinline__ int group_begin(const GemmArgs& g, int j, int nx, bool tails) {
+  return (j * nx + tails_before(g, j, tails) * g.n_xchunk) * g.splits;
 }
 
 __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int total_block) {
   (void)total_block;
   Unit u;
-  const int nb = g.n_xblk * g.splits;
-  int j = static_cast<int>(unit / (nb + g.splits * g.n_xchunk * (g.tail_rows > 0 ? g.BN / 256.0f : 0.0f) + 1e-6f));
+  int xb_base = 0, nx = g.n_xblk;
+  bool tails = g.tail_rows > 0;
+  if (g.band_xblk > 0) {
+    const int full = g.band_xblk * g.n_wtile * g.splits;          // units of a band that is not the last one
+    const int n_bands = (g.n_xblk + g.band_xblk - 1) / g.band_xblk;
+    int b = unit / full;
+    if (b > n_bands - 1) b = n_bands - 1;
+    unit -= b * full;
+    xb_base = b * g.band_xblk;
+    nx = min(g.band_xblk, g.n_xblk - xb_base);
+    tails = tails && b == n_bands - 1;
+  }
+  const int nb = nx * g.splits;
+  int j = static_cast<int>(unit / (nb + g.splits * g.n_xchunk * (tails ? g.BN / 256.0f : 0.0f) + 1e-6f));
   if (j > g.n_wtile - 1) j = g.n_wtile - 1;
-  while (j > 0 && group_begin(g, j) > unit) --j;
-  while (j + 1 < g.n_wtile && group_begin(g, j + 1) <= unit) ++j;
-  const int off = unit - group_begin(g, j);
+  while (j > 0 && group_begin(g, j, nx, tails) > unit) --j;
+  while (j + 1 < g.n_wtile && group_begin(g, j + 1, nx, tails) <= unit) ++j;
+  const int off = unit - group_begin(g, j, nx, tails);
   u.tail = off >= nb;
   if (!u.tail) {
-    u.xb = off % g.n_xblk;
-    u.split = off / g.n_xblk;
+    u.xb = xb_base + off % nx;
+    u.split = off / nx;
     u.wt = j;
     u.xc = 0;
   } else {
@@ -92,7 +108,7 @@ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int tot
     u.xb = g.n_xblk;
     u.xc = o2 % g.n_xchunk;                       // x chunk fastest: the chunks of one w tile run side by side
     u.split = (o2 / g.n_xchunk) % g.splits;
-    u.wt = tails_before(g, j) + o2 / (g.n_xchunk * g.splits);
+    u.wt = tails_before(g, j, tails) + o2 / (g.n_xchunk * g.splits);
   }
   u.kb0 = u.split * g.kb_per_split;
   u.kb1 = min(u.kb0 + g.kb_per_split, g.kb_total);

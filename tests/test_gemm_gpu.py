@@ -236,3 +236,24 @@ def test_bounded_wait_runs_out_and_reports_through_the_status_word():
     torch.cuda.synchronize()
     _lib.check_status()
     assert torch.equal(again, good)
+
+
+@pytest.mark.parametrize("M", [16384 + 32, 13 * 256 * 2])
+def test_x_larger_than_l2_runs_in_bands(M):
+    """With more rows of x than the L2 keeps (tens of thousands), the block kernel deals its units band by band (x blocks of
+    one band stay in L2, the weight is streamed once per band). Every output row must still be produced exactly once: plain,
+    SwiGLU and split-K forms, with and without a 32-row remainder after the last block, against fp32 matmul."""
+    from ojb200 import lt_ext, _lib
+    K, N = 5120, 1280
+    x, w = _mk(M, N, K, 21)
+    ref = _ref(x, w)
+    _close(lt_ext.lt_matmul(x, w, 3), ref)
+    parts = lt_ext.gemm_splitk(x, w, 2, 3)
+    assert (parts.sum(0) - ref).abs().max().item() <= ref.abs().max().item() * 2 ** -8 + 1e-3
+    I = N // 2
+    out = lt_ext.gemm_swiglu(x, lt_ext.interleave_gate_up(w[:I].contiguous(), w[I:].contiguous(), 128), 3)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    gg, uu = ref[:, :I], ref[:, I:]
+    want = torch.nn.functional.silu(gg) * uu
+    assert (out.float() - want).abs().max().item() <= want.abs().max().item() * 2 ** -7 + 2e-3
