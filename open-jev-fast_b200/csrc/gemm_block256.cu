@@ -652,11 +652,14 @@ int launch_gemm(const void* x, const void* w, void* out, int64_t M, int64_t N, i
   g.n_wtile = static_cast<int>(ceil_div(N, g.BN));
   g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
   {
-    // x beyond what the L2 keeps beside the streaming weight (64 MB): bands of about 40 MB of x, equal in size
+    // x beyond what the L2 keeps beside the streaming weight (64 MB) and at least 24 x blocks (with fewer, the CTAs that
+    // run at the same time already cover several weight tiles per x block, and x is re-read only a few times): bands of about
+    // 40 MB of x, equal in size. OJB_GEMM_BAND_MB changes the band size (0 = no bands) for measurements.
     const int64_t xblk_bytes = static_cast<int64_t>(kBlockM) * K * (FP8 ? 1 : 2);
+    static const int64_t band_mb = [] { const char* e = getenv("OJB_GEMM_BAND_MB"); return e ? static_cast<int64_t>(atoi(e)) : 40ll; }();
     g.band_xblk = 0;
-    if (static_cast<int64_t>(g.n_xblk) * xblk_bytes > (64ll << 20)) {
-      const int64_t per_band = (40ll << 20) / xblk_bytes > 2 ? (40ll << 20) / xblk_bytes : 2;
+    if (band_mb > 0 && g.n_xblk >= 24 && static_cast<int64_t>(g.n_xblk) * xblk_bytes > (64ll << 20)) {
+      const int64_t per_band = (band_mb << 20) / xblk_bytes > 2 ? (band_mb << 20) / xblk_bytes : 2;
       const int64_t n_bands = ceil_div(g.n_xblk, per_band);
       g.band_xblk = static_cast<int>(ceil_div(g.n_xblk, n_bands));
     }
