@@ -80,6 +80,14 @@ int ojb_gemm_e4m3(const void* xq, const float* sx, const void* wq, const float* 
  * an all-zero row), q[m,k] = e4m3(x[m,k] / scale[m]), round to nearest, saturating. */
 int ojb_quantize_rows_e4m3(const void* x, void* q, float* scale, int64_t rows, int64_t K, ojb_stream_t stream);
 
+/* Host-side listing (no GPU work) of the order in which the block GEMM kernels deal out their work units, for a geometry
+ * given directly: n_xblk 256-row blocks of x, tail_rows further rows in n_xchunk swapped-operand chunks, weight tiles of BN
+ * rows of an N-row weight, `splits` K ranges over kb_total k-blocks, and band_xblk (0 = one band). out int32 [cap, 5] receives
+ * (tail, x block, K range, w tile, x chunk) per unit; returns the number of units. Test support: every unit must occur once,
+ * and with bands every unit of a band must come before the units of the next band. */
+int64_t ojb_gemm_unit_order(int32_t n_xblk, int32_t tail_rows, int32_t n_xchunk, int32_t BN, int64_t N, int32_t splits,
+                            int32_t kb_total, int32_t band_xblk, int32_t* out, int64_t cap);
+
 /* Host-side plan (no GPU work): which kernel variant and how many K ranges the library's cost model picks for a shape.
  * kind = 0 bf16 output, 1 SwiGLU-fused, 2 fp32 split-K partials (the only kind that may use more than one range, up to
  * max_splits). *microseconds (optional) receives the modelled time. Takes the place of the algorithm search of

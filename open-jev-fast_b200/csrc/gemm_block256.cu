@@ -748,3 +748,26 @@ int gemm_block256_launch_e4m3(int epi, const void* xq, const float* sx, const vo
 }
 
 }  // namespace ojb
+
+// Host-side listing of the unit order of the block kernels for a given geometry (no GPU work): out[5 * i .. 5 * i + 4] =
+// (tail, x block, k range, w tile, x chunk) of the i-th unit. Returns the number of units, or a negative error code.
+extern "C" int64_t ojb_gemm_unit_order(int32_t n_xblk, int32_t tail_rows, int32_t n_xchunk, int32_t BN, int64_t N, int32_t splits,
+                                       int32_t kb_total, int32_t band_xblk, int32_t* out, int64_t cap) {
+  using namespace ojb;
+  if (n_xblk < 0 || tail_rows < 0 || n_xchunk < 1 || BN < 16 || BN > 256 || BN % 16 || N <= 0 || splits < 1 || kb_total < splits ||
+      band_xblk < 0 || !out)
+    return OJB_ERR_ARG;
+  GemmArgs g{};
+  g.n_xblk = n_xblk; g.tail_rows = tail_rows; g.n_xchunk = n_xchunk; g.BN = BN; g.N = static_cast<int>(N);
+  g.n_wtile = static_cast<int>(ceil_div(N, BN)); g.n_wtile256 = static_cast<int>(ceil_div(N, 256));
+  g.splits = splits; g.kb_total = kb_total; g.kb_per_split = static_cast<int>(ceil_div(kb_total, splits));
+  g.band_xblk = band_xblk;
+  const int64_t units = static_cast<int64_t>(n_xblk) * g.n_wtile * splits +
+                        (tail_rows > 0 ? static_cast<int64_t>(g.n_wtile256) * splits * n_xchunk : 0);
+  if (units > cap) return OJB_ERR_LIMIT;
+  for (int64_t i = 0; i < units; ++i) {
+    const Unit u = decode_unit(g, static_cast<int>(i), 0);
+    out[5 * i + 0] = u.tail ? 1 : 0; out[5 * i + 1] = u.xb; out[5 * i + 2] = u.split; out[5 * i + 3] = u.wt; out[5 * i + 4] = u.xc;
+  }
+  return units;
+}

@@ -67,16 +67,17 @@ struct Unit {
 // When x is larger than the L2 keeps (tens of thousands of rows), that order would stream all of x from HBM once per w tile:
 // the x blocks are then cut into bands of band_xblk blocks, each band small enough to stay in L2, and the whole order above
 // runs band after band (w is streamed once per band instead); the tail units belong to the last band.
-__device__ __forceinline__ int tails_before(const GemmArgs& g, int j, bool tails) {
+__host__ __device__ __forceinline__ int tails_before(const GemmArgs& g, int j, bool tails) {
   if (!tails) return 0;
   const int t = (j * g.BN + 255) / 256;
   return t < g.n_wtile256 ? t : g.n_wtile256;
 }
-__device__ __forceinline__ int group_begin(const GemmArgs& g, int j, int nx, bool tails) {
+__host__ __device__ __forceinline__ int group_begin(const GemmArgs& g, int j, int nx, bool tails) {
   return (j * nx + tails_before(g, j, tails) * g.n_xchunk) * g.splits;
 }
 
-__device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int total_block) {
+// (also compiled for the host: ojb_gemm_unit_order lists the order for the tests)
+__host__ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int total_block) {
   (void)total_block;
   Unit u;
   int xb_base = 0, nx = g.n_xblk;
@@ -88,7 +89,7 @@ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int tot
     if (b > n_bands - 1) b = n_bands - 1;
     unit -= b * full;
     xb_base = b * g.band_xblk;
-    nx = min(g.band_xblk, g.n_xblk - xb_base);
+    nx = g.band_xblk < g.n_xblk - xb_base ? g.band_xblk : g.n_xblk - xb_base;
     tails = tails && b == n_bands - 1;
   }
   const int nb = nx * g.splits;
@@ -111,7 +112,7 @@ __device__ __forceinline__ Unit decode_unit(const GemmArgs& g, int unit, int tot
     u.wt = tails_before(g, j, tails) + o2 / (g.n_xchunk * g.splits);
   }
   u.kb0 = u.split * g.kb_per_split;
-  u.kb1 = min(u.kb0 + g.kb_per_split, g.kb_total);
+  u.kb1 = u.kb0 + g.kb_per_split < g.kb_total ? u.kb0 + g.kb_per_split : g.kb_total;
   return u;
 }
 
